@@ -1,0 +1,123 @@
+"""ctypes binding of libgewell_b200.so (the C ABI declared in
+include/gewell_b200.h).  There is no CPU fallback: if the CUDA library has
+not been built, importing this module raises."""
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_size_t, c_uint32, c_uint64, c_void_p
+from pathlib import Path
+
+LIBRARY_PATH = Path(__file__).resolve().parent / "_C" / "libgewell_b200.so"
+
+GW_OK, GW_INVALID_ARGUMENT, GW_CUDA_ERROR, GW_KERNEL_ERROR, GW_UNSUPPORTED = range(5)
+TRANSFORM_IDENTITY, TRANSFORM_GELU_TANH_MULTIPLY = 0, 1
+QDQ_BF16, QDQ_FP8, QDQ_NVFP4 = 0, 1, 2
+STORAGE_BF16, STORAGE_NVFP4_W4A4, STORAGE_FP8_W8A8 = 0, 1, 2
+
+
+class Projection(ctypes.Structure):
+    """gw_projection (mirrors sm120::Projection, projection.cuh:11-17)."""
+    _fields_ = [
+        ("storage", c_uint32), ("input", c_uint32), ("output", c_uint32), ("physical_output", c_uint32),
+        ("bf16", c_void_p),
+        ("nvfp4_data", c_void_p), ("nvfp4_scales", c_void_p),
+        ("nvfp4_input_scale", c_float), ("nvfp4_weight_scale", c_float),
+        ("fp8_data", c_void_p),
+        ("fp8_input_scale", c_float), ("fp8_weight_scale", c_float),
+        ("fp8_channel_scales", c_void_p),
+    ]
+
+
+class ExpertWeights(ctypes.Structure):
+    """gw_expert_weights (mirrors sm120::ExpertWeights, moe.cuh:11-13)."""
+    _fields_ = [("gate", Projection), ("up", Projection), ("down", Projection)]
+
+
+_SIGNATURES = {
+    "gw_last_error": (c_char_p, []),
+    "gw_abi_version": (c_int, []),
+    "gw_nvfp4_scale_storage_bytes": (c_size_t, [c_size_t, c_size_t]),
+    "gw_nvfp4_scale_offset": (c_size_t, [c_size_t, c_size_t, c_size_t]),
+    "gw_nvfp4_scratch_upper_bound_bytes": (c_size_t, [c_size_t, c_size_t, c_size_t]),
+    "gw_fp8_scratch_upper_bound_bytes": (c_size_t, [c_size_t, c_size_t]),
+    "gw_nvfp4_dequantize": (c_int, [c_void_p, c_void_p, c_float, c_uint32, c_uint32, c_void_p, c_void_p]),
+    "gw_nvfp4_pack_weights": (c_int, [c_void_p, c_uint32, c_uint32, c_float, c_void_p, c_void_p, c_void_p]),
+    "gw_nvfp4_quantize_activations": (c_int, [c_void_p, c_uint32, c_uint32, c_float, c_int, c_void_p, c_void_p, c_void_p]),
+    "gw_nvfp4_plan_create": (c_int, [c_uint32, c_uint32, c_uint32, POINTER(c_void_p)]),
+    "gw_nvfp4_plan_scratch_bytes": (c_size_t, [c_void_p]),
+    "gw_nvfp4_plan_run": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, c_void_p, c_void_p,
+                                  c_size_t, c_void_p, c_int]),
+    "gw_nvfp4_plan_destroy": (None, [c_void_p]),
+    "gw_nvfp4_gemv_w4a16": (c_int, [c_void_p, c_uint32, c_void_p, c_void_p, c_float, c_uint32, c_uint32, c_void_p, c_void_p]),
+    "gw_fp8_quantize_activations": (c_int, [c_void_p, c_uint32, c_uint32, c_float, c_int, c_void_p, c_void_p]),
+    "gw_fp8_pack_weights": (c_int, [c_void_p, c_uint32, c_uint32, c_float, c_void_p, c_void_p, c_void_p]),
+    "gw_fp8_plan_create": (c_int, [c_uint32, c_uint32, c_uint32, c_int, POINTER(c_void_p)]),
+    "gw_fp8_plan_scratch_bytes": (c_size_t, [c_void_p]),
+    "gw_fp8_plan_run": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_float, c_void_p, c_void_p, c_void_p,
+                                c_size_t, c_void_p, c_int]),
+    "gw_fp8_plan_destroy": (None, [c_void_p]),
+    "gw_absmax_bf16": (c_int, [c_void_p, c_uint64, c_void_p, c_void_p]),
+    "gw_weight_qdq_apply": (c_int, [c_int, c_void_p, c_uint64, c_void_p, c_void_p]),
+    "gw_moe_expert_table_create": (c_int, [POINTER(ExpertWeights), c_uint32, POINTER(c_void_p)]),
+    "gw_moe_expert_table_destroy": (None, [c_void_p]),
+    "gw_moe_create": (c_int, [c_uint32, POINTER(c_void_p)]),
+    "gw_moe_destroy": (None, [c_void_p]),
+    "gw_moe_dispatch": (c_int, [c_void_p, c_void_p, c_void_p, c_uint32, c_void_p]),
+    "gw_moe_run": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_uint32, c_int, c_int,
+                           c_int, c_int, c_void_p]),
+    "gw_moe_selected_experts": (c_void_p, [c_void_p]),
+    "gw_moe_routing_weights": (c_void_p, [c_void_p]),
+    "gw_moe_offsets": (c_void_p, [c_void_p]),
+    "gw_moe_sorted_assignments": (c_void_p, [c_void_p]),
+    "gw_moe_gate_up_capture": (c_void_p, [c_void_p]),
+    "gw_moe_activated_capture": (c_void_p, [c_void_p]),
+    "gw_moe_down_capture": (c_void_p, [c_void_p]),
+    "gw_moe_bytes": (c_size_t, [c_void_p]),
+    "gw_moe_routing_bytes": (c_size_t, [c_void_p]),
+    "gw_moe_projection_bytes": (c_size_t, [c_void_p]),
+    "gw_moe_reduction_bytes": (c_size_t, [c_void_p]),
+    "gw_moe_run_sorted": (c_int, [c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_uint32, c_void_p, c_void_p, c_void_p]),
+    "gw_gather_rows_bf16": (c_int, [c_void_p, c_void_p, c_uint32, c_uint32, c_uint32, c_void_p, c_void_p]),
+    "gw_moe_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_void_p, c_void_p]),
+    "gw_debug_kernel_error": (c_uint32, []),
+}
+
+
+class GewellError(RuntimeError):
+    """CUDA / kernel failure (the reference throws std::runtime_error)."""
+
+
+class GewellInvalidArgument(ValueError):
+    """Contract violation (the reference throws std::invalid_argument)."""
+
+
+class GewellUnsupported(NotImplementedError):
+    pass
+
+
+def exported_symbols() -> list[str]:
+    return sorted(_SIGNATURES)
+
+
+def load() -> ctypes.CDLL:
+    if not LIBRARY_PATH.exists():
+        raise ImportError(
+            f"{LIBRARY_PATH} is missing: build it with `python -m gewell_b200.build` "
+            "(gewell_b200 has no CPU fallback)")
+    lib = ctypes.CDLL(str(LIBRARY_PATH))
+    for name, (restype, argtypes) in _SIGNATURES.items():
+        fn = getattr(lib, name)          # AttributeError if the symbol is missing
+        fn.restype = restype
+        fn.argtypes = argtypes
+    return lib
+
+
+def check(lib: ctypes.CDLL, status: int) -> None:
+    if status == GW_OK:
+        return
+    message = lib.gw_last_error().decode("utf-8", "replace")
+    if status == GW_INVALID_ARGUMENT:
+        raise GewellInvalidArgument(message)
+    if status == GW_UNSUPPORTED:
+        raise GewellUnsupported(message)
+    raise GewellError(message)

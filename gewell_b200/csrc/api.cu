@@ -1,0 +1,409 @@
+// C ABI of gewell_b200: argument validation (same contract as the reference
+// classes), plan objects and the element-wise entry points.
+#include <cmath>
+#include <cstring>
+#include <limits>
+#include <mutex>
+#include <new>
+#include <string>
+
+#include "common.cuh"
+#include "gemm_tc.cuh"
+#include "kernels.h"
+
+namespace gw {
+
+namespace {
+thread_local std::string g_last_error;
+}
+
+gw_status fail(gw_status code, const std::string& message) {
+  g_last_error = message;
+  return code;
+}
+void clear_error() { g_last_error.clear(); }
+
+uint32_t* device_error_word() {
+  static uint32_t* word = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    if (cudaMalloc(&word, sizeof(uint32_t)) == cudaSuccess) cudaMemset(word, 0, sizeof(uint32_t));
+    else word = nullptr;
+  });
+  return word;
+}
+
+int sm_count() {
+  static int count = 0;
+  if (count == 0) {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0)
+      count = 148;
+  }
+  return count;
+}
+
+namespace {
+
+bool finite_positive(float v) { return v > 0.0F && std::isfinite(v); }
+
+bool aligned(const void* p, size_t a) { return reinterpret_cast<uintptr_t>(p) % a == 0; }
+
+// Token-side tile of the tensor-core kernel for a dense projection.
+int pick_block_n(uint32_t rows) {
+  if (rows <= 32) return 32;
+  if (rows <= 64) return 64;
+  if (rows <= 128) return 128;
+  return 256;
+}
+
+}  // namespace
+}  // namespace gw
+
+using namespace gw;
+
+extern "C" {
+
+const char* gw_last_error(void) { return g_last_error.c_str(); }
+int gw_abi_version(void) { return 1; }
+
+size_t gw_nvfp4_scale_storage_bytes(size_t rows, size_t input_width) { return scale_storage_bytes(rows, input_width); }
+size_t gw_nvfp4_scale_offset(size_t row, size_t block, size_t input_width) { return scale_offset(row, block, input_width); }
+
+size_t gw_nvfp4_scratch_upper_bound_bytes(size_t max_rows, size_t input_width, size_t output_width) {
+  // include/gewell/nvfp4_linear.h:42-49 (kept identical so callers size the same buffer)
+  const size_t padded_rows = (max_rows + 31) / 32 * 32;
+  return padded_rows * (input_width / 2 + output_width * 2) + scale_storage_bytes(max_rows, input_width) +
+         size_t(36) * 1024 * 1024 + 3 * 255;
+}
+size_t gw_fp8_scratch_upper_bound_bytes(size_t max_rows, size_t input_width) {
+  return max_rows * input_width + size_t(32) * 1024 * 1024 + 255;   // include/gewell/fp8_linear.h:30-33
+}
+
+uint32_t gw_debug_kernel_error(void) {
+  uint32_t value = 0;
+  uint32_t* word = device_error_word();
+  if (word == nullptr) return 0xFFFFFFFFu;
+  if (cudaDeviceSynchronize() != cudaSuccess) return 0xFFFFFFFEu;
+  cudaMemcpy(&value, word, sizeof(value), cudaMemcpyDeviceToHost);
+  if (value != 0) cudaMemset(word, 0, sizeof(value));
+  return value;
+}
+
+// --------------------------------------------------------------------------- NVFP4 element-wise
+
+gw_status gw_nvfp4_dequantize(const uint8_t* data, const uint8_t* scales, float weight_scale, uint32_t input_width,
+                              uint32_t output_width, void* output_bf16, void* stream) {
+  clear_error();
+  if (!data || !scales || !output_bf16 || !input_width || input_width % 64 || !output_width ||
+      output_width % 128 || !finite_positive(weight_scale))
+    return fail(GW_INVALID_ARGUMENT,
+                "NVFP4 dequantize requires valid buffers, K divisible by 64, N divisible by 128, and a finite "
+                "positive weight scale");
+  if (!aligned(data, 8) || !aligned(output_bf16, 16))
+    return fail(GW_INVALID_ARGUMENT, "NVFP4 dequantize requires 8-byte aligned weights and 16-byte aligned output");
+  GW_CUDA_CHECK(launch_nvfp4_dequantize(data, scales, weight_scale, input_width, output_width, output_bf16,
+                                        as_stream(stream)),
+                "NVFP4 dequantize weights");
+  return GW_OK;
+}
+
+gw_status gw_nvfp4_pack_weights(const void* weights_bf16, uint32_t output_width, uint32_t input_width,
+                                float weight_scale, uint8_t* data, uint8_t* scales, void* stream) {
+  clear_error();
+  if (!weights_bf16 || !data || !scales || !output_width || !input_width || input_width % 64 ||
+      !finite_positive(weight_scale) || !aligned(weights_bf16, 16) || !aligned(data, 8))
+    return fail(GW_INVALID_ARGUMENT,
+                "NVFP4 weight packing requires aligned buffers, K divisible by 64 and a finite positive global scale");
+  GW_CUDA_CHECK(launch_nvfp4_pack_weights(weights_bf16, output_width, input_width, weight_scale, data, scales,
+                                          as_stream(stream)),
+                "NVFP4 pack weights");
+  return GW_OK;
+}
+
+gw_status gw_nvfp4_quantize_activations(const void* input_bf16, uint32_t rows, uint32_t input_width,
+                                        float input_scale, int transform, uint8_t* packed, uint8_t* scales,
+                                        void* stream) {
+  clear_error();
+  if (!input_bf16 || !packed || !scales || !rows || !input_width || input_width % 64 ||
+      !finite_positive(input_scale) || !std::isfinite(1.0F / input_scale) ||
+      (transform != GW_TRANSFORM_IDENTITY && transform != GW_TRANSFORM_GELU_TANH_MULTIPLY) ||
+      !aligned(input_bf16, 16) || !aligned(packed, 8))
+    return fail(GW_INVALID_ARGUMENT,
+                "NVFP4 activation quantisation requires 16-byte aligned input, K divisible by 64 and a finite "
+                "positive input scale with a finite reciprocal");
+  GW_CUDA_CHECK(launch_nvfp4_quantize(input_bf16, rows, input_width, 1.0F / input_scale,
+                                      transform == GW_TRANSFORM_GELU_TANH_MULTIPLY, packed, scales, as_stream(stream)),
+                "NVFP4 quantize activations");
+  return GW_OK;
+}
+
+gw_status gw_nvfp4_gemv_w4a16(const void* input_bf16, uint32_t rows, const uint8_t* weight_data,
+                              const uint8_t* weight_scales, float weight_scale, uint32_t input_width,
+                              uint32_t output_width, void* output_bf16, void* stream) {
+  clear_error();
+  if (!input_bf16 || !weight_data || !weight_scales || !output_bf16 || rows == 0 || rows > 8 || !input_width ||
+      input_width % 64 || !output_width || output_width % 128 || !finite_positive(weight_scale) ||
+      !aligned(input_bf16, 16) || !aligned(weight_data, 16))
+    return fail(GW_INVALID_ARGUMENT,
+                "W4A16 projection requires 1..8 rows, K divisible by 64, N divisible by 128, 16-byte aligned "
+                "input and weights and a finite positive weight scale");
+  GW_CUDA_CHECK(launch_gemv_w4a16(input_bf16, rows, weight_data, weight_scales, weight_scale, input_width,
+                                  output_width, output_bf16, as_stream(stream)),
+                "W4A16 projection");
+  return GW_OK;
+}
+
+// --------------------------------------------------------------------------- NVFP4 plan
+
+struct gw_nvfp4_plan {
+  uint32_t rows, input_width, output_width;
+  int block_n;
+  size_t scale_offset, total_bytes;
+  // descriptor cache: re-encoded only when a pointer changes
+  const void* cached_weight = nullptr;
+  const void* cached_packed = nullptr;
+  CUtensorMap map_a{}, map_b{};
+};
+
+gw_status gw_nvfp4_plan_create(uint32_t rows, uint32_t input_width, uint32_t output_width, gw_nvfp4_plan** plan) {
+  clear_error();
+  if (!plan || rows == 0 || rows > uint32_t(std::numeric_limits<int>::max() - 127) || input_width == 0 ||
+      input_width % 64 || output_width == 0 || output_width % 128)
+    return fail(GW_INVALID_ARGUMENT, "NVFP4 plan requires positive rows, K divisible by 64 and N divisible by 128");
+  auto* p = new (std::nothrow) gw_nvfp4_plan();
+  if (!p) return fail(GW_CUDA_ERROR, "out of host memory");
+  p->rows = rows;
+  p->input_width = input_width;
+  p->output_width = output_width;
+  p->block_n = pick_block_n(rows);
+  // scratch = packed activations | tiled activation scales   (each 256-byte aligned)
+  p->scale_offset = align_up(size_t(rows) * input_width / 2, 256);
+  p->total_bytes = p->scale_offset + align_up(scale_storage_bytes(rows, input_width), 256);
+  *plan = p;
+  return GW_OK;
+}
+
+size_t gw_nvfp4_plan_scratch_bytes(const gw_nvfp4_plan* plan) { return plan ? plan->total_bytes : 0; }
+void gw_nvfp4_plan_destroy(gw_nvfp4_plan* plan) { delete plan; }
+
+gw_status gw_nvfp4_plan_run(gw_nvfp4_plan* plan, const void* input_bf16, const uint8_t* weight_data,
+                            const uint8_t* weight_scales, float input_scale, float weight_scale, void* output_bf16,
+                            void* scratch, size_t scratch_capacity, void* stream, int transform) {
+  clear_error();
+  if (!plan) return fail(GW_INVALID_ARGUMENT, "NVFP4 run requires a plan");
+  const float alpha = input_scale * weight_scale;
+  if (!input_bf16 || !weight_data || !weight_scales || !output_bf16 || !scratch || !aligned(scratch, 256) ||
+      scratch_capacity < plan->total_bytes || !finite_positive(input_scale) || !finite_positive(weight_scale) ||
+      !finite_positive(alpha) || !std::isfinite(1.0F / input_scale) ||
+      (transform != GW_TRANSFORM_IDENTITY && transform != GW_TRANSFORM_GELU_TANH_MULTIPLY))
+    return fail(GW_INVALID_ARGUMENT,
+                "NVFP4 run requires valid device buffers, aligned sufficient scratch, and finite positive global "
+                "scales");
+  if (!aligned(input_bf16, 16) || !aligned(weight_data, 16) || !aligned(weight_scales, 16) || !aligned(output_bf16, 2))
+    return fail(GW_INVALID_ARGUMENT, "NVFP4 run requires 16-byte aligned input, weights and weight scales");
+  cudaStream_t s = as_stream(stream);
+  auto* packed = static_cast<uint8_t*>(scratch);
+  uint8_t* scales = packed + plan->scale_offset;
+  GW_CUDA_CHECK(launch_nvfp4_quantize(input_bf16, plan->rows, plan->input_width, 1.0F / input_scale,
+                                      transform == GW_TRANSFORM_GELU_TANH_MULTIPLY, packed, scales, s),
+                "NVFP4 quantize activations");
+  std::string error;
+  if (plan->cached_weight != weight_data) {
+    if (!encode_tensor_map_2d(&plan->map_a, weight_data, plan->input_width / 2, plan->output_width, 128, &error))
+      return fail(GW_CUDA_ERROR, "NVFP4 weight descriptor: " + error);
+    plan->cached_weight = weight_data;
+  }
+  if (plan->cached_packed != packed) {
+    if (!encode_tensor_map_2d(&plan->map_b, packed, plan->input_width / 2, plan->rows, plan->block_n, &error))
+      return fail(GW_CUDA_ERROR, "NVFP4 activation descriptor: " + error);
+    plan->cached_packed = packed;
+  }
+  GemmParams params{};
+  params.map_a = plan->map_a;
+  params.map_b = plan->map_b;
+  params.groups = nullptr;
+  params.num_groups = 1;
+  GemmGroup& g = params.single;
+  g.sf_a = weight_scales;
+  g.channel_alpha = nullptr;
+  g.alpha = alpha;
+  g.map_a = -1;
+  g.a_tiles = int32_t(plan->output_width / 128);
+  g.a_rows = int32_t(plan->output_width);
+  g.b_row0 = 0;
+  g.b_rows = int32_t(plan->rows);
+  g.sfb_row0 = 0;
+  g.out_row0 = 0;
+  g.out_col0 = 0;
+  g.work_begin = 0;
+  const int b_tiles = (plan->rows + plan->block_n - 1) / plan->block_n;
+  params.total_work = g.a_tiles * b_tiles;
+  params.sf_b = scales;
+  params.k = int32_t(plan->input_width);
+  params.out = output_bf16;
+  params.ld_out = plan->output_width;
+  params.error = device_error_word();
+  const int grid = params.total_work < sm_count() ? params.total_work : sm_count();
+  GW_CUDA_CHECK(launch_gemm_tc(GemmKind::nvfp4, plan->block_n, params, grid, s), "NVFP4 tensor-core GEMM");
+  return GW_OK;
+}
+
+// --------------------------------------------------------------------------- FP8
+
+gw_status gw_fp8_quantize_activations(const void* input_bf16, uint32_t rows, uint32_t input_width, float input_scale,
+                                      int transform, uint8_t* packed, void* stream) {
+  clear_error();
+  if (!input_bf16 || !packed || !rows || !input_width || input_width % 16 || !finite_positive(input_scale) ||
+      !std::isfinite(1.0F / input_scale) || !aligned(input_bf16, 2) || !aligned(packed, 8) ||
+      (transform != GW_TRANSFORM_IDENTITY && transform != GW_TRANSFORM_GELU_TANH_MULTIPLY))
+    return fail(GW_INVALID_ARGUMENT, "FP8 activation quantisation requires K divisible by 16 and a finite positive input scale");
+  GW_CUDA_CHECK(launch_fp8_quantize(input_bf16, rows, input_width, 1.0F / input_scale,
+                                    transform == GW_TRANSFORM_GELU_TANH_MULTIPLY, packed, as_stream(stream)),
+                "FP8 quantize activations");
+  return GW_OK;
+}
+
+gw_status gw_fp8_pack_weights(const void* weights_bf16, uint32_t output_width, uint32_t input_width, float weight_scale,
+                              const float* row_scales, uint8_t* data, void* stream) {
+  clear_error();
+  if (!weights_bf16 || !data || !output_width || !input_width || input_width % 16 ||
+      (!row_scales && !finite_positive(weight_scale)) || !aligned(weights_bf16, 16) || !aligned(data, 8))
+    return fail(GW_INVALID_ARGUMENT, "FP8 weight packing requires aligned buffers, K divisible by 16 and a finite positive scale");
+  GW_CUDA_CHECK(launch_fp8_pack_weights(weights_bf16, output_width, input_width, weight_scale, row_scales, data,
+                                        as_stream(stream)),
+                "FP8 pack weights");
+  return GW_OK;
+}
+
+struct gw_fp8_plan {
+  uint32_t rows, input_width, output_width;
+  bool channel_scales;
+  int block_n;
+  size_t total_bytes;
+  const void* cached_weight = nullptr;
+  const void* cached_packed = nullptr;
+  CUtensorMap map_a{}, map_b{};
+};
+
+gw_status gw_fp8_plan_create(uint32_t rows, uint32_t input_width, uint32_t output_width, int channel_scales,
+                             gw_fp8_plan** plan) {
+  clear_error();
+  const uint32_t int_max = uint32_t(std::numeric_limits<int>::max());
+  if (!plan || rows == 0 || rows > int_max || input_width == 0 || input_width % 16 || input_width > int_max ||
+      output_width == 0 || output_width % 16 || output_width > int_max)
+    return fail(GW_INVALID_ARGUMENT,
+                "FP8 plan requires positive rows, K and N divisible by 16, and dimensions within int range");
+  auto* p = new (std::nothrow) gw_fp8_plan();
+  if (!p) return fail(GW_CUDA_ERROR, "out of host memory");
+  p->rows = rows;
+  p->input_width = input_width;
+  p->output_width = output_width;
+  p->channel_scales = channel_scales != 0;
+  p->block_n = pick_block_n(rows);
+  p->total_bytes = align_up(size_t(rows) * input_width, 256);
+  *plan = p;
+  return GW_OK;
+}
+
+size_t gw_fp8_plan_scratch_bytes(const gw_fp8_plan* plan) { return plan ? plan->total_bytes : 0; }
+void gw_fp8_plan_destroy(gw_fp8_plan* plan) { delete plan; }
+
+gw_status gw_fp8_plan_run(gw_fp8_plan* plan, const void* input_bf16, const uint8_t* weight_data, float input_scale,
+                          float weight_scale, const float* channel_scales, void* output_bf16, void* scratch,
+                          size_t scratch_capacity, void* stream, int transform) {
+  clear_error();
+  if (!plan) return fail(GW_INVALID_ARGUMENT, "FP8 run requires a plan");
+  const float alpha = input_scale * weight_scale;
+  if (!input_bf16 || !weight_data || !output_bf16 || !scratch || !aligned(input_bf16, 2) ||
+      !aligned(weight_data, 16) || !aligned(output_bf16, 16) || !aligned(scratch, 256) ||
+      scratch_capacity < plan->total_bytes || !finite_positive(input_scale) || !finite_positive(weight_scale) ||
+      !finite_positive(alpha) || !std::isfinite(1.0F / input_scale) ||
+      (plan->channel_scales && (!channel_scales || !aligned(channel_scales, 16))) ||
+      (transform != GW_TRANSFORM_IDENTITY && transform != GW_TRANSFORM_GELU_TANH_MULTIPLY))
+    return fail(GW_INVALID_ARGUMENT,
+                "FP8 run requires valid aligned device buffers, sufficient scratch, and finite positive global "
+                "scales with a finite positive product and finite input-scale reciprocal");
+  cudaStream_t s = as_stream(stream);
+  auto* packed = static_cast<uint8_t*>(scratch);
+  GW_CUDA_CHECK(launch_fp8_quantize(input_bf16, plan->rows, plan->input_width, 1.0F / input_scale,
+                                    transform == GW_TRANSFORM_GELU_TANH_MULTIPLY, packed, s),
+                "FP8 quantize activations");
+  std::string error;
+  if (plan->cached_weight != weight_data) {
+    if (!encode_tensor_map_2d(&plan->map_a, weight_data, plan->input_width, plan->output_width, 128, &error))
+      return fail(GW_CUDA_ERROR, "FP8 weight descriptor: " + error);
+    plan->cached_weight = weight_data;
+  }
+  if (plan->cached_packed != packed) {
+    if (!encode_tensor_map_2d(&plan->map_b, packed, plan->input_width, plan->rows, plan->block_n, &error))
+      return fail(GW_CUDA_ERROR, "FP8 activation descriptor: " + error);
+    plan->cached_packed = packed;
+  }
+  GemmParams params{};
+  params.map_a = plan->map_a;
+  params.map_b = plan->map_b;
+  params.groups = nullptr;
+  params.num_groups = 1;
+  GemmGroup& g = params.single;
+  g.sf_a = nullptr;
+  g.channel_alpha = plan->channel_scales ? channel_scales : nullptr;
+  g.alpha = alpha;
+  g.map_a = -1;
+  g.a_tiles = int32_t((plan->output_width + 127) / 128);
+  g.a_rows = int32_t(plan->output_width);
+  g.b_row0 = 0;
+  g.b_rows = int32_t(plan->rows);
+  g.sfb_row0 = 0;
+  g.out_row0 = 0;
+  g.out_col0 = 0;
+  g.work_begin = 0;
+  const int b_tiles = (plan->rows + plan->block_n - 1) / plan->block_n;
+  params.total_work = g.a_tiles * b_tiles;
+  params.sf_b = nullptr;
+  params.k = int32_t(plan->input_width);
+  params.out = output_bf16;
+  params.ld_out = plan->output_width;
+  params.error = device_error_word();
+  const int grid = params.total_work < sm_count() ? params.total_work : sm_count();
+  GW_CUDA_CHECK(launch_gemm_tc(GemmKind::fp8, plan->block_n, params, grid, s), "FP8 tensor-core GEMM");
+  return GW_OK;
+}
+
+// --------------------------------------------------------------------------- weight QDQ
+
+gw_status gw_absmax_bf16(const void* values_bf16, uint64_t elements, uint32_t* state, void* stream) {
+  clear_error();
+  if (!values_bf16 || !state || !aligned(values_bf16, 2) || !aligned(state, 4))
+    return fail(GW_INVALID_ARGUMENT, "absmax requires a tensor and a device state word pair");
+  GW_CUDA_CHECK(launch_absmax(values_bf16, elements, state, as_stream(stream)), "launch QDQ absmax kernel");
+  return GW_OK;
+}
+
+gw_status gw_weight_qdq_apply(int type, void* values_bf16, uint64_t elements, uint32_t* state, void* stream) {
+  clear_error();
+  if (type != GW_QDQ_BF16 && type != GW_QDQ_FP8 && type != GW_QDQ_NVFP4)
+    return fail(GW_INVALID_ARGUMENT, "unknown QDQ type");
+  if (type == GW_QDQ_BF16 || elements == 0) return GW_OK;
+  if (!values_bf16 || !state) return fail(GW_INVALID_ARGUMENT, "QDQ requires a tensor and a device state word pair");
+  cudaStream_t s = as_stream(stream);
+  GW_CUDA_CHECK(launch_absmax(values_bf16, elements, state, s), "launch QDQ absmax kernel");
+  uint32_t host[2] = {0, 0};
+  GW_CUDA_CHECK(cudaMemcpyAsync(host, state, sizeof(host), cudaMemcpyDeviceToHost, s), "copy QDQ reduction state");
+  GW_CUDA_CHECK(cudaStreamSynchronize(s), "synchronize QDQ reduction");
+  if (host[1] != 0) return fail(GW_INVALID_ARGUMENT, "selected QDQ weight contains a non-finite BF16 value");
+  float amax;
+  std::memcpy(&amax, &host[0], sizeof(amax));
+  if (amax == 0.0F) return GW_OK;
+  if (type == GW_QDQ_FP8) {
+    GW_CUDA_CHECK(launch_fp8_qdq(values_bf16, elements, amax / 448.0F, s), "launch static FP8 QDQ kernel");
+  } else {
+    if (elements % 16 != 0 || !aligned(values_bf16, 16))
+      return fail(GW_INVALID_ARGUMENT, "NVFP4 QDQ tensor element count is not divisible by 16");
+    GW_CUDA_CHECK(launch_nvfp4_qdq(values_bf16, elements, amax / (6.0F * 448.0F), s), "launch NVFP4 QDQ kernel");
+  }
+  return GW_OK;
+}
+
+}  // extern "C"

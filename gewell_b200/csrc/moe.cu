@@ -1,0 +1,295 @@
+// MoE workspace and expert table behind the C ABI: owns every buffer, strings
+// the routing / permutation / quantise kernels and the two grouped tcgen05
+// GEMMs together on one stream.  Mirrors sm120::MoeWorkspace
+// (models/gemma4/26b_a4b/sm120/moe.cuh:20-48, moe.cu:462-545).
+#include <cmath>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+#include "gemm_tc.cuh"
+#include "moe_kernels.h"
+
+using namespace gw;
+
+namespace {
+
+constexpr uint32_t kExperts = 128;
+constexpr uint32_t kHidden = 2816;
+constexpr uint32_t kInter = 704;
+constexpr uint32_t kMaxRows = 65536;
+
+bool finite_positive(float v) { return v > 0.0F && std::isfinite(v); }
+
+struct DeviceBuffer {
+  void* data = nullptr;
+  size_t bytes = 0;
+  cudaError_t allocate(size_t n) {
+    bytes = n;
+    return cudaMalloc(&data, n ? n : 1);
+  }
+  ~DeviceBuffer() { if (data) cudaFree(data); }
+  template <typename T> T* as() const { return static_cast<T*>(data); }
+};
+
+}  // namespace
+
+struct gw_expert_table {
+  DeviceBuffer maps;    // CUtensorMap[128*3]: gate, up, down of every expert (box 128 rows)
+  DeviceBuffer info;    // MoeExpertInfo[128]
+  bool shared_gate_up = false;   // every expert quantises gate and up inputs with one scale
+};
+
+struct gw_moe_workspace {
+  uint32_t max_rows = 0, n = 0, scale_rows = 0, chunks = 0;
+  DeviceBuffer metadata, bitmaps, groups, packed_in, scales_in, gate_up, activated, packed_act, scales_act, down;
+  int32_t *keys = nullptr, *sorted_keys = nullptr, *sorted_assignments = nullptr, *inverse = nullptr;
+  int32_t *offsets = nullptr, *chunk_counts = nullptr, *local_offsets = nullptr;
+  float* weights = nullptr;
+};
+
+extern "C" {
+
+gw_status gw_moe_expert_table_create(const gw_expert_weights* experts, uint32_t count, gw_expert_table** table) {
+  clear_error();
+  if (!experts || !table || count != kExperts)
+    return fail(GW_INVALID_ARGUMENT, "expert table requires 128 host-resident entries");
+  std::vector<CUtensorMap> maps(kExperts * 3);
+  std::vector<MoeExpertInfo> info(kExperts);
+  bool shared = true;
+  std::string error;
+  for (uint32_t e = 0; e < kExperts; ++e) {
+    const gw_projection* proj[3] = {&experts[e].gate, &experts[e].up, &experts[e].down};
+    for (int i = 0; i < 3; ++i) {
+      const gw_projection& p = *proj[i];
+      const uint32_t want_in = i < 2 ? kHidden : kInter, want_out = i < 2 ? kInter : kHidden;
+      if (p.storage != GW_STORAGE_NVFP4_W4A4)
+        return fail(GW_UNSUPPORTED, "only NVFP4 (W4A4) experts are built; expert " + std::to_string(e) +
+                                        " uses another storage type");
+      if (p.input != want_in || p.output != want_out || p.physical_output != (want_out + 127) / 128 * 128 ||
+          !p.nvfp4_data || !p.nvfp4_scales || reinterpret_cast<uintptr_t>(p.nvfp4_data) % 16 ||
+          reinterpret_cast<uintptr_t>(p.nvfp4_scales) % 16 || !finite_positive(p.nvfp4_input_scale) ||
+          !finite_positive(p.nvfp4_weight_scale) || !std::isfinite(1.0F / p.nvfp4_input_scale) ||
+          !finite_positive(p.nvfp4_input_scale * p.nvfp4_weight_scale))
+        return fail(GW_INVALID_ARGUMENT, "invalid 26B expert projection binding (expert " + std::to_string(e) + ")");
+      if (!encode_tensor_map_2d(&maps[e * 3 + i], p.nvfp4_data, p.input / 2, p.physical_output, 128, &error))
+        return fail(GW_CUDA_ERROR, "expert weight descriptor: " + error);
+      info[e].scales[i] = p.nvfp4_scales;
+      info[e].alpha[i] = p.nvfp4_input_scale * p.nvfp4_weight_scale;   // == __fmul_rn on the device
+      info[e].inverse_input_scale[i] = 1.0F / p.nvfp4_input_scale;
+    }
+    if (experts[e].gate.nvfp4_input_scale != experts[e].up.nvfp4_input_scale) shared = false;
+  }
+  auto* t = new (std::nothrow) gw_expert_table();
+  if (!t) return fail(GW_CUDA_ERROR, "out of host memory");
+  t->shared_gate_up = shared;
+  cudaError_t status = t->maps.allocate(maps.size() * sizeof(CUtensorMap));
+  if (status == cudaSuccess) status = t->info.allocate(info.size() * sizeof(MoeExpertInfo));
+  if (status == cudaSuccess)
+    status = cudaMemcpy(t->maps.data, maps.data(), maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice);
+  if (status == cudaSuccess)
+    status = cudaMemcpy(t->info.data, info.data(), info.size() * sizeof(MoeExpertInfo), cudaMemcpyHostToDevice);
+  if (status != cudaSuccess) {
+    delete t;
+    return fail(GW_CUDA_ERROR, std::string("expert table upload: ") + cudaGetErrorString(status));
+  }
+  *table = t;
+  return GW_OK;
+}
+
+void gw_moe_expert_table_destroy(gw_expert_table* table) { delete table; }
+
+gw_status gw_moe_create(uint32_t max_rows, gw_moe_workspace** workspace) {
+  clear_error();
+  if (!workspace || max_rows == 0 || max_rows > kMaxRows)
+    return fail(GW_INVALID_ARGUMENT, "MoE capacity must be in 1..65536");
+  auto* w = new (std::nothrow) gw_moe_workspace();
+  if (!w) return fail(GW_CUDA_ERROR, "out of host memory");
+  w->max_rows = max_rows;
+  w->n = 8 * max_rows;
+  const size_t n = w->n;
+  w->scale_rows = uint32_t(((n + 127) / 128 + 128) * 128);
+  w->chunks = moe_chunks(max_rows);
+  const size_t metadata_ints = 5 * n + 2 * 132 + size_t(w->chunks) * kExperts;
+  cudaError_t status = w->metadata.allocate((metadata_ints + n) * sizeof(int32_t));
+  if (status == cudaSuccess) status = w->bitmaps.allocate(size_t(w->chunks) * kExperts * 2 * sizeof(uint32_t));
+  if (status == cudaSuccess) status = w->groups.allocate((2 * kExperts + 1 + kExperts + 1) * sizeof(GemmGroup));
+  if (status == cudaSuccess) status = w->packed_in.allocate(2 * n * (kHidden / 2));
+  if (status == cudaSuccess) status = w->scales_in.allocate(2 * size_t(w->scale_rows) * (kHidden / 16));
+  if (status == cudaSuccess) status = w->gate_up.allocate(n * 2 * kInter * sizeof(bf16));
+  if (status == cudaSuccess) status = w->activated.allocate(n * kInter * sizeof(bf16));
+  if (status == cudaSuccess) status = w->packed_act.allocate(n * (kInter / 2));
+  if (status == cudaSuccess) status = w->scales_act.allocate(size_t(w->scale_rows) * (kInter / 16));
+  if (status == cudaSuccess) status = w->down.allocate(n * kHidden * sizeof(bf16));
+  // Scale regions contain rows no kernel writes (tile padding); start from zero so
+  // that they never hold NaN patterns.
+  if (status == cudaSuccess) status = cudaMemset(w->scales_in.data, 0, w->scales_in.bytes);
+  if (status == cudaSuccess) status = cudaMemset(w->scales_act.data, 0, w->scales_act.bytes);
+  if (status != cudaSuccess) {
+    delete w;
+    return fail(GW_CUDA_ERROR, std::string("MoE workspace allocation: ") + cudaGetErrorString(status));
+  }
+  auto* p = w->metadata.as<int32_t>();
+  w->keys = p;
+  w->sorted_keys = p + n;
+  w->sorted_assignments = p + 2 * n;
+  w->inverse = p + 3 * n;
+  w->weights = reinterpret_cast<float*>(p + 4 * n);
+  w->offsets = p + 5 * n;
+  w->local_offsets = p + 5 * n + 132;
+  w->chunk_counts = p + 5 * n + 264;
+  *workspace = w;
+  return GW_OK;
+}
+
+void gw_moe_destroy(gw_moe_workspace* workspace) { delete workspace; }
+
+gw_status gw_moe_dispatch(gw_moe_workspace* w, const void* scores_bf16, const void* expert_scales_bf16, uint32_t rows,
+                          void* stream) {
+  clear_error();
+  if (!w) return fail(GW_INVALID_ARGUMENT, "MoE dispatch requires a workspace");
+  if (rows > w->max_rows) return fail(GW_INVALID_ARGUMENT, "MoE rows exceed workspace");
+  if (!rows) return GW_OK;
+  if (!scores_bf16 || !expert_scales_bf16) return fail(GW_INVALID_ARGUMENT, "MoE dispatch requires scores and expert scales");
+  GW_CUDA_CHECK(launch_moe_dispatch(scores_bf16, expert_scales_bf16, rows, w->keys, w->weights, w->bitmaps.as<uint32_t>(),
+                                    w->chunk_counts, w->offsets, w->sorted_assignments, w->sorted_keys, w->inverse,
+                                    as_stream(stream)),
+                "MoE dispatch");
+  return GW_OK;
+}
+
+}  // extern "C"
+
+namespace {
+
+// Expert MLP over rows sorted by expert: quantise -> gate/up GEMM -> GeGLU +
+// quantise -> down GEMM.  `gather_index` != nullptr reads input rows through
+// the permutation (token = index / 8); otherwise input row i is sorted row i.
+gw_status run_experts(gw_moe_workspace* w, const void* input, const int32_t* gather_index, const int32_t* offsets,
+                      uint32_t n, const gw_expert_table* table, void* down_out, cudaStream_t s) {
+  const auto* info = table->info.as<MoeExpertInfo>();
+  auto* gate_up_groups = w->groups.as<GemmGroup>();
+  auto* down_groups = gate_up_groups + 2 * kExperts + 1;
+  // Token-side tile: small batches leave most experts with a handful of rows.
+  const int block_n = n <= 8 * 64 ? 32 : (n <= 8 * 1024 ? 128 : 256);
+  const int parts = table->shared_gate_up ? 1 : 2;
+  GW_CUDA_CHECK(launch_moe_prepare_groups(offsets, info, n, w->scale_rows, block_n, table->shared_gate_up,
+                                          gate_up_groups, down_groups, s),
+                "MoE group descriptors");
+  GW_CUDA_CHECK(launch_moe_quantize_input(input, gather_index, w->sorted_keys, offsets, info, n, w->scale_rows, parts,
+                                          w->packed_in.as<uint8_t>(), w->scales_in.as<uint8_t>(), s),
+                "MoE gather + quantise");
+  std::string error;
+  GemmParams params{};
+  if (!encode_tensor_map_2d(&params.map_b, w->packed_in.data, kHidden / 2, size_t(parts) * n, block_n, &error))
+    return fail(GW_CUDA_ERROR, "MoE activation descriptor: " + error);
+  params.map_a_table = table->maps.as<CUtensorMap>();
+  params.groups = gate_up_groups;
+  params.num_groups = 2 * kExperts;
+  params.sf_b = w->scales_in.as<uint8_t>();
+  params.k = kHidden;
+  params.out = w->gate_up.data;
+  params.ld_out = 2 * kInter;
+  params.error = device_error_word();
+  GW_CUDA_CHECK(launch_gemm_tc(GemmKind::nvfp4, block_n, params, sm_count(), s), "MoE grouped gate/up GEMM");
+  GW_CUDA_CHECK(launch_moe_activate_quantize(w->gate_up.data, w->sorted_keys, offsets, info, n, w->scale_rows,
+                                             w->packed_act.as<uint8_t>(), w->scales_act.as<uint8_t>(), w->activated.data, s),
+                "MoE GeGLU + quantise");
+  GemmParams down{};
+  if (!encode_tensor_map_2d(&down.map_b, w->packed_act.data, kInter / 2, n, block_n, &error))
+    return fail(GW_CUDA_ERROR, "MoE activation descriptor: " + error);
+  down.map_a_table = table->maps.as<CUtensorMap>();
+  down.groups = down_groups;
+  down.num_groups = kExperts;
+  down.sf_b = w->scales_act.as<uint8_t>();
+  down.k = kInter;
+  down.out = down_out;
+  down.ld_out = kHidden;
+  down.error = device_error_word();
+  GW_CUDA_CHECK(launch_gemm_tc(GemmKind::nvfp4, block_n, down, sm_count(), s), "MoE grouped down GEMM");
+  return GW_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+gw_status gw_moe_run(gw_moe_workspace* w, const void* input_bf16, const void* scores_bf16,
+                     const void* expert_scales_bf16, const gw_expert_table* table, void* output_bf16, uint32_t rows,
+                     int has_bf16, int has_fp8, int has_nvfp4, int fp4, void* stream) {
+  clear_error();
+  if (!w) return fail(GW_INVALID_ARGUMENT, "MoE run requires a workspace");
+  if (rows > w->max_rows) return fail(GW_INVALID_ARGUMENT, "MoE rows exceed workspace");
+  if (!rows) return GW_OK;
+  if (!input_bf16 || !scores_bf16 || !expert_scales_bf16 || !table || !output_bf16 ||
+      reinterpret_cast<uintptr_t>(input_bf16) % 16 || reinterpret_cast<uintptr_t>(output_bf16) % 16)
+    return fail(GW_INVALID_ARGUMENT, "MoE run requires 16-byte aligned input/output, scores, expert scales and a bound expert table");
+  if (has_bf16 || has_fp8 || !has_nvfp4 || !fp4)
+    return fail(GW_UNSUPPORTED, "only NVFP4 experts with FP4 activations (W4A4) are built");
+  gw_status status = gw_moe_dispatch(w, scores_bf16, expert_scales_bf16, rows, stream);
+  if (status != GW_OK) return status;
+  cudaStream_t s = as_stream(stream);
+  status = run_experts(w, input_bf16, w->sorted_assignments, w->offsets, 8 * rows, table, w->down.data, s);
+  if (status != GW_OK) return status;
+  GW_CUDA_CHECK(launch_moe_combine(w->down.data, w->inverse, w->weights, rows, kHidden, output_bf16, s), "MoE combine");
+  return GW_OK;
+}
+
+gw_status gw_moe_run_sorted(gw_moe_workspace* w, const void* input_bf16, const int32_t* offsets, uint32_t first_expert,
+                            uint32_t expert_count, uint32_t total_rows, const gw_expert_table* table, void* output_bf16,
+                            void* stream) {
+  clear_error();
+  if (!w || !table) return fail(GW_INVALID_ARGUMENT, "sorted MoE run requires a workspace and an expert table");
+  if (total_rows > w->n) return fail(GW_INVALID_ARGUMENT, "sorted MoE rows exceed workspace (8 x max_rows)");
+  if (!total_rows) return GW_OK;
+  if (!input_bf16 || !offsets || !output_bf16 || expert_count == 0 || first_expert + expert_count > kExperts ||
+      reinterpret_cast<uintptr_t>(input_bf16) % 16 || reinterpret_cast<uintptr_t>(output_bf16) % 16)
+    return fail(GW_INVALID_ARGUMENT, "sorted MoE run requires aligned buffers and an expert range inside 0..128");
+  cudaStream_t s = as_stream(stream);
+  GW_CUDA_CHECK(launch_moe_keys_from_offsets(offsets, first_expert, expert_count, total_rows, w->sorted_keys,
+                                             w->local_offsets, s),
+                "MoE keys from offsets");
+  return run_experts(w, input_bf16, nullptr, w->local_offsets, total_rows, table, output_bf16, s);
+}
+
+gw_status gw_gather_rows_bf16(const void* input_bf16, const int32_t* index, uint32_t divisor, uint32_t rows,
+                              uint32_t width, void* output_bf16, void* stream) {
+  clear_error();
+  if (!rows) return GW_OK;
+  if (!input_bf16 || !index || !output_bf16 || !divisor || !width || width % 8 ||
+      reinterpret_cast<uintptr_t>(input_bf16) % 16 || reinterpret_cast<uintptr_t>(output_bf16) % 16)
+    return fail(GW_INVALID_ARGUMENT, "row gather requires 16-byte aligned buffers and a width divisible by 8");
+  GW_CUDA_CHECK(launch_gather_rows(input_bf16, index, divisor, rows, width, output_bf16, as_stream(stream)), "row gather");
+  return GW_OK;
+}
+
+gw_status gw_moe_combine(const void* down_bf16, const int32_t* inverse, const float* weights, uint32_t rows,
+                         uint32_t width, void* output_bf16, void* stream) {
+  clear_error();
+  if (!rows) return GW_OK;
+  if (!down_bf16 || !inverse || !weights || !output_bf16 || !width || width % 8 ||
+      reinterpret_cast<uintptr_t>(down_bf16) % 16 || reinterpret_cast<uintptr_t>(output_bf16) % 16)
+    return fail(GW_INVALID_ARGUMENT, "MoE combine requires 16-byte aligned buffers and a width divisible by 8");
+  GW_CUDA_CHECK(launch_moe_combine(down_bf16, inverse, weights, rows, width, output_bf16, as_stream(stream)), "MoE combine");
+  return GW_OK;
+}
+
+const int32_t* gw_moe_selected_experts(const gw_moe_workspace* w) { return w ? w->keys : nullptr; }
+const float* gw_moe_routing_weights(const gw_moe_workspace* w) { return w ? w->weights : nullptr; }
+const int32_t* gw_moe_offsets(const gw_moe_workspace* w) { return w ? w->offsets : nullptr; }
+const int32_t* gw_moe_sorted_assignments(const gw_moe_workspace* w) { return w ? w->sorted_assignments : nullptr; }
+const void* gw_moe_gate_up_capture(const gw_moe_workspace* w) { return w ? w->gate_up.data : nullptr; }
+const void* gw_moe_activated_capture(const gw_moe_workspace* w) { return w ? w->activated.data : nullptr; }
+const void* gw_moe_down_capture(const gw_moe_workspace* w) { return w ? w->down.data : nullptr; }
+size_t gw_moe_routing_bytes(const gw_moe_workspace* w) { return w ? w->metadata.bytes + w->bitmaps.bytes + w->groups.bytes : 0; }
+size_t gw_moe_projection_bytes(const gw_moe_workspace* w) {
+  return w ? w->packed_in.bytes + w->scales_in.bytes + w->gate_up.bytes + w->activated.bytes + w->packed_act.bytes +
+                 w->scales_act.bytes : 0;
+}
+size_t gw_moe_reduction_bytes(const gw_moe_workspace* w) { return w ? w->down.bytes : 0; }
+size_t gw_moe_bytes(const gw_moe_workspace* w) {
+  return gw_moe_routing_bytes(w) + gw_moe_projection_bytes(w) + gw_moe_reduction_bytes(w);
+}
+
+}  // extern "C"

@@ -1,0 +1,440 @@
+// MoE routing, permutation, fused gather+quantise, GeGLU+quantise and the
+// ordered combine for the 128-expert / top-8 layer (hidden 2816, expert MLP
+// 704).  Everything stays on the device: no routing data is read back.
+//
+// Permutation.  The reference radix-sorts (expert, assignment) pairs; because
+// the eight experts of a token are distinct, the stable order inside an expert
+// is simply token order.  So the position of assignment (t, slot) is
+//   offsets[e] + #tokens t' < t that chose e,
+// computed here with per-64-token bitmaps and popcounts: kernel 1 routes and
+// builds the bitmaps, kernel 2 scans the per-chunk counts, kernel 3 scatters.
+#include "common.cuh"
+#include "moe_kernels.h"
+
+namespace gw {
+namespace {
+
+constexpr int kExperts = 128;
+constexpr int kTopK = 8;
+constexpr int kHidden = 2816;
+constexpr int kInter = 704;
+constexpr int kChunkTokens = 64;   // tokens per routing block (two 32-bit bitmap words per expert)
+
+__device__ __forceinline__ void unpack8(const uint4& raw, float* out) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    out[2 * i] = __uint_as_float(w[i] << 16);
+    out[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// 1. route: FP32 softmax over 128 BF16 logits, eight winners (lower id wins
+//    ties), renormalise, times the per-expert scale, sort the eight by id.
+//    Arithmetic and reduction order follow the reference's select kernel
+//    (models/gemma4/26b_a4b/sm120/moe.cu:104-157) so ids and FP32 weights match
+//    it bit for bit.  One warp per token, eight tokens per warp.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+moe_route_kernel(const bf16* __restrict__ scores, const bf16* __restrict__ expert_scales, uint32_t rows,
+                 int32_t* __restrict__ keys, float* __restrict__ weights, uint32_t* __restrict__ bitmaps,
+                 int32_t* __restrict__ chunk_counts) {
+  __shared__ uint32_t bitmap[kExperts][2];
+  const unsigned lane = threadIdx.x % 32, warp = threadIdx.x / 32;
+  if (threadIdx.x < kExperts) { bitmap[threadIdx.x][0] = 0; bitmap[threadIdx.x][1] = 0; }
+  __syncthreads();
+  const uint32_t chunk = blockIdx.x;
+  for (int t = 0; t < kChunkTokens / 8; ++t) {
+    const uint32_t local = warp * (kChunkTokens / 8) + t;
+    const uint32_t row = chunk * kChunkTokens + local;
+    if (row >= rows) break;
+    float elements[4], maximum = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      elements[i] = __bfloat162float(scores[size_t(row) * kExperts + lane + i * 32]);
+      maximum = fmaxf(maximum, elements[i]);
+    }
+    for (int offset = 16; offset; offset /= 2)
+      maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, offset));
+    float total = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { elements[i] = expf(elements[i] - maximum); total += elements[i]; }
+    for (int offset = 16; offset; offset /= 2) total += __shfl_xor_sync(0xffffffffu, total, offset);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) elements[i] = __fdiv_rn(elements[i], total);
+    int ids[kTopK];
+    float chosen[kTopK];
+    unsigned used = 0;
+#pragma unroll
+    for (int i = 0; i < kTopK; ++i) {
+      int best = kExperts;
+      float probability = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (!(used & (1u << j)) && (best == kExperts || elements[j] > probability)) {
+          best = lane + j * 32;
+          probability = elements[j];
+        }
+      for (int offset = 16; offset; offset /= 2) {
+        const float other = __shfl_xor_sync(0xffffffffu, probability, offset);
+        const int expert = __shfl_xor_sync(0xffffffffu, best, offset);
+        if (other > probability || (other == probability && expert < best)) { best = expert; probability = other; }
+      }
+      ids[i] = best;
+      chosen[i] = probability;
+      if (unsigned(best) % 32 == lane) used |= 1u << (unsigned(best) / 32);
+    }
+    // ((p0+p4)+(p2+p6)) + ((p1+p5)+(p3+p7)), as the reference's stride-4/2/1 fold
+    const float s0 = chosen[0] + chosen[4], s1 = chosen[1] + chosen[5];
+    const float s2 = chosen[2] + chosen[6], s3 = chosen[3] + chosen[7];
+    const float sum = (s0 + s2) + (s1 + s3);
+    int my_id = 0;
+    float my_p = 0;
+#pragma unroll
+    for (int i = 0; i < kTopK; ++i) if (lane == unsigned(i)) { my_id = ids[i]; my_p = chosen[i]; }
+    if (lane < kTopK) {
+      int rank = 0;
+#pragma unroll
+      for (int i = 0; i < kTopK; ++i) rank += ids[i] < my_id;
+      const float weight = __fmul_rn(__fdiv_rn(my_p, sum), __bfloat162float(expert_scales[my_id]));
+      keys[size_t(row) * kTopK + rank] = my_id;
+      weights[size_t(row) * kTopK + rank] = weight;
+      atomicOr(&bitmap[my_id][local / 32], 1u << (local % 32));
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < kExperts) {
+    const uint32_t w0 = bitmap[threadIdx.x][0], w1 = bitmap[threadIdx.x][1];
+    bitmaps[(size_t(chunk) * kExperts + threadIdx.x) * 2] = w0;
+    bitmaps[(size_t(chunk) * kExperts + threadIdx.x) * 2 + 1] = w1;
+    chunk_counts[size_t(chunk) * kExperts + threadIdx.x] = __popc(w0) + __popc(w1);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// 2. scan: per expert, exclusive prefix of the chunk counts (in place) and the
+//    expert offsets (== searchsorted of the sorted keys, moe.cu:158-167).
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(kExperts)
+moe_scan_kernel(int32_t* __restrict__ chunk_counts, uint32_t chunks, int32_t* __restrict__ offsets) {
+  __shared__ int32_t totals[kExperts];
+  const unsigned e = threadIdx.x;
+  int32_t running = 0;
+#pragma unroll 8
+  for (uint32_t c = 0; c < chunks; ++c) {
+    const int32_t v = chunk_counts[size_t(c) * kExperts + e];
+    chunk_counts[size_t(c) * kExperts + e] = running;
+    running += v;
+  }
+  totals[e] = running;
+  __syncthreads();
+  if (e == 0) {
+    int32_t acc = 0;
+    for (int i = 0; i < kExperts; ++i) { offsets[i] = acc; acc += totals[i]; }
+    offsets[kExperts] = acc;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// 3. scatter: stable position of every assignment, sorted assignments/keys and
+//    the inverse permutation (moe.cu:179-182).
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+moe_scatter_kernel(const int32_t* __restrict__ keys, const uint32_t* __restrict__ bitmaps,
+                   const int32_t* __restrict__ chunk_base, const int32_t* __restrict__ offsets, uint32_t rows,
+                   int32_t* __restrict__ sorted_assignments, int32_t* __restrict__ sorted_keys,
+                   int32_t* __restrict__ inverse) {
+  __shared__ uint32_t bitmap[kExperts][2];
+  __shared__ int32_t base[kExperts];
+  const uint32_t chunk = blockIdx.x;
+  if (threadIdx.x < kExperts) {
+    bitmap[threadIdx.x][0] = bitmaps[(size_t(chunk) * kExperts + threadIdx.x) * 2];
+    bitmap[threadIdx.x][1] = bitmaps[(size_t(chunk) * kExperts + threadIdx.x) * 2 + 1];
+    base[threadIdx.x] = offsets[threadIdx.x] + chunk_base[size_t(chunk) * kExperts + threadIdx.x];
+  }
+  __syncthreads();
+  for (uint32_t i = threadIdx.x; i < kChunkTokens * kTopK; i += 256) {
+    const uint32_t local = i / kTopK;
+    const uint32_t row = chunk * kChunkTokens + local;
+    if (row >= rows) continue;
+    const uint32_t assignment = row * kTopK + i % kTopK;
+    const int32_t e = keys[assignment];
+    const uint32_t w0 = bitmap[e][0], w1 = bitmap[e][1];
+    const int rank = local < 32 ? __popc(w0 & ((1u << local) - 1u))
+                                : __popc(w0) + __popc(w1 & ((1u << (local - 32)) - 1u));
+    const int32_t position = base[e] + rank;
+    sorted_assignments[position] = int32_t(assignment);
+    sorted_keys[position] = e;
+    inverse[assignment] = position;
+  }
+}
+
+// Expert id of every row of an already sorted buffer (expert-parallel entry).
+__global__ void __launch_bounds__(256)
+moe_keys_from_offsets_kernel(const int32_t* __restrict__ offsets, uint32_t first_expert, uint32_t expert_count,
+                             uint32_t rows, int32_t* __restrict__ sorted_keys, int32_t* __restrict__ full_offsets) {
+  const uint32_t i = blockIdx.x * 256 + threadIdx.x;
+  if (blockIdx.x == 0 && threadIdx.x <= kExperts) {
+    // offsets over all 128 experts: empty outside [first, first+count)
+    const uint32_t e = threadIdx.x;
+    int32_t v;
+    if (e < first_expert) v = 0;
+    else if (e <= first_expert + expert_count) v = offsets[e - first_expert];
+    else v = offsets[expert_count];
+    full_offsets[e] = v;
+  }
+  if (i >= rows) return;
+  uint32_t lo = 0, hi = expert_count;   // largest e with offsets[e] <= i
+  while (lo + 1 < hi) {
+    const uint32_t mid = (lo + hi) / 2;
+    if (uint32_t(offsets[mid]) <= i) lo = mid; else hi = mid;
+  }
+  sorted_keys[i] = int32_t(first_expert + lo);
+}
+
+// ---------------------------------------------------------------------------
+// 4. group descriptors of the two grouped GEMMs, from the offsets (the role of
+//    grouped_nvfp4::prepare, moe_nvfp4.cuh:51-78).
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+moe_prepare_groups_kernel(const int32_t* __restrict__ offsets, const MoeExpertInfo* __restrict__ experts,
+                          uint32_t n, uint32_t scale_rows, int block_n, int shared_gate_up,
+                          GemmGroup* __restrict__ gate_up_groups, GemmGroup* __restrict__ down_groups) {
+  __shared__ int32_t items_gu[2 * kExperts], items_dn[kExperts];
+  const unsigned g = threadIdx.x;            // 0..255: expert = g/2, part = g%2
+  const unsigned e = g / 2, part = g % 2;
+  const int32_t first = offsets[e], count = offsets[e + 1] - first;
+  const int32_t b_tiles = (count + block_n - 1) / block_n;
+  const int32_t padded_first = (first / 128 + int32_t(e)) * 128;
+  const MoeExpertInfo info = experts[e];
+  {
+    GemmGroup grp{};
+    const int proj = part;                   // 0 gate, 1 up
+    const int src_part = shared_gate_up ? 0 : int(part);
+    grp.sf_a = info.scales[proj];
+    grp.channel_alpha = nullptr;
+    grp.alpha = info.alpha[proj];
+    grp.map_a = int32_t(e) * 3 + proj;
+    grp.a_tiles = (kInter + 127) / 128;
+    grp.a_rows = kInter;
+    grp.b_row0 = src_part * int32_t(n) + first;
+    grp.b_rows = count;
+    grp.sfb_row0 = src_part * int32_t(scale_rows) + padded_first;
+    grp.out_row0 = first;
+    grp.out_col0 = proj * kInter;
+    items_gu[g] = grp.a_tiles * b_tiles;
+    gate_up_groups[g] = grp;
+  }
+  if (part == 0) {
+    GemmGroup grp{};
+    grp.sf_a = info.scales[2];
+    grp.channel_alpha = nullptr;
+    grp.alpha = info.alpha[2];
+    grp.map_a = int32_t(e) * 3 + 2;
+    grp.a_tiles = kHidden / 128;
+    grp.a_rows = kHidden;
+    grp.b_row0 = first;
+    grp.b_rows = count;
+    grp.sfb_row0 = padded_first;
+    grp.out_row0 = first;
+    grp.out_col0 = 0;
+    items_dn[e] = grp.a_tiles * b_tiles;
+    down_groups[e] = grp;
+  }
+  __syncthreads();
+  if (g == 0) {
+    int32_t acc = 0;
+    for (int i = 0; i < 2 * kExperts; ++i) { gate_up_groups[i].work_begin = acc; acc += items_gu[i]; }
+    GemmGroup sentinel{};
+    sentinel.work_begin = acc;
+    sentinel.a_tiles = 1;
+    gate_up_groups[2 * kExperts] = sentinel;
+  }
+  if (g == 1) {
+    int32_t acc = 0;
+    for (int i = 0; i < kExperts; ++i) { down_groups[i].work_begin = acc; acc += items_dn[i]; }
+    GemmGroup sentinel{};
+    sentinel.work_begin = acc;
+    sentinel.a_tiles = 1;
+    down_groups[kExperts] = sentinel;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// 5. NVFP4 quantisation of sorted rows with the destination expert's input
+//    scale (recipe of moe.cu:254-304 == src/nvfp4_linear.cu:61-116), reading
+//    either through the permutation (fused gather, moe.cu:183-186) or in place.
+//    One thread per K16 block.  Scales go to the expert's 128-row aligned
+//    region ((first/128 + e) * 128, moe.cu:296-300) in the tiled layout.
+//    Source modes: plain rows of width K, or [rows, 2K] gate|up with GeGLU
+//    (moe.cu:439-445) whose BF16 result is also stored for the capture accessor.
+// ---------------------------------------------------------------------------
+template <int K, bool Gelu>
+__global__ void __launch_bounds__(256)
+moe_quantize_kernel(const uint4* __restrict__ input, const int32_t* __restrict__ gather_index,
+                    const int32_t* __restrict__ sorted_keys, const int32_t* __restrict__ offsets,
+                    const MoeExpertInfo* __restrict__ experts, uint32_t n, uint32_t scale_rows, int projection,
+                    uint2* __restrict__ packed, uint8_t* __restrict__ scales, uint4* __restrict__ activated) {
+  constexpr uint32_t kBlocks = K / 16;
+  const size_t index = size_t(blockIdx.x) * 256 + threadIdx.x;
+  const uint32_t part = blockIdx.y;             // gate/up copy (0 unless the scales differ)
+  if (index >= size_t(n) * kBlocks) return;
+  const uint32_t row = index / kBlocks, kb = index % kBlocks;
+  const int32_t e = sorted_keys[row];
+  const int32_t first = offsets[e];
+  const float inverse_scale = experts[e].inverse_input_scale[projection + part];
+  float values[16];
+  if constexpr (Gelu) {
+    const size_t gate = size_t(row) * (2 * kBlocks) + kb;
+    float g[16], u[16];
+    unpack8(input[2 * gate], g);
+    unpack8(input[2 * gate + 1], g + 8);
+    unpack8(input[2 * (gate + kBlocks)], u);
+    unpack8(input[2 * (gate + kBlocks) + 1], u + 8);
+    uint32_t words[8];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) values[i] = gelu_tanh_multiply_bf16(g[i], u[i]);
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      words[i] = (__float_as_uint(values[2 * i]) >> 16) | (__float_as_uint(values[2 * i + 1]) & 0xFFFF0000u);
+    if (activated != nullptr) {
+      activated[2 * index] = make_uint4(words[0], words[1], words[2], words[3]);
+      activated[2 * index + 1] = make_uint4(words[4], words[5], words[6], words[7]);
+    }
+  } else {
+    const size_t source_row = gather_index ? size_t(gather_index[row]) / kTopK : row;
+    const size_t block = source_row * kBlocks + kb;
+    unpack8(input[2 * block], values);
+    unpack8(input[2 * block + 1], values + 8);
+  }
+  float amax = 0.0F;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(values[i]));
+  const uint8_t scale_code = float_to_e4m3(inverse_scale * (amax * rcp_approx_ftz(6.0F)));
+  const float block_scale = e4m3_to_float(scale_code);
+  const float factor =
+      block_scale == 0.0F ? 0.0F : rcp_approx_ftz(block_scale * rcp_approx_ftz(inverse_scale));
+  uint32_t out[2] = {0, 0};
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    out[i / 4] |= uint32_t(float2_to_e2m1x2(values[2 * i] * factor, values[2 * i + 1] * factor)) << (8 * (i % 4));
+  packed[(size_t(part) * n + row) * kBlocks + kb] = make_uint2(out[0], out[1]);
+  const size_t region = (size_t(part) * scale_rows + size_t(first / 128 + e) * 128) * kBlocks;
+  scales[region + scale_offset(row - first, kb, K)] = scale_code;
+}
+
+// ---------------------------------------------------------------------------
+// 6. combine: out[t,:] = ordered BF16 fold over the token's eight slots
+//    (ascending expert id) of bf16(down[inverse[8t+j],:] * w[8t+j])
+//    (moe.cu:446-456).  Eight columns per thread.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const uint4* __restrict__ down, const int32_t* __restrict__ inverse,
+                   const float* __restrict__ weights, uint32_t rows, uint32_t width, uint4* __restrict__ output) {
+  const uint32_t vectors = width / 8;
+  const size_t index = size_t(blockIdx.x) * 256 + threadIdx.x;
+  if (index >= size_t(rows) * vectors) return;
+  const uint32_t row = index / vectors, v = index % vectors;
+  float sum[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) sum[i] = 0.0F;
+#pragma unroll
+  for (int j = 0; j < kTopK; ++j) {
+    const uint32_t assignment = row * kTopK + j;
+    const float w = weights[assignment];
+    float x[8];
+    unpack8(down[size_t(inverse[assignment]) * vectors + v], x);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float product = __bfloat162float(__float2bfloat16_rn(__fmul_rn(x[i], w)));
+      sum[i] = __bfloat162float(__float2bfloat16_rn(__fadd_rn(sum[i], product)));
+    }
+  }
+  uint32_t words[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    words[i] = (__float_as_uint(sum[2 * i]) >> 16) | (__float_as_uint(sum[2 * i + 1]) & 0xFFFF0000u);
+  output[index] = make_uint4(words[0], words[1], words[2], words[3]);
+}
+
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const uint4* __restrict__ input, const int32_t* __restrict__ index, uint32_t divisor,
+                   uint32_t rows, uint32_t vectors, uint4* __restrict__ output) {
+  const size_t i = size_t(blockIdx.x) * 256 + threadIdx.x;
+  if (i >= size_t(rows) * vectors) return;
+  const uint32_t row = i / vectors, v = i % vectors;
+  output[i] = input[size_t(uint32_t(index[row]) / divisor) * vectors + v];
+}
+
+unsigned blocks_for(size_t items) { return unsigned((items + 255) / 256); }
+
+}  // namespace
+
+uint32_t moe_chunks(uint32_t rows) { return (rows + kChunkTokens - 1) / kChunkTokens; }
+
+cudaError_t launch_moe_dispatch(const void* scores, const void* expert_scales, uint32_t rows, int32_t* keys,
+                                float* weights, uint32_t* bitmaps, int32_t* chunk_counts, int32_t* offsets,
+                                int32_t* sorted_assignments, int32_t* sorted_keys, int32_t* inverse,
+                                cudaStream_t stream) {
+  const uint32_t chunks = moe_chunks(rows);
+  moe_route_kernel<<<chunks, 256, 0, stream>>>(static_cast<const bf16*>(scores), static_cast<const bf16*>(expert_scales),
+                                               rows, keys, weights, bitmaps, chunk_counts);
+  moe_scan_kernel<<<1, kExperts, 0, stream>>>(chunk_counts, chunks, offsets);
+  moe_scatter_kernel<<<chunks, 256, 0, stream>>>(keys, bitmaps, chunk_counts, offsets, rows, sorted_assignments,
+                                                 sorted_keys, inverse);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_moe_keys_from_offsets(const int32_t* offsets, uint32_t first_expert, uint32_t expert_count,
+                                         uint32_t rows, int32_t* sorted_keys, int32_t* full_offsets,
+                                         cudaStream_t stream) {
+  moe_keys_from_offsets_kernel<<<blocks_for(rows > 256 ? rows : 256), 256, 0, stream>>>(
+      offsets, first_expert, expert_count, rows, sorted_keys, full_offsets);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_moe_prepare_groups(const int32_t* offsets, const MoeExpertInfo* experts, uint32_t n,
+                                      uint32_t scale_rows, int block_n, bool shared_gate_up, GemmGroup* gate_up_groups,
+                                      GemmGroup* down_groups, cudaStream_t stream) {
+  moe_prepare_groups_kernel<<<1, 256, 0, stream>>>(offsets, experts, n, scale_rows, block_n, shared_gate_up ? 1 : 0,
+                                                   gate_up_groups, down_groups);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_moe_quantize_input(const void* input, const int32_t* gather_index, const int32_t* sorted_keys,
+                                      const int32_t* offsets, const MoeExpertInfo* experts, uint32_t n,
+                                      uint32_t scale_rows, int parts, uint8_t* packed, uint8_t* scales,
+                                      cudaStream_t stream) {
+  const dim3 grid(blocks_for(size_t(n) * (kHidden / 16)), parts);
+  moe_quantize_kernel<kHidden, false><<<grid, 256, 0, stream>>>(
+      static_cast<const uint4*>(input), gather_index, sorted_keys, offsets, experts, n, scale_rows, 0,
+      reinterpret_cast<uint2*>(packed), scales, nullptr);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_moe_activate_quantize(const void* gate_up, const int32_t* sorted_keys, const int32_t* offsets,
+                                         const MoeExpertInfo* experts, uint32_t n, uint32_t scale_rows, uint8_t* packed,
+                                         uint8_t* scales, void* activated, cudaStream_t stream) {
+  const dim3 grid(blocks_for(size_t(n) * (kInter / 16)), 1);
+  moe_quantize_kernel<kInter, true><<<grid, 256, 0, stream>>>(
+      static_cast<const uint4*>(gate_up), nullptr, sorted_keys, offsets, experts, n, scale_rows, 2,
+      reinterpret_cast<uint2*>(packed), scales, static_cast<uint4*>(activated));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_moe_combine(const void* down, const int32_t* inverse, const float* weights, uint32_t rows,
+                               uint32_t width, void* output, cudaStream_t stream) {
+  moe_combine_kernel<<<blocks_for(size_t(rows) * (width / 8)), 256, 0, stream>>>(
+      static_cast<const uint4*>(down), inverse, weights, rows, width, static_cast<uint4*>(output));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_gather_rows(const void* input, const int32_t* index, uint32_t divisor, uint32_t rows,
+                               uint32_t width, void* output, cudaStream_t stream) {
+  gather_rows_kernel<<<blocks_for(size_t(rows) * (width / 8)), 256, 0, stream>>>(
+      static_cast<const uint4*>(input), index, divisor, rows, width / 8, static_cast<uint4*>(output));
+  return cudaGetLastError();
+}
+
+}  // namespace gw

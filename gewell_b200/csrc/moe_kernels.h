@@ -1,0 +1,45 @@
+// Internal launch functions of the MoE routing / permutation / quantise /
+// combine kernels (moe_kernels.cu).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cstdint>
+
+#include "gemm_tc.cuh"
+
+namespace gw {
+
+// Static per-expert data the device kernels need; built once when the expert
+// table is bound.  Index 0 gate, 1 up, 2 down.
+struct MoeExpertInfo {
+  const uint8_t* scales[3];        // tiled E4M3 weight scales
+  float alpha[3];                  // fmul_rn(input_scale, weight_scale)
+  float inverse_input_scale[3];    // 1 / input_scale (IEEE division)
+  int32_t pad_;
+};
+
+uint32_t moe_chunks(uint32_t rows);
+
+cudaError_t launch_moe_dispatch(const void* scores, const void* expert_scales, uint32_t rows, int32_t* keys,
+                                float* weights, uint32_t* bitmaps, int32_t* chunk_counts, int32_t* offsets,
+                                int32_t* sorted_assignments, int32_t* sorted_keys, int32_t* inverse,
+                                cudaStream_t stream);
+cudaError_t launch_moe_keys_from_offsets(const int32_t* offsets, uint32_t first_expert, uint32_t expert_count,
+                                         uint32_t rows, int32_t* sorted_keys, int32_t* full_offsets,
+                                         cudaStream_t stream);
+cudaError_t launch_moe_prepare_groups(const int32_t* offsets, const MoeExpertInfo* experts, uint32_t n,
+                                      uint32_t scale_rows, int block_n, bool shared_gate_up, GemmGroup* gate_up_groups,
+                                      GemmGroup* down_groups, cudaStream_t stream);
+cudaError_t launch_moe_quantize_input(const void* input, const int32_t* gather_index, const int32_t* sorted_keys,
+                                      const int32_t* offsets, const MoeExpertInfo* experts, uint32_t n,
+                                      uint32_t scale_rows, int parts, uint8_t* packed, uint8_t* scales,
+                                      cudaStream_t stream);
+cudaError_t launch_moe_activate_quantize(const void* gate_up, const int32_t* sorted_keys, const int32_t* offsets,
+                                         const MoeExpertInfo* experts, uint32_t n, uint32_t scale_rows, uint8_t* packed,
+                                         uint8_t* scales, void* activated, cudaStream_t stream);
+cudaError_t launch_moe_combine(const void* down, const int32_t* inverse, const float* weights, uint32_t rows,
+                               uint32_t width, void* output, cudaStream_t stream);
+cudaError_t launch_gather_rows(const void* input, const int32_t* index, uint32_t divisor, uint32_t rows,
+                               uint32_t width, void* output, cudaStream_t stream);
+
+}  // namespace gw

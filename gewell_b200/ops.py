@@ -1,0 +1,344 @@
+"""Host-side mirror of the reference's operator interface over the C ABI.
+
+Names and argument meaning follow the reference classes
+(gewell::nvfp4::{Weight,Plan,dequantize}, gewell::fp8::{Weight,Plan},
+sm120::{Projection,ExpertWeights,MoeWorkspace}); torch is used only for device
+memory and the current stream.  Every call goes through libgewell_b200.so.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+
+TRANSFORM_IDENTITY = _lib.TRANSFORM_IDENTITY
+TRANSFORM_GELU_TANH_MULTIPLY = _lib.TRANSFORM_GELU_TANH_MULTIPLY
+
+
+def _library():
+    from . import lib
+    return lib
+
+
+def _ptr(t) -> int:
+    if t is None:
+        return 0
+    if isinstance(t, int):
+        return t
+    return t.data_ptr()
+
+
+def _stream(stream=None) -> int:
+    if stream is None:
+        return torch.cuda.current_stream().cuda_stream
+    return stream.cuda_stream if hasattr(stream, "cuda_stream") else int(stream)
+
+
+def _check(status: int) -> None:
+    _lib.check(_library(), status)
+
+
+def kernel_error() -> int:
+    """Error word written by the bounded waits of the tensor-core kernels
+    (0 = none).  Synchronises the device and clears the word."""
+    return int(_library().gw_debug_kernel_error())
+
+
+# --------------------------------------------------------------------------- layout helpers
+
+def nvfp4_scale_storage_bytes(rows: int, width: int) -> int:
+    return int(_library().gw_nvfp4_scale_storage_bytes(rows, width))
+
+
+def nvfp4_scale_offset(row: int, block: int, width: int) -> int:
+    return int(_library().gw_nvfp4_scale_offset(row, block, width))
+
+
+# --------------------------------------------------------------------------- NVFP4
+
+@dataclass
+class Nvfp4Weight:
+    """gewell::nvfp4::Weight: packed [N,K/2] uint8 (even k low nibble), tiled
+    E4M3 scales, FP32 dequantisation globals."""
+    data: torch.Tensor
+    scales: torch.Tensor
+    input_scale: float
+    weight_scale: float
+
+
+def nvfp4_dequantize(weight: Nvfp4Weight, input_width: int, output_width: int, output=None, stream=None):
+    """gewell::nvfp4::dequantize -> BF16 [N,K]."""
+    if output is None:
+        output = torch.empty((output_width, input_width), dtype=torch.bfloat16, device=weight.data.device)
+    _check(_library().gw_nvfp4_dequantize(_ptr(weight.data), _ptr(weight.scales), weight.weight_scale,
+                                          input_width, output_width, _ptr(output), _stream(stream)))
+    return output
+
+
+def absmax_bf16(values: torch.Tensor, stream=None):
+    """(amax, nonfinite) of a BF16 tensor; reads the result back (synchronises)."""
+    state = torch.zeros(2, dtype=torch.int32, device=values.device)
+    _check(_library().gw_absmax_bf16(_ptr(values), values.numel(), _ptr(state), _stream(stream)))
+    host = state.cpu()
+    return host[:1].view(torch.float32).item(), bool(host[1].item())
+
+
+def nvfp4_pack_weights(weights: torch.Tensor, input_scale: float = 1.0, weight_scale: float | None = None,
+                       stream=None) -> Nvfp4Weight:
+    """Device packer: BF16 [N,K] -> Nvfp4Weight (global = amax/(6*448) unless given)."""
+    n, k = weights.shape
+    if weight_scale is None:
+        amax, bad = absmax_bf16(weights, stream)
+        if bad:
+            raise _lib.GewellInvalidArgument("NVFP4 source contains nonfinite weights")
+        weight_scale = float(torch.tensor(amax / (6 * 448), dtype=torch.float64).to(torch.float32)) if amax else 1.0
+    data = torch.empty((n, k // 2), dtype=torch.uint8, device=weights.device)
+    scales = torch.empty(nvfp4_scale_storage_bytes(n, k), dtype=torch.uint8, device=weights.device)
+    _check(_library().gw_nvfp4_pack_weights(_ptr(weights), n, k, weight_scale, _ptr(data), _ptr(scales), _stream(stream)))
+    return Nvfp4Weight(data, scales, float(input_scale), float(weight_scale))
+
+
+def nvfp4_quantize_activations(x: torch.Tensor, input_scale: float, width: int | None = None, gelu: bool = False,
+                               stream=None):
+    """Activation quantiser of nvfp4::Plan::run -> (packed [M,K/2], tiled scales)."""
+    rows = x.shape[0]
+    k = width if width is not None else (x.shape[1] // 2 if gelu else x.shape[1])
+    packed = torch.empty((rows, k // 2), dtype=torch.uint8, device=x.device)
+    scales = torch.empty(nvfp4_scale_storage_bytes(rows, k), dtype=torch.uint8, device=x.device)
+    _check(_library().gw_nvfp4_quantize_activations(
+        _ptr(x), rows, k, input_scale, TRANSFORM_GELU_TANH_MULTIPLY if gelu else TRANSFORM_IDENTITY,
+        _ptr(packed), _ptr(scales), _stream(stream)))
+    return packed, scales
+
+
+def nvfp4_gemv_w4a16(x: torch.Tensor, weight: Nvfp4Weight, input_width: int, output_width: int, stream=None):
+    y = torch.empty((x.shape[0], output_width), dtype=torch.bfloat16, device=x.device)
+    _check(_library().gw_nvfp4_gemv_w4a16(_ptr(x), x.shape[0], _ptr(weight.data), _ptr(weight.scales),
+                                          weight.weight_scale, input_width, output_width, _ptr(y), _stream(stream)))
+    return y
+
+
+class Nvfp4Plan:
+    """gewell::nvfp4::Plan(handle, rows, K, N): scratch_bytes(), run(...)."""
+
+    def __init__(self, rows: int, input_width: int, output_width: int):
+        self._lib = _library()
+        self._plan = ctypes.c_void_p()
+        _check(self._lib.gw_nvfp4_plan_create(rows, input_width, output_width, ctypes.byref(self._plan)))
+        self.rows, self.input_width, self.output_width = rows, input_width, output_width
+
+    def scratch_bytes(self) -> int:
+        return int(self._lib.gw_nvfp4_plan_scratch_bytes(self._plan))
+
+    def run(self, x, weight: Nvfp4Weight, y, scratch, scratch_capacity=None, stream=None,
+            transform: int = TRANSFORM_IDENTITY):
+        capacity = scratch_capacity if scratch_capacity is not None else (
+            scratch.numel() * scratch.element_size() if hasattr(scratch, "numel") else 0)
+        _check(self._lib.gw_nvfp4_plan_run(self._plan, _ptr(x), _ptr(weight.data), _ptr(weight.scales),
+                                           weight.input_scale, weight.weight_scale, _ptr(y), _ptr(scratch),
+                                           capacity, _stream(stream), transform))
+        return y
+
+    def __del__(self):
+        if getattr(self, "_plan", None):
+            self._lib.gw_nvfp4_plan_destroy(self._plan)
+            self._plan = None
+
+
+# --------------------------------------------------------------------------- FP8
+
+@dataclass
+class Fp8Weight:
+    """gewell::fp8::Weight: [N,K] E4M3FN codes, FP32 globals, optional
+    per-output-channel alpha vector (input*weight scale) for joined projections."""
+    data: torch.Tensor
+    input_scale: float
+    weight_scale: float
+    channel_scales: torch.Tensor | None = None
+
+
+def fp8_quantize_activations(x: torch.Tensor, input_scale: float, gelu: bool = False, stream=None):
+    rows = x.shape[0]
+    k = x.shape[1] // 2 if gelu else x.shape[1]
+    packed = torch.empty((rows, k), dtype=torch.uint8, device=x.device)
+    _check(_library().gw_fp8_quantize_activations(
+        _ptr(x), rows, k, input_scale, TRANSFORM_GELU_TANH_MULTIPLY if gelu else TRANSFORM_IDENTITY,
+        _ptr(packed), _stream(stream)))
+    return packed
+
+
+def fp8_pack_weights(weights: torch.Tensor, weight_scale: float = 0.0, row_scales: torch.Tensor | None = None,
+                     stream=None) -> torch.Tensor:
+    n, k = weights.shape
+    data = torch.empty((n, k), dtype=torch.uint8, device=weights.device)
+    _check(_library().gw_fp8_pack_weights(_ptr(weights), n, k, weight_scale, _ptr(row_scales), _ptr(data),
+                                          _stream(stream)))
+    return data
+
+
+class Fp8Plan:
+    """gewell::fp8::Plan(handle, rows, K, N, channel_scales)."""
+
+    def __init__(self, rows: int, input_width: int, output_width: int, channel_scales: bool = False):
+        self._lib = _library()
+        self._plan = ctypes.c_void_p()
+        _check(self._lib.gw_fp8_plan_create(rows, input_width, output_width, int(channel_scales),
+                                            ctypes.byref(self._plan)))
+        self.rows, self.input_width, self.output_width = rows, input_width, output_width
+
+    def scratch_bytes(self) -> int:
+        return int(self._lib.gw_fp8_plan_scratch_bytes(self._plan))
+
+    def run(self, x, weight: Fp8Weight, y, scratch, scratch_capacity=None, stream=None,
+            transform: int = TRANSFORM_IDENTITY):
+        capacity = scratch_capacity if scratch_capacity is not None else (
+            scratch.numel() * scratch.element_size() if hasattr(scratch, "numel") else 0)
+        _check(self._lib.gw_fp8_plan_run(self._plan, _ptr(x), _ptr(weight.data), weight.input_scale,
+                                         weight.weight_scale, _ptr(weight.channel_scales), _ptr(y), _ptr(scratch),
+                                         capacity, _stream(stream), transform))
+        return y
+
+    def __del__(self):
+        if getattr(self, "_plan", None):
+            self._lib.gw_fp8_plan_destroy(self._plan)
+            self._plan = None
+
+
+# --------------------------------------------------------------------------- weight QDQ
+
+def weight_qdq_apply(kind: int, values: torch.Tensor, stream=None) -> torch.Tensor:
+    """weight_qdq::detail::apply_tensor: in-place fake quantisation (synchronises)."""
+    state = torch.zeros(2, dtype=torch.int32, device=values.device)
+    _check(_library().gw_weight_qdq_apply(kind, _ptr(values), values.numel(), _ptr(state), _stream(stream)))
+    return values
+
+
+# --------------------------------------------------------------------------- MoE
+
+def make_projection(weight: Nvfp4Weight, input_width: int, output_width: int) -> _lib.Projection:
+    """sm120::Projection for an NVFP4 expert matrix whose rows are already
+    padded to a multiple of 128 (bind_projection, projection.cu:31-50)."""
+    p = _lib.Projection()
+    p.storage = _lib.STORAGE_NVFP4_W4A4
+    p.input, p.output = input_width, output_width
+    p.physical_output = (output_width + 127) // 128 * 128
+    p.nvfp4_data, p.nvfp4_scales = weight.data.data_ptr(), weight.scales.data_ptr()
+    p.nvfp4_input_scale, p.nvfp4_weight_scale = weight.input_scale, weight.weight_scale
+    return p
+
+
+class _RawDeviceBytes:
+    """Zero-copy view of device memory through the CUDA array interface."""
+
+    def __init__(self, pointer: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (int(pointer), False),
+                                         "version": 2}
+
+
+class ExpertTable:
+    """The 128-entry ExpertWeights table, bound once (keeps the tensors alive)."""
+
+    def __init__(self, experts: list[tuple[Nvfp4Weight, Nvfp4Weight, Nvfp4Weight]]):
+        self._lib = _library()
+        self._keep = experts
+        array = (_lib.ExpertWeights * len(experts))()
+        for i, (gate, up, down) in enumerate(experts):
+            array[i].gate = make_projection(gate, 2816, 704)
+            array[i].up = make_projection(up, 2816, 704)
+            array[i].down = make_projection(down, 704, 2816)
+        self._table = ctypes.c_void_p()
+        _check(self._lib.gw_moe_expert_table_create(array, len(experts), ctypes.byref(self._table)))
+
+    @property
+    def handle(self):
+        return self._table
+
+    def __del__(self):
+        if getattr(self, "_table", None):
+            self._lib.gw_moe_expert_table_destroy(self._table)
+            self._table = None
+
+
+class MoeWorkspace:
+    """sm120::MoeWorkspace(max_rows): run, dispatch and the capture accessors."""
+
+    def __init__(self, max_rows: int, device=None):
+        self._lib = _library()
+        self._ws = ctypes.c_void_p()
+        self.max_rows = max_rows
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+        _check(self._lib.gw_moe_create(max_rows, ctypes.byref(self._ws)))
+        self.rows = 0
+
+    def dispatch(self, scores, expert_scales, rows: int, stream=None):
+        _check(self._lib.gw_moe_dispatch(self._ws, _ptr(scores), _ptr(expert_scales), rows, _stream(stream)))
+        self.rows = rows
+
+    def run(self, x, scores, expert_scales, table: ExpertTable, y, rows: int, has_bf16=False, has_fp8=False,
+            has_nvfp4=True, fp4=True, stream=None):
+        _check(self._lib.gw_moe_run(self._ws, _ptr(x), _ptr(scores), _ptr(expert_scales), table.handle, _ptr(y), rows,
+                                    int(has_bf16), int(has_fp8), int(has_nvfp4), int(fp4), _stream(stream)))
+        self.rows = rows
+        return y
+
+    def run_sorted(self, x, offsets, first_expert: int, expert_count: int, total_rows: int, table: ExpertTable, y,
+                   stream=None):
+        _check(self._lib.gw_moe_run_sorted(self._ws, _ptr(x), _ptr(offsets), first_expert, expert_count, total_rows,
+                                           table.handle, _ptr(y), _stream(stream)))
+        return y
+
+    def _view(self, pointer: int, shape, dtype):
+        """Copy of a workspace buffer as a tensor (the workspace owns the memory)."""
+        count = 1
+        for s in shape:
+            count *= s
+        if count == 0:
+            return torch.empty(shape, dtype=dtype, device=self.device)
+        nbytes = count * torch.empty((), dtype=dtype).element_size()
+        raw = torch.as_tensor(_RawDeviceBytes(pointer, nbytes), device=self.device)
+        return raw.view(dtype).reshape(shape).clone()
+
+    def selected_experts(self):
+        return self._view(self._lib.gw_moe_selected_experts(self._ws), (self.rows, 8), torch.int32)
+
+    def routing_weights(self):
+        return self._view(self._lib.gw_moe_routing_weights(self._ws), (self.rows, 8), torch.float32)
+
+    def offsets(self):
+        return self._view(self._lib.gw_moe_offsets(self._ws), (129,), torch.int32)
+
+    def sorted_assignments(self):
+        return self._view(self._lib.gw_moe_sorted_assignments(self._ws), (8 * self.rows,), torch.int32)
+
+    def gate_up_capture(self):
+        return self._view(self._lib.gw_moe_gate_up_capture(self._ws), (8 * self.rows, 1408), torch.bfloat16)
+
+    def activated_capture(self):
+        return self._view(self._lib.gw_moe_activated_capture(self._ws), (8 * self.rows, 704), torch.bfloat16)
+
+    def down_capture(self):
+        return self._view(self._lib.gw_moe_down_capture(self._ws), (8 * self.rows, 2816), torch.bfloat16)
+
+    def bytes(self) -> int:
+        return int(self._lib.gw_moe_bytes(self._ws))
+
+    def __del__(self):
+        if getattr(self, "_ws", None):
+            self._lib.gw_moe_destroy(self._ws)
+            self._ws = None
+
+
+def gather_rows(x, index, divisor: int, rows: int, stream=None):
+    out = torch.empty((rows, x.shape[1]), dtype=torch.bfloat16, device=x.device)
+    _check(_library().gw_gather_rows_bf16(_ptr(x), _ptr(index), divisor, rows, x.shape[1], _ptr(out), _stream(stream)))
+    return out
+
+
+def moe_combine(down, inverse, weights, rows: int, stream=None):
+    out = torch.empty((rows, down.shape[1]), dtype=torch.bfloat16, device=down.device)
+    _check(_library().gw_moe_combine(_ptr(down), _ptr(inverse), _ptr(weights), rows, down.shape[1], _ptr(out),
+                                     _stream(stream)))
+    return out

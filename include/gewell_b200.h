@@ -1,0 +1,232 @@
+/*
+ * gewell_b200 -- C ABI of the B200 (sm_100a) quantised-projection and MoE path.
+ *
+ * Plain pointers and sizes only.  Every device pointer is a CUDA device
+ * address in the current context; `stream` is a cudaStream_t passed as void*
+ * (NULL = the legacy default stream).  Functions return GW_OK or an error code
+ * and leave a message retrievable with gw_last_error() (thread local).
+ *
+ * "Reference" below means the leDissolution/gewell sources; each entry point
+ * names the reference interface it stands in for (path:line in that project).
+ *
+ * Unless stated otherwise a call neither allocates device memory nor
+ * synchronises, and is ordered on `stream` only, so it may be captured in a
+ * CUDA graph (plan / workspace construction must happen outside capture).
+ */
+#ifndef GEWELL_B200_H_
+#define GEWELL_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef int gw_status;
+enum {
+  GW_OK = 0,
+  GW_INVALID_ARGUMENT = 1, /* contract violation; the reference throws std::invalid_argument */
+  GW_CUDA_ERROR = 2,       /* CUDA runtime/driver failure; the reference throws std::runtime_error */
+  GW_KERNEL_ERROR = 3,     /* a kernel reported a bounded-wait timeout or internal check */
+  GW_UNSUPPORTED = 4       /* valid in the reference, not built here (see message) */
+};
+
+/* Message of the last failing call on this host thread ("" if none). */
+const char* gw_last_error(void);
+/* ABI version of this library (bumped on incompatible change). */
+int gw_abi_version(void);
+
+/* ------------------------------------------------------------------------- */
+/* Layout helpers -- include/gewell/nvfp4_linear.h:35-56, fp8_linear.h:28-33  */
+/* ------------------------------------------------------------------------- */
+size_t gw_nvfp4_scale_storage_bytes(size_t rows, size_t input_width);
+size_t gw_nvfp4_scale_offset(size_t row, size_t block, size_t input_width);
+size_t gw_nvfp4_scratch_upper_bound_bytes(size_t max_rows, size_t input_width, size_t output_width);
+size_t gw_fp8_scratch_upper_bound_bytes(size_t max_rows, size_t input_width);
+
+enum { GW_TRANSFORM_IDENTITY = 0, GW_TRANSFORM_GELU_TANH_MULTIPLY = 1 };
+
+/* ------------------------------------------------------------------------- */
+/* NVFP4                                                                      */
+/* ------------------------------------------------------------------------- */
+
+/* gewell::nvfp4::dequantize (include/gewell/nvfp4_linear.h:28-33,
+ * src/nvfp4_linear.cu:39-56,120-132): packed E2M1 [N,K/2] + tiled E4M3 scales
+ * -> row-major BF16 [N,K] = bf16(e2m1 * (e4m3 * weight_scale)).
+ * K % 64 == 0, N % 128 == 0, weight_scale finite and > 0. */
+gw_status gw_nvfp4_dequantize(const uint8_t* data, const uint8_t* scales, float weight_scale,
+                              uint32_t input_width, uint32_t output_width, void* output_bf16,
+                              void* stream);
+
+/* Device weight packer: the recipe of tools/convert.py:111-137
+ * (quantize_nvfp4_tensor) and src/weight_qdq_detail.cuh:73-82 applied to a
+ * BF16 matrix [N,K] with a caller-supplied global weight_scale
+ * (= amax/(6*448), see gw_absmax_bf16).  Writes packed [N,K/2] and tiled scale
+ * storage (gw_nvfp4_scale_storage_bytes(N,K) bytes, padding zeroed). */
+gw_status gw_nvfp4_pack_weights(const void* weights_bf16, uint32_t output_width, uint32_t input_width,
+                                float weight_scale, uint8_t* data, uint8_t* scales, void* stream);
+
+/* Activation quantiser of nvfp4::Plan::run (src/nvfp4_linear.cu:61-116),
+ * exposed for tests: BF16 [rows,K] (or [rows,2K] gate|up with the GeGLU
+ * transform) -> packed [rows,K/2] + tiled scales for `rows` rows. */
+gw_status gw_nvfp4_quantize_activations(const void* input_bf16, uint32_t rows, uint32_t input_width,
+                                        float input_scale, int transform, uint8_t* packed,
+                                        uint8_t* scales, void* stream);
+
+/* gewell::nvfp4::Plan (include/gewell/nvfp4_linear.h:64-91,
+ * src/nvfp4_linear.cu:134-330).  Y[rows,N] = bf16(alpha * Xq . Wq^T),
+ * alpha = input_scale*weight_scale, tcgen05 block-scaled MMA.  The cuBLASLt
+ * handle of the reference constructor has no counterpart (no library GEMM). */
+typedef struct gw_nvfp4_plan gw_nvfp4_plan;
+gw_status gw_nvfp4_plan_create(uint32_t rows, uint32_t input_width, uint32_t output_width,
+                               gw_nvfp4_plan** plan);
+size_t gw_nvfp4_plan_scratch_bytes(const gw_nvfp4_plan* plan);
+gw_status gw_nvfp4_plan_run(gw_nvfp4_plan* plan, const void* input_bf16, const uint8_t* weight_data,
+                            const uint8_t* weight_scales, float input_scale, float weight_scale,
+                            void* output_bf16, void* scratch, size_t scratch_capacity, void* stream,
+                            int transform);
+void gw_nvfp4_plan_destroy(gw_nvfp4_plan* plan);
+
+/* W4A16 projection (models/gemma4/26b_a4b/sm120/projection.cu:129-139 and the
+ * north-star host path): BF16 activations times NVFP4 weights without
+ * activation quantisation, for small row counts; weights are streamed once
+ * and decoded in registers.  rows <= 8. */
+gw_status gw_nvfp4_gemv_w4a16(const void* input_bf16, uint32_t rows, const uint8_t* weight_data,
+                              const uint8_t* weight_scales, float weight_scale, uint32_t input_width,
+                              uint32_t output_width, void* output_bf16, void* stream);
+
+/* ------------------------------------------------------------------------- */
+/* FP8                                                                        */
+/* ------------------------------------------------------------------------- */
+
+/* Activation quantiser of fp8::Plan::run (src/fp8_linear.cu:33-52). */
+gw_status gw_fp8_quantize_activations(const void* input_bf16, uint32_t rows, uint32_t input_width,
+                                      float input_scale, int transform, uint8_t* packed, void* stream);
+
+/* Device E4M3 weight packer: tools/convert.py:49-62 with a caller-supplied
+ * scalar scale, or one scale per output row when row_scales != NULL. */
+gw_status gw_fp8_pack_weights(const void* weights_bf16, uint32_t output_width, uint32_t input_width,
+                              float weight_scale, const float* row_scales, uint8_t* data, void* stream);
+
+/* gewell::fp8::Plan (include/gewell/fp8_linear.h:40-69, src/fp8_linear.cu:56-271)
+ * including the per-output-channel ("joined") variant that the reference
+ * serves with fp8::detail::ScaledGemm (src/fp8_scaled_gemm.cuh:18-97). */
+typedef struct gw_fp8_plan gw_fp8_plan;
+gw_status gw_fp8_plan_create(uint32_t rows, uint32_t input_width, uint32_t output_width,
+                             int channel_scales, gw_fp8_plan** plan);
+size_t gw_fp8_plan_scratch_bytes(const gw_fp8_plan* plan);
+gw_status gw_fp8_plan_run(gw_fp8_plan* plan, const void* input_bf16, const uint8_t* weight_data,
+                          float input_scale, float weight_scale, const float* channel_scales,
+                          void* output_bf16, void* scratch, size_t scratch_capacity, void* stream,
+                          int transform);
+void gw_fp8_plan_destroy(gw_fp8_plan* plan);
+
+/* ------------------------------------------------------------------------- */
+/* Weight QDQ -- src/weight_qdq.cu:105-189,222-258 (detail::apply_tensor)     */
+/* ------------------------------------------------------------------------- */
+enum { GW_QDQ_BF16 = 0, GW_QDQ_FP8 = 1, GW_QDQ_NVFP4 = 2 };
+
+/* |x| maximum of a BF16 tensor and a non-finite flag, as
+ * accumulate_absmax_kernel (src/weight_qdq.cu:105-148).  state = two uint32
+ * on the device {float bits of amax, nonfinite flag}; cleared by this call. */
+gw_status gw_absmax_bf16(const void* values_bf16, uint64_t elements, uint32_t* state, void* stream);
+
+/* In-place BF16 -> grid -> BF16 fake quantisation of one tensor.  Like the
+ * reference this reads the maximum back to the host, so it SYNCHRONISES the
+ * stream; non-finite input is rejected (GW_INVALID_ARGUMENT).  `state` as above. */
+gw_status gw_weight_qdq_apply(int type, void* values_bf16, uint64_t elements, uint32_t* state,
+                              void* stream);
+
+/* ------------------------------------------------------------------------- */
+/* MoE -- models/gemma4/26b_a4b/sm120/{projection.cuh:11-17, moe.cuh:11-48}   */
+/* ------------------------------------------------------------------------- */
+enum { GW_STORAGE_BF16 = 0, GW_STORAGE_NVFP4_W4A4 = 1, GW_STORAGE_FP8_W8A8 = 2 };
+
+/* sm120::Projection (projection.cuh:11-17), flattened. */
+typedef struct gw_projection {
+  uint32_t storage;
+  uint32_t input, output, physical_output;
+  const void* bf16;
+  const uint8_t* nvfp4_data;   /* [physical_output, input/2], padding rows zero */
+  const uint8_t* nvfp4_scales; /* tiled, padding zero */
+  float nvfp4_input_scale, nvfp4_weight_scale;
+  const uint8_t* fp8_data;
+  float fp8_input_scale, fp8_weight_scale;
+  const float* fp8_channel_scales;
+} gw_projection;
+
+/* sm120::ExpertWeights (moe.cuh:11-13). */
+typedef struct gw_expert_weights {
+  gw_projection gate, up, down;
+} gw_expert_weights;
+
+/* The reference keeps the 128-entry ExpertWeights table in device memory and
+ * reads it from its kernels (batched_executor.cu:62-88).  Here the table is
+ * bound once from the host copy: the call validates it, builds the TMA
+ * descriptors of every expert matrix and uploads both.  Allocates; not
+ * capturable.  `experts` has `count` (=128) entries in host memory. */
+typedef struct gw_expert_table gw_expert_table;
+gw_status gw_moe_expert_table_create(const gw_expert_weights* experts, uint32_t count,
+                                     gw_expert_table** table);
+void gw_moe_expert_table_destroy(gw_expert_table* table);
+
+/* sm120::MoeWorkspace (moe.cuh:20-48, moe.cu:462-545).  max_rows in 1..65536
+ * (the reference stops at 4096).  All buffers are allocated here, once. */
+typedef struct gw_moe_workspace gw_moe_workspace;
+gw_status gw_moe_create(uint32_t max_rows, gw_moe_workspace** workspace);
+void gw_moe_destroy(gw_moe_workspace* workspace);
+
+/* MoeWorkspace::dispatch (moe.cu:477-488): routing, stable sort by expert,
+ * offsets, inverse permutation.  rows == 0 is a no-op. */
+gw_status gw_moe_dispatch(gw_moe_workspace* workspace, const void* scores_bf16,
+                          const void* expert_scales_bf16, uint32_t rows, void* stream);
+
+/* MoeWorkspace::run (moe.cu:489-534).  fp4 != 0 selects W4A4 (NVFP4
+ * activations); only NVFP4 experts with fp4 != 0 are built here, other
+ * combinations return GW_UNSUPPORTED. */
+gw_status gw_moe_run(gw_moe_workspace* workspace, const void* input_bf16, const void* scores_bf16,
+                     const void* expert_scales_bf16, const gw_expert_table* table, void* output_bf16,
+                     uint32_t rows, int has_bf16, int has_fp8, int has_nvfp4, int fp4, void* stream);
+
+/* Accessors of the reference workspace (moe.cuh:29-40, moe.cu:541-544);
+ * device pointers valid after the stream has reached the end of run/dispatch. */
+const int32_t* gw_moe_selected_experts(const gw_moe_workspace* workspace);   /* [8*rows] ascending per token */
+const float* gw_moe_routing_weights(const gw_moe_workspace* workspace);      /* [8*rows] */
+const int32_t* gw_moe_offsets(const gw_moe_workspace* workspace);            /* [129] */
+const int32_t* gw_moe_sorted_assignments(const gw_moe_workspace* workspace); /* [8*rows] */
+const void* gw_moe_gate_up_capture(const gw_moe_workspace* workspace);       /* BF16 [8*rows,1408] */
+const void* gw_moe_activated_capture(const gw_moe_workspace* workspace);     /* BF16 [8*rows,704] */
+const void* gw_moe_down_capture(const gw_moe_workspace* workspace);          /* BF16 [8*rows,2816] */
+size_t gw_moe_bytes(const gw_moe_workspace* workspace);
+size_t gw_moe_routing_bytes(const gw_moe_workspace* workspace);
+size_t gw_moe_projection_bytes(const gw_moe_workspace* workspace);
+size_t gw_moe_reduction_bytes(const gw_moe_workspace* workspace);
+
+/* Expert-parallel building blocks (no counterpart in the reference, which is
+ * single GPU).  A rank that owns experts [first, first+count) runs the expert
+ * MLP over rows that are already sorted by expert: `offsets` (device, int32,
+ * count+1 entries) delimit each local expert's rows inside `input_bf16`
+ * [total_rows, 2816]; output BF16 [total_rows, 2816], unweighted. */
+gw_status gw_moe_run_sorted(gw_moe_workspace* workspace, const void* input_bf16,
+                            const int32_t* offsets, uint32_t first_expert, uint32_t expert_count,
+                            uint32_t total_rows, const gw_expert_table* table, void* output_bf16,
+                            void* stream);
+
+/* Gather rows by an index vector: out[i,:] = in[index[i] / divisor, :]. */
+gw_status gw_gather_rows_bf16(const void* input_bf16, const int32_t* index, uint32_t divisor,
+                              uint32_t rows, uint32_t width, void* output_bf16, void* stream);
+
+/* MoeWorkspace reduce step alone (moe.cu:446-456) over caller buffers:
+ * out[t,:] = ordered BF16 fold over the 8 slots of down[inverse[8t+j],:]*w[8t+j]. */
+gw_status gw_moe_combine(const void* down_bf16, const int32_t* inverse, const float* weights,
+                         uint32_t rows, uint32_t width, void* output_bf16, void* stream);
+
+/* Last kernel-reported error word of this process's device (0 = none); set by
+ * bounded waits inside the tensor-core kernels.  Synchronises the device. */
+uint32_t gw_debug_kernel_error(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GEWELL_B200_H_ */
