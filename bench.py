@@ -1,0 +1,306 @@
+#!/usr/bin/env python3
+"""Benchmark of the NVFP4 MoE layer (Gemma-4-26B-A4B shape: 128 experts, top-8,
+hidden 2816, expert MLP 704) on synthetic data.
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
+    python bench.py --impl reference          # CPU host path, same metric
+
+One "step" is one pass of the whole layer (routing, permutation,
+gather+quantise, grouped gate/up GEMM, GeGLU+quantise, grouped down GEMM,
+ordered combine) over one batch of tokens.  N=1 runs T=8192 tokens on one
+GPU; N>1 runs the expert-parallel layer over T=32768 tokens (T/N routed per
+rank, experts sharded, all-to-all dispatch and combine over NCCL).
+Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+E, TOPK, H, I = 128, 8, 2816, 704
+FLOPS_PER_ASSIGNMENT = 2 * H * 2 * I + 2 * I * H          # 11,894,784
+METRIC = "nvfp4_moe_layer_tflops"
+
+
+def measured_peaks() -> dict:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return json.loads(path.read_text()) | {"source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed
+    region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.lines, self.proc = [], None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={device_index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def stop(self, t0: float, t1: float) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, smax, reasons = [], [], set()
+        chosen = [l for (t, l) in self.lines if t0 <= t <= t1 + 0.2] or [l for (_, l) in self.lines]
+        for line in chosen:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1])); smax.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, flag in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[5:9]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def zipf_bias(alpha: float = 1.2):
+    import torch
+    ranks = torch.arange(1, E + 1, dtype=torch.float32)
+    p = ranks.pow(-alpha)
+    return (p / p.sum()).log()
+
+
+def build_experts(gw, torch, device, seed=4):
+    """128 experts ~ N(0, 0.02), packed to NVFP4 by the device packer; gate
+    and up share one input scale per expert (they are one fused tensor in the
+    checkpoint), so the layer quantises its input once."""
+    experts = []
+    g = torch.Generator(device=device).manual_seed(seed)
+    for e in range(E):
+        mats = [(torch.randn((I, H), generator=g, device=device) * 0.02).bfloat16(),
+                (torch.randn((I, H), generator=g, device=device) * 0.02).bfloat16(),
+                (torch.randn((H, I), generator=g, device=device) * 0.02).bfloat16()]
+        scales = [6.0 / 2688, 6.0 / 2688, 16.0 / 2688]
+        packs = []
+        for m, s in zip(mats, scales):
+            w = gw.nvfp4_pack_weights(m, s)
+            physical = (m.shape[0] + 127) // 128 * 128
+            if physical != m.shape[0]:
+                data = torch.zeros((physical, m.shape[1] // 2), dtype=torch.uint8, device=device)
+                data[:m.shape[0]] = w.data
+                w = gw.Nvfp4Weight(data, w.scales, w.input_scale, w.weight_scale)
+            packs.append(w)
+        experts.append(tuple(packs))
+    return experts
+
+
+def cpu_baseline_sample(experts, tokens: int, seed: int = 11) -> dict:
+    """The reference's host path for this layer (dequantise the NVFP4 weights,
+    FP32 matmul per expert, ordered BF16 combine) timed on this box's host
+    cores over a bounded sample of the workload."""
+    import numpy as np
+    import torch
+    from oracle import moe as omoe
+    from oracle import nvfp4 as onv
+    host = [omoe.ExpertWeights(*[onv.Weight(p.data.cpu().numpy(), p.scales.cpu().numpy(), p.input_scale, p.weight_scale,
+                                            p.data.shape[0], p.data.shape[1] * 2) for p in ex]) for ex in experts]
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn((tokens, H), generator=g).bfloat16().float().numpy()
+    scores = torch.randn((tokens, E), generator=g).bfloat16().float().numpy()
+    start = time.perf_counter()
+    omoe.forward(x, scores, np.ones(E, dtype=np.float32), host, mode="w4a16")
+    seconds = time.perf_counter() - start
+    return {"value": tokens * TOPK * FLOPS_PER_ASSIGNMENT / seconds / 1e12, "unit": "TFLOP/s",
+            "cores": os.cpu_count(), "kind": "port",
+            "sample": f"{tokens} tokens of the same layer (dequantise + FP32 matmul per expert, NumPy/BLAS), {seconds:.1f} s"}
+
+
+def run_reference_arm(args):
+    """CPU arm: the host path of the reference for this layer, all host threads."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+    import gewell_b200 as gw
+    device = torch.device("cuda", 0) if torch.cuda.is_available() else None
+    if device is None:
+        print(json.dumps({"impl": "reference", "unavailable": "needs a CUDA device to build the packed expert weights"}))
+        return
+    experts = build_experts(gw, torch, device)
+    tokens = 96
+    values = []
+    for step in range(args.warmup + args.steps):
+        sample = cpu_baseline_sample(experts, tokens, seed=100 + step)
+        if step >= args.warmup:
+            values.append(sample)
+    value = statistics.mean(v["value"] for v in values)
+    seconds = tokens * TOPK * FLOPS_PER_ASSIGNMENT / value / 1e12
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": seconds * 1e3, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(args.gpus) | {"sample_tokens_per_step": tokens},
+            "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
+                             "sample": f"{tokens} tokens per step, dequantise + FP32 matmul per expert"},
+            "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def workload_config(n_gpus: int) -> dict:
+    tokens = 8192 if n_gpus == 1 else 32768
+    return {"workload": ("config 4: Gemma-4-26B-A4B MoE layer on one GPU" if n_gpus == 1 else
+                         "config 5: the same layer expert-parallel, Zipf(1.2) routing bias"),
+            "tokens": tokens, "experts": E, "top_k": TOPK, "hidden": H, "expert_intermediate": I,
+            "weights": "NVFP4 W4A4 (E2M1 + E4M3 K16 scales + FP32 global)",
+            "l2": "inputs larger than L2: 450 MB of expert weights and >400 MB of intermediates are streamed every step",
+            "parallelism": "single GPU" if n_gpus == 1 else f"ep{n_gpus}"}
+
+
+def main():
+    parser = argparse.ArgumentParser(description=__doc__)
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--tokens", type=int, default=0, help="override the token count (testing)")
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    args = parser.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        return run_reference_arm(args)
+
+    import torch
+    import gewell_b200 as gw
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        from gewell_b200 import expert_parallel
+        return expert_parallel.bench_main(args, world, rank, local_rank, workload_config(world), METRIC,
+                                          build_experts, ClockSampler, measured_peaks)
+
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    config = workload_config(1)
+    tokens = args.tokens or config["tokens"]
+    config["tokens"] = tokens
+    experts = build_experts(gw, torch, device)
+    table = gw.ExpertTable(experts)
+    ws = gw.MoeWorkspace(tokens)
+    g = torch.Generator(device=device).manual_seed(1)
+    x = torch.randn((tokens, H), generator=g, device=device).bfloat16()
+    scores = torch.randn((tokens, E), generator=g, device=device).bfloat16()
+    expert_scales = torch.ones(E, dtype=torch.bfloat16, device=device)
+    y = torch.empty((tokens, H), dtype=torch.bfloat16, device=device)
+    stream = torch.cuda.current_stream()
+
+    def step():
+        ws.run(x, scores, expert_scales, table, y, tokens)
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    if gw.kernel_error() != 0:
+        raise SystemExit("tensor-core kernel reported an error during warm-up")
+
+    sampler = ClockSampler(local_rank)
+    time.sleep(0.25)
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    t0 = time.time()
+    begin.record(stream)
+    for _ in range(args.steps):
+        step()
+    end.record(stream)
+    torch.cuda.synchronize()
+    t1 = time.time()
+    ms = begin.elapsed_time(end) / args.steps
+    flops = tokens * TOPK * FLOPS_PER_ASSIGNMENT
+    value = flops / (ms * 1e-3) / 1e12
+
+    # end to end through the public call with HOST buffers: pinned inputs are
+    # copied in and the layer output is copied out inside the timed region
+    hx = x.cpu().pin_memory()
+    hs = scores.cpu().pin_memory()
+    hy = torch.empty((tokens, H), dtype=torch.bfloat16).pin_memory()
+    dx, ds = torch.empty_like(x), torch.empty_like(scores)
+
+    def e2e_step():
+        dx.copy_(hx, non_blocking=True)
+        ds.copy_(hs, non_blocking=True)
+        ws.run(dx, ds, expert_scales, table, y, tokens)
+        hy.copy_(y, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    torch.cuda.synchronize()
+    begin.record(stream)
+    for _ in range(args.steps):
+        e2e_step()
+    end.record(stream)
+    torch.cuda.synchronize()
+    t2 = time.time()
+    clocks = sampler.stop(t0, t2)
+    e2e_ms = begin.elapsed_time(end) / args.steps
+    e2e = {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+           "h2d_bytes_per_step": hx.numel() * 2 + hs.numel() * 2, "d2h_bytes_per_step": hy.numel() * 2,
+           "ms_per_step": e2e_ms}
+
+    # roofline of the dominant kernel (the two grouped tcgen05 GEMMs), timed live
+    # with CUDA events recorded on the launching stream between the stages
+    ws.stage_timing(True)
+    stage_sum = {}
+    for _ in range(args.steps):
+        step()
+        for name, v in ws.stage_elapsed_ms().items():
+            stage_sum[name] = stage_sum.get(name, 0.0) + v
+    ws.stage_timing(False)
+    stages = {k: v / args.steps for k, v in stage_sum.items()}
+    gemm_ms = stages["gate_up_gemm"] + stages["down_gemm"]
+    peaks = measured_peaks()
+    fp4_peak = 4.0 * peaks["bf16_tflops"]
+    achieved = flops / (gemm_ms * 1e-3) / 1e12
+    roofline = {"kernel": "gemm_tc_kernel<nvfp4> (grouped gate/up + grouped down)", "bound": "tensor",
+                "achieved": achieved, "peak": fp4_peak, "unit": "TFLOP/s", "frac": achieved / fp4_peak,
+                "traffic": None,
+                "peak_note": f"4 x the {peaks['source']} dense BF16 burst figure ({peaks['bf16_tflops']} TFLOP/s); "
+                             "no FP4 GEMM peak was measured on this pool (nominal dense FP4: 9000 TFLOP/s)",
+                "frac_of_nominal_fp4": achieved / 9000.0,
+                "ms_per_launch": {"gate_up": stages["gate_up_gemm"], "down": stages["down_gemm"]},
+                "stage_ms": stages}
+
+    cpu = None
+    if not args.no_cpu_baseline:
+        cpu = cpu_baseline_sample(experts, 96)
+
+    line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "nvfp4 (e2m1 x e2m1, fp32 accumulate)", "data": "synthetic",
+            "config": config, "e2e": e2e, "gpu_launches": 9 * args.steps, "clocks": clocks,
+            "roofline": roofline, "cpu_baseline": cpu}
+    print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()

@@ -47,6 +47,10 @@ struct gw_moe_workspace {
   int32_t *keys = nullptr, *sorted_keys = nullptr, *sorted_assignments = nullptr, *inverse = nullptr;
   int32_t *offsets = nullptr, *chunk_counts = nullptr, *local_offsets = nullptr;
   float* weights = nullptr;
+  bool timing = false;
+  cudaEvent_t events[7] = {};
+  ~gw_moe_workspace() { for (auto& e : events) if (e) cudaEventDestroy(e); }
+  void mark(int i, cudaStream_t s) const { if (timing) cudaEventRecord(events[i], s); }
 };
 
 extern "C" {
@@ -174,6 +178,7 @@ gw_status run_experts(gw_moe_workspace* w, const void* input, const int32_t* gat
   // Token-side tile: small batches leave most experts with a handful of rows.
   const int block_n = n <= 8 * 64 ? 32 : (n <= 8 * 1024 ? 128 : 256);
   const int parts = table->shared_gate_up ? 1 : 2;
+  w->mark(1, s);
   GW_CUDA_CHECK(launch_moe_prepare_groups(offsets, info, n, w->scale_rows, block_n, table->shared_gate_up,
                                           gate_up_groups, down_groups, s),
                 "MoE group descriptors");
@@ -192,7 +197,9 @@ gw_status run_experts(gw_moe_workspace* w, const void* input, const int32_t* gat
   params.out = w->gate_up.data;
   params.ld_out = 2 * kInter;
   params.error = device_error_word();
+  w->mark(2, s);
   GW_CUDA_CHECK(launch_gemm_tc(GemmKind::nvfp4, block_n, params, sm_count(), s), "MoE grouped gate/up GEMM");
+  w->mark(3, s);
   GW_CUDA_CHECK(launch_moe_activate_quantize(w->gate_up.data, w->sorted_keys, offsets, info, n, w->scale_rows,
                                              w->packed_act.as<uint8_t>(), w->scales_act.as<uint8_t>(), w->activated.data, s),
                 "MoE GeGLU + quantise");
@@ -207,7 +214,9 @@ gw_status run_experts(gw_moe_workspace* w, const void* input, const int32_t* gat
   down.out = down_out;
   down.ld_out = kHidden;
   down.error = device_error_word();
+  w->mark(4, s);
   GW_CUDA_CHECK(launch_gemm_tc(GemmKind::nvfp4, block_n, down, sm_count(), s), "MoE grouped down GEMM");
+  w->mark(5, s);
   return GW_OK;
 }
 
@@ -227,12 +236,32 @@ gw_status gw_moe_run(gw_moe_workspace* w, const void* input_bf16, const void* sc
     return fail(GW_INVALID_ARGUMENT, "MoE run requires 16-byte aligned input/output, scores, expert scales and a bound expert table");
   if (has_bf16 || has_fp8 || !has_nvfp4 || !fp4)
     return fail(GW_UNSUPPORTED, "only NVFP4 experts with FP4 activations (W4A4) are built");
+  cudaStream_t s = as_stream(stream);
+  w->mark(0, s);
   gw_status status = gw_moe_dispatch(w, scores_bf16, expert_scales_bf16, rows, stream);
   if (status != GW_OK) return status;
-  cudaStream_t s = as_stream(stream);
   status = run_experts(w, input_bf16, w->sorted_assignments, w->offsets, 8 * rows, table, w->down.data, s);
   if (status != GW_OK) return status;
   GW_CUDA_CHECK(launch_moe_combine(w->down.data, w->inverse, w->weights, rows, kHidden, output_bf16, s), "MoE combine");
+  w->mark(6, s);
+  return GW_OK;
+}
+
+gw_status gw_moe_stage_timing(gw_moe_workspace* w, int enable) {
+  clear_error();
+  if (!w) return fail(GW_INVALID_ARGUMENT, "stage timing requires a workspace");
+  if (enable && !w->events[0])
+    for (auto& e : w->events) GW_CUDA_CHECK(cudaEventCreate(&e), "create stage timing event");
+  w->timing = enable != 0;
+  return GW_OK;
+}
+
+gw_status gw_moe_stage_elapsed_ms(gw_moe_workspace* w, float* milliseconds) {
+  clear_error();
+  if (!w || !milliseconds || !w->events[0]) return fail(GW_INVALID_ARGUMENT, "stage timing was never enabled");
+  GW_CUDA_CHECK(cudaEventSynchronize(w->events[6]), "wait for the last stage event");
+  for (int i = 0; i < 6; ++i)
+    GW_CUDA_CHECK(cudaEventElapsedTime(milliseconds + i, w->events[i], w->events[i + 1]), "stage elapsed time");
   return GW_OK;
 }
 

@@ -325,6 +325,16 @@ class MoeWorkspace:
     def bytes(self) -> int:
         return int(self._lib.gw_moe_bytes(self._ws))
 
+    STAGES = ("route_permute", "gather_quantise", "gate_up_gemm", "geglu_quantise", "down_gemm", "combine")
+
+    def stage_timing(self, enable: bool = True):
+        _check(self._lib.gw_moe_stage_timing(self._ws, int(enable)))
+
+    def stage_elapsed_ms(self) -> dict:
+        out = (ctypes.c_float * 6)()
+        _check(self._lib.gw_moe_stage_elapsed_ms(self._ws, out))
+        return dict(zip(self.STAGES, [float(v) for v in out]))
+
     def __del__(self):
         if getattr(self, "_ws", None):
             self._lib.gw_moe_destroy(self._ws)

@@ -203,6 +203,15 @@ size_t gw_moe_routing_bytes(const gw_moe_workspace* workspace);
 size_t gw_moe_projection_bytes(const gw_moe_workspace* workspace);
 size_t gw_moe_reduction_bytes(const gw_moe_workspace* workspace);
 
+/* Optional per-stage timing of gw_moe_run (no counterpart in the reference;
+ * its backends time whole steps with CUDA events, runtime/backend.h:127-129).
+ * When enabled, run records CUDA events on its stream between the stages
+ *   0 routing+permutation, 1 group descriptors + gather/quantise,
+ *   2 grouped gate/up GEMM, 3 GeGLU + quantise, 4 grouped down GEMM, 5 combine;
+ * gw_moe_stage_elapsed_ms waits for the last run and writes six durations. */
+gw_status gw_moe_stage_timing(gw_moe_workspace* workspace, int enable);
+gw_status gw_moe_stage_elapsed_ms(gw_moe_workspace* workspace, float* milliseconds);
+
 /* Expert-parallel building blocks (no counterpart in the reference, which is
  * single GPU).  A rank that owns experts [first, first+count) runs the expert
  * MLP over rows that are already sorted by expert: `offsets` (device, int32,

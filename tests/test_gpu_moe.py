@@ -1,0 +1,172 @@
+"""GPU parity of the MoE layer (routing, permutation, grouped expert GEMMs,
+GeGLU, ordered combine) against the CPU oracle, through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import codecs as C
+from oracle import moe as omoe
+from oracle import nvfp4 as onv
+from tests.gpu_helpers import assert_gemm_close, bf16_normal, bits, error_metrics, to_f32
+
+pytestmark = pytest.mark.gpu
+
+E, H, I = 128, 2816, 704
+
+
+@pytest.fixture(scope="module")
+def gw():
+    import gewell_b200
+    return gewell_b200
+
+
+def pack_padded(gw, w_bf16, input_scale, physical_rows):
+    """Device-pack [rows,K] and place it in a zero buffer of `physical_rows`
+    rows (the 26B artifact pads N to 128 with zero rows and zero scales)."""
+    rows, k = w_bf16.shape
+    packed = gw.nvfp4_pack_weights(w_bf16, input_scale)
+    if physical_rows != rows:
+        data = torch.zeros((physical_rows, k // 2), dtype=torch.uint8, device=w_bf16.device)
+        data[:rows] = packed.data
+        packed = gw.Nvfp4Weight(data, packed.scales, packed.input_scale, packed.weight_scale)
+    return packed
+
+
+@pytest.fixture(scope="module")
+def experts(gw):
+    """128 experts, gate/up [704,2816] and down [2816,704] ~ N(0,0.02) from
+    seed 4 with per-expert sub-seeds; packed on the device (that packer is
+    checked bit-exact against the oracle in test_gpu_quant.py)."""
+    device, host = [], []
+    for e in range(E):
+        g = torch.Generator().manual_seed(4 * 1000 + e)
+        mats = [(torch.randn((I, H), generator=g) * 0.02).bfloat16(),
+                (torch.randn((I, H), generator=g) * 0.02).bfloat16(),
+                (torch.randn((H, I), generator=g) * 0.02).bfloat16()]
+        scales = [0.004 + 0.0001 * (e % 5), 0.004 + 0.0001 * (e % 5) if e % 2 == 0 else 0.0045, 0.0007 + 0.00001 * (e % 3)]
+        packs = [pack_padded(gw, m.cuda(), s, (m.shape[0] + 127) // 128 * 128) for m, s in zip(mats, scales)]
+        device.append(tuple(packs))
+        host.append(omoe.ExpertWeights(*[
+            onv.Weight(p.data.cpu().numpy(), p.scales.cpu().numpy(), p.input_scale, p.weight_scale,
+                       p.data.shape[0], m.shape[1]) for p, m in zip(packs, mats)]))
+    return gw.ExpertTable(device), host
+
+
+def make_scores(rows, mode, seed=0):
+    if mode == "normal":
+        return bf16_normal((rows, E), 100 + seed)
+    scores = torch.full((rows, E), -4.0, dtype=torch.bfloat16)
+    r = torch.arange(rows)
+    starts = (r * 13) % E if mode == "distributed" else torch.where(r % 11 == 0, 120, 0) if mode == "uneven" else torch.zeros_like(r)
+    ranks = torch.arange(8)
+    scores.scatter_(1, (starts[:, None] + ranks) % E, (5.0 - ranks * .125).bfloat16().expand(rows, 8))
+    if mode == "ties":
+        scores.zero_()
+    return scores
+
+
+@pytest.mark.parametrize("rows,mode", [(1, "hot"), (17, "distributed"), (129, "uneven"), (257, "distributed"),
+                                       (17, "ties"), (4096, "hot"), (4096, "distributed"), (1000, "normal"),
+                                       (8192, "normal")])
+def test_dispatch_exact(gw, rows, mode):
+    """Selected ids, stable permutation and offsets are bit-exact; the FP32
+    routing weights agree to a few ulps (host exp vs device expf)."""
+    scores = make_scores(rows, mode)
+    scales = C.bf16_round(1.0 + 0.1 * np.sin(np.arange(E, dtype=np.float32)))
+    ws = gw.MoeWorkspace(rows)
+    ws.dispatch(scores.cuda(), torch.from_numpy(scales).to(torch.bfloat16).cuda(), rows)
+    torch.cuda.synchronize()
+    ids, weights = omoe.route(to_f32(scores), scales)
+    order, offsets = omoe.permutation(ids)
+    assert np.array_equal(ws.selected_experts().cpu().numpy(), ids)
+    np.testing.assert_allclose(ws.routing_weights().cpu().numpy(), weights, rtol=3e-6, atol=0)
+    assert np.array_equal(ws.offsets().cpu().numpy(), offsets)
+    assert np.array_equal(ws.sorted_assignments().cpu().numpy(), order)
+    # run-to-run determinism (tests/gemma4_26b_moe.cu:74-77)
+    first = ws.routing_weights().clone()
+    ws.dispatch(scores.cuda(), torch.from_numpy(scales).to(torch.bfloat16).cuda(), rows)
+    assert torch.equal(first, ws.routing_weights())
+
+
+def test_dispatch_zero_rows_and_capacity(gw):
+    ws = gw.MoeWorkspace(8)
+    ws.dispatch(None, None, 0)                     # no-op (moe.cu:479)
+    with pytest.raises(gw.GewellInvalidArgument):
+        ws.dispatch(torch.zeros((9, E), dtype=torch.bfloat16, device="cuda"),
+                    torch.ones(E, dtype=torch.bfloat16, device="cuda"), 9)
+    with pytest.raises(gw.GewellInvalidArgument):
+        gw.MoeWorkspace(0)
+
+
+def test_combine_kernel_exact(gw):
+    rows = 37
+    rng = np.random.default_rng(0)
+    down = bf16_normal((rows * 8, H), 7)
+    weights = rng.random((rows, 8)).astype(np.float32)
+    inverse = rng.permutation(rows * 8).astype(np.int32)
+    out = gw.moe_combine(down.cuda(), torch.from_numpy(inverse).cuda(), torch.from_numpy(weights).cuda(), rows)
+    torch.cuda.synchronize()
+    assert np.array_equal(bits(out), omoe.combine(to_f32(down), inverse, weights))
+
+
+@pytest.mark.parametrize("rows,mode", [(1, "hot"), (7, "normal"), (17, "distributed"), (33, "normal"),
+                                       (64, "normal"), (129, "uneven"), (300, "normal")])
+def test_moe_layer_vs_oracle(gw, experts, rows, mode):
+    table, host = experts
+    x = bf16_normal((rows, H), 200 + rows)
+    scores = make_scores(rows, mode, rows)
+    scales = np.ones(E, dtype=np.float32)
+    ws = gw.MoeWorkspace(max(rows, 64))
+    y = torch.full((rows * H + 64,), -3.0, dtype=torch.bfloat16, device="cuda")
+    ws.run(x.cuda(), scores.cuda(), torch.ones(E, dtype=torch.bfloat16, device="cuda"), table, y, rows)
+    torch.cuda.synchronize()
+    assert gw.kernel_error() == 0
+    assert torch.all(y[rows * H:] == -3.0)
+    capture = {}
+    expected = omoe.forward(to_f32(x), to_f32(scores), scales, host, capture=capture)
+    assert np.array_equal(ws.selected_experts().cpu().numpy(), capture["ids"])
+    assert np.array_equal(ws.sorted_assignments().cpu().numpy(), capture["order"])
+    m_gu = assert_gemm_close(bits(ws.gate_up_capture()), C.bf16_bits(capture["gate_up"]), "gate/up capture")
+    m_act = assert_gemm_close(bits(ws.activated_capture()), C.bf16_bits(capture["activated"]), "activated capture")
+    m_dn = assert_gemm_close(bits(ws.down_capture()), C.bf16_bits(capture["down"]), "down capture")
+    m = assert_gemm_close(bits(y[:rows * H].reshape(rows, H)), expected, f"MoE rows={rows} {mode}")
+    host_path = omoe.forward(to_f32(x), to_f32(scores), scales, host, mode="w4a16")
+    print(f"rows={rows} {mode}: gate_up {m_gu['rel_fro']:.2e} act {m_act['rel_fro']:.2e} down {m_dn['rel_fro']:.2e} "
+          f"out {m['rel_fro']:.2e} max_abs/max {m['max_abs'] / m['max_ref']:.2e}; vs W4A16 host path "
+          f"{error_metrics(bits(y[:rows * H].reshape(rows, H)), host_path)}")
+
+
+def test_moe_layer_combine_consistency(gw, experts):
+    """The layer output is exactly the ordered BF16 fold of its own down
+    capture (moe.cu:446-456): checked at a size where the full oracle is slow."""
+    table, _ = experts
+    rows = 2048
+    x = bf16_normal((rows, H), 77)
+    scores = make_scores(rows, "normal", 5)
+    ws = gw.MoeWorkspace(rows)
+    y = torch.empty((rows, H), dtype=torch.bfloat16, device="cuda")
+    ws.run(x.cuda(), scores.cuda(), torch.ones(E, dtype=torch.bfloat16, device="cuda"), table, y, rows)
+    torch.cuda.synchronize()
+    assert gw.kernel_error() == 0
+    order = ws.sorted_assignments().cpu().numpy()
+    inverse = np.empty_like(order)
+    inverse[order] = np.arange(order.size, dtype=order.dtype)
+    expected = omoe.combine(to_f32(ws.down_capture()), inverse, ws.routing_weights().cpu().numpy())
+    assert np.array_equal(bits(y), expected)
+    # every expert's rows: spot-check one expert's gate/up tile against the oracle
+    offsets = ws.offsets().cpu().numpy()
+    ids = ws.selected_experts().cpu().numpy()
+    assert offsets[-1] == rows * 8 and np.array_equal(np.bincount(ids.reshape(-1), minlength=E), np.diff(offsets))
+
+
+def test_moe_unsupported_modes(gw, experts):
+    table, _ = experts
+    ws = gw.MoeWorkspace(4)
+    x = torch.zeros((4, H), dtype=torch.bfloat16, device="cuda")
+    s = torch.zeros((4, E), dtype=torch.bfloat16, device="cuda")
+    one = torch.ones(E, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(gw.GewellUnsupported):
+        ws.run(x, s, one, table, x.clone(), 4, fp4=False)
+    with pytest.raises(gw.GewellUnsupported):
+        ws.run(x, s, one, table, x.clone(), 4, has_bf16=True)
+    ws.run(x, s, one, table, x.clone(), 0)          # rows == 0 is a no-op
