@@ -1,6 +1,7 @@
 // C ABI of gewell_b200: argument validation (same contract as the reference
 // classes), plan objects and the element-wise entry points.
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <limits>
 #include <mutex>
@@ -52,6 +53,11 @@ bool aligned(const void* p, size_t a) { return reinterpret_cast<uintptr_t>(p) % 
 
 // Token-side tile of the tensor-core kernel for a dense projection.
 int pick_block_n(uint32_t rows) {
+  // GW_DENSE_BLOCK_N (32/64/128/256) overrides the choice, for tuning runs.
+  if (const char* forced = std::getenv("GW_DENSE_BLOCK_N")) {
+    const int v = std::atoi(forced);
+    if (v == 32 || v == 64 || v == 128 || v == 256) return v;
+  }
   if (rows <= 32) return 32;
   if (rows <= 64) return 64;
   if (rows <= 128) return 128;
@@ -89,6 +95,23 @@ uint32_t gw_debug_kernel_error(void) {
   cudaMemcpy(&value, word, sizeof(value), cudaMemcpyDeviceToHost);
   if (value != 0) cudaMemset(word, 0, sizeof(value));
   return value;
+}
+
+gw_status gw_debug_rcp_approx(const float* input, float* output, uint64_t count, void* stream) {
+  clear_error();
+  if (!input || !output) return fail(GW_INVALID_ARGUMENT, "rcp probe requires input and output buffers");
+  if (!count) return GW_OK;
+  GW_CUDA_CHECK(launch_rcp_approx(input, output, count, as_stream(stream)), "approximate reciprocal probe");
+  return GW_OK;
+}
+
+gw_status gw_debug_geglu_bf16(const void* gate_bf16, const void* up_bf16, void* output_bf16, uint64_t count,
+                              void* stream) {
+  clear_error();
+  if (!gate_bf16 || !up_bf16 || !output_bf16) return fail(GW_INVALID_ARGUMENT, "GeGLU probe requires three buffers");
+  if (!count) return GW_OK;
+  GW_CUDA_CHECK(launch_geglu(gate_bf16, up_bf16, output_bf16, count, as_stream(stream)), "GeGLU probe");
+  return GW_OK;
 }
 
 // --------------------------------------------------------------------------- NVFP4 element-wise

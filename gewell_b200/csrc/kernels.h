@@ -18,6 +18,8 @@ cudaError_t launch_fp8_quantize(const void* input, uint32_t rows, uint32_t width
                                 bool gelu, uint8_t* packed, cudaStream_t stream);
 cudaError_t launch_fp8_pack_weights(const void* weights, uint32_t rows, uint32_t width, float scale,
                                     const float* row_scales, uint8_t* data, cudaStream_t stream);
+cudaError_t launch_rcp_approx(const float* in, float* out, size_t n, cudaStream_t stream);
+cudaError_t launch_geglu(const void* gate, const void* up, void* out, size_t n, cudaStream_t stream);
 cudaError_t launch_absmax(const void* values, uint64_t elements, uint32_t* state, cudaStream_t stream);
 cudaError_t launch_fp8_qdq(void* values, uint64_t elements, float scale, cudaStream_t stream);
 cudaError_t launch_nvfp4_qdq(void* values, uint64_t elements, float global_scale, cudaStream_t stream);

@@ -3,6 +3,7 @@
 // GEMMs together on one stream.  Mirrors sm120::MoeWorkspace
 // (models/gemma4/26b_a4b/sm120/moe.cuh:20-48, moe.cu:462-545).
 #include <cmath>
+#include <cstdlib>
 #include <new>
 #include <string>
 #include <vector>
@@ -176,7 +177,11 @@ gw_status run_experts(gw_moe_workspace* w, const void* input, const int32_t* gat
   auto* gate_up_groups = w->groups.as<GemmGroup>();
   auto* down_groups = gate_up_groups + 2 * kExperts + 1;
   // Token-side tile: small batches leave most experts with a handful of rows.
-  const int block_n = n <= 8 * 64 ? 32 : (n <= 8 * 1024 ? 128 : 256);
+  int block_n = n <= 8 * 64 ? 32 : (n <= 8 * 1024 ? 128 : 256);
+  if (const char* forced = std::getenv("GW_MOE_BLOCK_N")) {   // tuning override
+    const int v = std::atoi(forced);
+    if (v == 32 || v == 64 || v == 128 || v == 256) block_n = v;
+  }
   const int parts = table->shared_gate_up ? 1 : 2;
   w->mark(1, s);
   GW_CUDA_CHECK(launch_moe_prepare_groups(offsets, info, n, w->scale_rows, block_n, table->shared_gate_up,

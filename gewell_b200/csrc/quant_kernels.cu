@@ -276,6 +276,16 @@ nvfp4_qdq_kernel(uint4* __restrict__ values, uint64_t blocks, float global_scale
   }
 }
 
+__global__ void rcp_approx_kernel(const float* __restrict__ in, float* __restrict__ out, size_t n) {
+  const size_t i = size_t(blockIdx.x) * kThreads + threadIdx.x;
+  if (i < n) out[i] = rcp_approx_ftz(in[i]);
+}
+
+__global__ void geglu_kernel(const bf16* __restrict__ gate, const bf16* __restrict__ up, bf16* __restrict__ out, size_t n) {
+  const size_t i = size_t(blockIdx.x) * kThreads + threadIdx.x;
+  if (i < n) out[i] = __float2bfloat16_rn(gelu_tanh_multiply_bf16(__bfloat162float(gate[i]), __bfloat162float(up[i])));
+}
+
 unsigned grid_for(size_t items, size_t cap = 1u << 20) {
   size_t blocks = (items + kThreads - 1) / kThreads;
   if (blocks < 1) blocks = 1;
@@ -339,6 +349,17 @@ cudaError_t launch_fp8_pack_weights(const void* weights, uint32_t rows, uint32_t
   const size_t groups = size_t(rows) * (width / 8);
   fp8_pack_weights_kernel<<<grid_for(groups, 148 * 32), kThreads, 0, stream>>>(
       static_cast<const uint4*>(weights), groups, width, scale, row_scales, reinterpret_cast<uint2*>(data));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_rcp_approx(const float* in, float* out, size_t n, cudaStream_t stream) {
+  rcp_approx_kernel<<<grid_for(n, ~0u), kThreads, 0, stream>>>(in, out, n);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_geglu(const void* gate, const void* up, void* out, size_t n, cudaStream_t stream) {
+  geglu_kernel<<<grid_for(n, ~0u), kThreads, 0, stream>>>(static_cast<const bf16*>(gate), static_cast<const bf16*>(up),
+                                                          static_cast<bf16*>(out), n);
   return cudaGetLastError();
 }
 

@@ -47,6 +47,27 @@ def kernel_error() -> int:
     return int(_library().gw_debug_kernel_error())
 
 
+def rcp_approx(values):
+    """rcp.approx.ftz.f32 of a NumPy float32 array, evaluated on the device
+    (test aid: lets the CPU oracle use the hardware's reciprocal bits)."""
+    import numpy as np
+    flat = np.ascontiguousarray(values, dtype=np.float32)
+    src = torch.from_numpy(flat.reshape(-1).copy()).cuda()
+    dst = torch.empty_like(src)
+    _check(_library().gw_debug_rcp_approx(_ptr(src), _ptr(dst), src.numel(), _stream()))
+    return dst.cpu().numpy().reshape(flat.shape)
+
+
+def geglu_bf16(gate, up):
+    """Device GeGLU of BF16-valued NumPy float32 arrays (test aid, see rcp_approx)."""
+    import numpy as np
+    g = torch.from_numpy(np.ascontiguousarray(gate, dtype=np.float32)).to(torch.bfloat16).cuda()
+    u = torch.from_numpy(np.ascontiguousarray(up, dtype=np.float32)).to(torch.bfloat16).cuda()
+    out = torch.empty_like(g)
+    _check(_library().gw_debug_geglu_bf16(_ptr(g), _ptr(u), _ptr(out), g.numel(), _stream()))
+    return out.float().cpu().numpy()
+
+
 # --------------------------------------------------------------------------- layout helpers
 
 def nvfp4_scale_storage_bytes(rows: int, width: int) -> int:

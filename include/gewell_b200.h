@@ -235,6 +235,18 @@ gw_status gw_moe_combine(const void* down_bf16, const int32_t* inverse, const fl
  * bounded waits inside the tensor-core kernels.  Synchronises the device. */
 uint32_t gw_debug_kernel_error(void);
 
+/* Test aid: output[i] = rcp.approx.ftz.f32(input[i]) evaluated on the device.
+ * The activation recipe (src/nvfp4_linear.cu:92-114) is defined in terms of
+ * this instruction, whose last bit a CPU cannot predict; the parity tests feed
+ * the hardware's values into the CPU oracle so that the comparison is exact. */
+gw_status gw_debug_rcp_approx(const float* input, float* output, uint64_t count, void* stream);
+
+/* Test aid: element-wise GeGLU with both BF16 roundings
+ * (src/bf16_activation.cuh:10-16) on the device, so that the CPU oracle can use
+ * the device's tanhf bits where a one-ulp difference would flip an FP4 code. */
+gw_status gw_debug_geglu_bf16(const void* gate_bf16, const void* up_bf16, void* output_bf16, uint64_t count,
+                              void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -85,11 +85,11 @@ def permutation(ids: np.ndarray):
     return order, offsets
 
 
-def _project(x: np.ndarray, weight: nvfp4.Weight, logical: int, mode: str, accumulate: str) -> np.ndarray:
+def _project(x: np.ndarray, weight: nvfp4.Weight, logical: int, mode: str, accumulate: str, rcp_fn=None) -> np.ndarray:
     """One expert projection; BF16-valued FP32 result [rows, logical]."""
     if mode == "w4a16":
         return C.bf16_to_f32(nvfp4.linear_w4a16(x, weight, logical))
-    q = nvfp4.quantize_activations(x, weight.input_scale)
+    q = nvfp4.quantize_activations(x, weight.input_scale, rcp_fn=rcp_fn)
     aq = nvfp4.dequantized_activations(q)
     if accumulate == "f64":
         return C.bf16_to_f32(nvfp4.linear_w4a4_from_quantized(aq, weight, logical))
@@ -101,7 +101,7 @@ def _project(x: np.ndarray, weight: nvfp4.Weight, logical: int, mode: str, accum
 
 def forward(x_bf16: np.ndarray, scores_bf16: np.ndarray, expert_scales_bf16: np.ndarray,
             experts: list[ExpertWeights], mode: str = "w4a4", accumulate: str = "f64",
-            capture: dict | None = None) -> np.ndarray:
+            capture: dict | None = None, rcp_fn=None, gelu_fn=None) -> np.ndarray:
     """Whole layer.  Inputs are BF16-valued FP32 arrays; returns BF16 bits
     [T, 2816].  `capture` (optional dict) receives ids, weights, order, offsets
     and the unfused intermediates gate_up / activated / down in sorted-row order
@@ -120,12 +120,12 @@ def forward(x_bf16: np.ndarray, scores_bf16: np.ndarray, expert_scales_bf16: np.
             continue
         rows = x[order[lo:hi] // TOP_K]
         w = experts[e]
-        g = _project(rows, w.gate, INTERMEDIATE, mode, accumulate)
-        u = _project(rows, w.up, INTERMEDIATE, mode, accumulate)
-        a = C.gelu_tanh_multiply_bf16(g, u)
+        g = _project(rows, w.gate, INTERMEDIATE, mode, accumulate, rcp_fn)
+        u = _project(rows, w.up, INTERMEDIATE, mode, accumulate, rcp_fn)
+        a = (gelu_fn or C.gelu_tanh_multiply_bf16)(g, u)
         gate_up[lo:hi, :INTERMEDIATE], gate_up[lo:hi, INTERMEDIATE:] = g, u
         activated[lo:hi] = a
-        down[lo:hi] = _project(a, w.down, HIDDEN, mode, accumulate)
+        down[lo:hi] = _project(a, w.down, HIDDEN, mode, accumulate, rcp_fn)
     inverse = np.empty(n, dtype=np.int64)
     inverse[order] = np.arange(n)
     out = combine(down, inverse, weights)

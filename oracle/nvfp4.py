@@ -197,7 +197,7 @@ class QuantizedActivations:
 
 def quantize_activations(x: np.ndarray, input_scale: float, *, rcp6=None,
                          rcp_inverse=None, factor_delta: int = 0,
-                         pad_to: int = 32) -> QuantizedActivations:
+                         pad_to: int = 32, rcp_fn=None) -> QuantizedActivations:
     """BF16-valued FP32 activations [M,K] -> packed E2M1 + E4M3 K16 scales.
 
     src/nvfp4_linear.cu:61-116:
@@ -207,20 +207,22 @@ def quantize_activations(x: np.ndarray, input_scale: float, *, rcp6=None,
         code   = e2m1_rn( x * factor )
     `rcp6`, `rcp_inverse` override the two data-independent approximate
     reciprocals and `factor_delta` nudges the third by that many ulps; the
-    defaults are the correctly rounded values."""
+    defaults are the correctly rounded values.  `rcp_fn` replaces the reciprocal
+    model altogether (the GPU tests pass the hardware instruction itself)."""
     x = np.ascontiguousarray(x, dtype=np.float32)
     m, k = x.shape
     assert k % 64 == 0
     inverse = np.float32(1) / np.float32(input_scale)
-    r6 = rcp(np.float32(6)) if rcp6 is None else np.float32(rcp6)
-    rinv = rcp(inverse) if rcp_inverse is None else np.float32(rcp_inverse)
+    rcp_ = rcp if rcp_fn is None else (lambda v: np.asarray(rcp_fn(np.asarray(v, dtype=np.float32)), dtype=np.float32))
+    r6 = rcp_(np.float32(6)) if rcp6 is None else np.float32(rcp6)
+    rinv = rcp_(inverse) if rcp_inverse is None else np.float32(rcp_inverse)
     blocks = x.reshape(m, k // BLOCK, BLOCK)
     amax = np.max(np.abs(blocks), axis=2).astype(np.float32)
     with np.errstate(over="ignore"):
         sf_code = C.e4m3_encode((inverse * (amax * r6).astype(np.float32)).astype(np.float32))
     sf = C.e4m3_decode(sf_code)
     denominator = (sf * rinv).astype(np.float32)
-    factor = rcp(np.where(sf == 0, np.float32(1), denominator))
+    factor = rcp_(np.where(sf == 0, np.float32(1), denominator))
     if factor_delta:
         step = np.float32(np.inf if factor_delta > 0 else -np.inf)
         for _ in range(abs(factor_delta)):
@@ -274,15 +276,16 @@ def linear_w4a4_from_quantized(aq: np.ndarray, weight: Weight, logical_rows=None
     return C.bf16_bits((acc * np.float64(alpha)).astype(np.float32))
 
 
-def linear_w4a4(x: np.ndarray, weight: Weight, gelu: bool = False, logical_rows=None) -> np.ndarray:
+def linear_w4a4(x: np.ndarray, weight: Weight, gelu: bool = False, logical_rows=None, rcp_fn=None,
+                gelu_fn=None) -> np.ndarray:
     """Faithful W4A4 oracle of nvfp4::Plan::run: quantise activations with the
     weight's input scale (optionally after GeGLU of [M,2K] gate|up slices,
     src/nvfp4_linear.cu:77-83), then the FP64 dot above."""
     x = np.asarray(x, dtype=np.float32)
     if gelu:
         k = weight.width
-        x = C.gelu_tanh_multiply_bf16(x[:, :k], x[:, k:2 * k])
-    q = quantize_activations(x, weight.input_scale)
+        x = (gelu_fn or C.gelu_tanh_multiply_bf16)(x[:, :k], x[:, k:2 * k])
+    q = quantize_activations(x, weight.input_scale, rcp_fn=rcp_fn)
     return linear_w4a4_from_quantized(dequantized_activations(q), weight, logical_rows)
 
 

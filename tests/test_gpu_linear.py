@@ -54,7 +54,7 @@ def test_config1_nvfp4_linear(gw):
     y, packed, scales = run_nvfp4(gw, x.cuda(), oracle_weight_to_device(w), n, k)
     exact = oracle_from_device_quantisation(packed, scales, 16, k, w)
     assert_reference_tolerance(bits(y), exact, "config 1 vs FP64 dot of device-quantised operands")
-    faithful = onv.linear_w4a4(to_f32(x), w)
+    faithful = onv.linear_w4a4(to_f32(x), w, rcp_fn=gw.rcp_approx)
     m = assert_gemm_close(bits(y), faithful, "config 1 vs faithful W4A4 oracle")
     host_path = onv.linear_w4a16(to_f32(x), w)
     from tests.gpu_helpers import error_metrics
@@ -106,7 +106,8 @@ def test_nvfp4_gelu_input(gw):
     y, packed, scales = run_nvfp4(gw, x.cuda(), oracle_weight_to_device(w), n, k, gelu=True)
     exact = oracle_from_device_quantisation(packed, scales, rows, k, w)
     assert_reference_tolerance(bits(y), exact, "GeGLU input")
-    assert_gemm_close(bits(y), onv.linear_w4a4(to_f32(x), w, gelu=True), "GeGLU input vs faithful oracle")
+    faithful = onv.linear_w4a4(to_f32(x), w, gelu=True, rcp_fn=gw.rcp_approx, gelu_fn=gw.geglu_bf16)
+    assert_gemm_close(bits(y), faithful, "GeGLU input vs faithful oracle")
 
 
 def test_nvfp4_argument_validation(gw):

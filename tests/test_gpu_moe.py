@@ -123,7 +123,8 @@ def test_moe_layer_vs_oracle(gw, experts, rows, mode):
     assert gw.kernel_error() == 0
     assert torch.all(y[rows * H:] == -3.0)
     capture = {}
-    expected = omoe.forward(to_f32(x), to_f32(scores), scales, host, capture=capture)
+    expected = omoe.forward(to_f32(x), to_f32(scores), scales, host, capture=capture, rcp_fn=gw.rcp_approx,
+                            gelu_fn=gw.geglu_bf16)
     assert np.array_equal(ws.selected_experts().cpu().numpy(), capture["ids"])
     assert np.array_equal(ws.sorted_assignments().cpu().numpy(), capture["order"])
     m_gu = assert_gemm_close(bits(ws.gate_up_capture()), C.bf16_bits(capture["gate_up"]), "gate/up capture")
