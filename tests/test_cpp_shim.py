@@ -1,0 +1,24 @@
+"""Compile and run the host-only C++ shim contract test against the built
+library (no GPU needed: every check fails validation before CUDA is touched)."""
+import shutil
+import subprocess
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parents[1]
+CUDA_INCLUDE = Path("/usr/local/cuda/include")
+
+
+@pytest.mark.skipif(shutil.which("g++") is None or not CUDA_INCLUDE.exists(), reason="needs g++ and the CUDA headers")
+def test_shim_contract(tmp_path):
+    from gewell_b200 import _lib
+    assert _lib.LIBRARY_PATH.exists(), "build the library first: python -m gewell_b200.build"
+    exe = tmp_path / "shim_contract"
+    subprocess.run(["g++", "-std=c++17", "-I", str(ROOT / "include"), "-I", str(CUDA_INCLUDE),
+                    str(ROOT / "tests" / "cpp" / "shim_contract.cpp"), "-o", str(exe),
+                    str(_lib.LIBRARY_PATH), f"-Wl,-rpath,{_lib.LIBRARY_PATH.parent}",
+                    "-L/usr/local/cuda/lib64", "-lcudart", "-Wl,-rpath,/usr/local/cuda/lib64"], check=True)
+    done = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert done.returncode == 0, done.stdout + done.stderr
+    assert "PASS" in done.stdout
