@@ -48,6 +48,9 @@ _SIGNATURES = {
     "gw_nvfp4_plan_run": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, c_void_p, c_void_p,
                                   c_size_t, c_void_p, c_int]),
     "gw_nvfp4_plan_destroy": (None, [c_void_p]),
+    "gw_nvfp4_linear_static_scratch_limit": (c_size_t, []),
+    "gw_nvfp4_linear_static_scratch": (c_int, [c_void_p, c_uint32, c_uint32, c_uint32, c_void_p, c_void_p, c_float,
+                                               c_float, c_void_p, c_void_p, c_int]),
     "gw_nvfp4_gemv_w4a16": (c_int, [c_void_p, c_uint32, c_void_p, c_void_p, c_float, c_uint32, c_uint32, c_void_p, c_void_p]),
     "gw_fp8_quantize_activations": (c_int, [c_void_p, c_uint32, c_uint32, c_float, c_int, c_void_p, c_void_p]),
     "gw_fp8_pack_weights": (c_int, [c_void_p, c_uint32, c_uint32, c_float, c_void_p, c_void_p, c_void_p]),

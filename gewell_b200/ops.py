@@ -142,6 +142,20 @@ def nvfp4_gemv_w4a16(x: torch.Tensor, weight: Nvfp4Weight, input_width: int, out
     return y
 
 
+def nvfp4_linear_static_scratch(x, weight: Nvfp4Weight, input_width: int, output_width: int, y=None,
+                                transform: int = TRANSFORM_IDENTITY, stream=None):
+    """NVFP4 linear through the library's built-in scratch array: for callers
+    that can neither allocate device memory nor spare a scratch buffer.  Takes
+    inputs and outputs only; sizes above the built-in limit are rejected."""
+    rows = x.shape[0]
+    if y is None:
+        y = torch.empty((rows, output_width), dtype=torch.bfloat16, device=x.device)
+    _check(_library().gw_nvfp4_linear_static_scratch(_ptr(x), rows, input_width, output_width, _ptr(weight.data),
+                                                     _ptr(weight.scales), weight.input_scale, weight.weight_scale,
+                                                     _ptr(y), _stream(stream), transform))
+    return y
+
+
 class Nvfp4Plan:
     """gewell::nvfp4::Plan(handle, rows, K, N): scratch_bytes(), run(...)."""
 

@@ -88,6 +88,27 @@ gw_status gw_nvfp4_plan_run(gw_nvfp4_plan* plan, const void* input_bf16, const u
                             int transform);
 void gw_nvfp4_plan_destroy(gw_nvfp4_plan* plan);
 
+/* NVFP4 linear layer for callers that cannot allocate device memory and have
+ * no scratch region to lend (no counterpart in the reference, whose Plan::run
+ * always takes caller scratch).  Same arithmetic and kernels as
+ * gw_nvfp4_plan_run, but the packed activations and their scale tiles go to a
+ * fixed array built into this library, so the call takes inputs and outputs
+ * only and performs no allocation of any kind.
+ *   - limit: rows*K/2 (rounded up to 256) + gw_nvfp4_scale_storage_bytes(rows,K)
+ *     must not exceed gw_nvfp4_linear_static_scratch_limit() (2 MiB); larger
+ *     problems are rejected with GW_INVALID_ARGUMENT;
+ *   - the array is resident on every GPU that loads the library, for the
+ *     lifetime of the process;
+ *   - the first call on each GPU looks up the array's device address; make
+ *     that first call before starting any stream capture;
+ *   - all calls on a GPU share the array: calls that overlap on the GPU
+ *     (several streams or host threads) race -- keep them on one stream. */
+size_t gw_nvfp4_linear_static_scratch_limit(void);
+gw_status gw_nvfp4_linear_static_scratch(const void* input_bf16, uint32_t rows, uint32_t input_width,
+                                         uint32_t output_width, const uint8_t* weight_data,
+                                         const uint8_t* weight_scales, float input_scale, float weight_scale,
+                                         void* output_bf16, void* stream, int transform);
+
 /* W4A16 projection (models/gemma4/26b_a4b/sm120/projection.cu:129-139 and the
  * north-star host path): BF16 activations times NVFP4 weights without
  * activation quantisation, for small row counts; weights are streamed once
