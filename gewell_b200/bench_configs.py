@@ -162,6 +162,13 @@ def main():
             print(json.dumps(row), flush=True)
     if "c3" in wanted:
         print(json.dumps(bench_nvfp4_linear(4096, 5376, 21504, "c3_nvfp4_prefill", args.iters)), flush=True)
+    if "c3small" in wanted:   # profiling-sized slice of config 3 (same N and K, 1024 rows)
+        print(json.dumps(bench_nvfp4_linear(1024, 5376, 21504, "c3_nvfp4_prefill_rows1024", args.iters)), flush=True)
+    if "c2m64" in wanted:
+        for row in bench_fp8_decode(rows_list=(64,), iters=args.iters):
+            print(json.dumps(row), flush=True)
+    if "moe2048" in wanted:
+        print(json.dumps(bench_moe(2048, iters=args.iters)), flush=True)
     if "moe64" in wanted:
         print(json.dumps(bench_moe(64, iters=args.iters)), flush=True)
     if "moe8192" in wanted:
