@@ -79,6 +79,7 @@ _SIGNATURES = {
     "gw_moe_routing_bytes": (c_size_t, [c_void_p]),
     "gw_moe_projection_bytes": (c_size_t, [c_void_p]),
     "gw_moe_reduction_bytes": (c_size_t, [c_void_p]),
+    "gw_moe_capture": (c_int, [c_void_p, c_int]),
     "gw_moe_stage_timing": (c_int, [c_void_p, c_int]),
     "gw_moe_stage_elapsed_ms": (c_int, [c_void_p, POINTER(c_float)]),
     "gw_moe_run_sorted": (c_int, [c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_uint32, c_void_p, c_void_p, c_void_p]),

@@ -9,6 +9,7 @@
 #include <string>
 
 #include "common.cuh"
+#include "dense.h"
 #include "gemm_tc.cuh"
 #include "kernels.h"
 
@@ -50,19 +51,6 @@ namespace {
 bool finite_positive(float v) { return v > 0.0F && std::isfinite(v); }
 
 bool aligned(const void* p, size_t a) { return reinterpret_cast<uintptr_t>(p) % a == 0; }
-
-// Token-side tile of the tensor-core kernel for a dense projection.
-int pick_block_n(uint32_t rows) {
-  // GW_DENSE_BLOCK_N (32/64/128/256) overrides the choice, for tuning runs.
-  if (const char* forced = std::getenv("GW_DENSE_BLOCK_N")) {
-    const int v = std::atoi(forced);
-    if (v == 32 || v == 64 || v == 128 || v == 256) return v;
-  }
-  if (rows <= 32) return 32;
-  if (rows <= 64) return 64;
-  if (rows <= 128) return 128;
-  return 256;
-}
 
 }  // namespace
 }  // namespace gw
@@ -182,12 +170,8 @@ gw_status gw_nvfp4_gemv_w4a16(const void* input_bf16, uint32_t rows, const uint8
 
 struct gw_nvfp4_plan {
   uint32_t rows, input_width, output_width;
-  int block_n;
   size_t scale_offset, total_bytes;
-  // descriptor cache: re-encoded only when a pointer changes
-  const void* cached_weight = nullptr;
-  const void* cached_packed = nullptr;
-  CUtensorMap map_a{}, map_b{};
+  DenseDescriptors descriptors;
 };
 
 gw_status gw_nvfp4_plan_create(uint32_t rows, uint32_t input_width, uint32_t output_width, gw_nvfp4_plan** plan) {
@@ -200,7 +184,6 @@ gw_status gw_nvfp4_plan_create(uint32_t rows, uint32_t input_width, uint32_t out
   p->rows = rows;
   p->input_width = input_width;
   p->output_width = output_width;
-  p->block_n = pick_block_n(rows);
   // scratch = packed activations | tiled activation scales   (each 256-byte aligned)
   p->scale_offset = align_up(size_t(rows) * input_width / 2, 256);
   p->total_bytes = p->scale_offset + align_up(scale_storage_bytes(rows, input_width), 256);
@@ -232,45 +215,9 @@ gw_status gw_nvfp4_plan_run(gw_nvfp4_plan* plan, const void* input_bf16, const u
   GW_CUDA_CHECK(launch_nvfp4_quantize(input_bf16, plan->rows, plan->input_width, 1.0F / input_scale,
                                       transform == GW_TRANSFORM_GELU_TANH_MULTIPLY, packed, scales, s),
                 "NVFP4 quantize activations");
-  std::string error;
-  if (plan->cached_weight != weight_data) {
-    if (!encode_tensor_map_2d(&plan->map_a, weight_data, plan->input_width / 2, plan->output_width, 128, &error))
-      return fail(GW_CUDA_ERROR, "NVFP4 weight descriptor: " + error);
-    plan->cached_weight = weight_data;
-  }
-  if (plan->cached_packed != packed) {
-    if (!encode_tensor_map_2d(&plan->map_b, packed, plan->input_width / 2, plan->rows, plan->block_n, &error))
-      return fail(GW_CUDA_ERROR, "NVFP4 activation descriptor: " + error);
-    plan->cached_packed = packed;
-  }
-  GemmParams params{};
-  params.map_a = plan->map_a;
-  params.map_b = plan->map_b;
-  params.groups = nullptr;
-  params.num_groups = 1;
-  GemmGroup& g = params.single;
-  g.sf_a = weight_scales;
-  g.channel_alpha = nullptr;
-  g.alpha = alpha;
-  g.map_a = -1;
-  g.a_tiles = int32_t(plan->output_width / 128);
-  g.a_rows = int32_t(plan->output_width);
-  g.b_row0 = 0;
-  g.b_rows = int32_t(plan->rows);
-  g.sfb_row0 = 0;
-  g.out_row0 = 0;
-  g.out_col0 = 0;
-  g.work_begin = 0;
-  const int b_tiles = (plan->rows + plan->block_n - 1) / plan->block_n;
-  params.total_work = g.a_tiles * b_tiles;
-  params.sf_b = scales;
-  params.k = int32_t(plan->input_width);
-  params.out = output_bf16;
-  params.ld_out = plan->output_width;
-  params.error = device_error_word();
-  const int grid = params.total_work < sm_count() ? params.total_work : sm_count();
-  GW_CUDA_CHECK(launch_gemm_tc(GemmKind::nvfp4, plan->block_n, params, grid, s), "NVFP4 tensor-core GEMM");
-  return GW_OK;
+  DenseProblem problem{GemmKind::nvfp4, plan->rows, plan->input_width, plan->output_width, weight_data, weight_scales,
+                       packed, scales, alpha, nullptr, output_bf16, device_error_word()};
+  return launch_dense(problem, &plan->descriptors, s);
 }
 
 // --------------------------------------------------------------------------- FP8
@@ -303,11 +250,8 @@ gw_status gw_fp8_pack_weights(const void* weights_bf16, uint32_t output_width, u
 struct gw_fp8_plan {
   uint32_t rows, input_width, output_width;
   bool channel_scales;
-  int block_n;
   size_t total_bytes;
-  const void* cached_weight = nullptr;
-  const void* cached_packed = nullptr;
-  CUtensorMap map_a{}, map_b{};
+  DenseDescriptors descriptors;
 };
 
 gw_status gw_fp8_plan_create(uint32_t rows, uint32_t input_width, uint32_t output_width, int channel_scales,
@@ -324,7 +268,6 @@ gw_status gw_fp8_plan_create(uint32_t rows, uint32_t input_width, uint32_t outpu
   p->input_width = input_width;
   p->output_width = output_width;
   p->channel_scales = channel_scales != 0;
-  p->block_n = pick_block_n(rows);
   p->total_bytes = align_up(size_t(rows) * input_width, 256);
   *plan = p;
   return GW_OK;
@@ -353,45 +296,10 @@ gw_status gw_fp8_plan_run(gw_fp8_plan* plan, const void* input_bf16, const uint8
   GW_CUDA_CHECK(launch_fp8_quantize(input_bf16, plan->rows, plan->input_width, 1.0F / input_scale,
                                     transform == GW_TRANSFORM_GELU_TANH_MULTIPLY, packed, s),
                 "FP8 quantize activations");
-  std::string error;
-  if (plan->cached_weight != weight_data) {
-    if (!encode_tensor_map_2d(&plan->map_a, weight_data, plan->input_width, plan->output_width, 128, &error))
-      return fail(GW_CUDA_ERROR, "FP8 weight descriptor: " + error);
-    plan->cached_weight = weight_data;
-  }
-  if (plan->cached_packed != packed) {
-    if (!encode_tensor_map_2d(&plan->map_b, packed, plan->input_width, plan->rows, plan->block_n, &error))
-      return fail(GW_CUDA_ERROR, "FP8 activation descriptor: " + error);
-    plan->cached_packed = packed;
-  }
-  GemmParams params{};
-  params.map_a = plan->map_a;
-  params.map_b = plan->map_b;
-  params.groups = nullptr;
-  params.num_groups = 1;
-  GemmGroup& g = params.single;
-  g.sf_a = nullptr;
-  g.channel_alpha = plan->channel_scales ? channel_scales : nullptr;
-  g.alpha = alpha;
-  g.map_a = -1;
-  g.a_tiles = int32_t((plan->output_width + 127) / 128);
-  g.a_rows = int32_t(plan->output_width);
-  g.b_row0 = 0;
-  g.b_rows = int32_t(plan->rows);
-  g.sfb_row0 = 0;
-  g.out_row0 = 0;
-  g.out_col0 = 0;
-  g.work_begin = 0;
-  const int b_tiles = (plan->rows + plan->block_n - 1) / plan->block_n;
-  params.total_work = g.a_tiles * b_tiles;
-  params.sf_b = nullptr;
-  params.k = int32_t(plan->input_width);
-  params.out = output_bf16;
-  params.ld_out = plan->output_width;
-  params.error = device_error_word();
-  const int grid = params.total_work < sm_count() ? params.total_work : sm_count();
-  GW_CUDA_CHECK(launch_gemm_tc(GemmKind::fp8, plan->block_n, params, grid, s), "FP8 tensor-core GEMM");
-  return GW_OK;
+  DenseProblem problem{GemmKind::fp8, plan->rows, plan->input_width, plan->output_width, weight_data, nullptr,
+                       packed, nullptr, alpha, plan->channel_scales ? channel_scales : nullptr, output_bf16,
+                       device_error_word()};
+  return launch_dense(problem, &plan->descriptors, s);
 }
 
 // --------------------------------------------------------------------------- weight QDQ

@@ -1,0 +1,84 @@
+#include "dense.h"
+
+#include <cstdlib>
+#include <string>
+
+namespace gw {
+
+bool dense_uses_swap_form(uint32_t rows) {
+  if (const char* forced = std::getenv("GW_DENSE_FORM")) {   // tuning override: "swap" / "direct"
+    if (forced[0] == 's' && rows <= 128) return true;
+    if (forced[0] == 'd') return false;
+  }
+  return rows <= 128;
+}
+
+int dense_block_n(uint32_t rows) {
+  if (dense_uses_swap_form(rows)) return rows <= 32 ? 32 : rows <= 64 ? 64 : 128;
+  if (const char* forced = std::getenv("GW_DENSE_BLOCK_N")) {   // tuning override
+    const int v = std::atoi(forced);
+    if (v == 128 || v == 256) return v;
+  }
+  return 256;
+}
+
+gw_status launch_dense(const DenseProblem& q, DenseDescriptors* cache, cudaStream_t stream) {
+  const bool swap = dense_uses_swap_form(q.rows);
+  const int block_n = dense_block_n(q.rows);
+  const bool fp4 = q.kind == GemmKind::nvfp4;
+  const uint64_t row_bytes = fp4 ? q.k / 2 : q.k;
+  std::string error;
+  if (cache->weight != q.weight) {
+    if (!encode_tensor_map_2d(&cache->weight_map, q.weight, row_bytes, q.n, 128, &error))
+      return fail(GW_CUDA_ERROR, "weight descriptor: " + error);
+    cache->weight = q.weight;
+  }
+  if (cache->activations != q.activations) {
+    if (!encode_tensor_map_2d(&cache->activation_map, q.activations, row_bytes, q.rows, swap ? block_n : 128, &error))
+      return fail(GW_CUDA_ERROR, "activation descriptor: " + error);
+    cache->activations = q.activations;
+  }
+  GemmParams params{};
+  GemmGroup& g = params.single;
+  params.groups = nullptr;
+  params.num_groups = 1;
+  params.k = int32_t(q.k);
+  params.out = q.output;
+  params.ld_out = q.n;
+  params.error = q.error;
+  g.alpha[0] = g.alpha[1] = q.alpha;
+  g.channel_alpha = q.channel_alpha;
+  g.map_l = -1;
+  g.map_c[0] = g.map_c[1] = -1;
+  if (swap) {
+    params.map_l = cache->weight_map;
+    params.map_c = cache->activation_map;
+    params.c_rows_per_tile = block_n;
+    g.sf_l = q.weight_scales;
+    g.l_rows = int32_t(q.n);
+    g.l_tiles = int32_t((q.n + 127) / 128);
+    g.sf_c[0] = g.sf_c[1] = q.activation_scales;
+    g.c_rows = int32_t(q.rows);
+    g.c_tiles = int32_t((q.rows + block_n - 1) / block_n);
+    g.c_half_stride = 0;
+  } else {
+    params.map_l = cache->activation_map;
+    params.map_c = cache->weight_map;
+    params.c_rows_per_tile = block_n;
+    g.sf_l = q.activation_scales;
+    g.l_rows = int32_t(q.rows);
+    g.l_tiles = int32_t((q.rows + 127) / 128);
+    g.sf_c[0] = g.sf_c[1] = q.weight_scales;
+    g.c_rows = int32_t(q.n);
+    g.c_tiles = int32_t((q.n + block_n - 1) / block_n);
+    g.c_half_stride = block_n > 128 ? 128 : 0;
+  }
+  params.total_work = g.l_tiles * g.c_tiles;
+  const int grid = params.total_work < sm_count() ? params.total_work : sm_count();
+  GW_CUDA_CHECK(launch_gemm_tc(q.kind, swap ? GemmEpilogue::swap_store : GemmEpilogue::direct_store, block_n, params,
+                               grid, stream),
+                fp4 ? "NVFP4 tensor-core GEMM" : "FP8 tensor-core GEMM");
+  return GW_OK;
+}
+
+}  // namespace gw

@@ -1,0 +1,36 @@
+// One dense projection Y[rows, n] = bf16(alpha * Xq . Wq^T) on the tcgen05
+// kernel: picks the operand roles and tile for the row count, builds the TMA
+// descriptors (cached per plan) and launches.
+#pragma once
+
+#include "common.cuh"
+#include "gemm_tc.cuh"
+
+namespace gw {
+
+struct DenseDescriptors {          // re-encoded only when a pointer changes
+  const void* weight = nullptr;
+  const void* activations = nullptr;
+  CUtensorMap weight_map{}, activation_map{};
+};
+
+struct DenseProblem {
+  GemmKind kind;
+  uint32_t rows, k, n;
+  const void* weight;              // [n, k] E4M3 or [n, k/2] packed E2M1
+  const uint8_t* weight_scales;    // NVFP4 only
+  const void* activations;         // quantised [rows, k(/2)]
+  const uint8_t* activation_scales;
+  float alpha;
+  const float* channel_alpha;
+  void* output;
+  uint32_t* error;
+};
+
+// true: weights on the 128-lane operand and tokens on the column operand.
+bool dense_uses_swap_form(uint32_t rows);
+int dense_block_n(uint32_t rows);
+
+gw_status launch_dense(const DenseProblem& problem, DenseDescriptors* cache, cudaStream_t stream);
+
+}  // namespace gw

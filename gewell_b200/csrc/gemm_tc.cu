@@ -1,18 +1,18 @@
 // Persistent, warp-specialised tcgen05 GEMM for sm_100a.
 //
-//   warp 0      TMA producer: operand tiles (cp.async.bulk.tensor, 128B swizzle)
-//               and scale-factor atoms (cp.async.bulk) into a ring of smem stages
-//   warp 1      MMA issuer: scale atoms smem->TMEM (tcgen05.cp), block-scaled
-//               tcgen05.mma (kind::mxf4nvf4, or kind::f8f6f4 for FP8) into a
-//               TMEM accumulator, tcgen05.commit to free stages / publish tiles
-//   warps 2..5  epilogue: tcgen05.ld the accumulator (one TMEM lane quadrant
-//               per warp), scale, round to BF16, store
+//   warp 0       TMA producer: operand tiles (cp.async.bulk.tensor, 128B swizzle)
+//                and scale-factor atoms (cp.async.bulk) into a ring of smem stages
+//   warp 1       MMA issuer: scale atoms smem->TMEM (tcgen05.cp) interleaved with
+//                the block-scaled tcgen05.mma (kind::mxf4nvf4, or kind::f8f6f4 for
+//                FP8) so that the copies hide behind the preceding MMA;
+//                tcgen05.commit frees stages / publishes accumulators
+//   warps 2..9   epilogue: two warps per TMEM lane quadrant, each draining half of
+//                the accumulator columns with tcgen05.ld
 //
-// A (128 rows per tile) sits on the TMEM-lane side, B (BLOCK_N rows per tile,
-// any multiple of 16 valid) on the TMEM-column side; see gemm_tc.cuh.
-// Every wait is bounded: on a timeout the role records an error word, raises
-// the CTA's abort flag and all roles unwind to the common exit, where TMEM is
-// released.
+// Operand roles and the three epilogues are described in gemm_tc.cuh.  Every
+// wait is bounded: on a timeout the role records an error word, raises the
+// CTA's abort flag and all roles unwind to the common exit, where TMEM is
+// released.  No load in this file fans out to other CTAs.
 #include <string>
 
 #include "common.cuh"
@@ -22,8 +22,9 @@
 namespace gw {
 namespace {
 
-constexpr int kThreads = 192;
-constexpr int kTileA = 128;
+constexpr int kEpilogueWarps = 8;
+constexpr int kThreads = 64 + 32 * kEpilogueWarps;
+constexpr int kTileL = 128;
 constexpr int kStageRowBytes = 128;   // bytes of K per stage row (= swizzle span)
 constexpr int kAtomBytes = 512;       // one scale atom: 128 rows x 4 K16 blocks
 constexpr int kKBlocksPerStage = 4;   // MMAs per stage (K=64 FP4 / K=32 FP8 each: 32 bytes)
@@ -31,20 +32,21 @@ constexpr int kKBlocksPerStage = 4;   // MMAs per stage (K=64 FP4 / K=32 FP8 eac
 template <bool kNvfp4, int BLOCK_N>
 struct Config {
   static constexpr int kAccStages = BLOCK_N >= 256 ? 1 : 2;
-  static constexpr int kBAtomRows = BLOCK_N > 128 ? BLOCK_N / 128 : 1;
-  static constexpr int kABytes = kTileA * kStageRowBytes;
-  static constexpr int kBBytes = BLOCK_N * kStageRowBytes;
-  static constexpr int kSfaBytes = kNvfp4 ? kKBlocksPerStage * kAtomBytes : 0;
-  static constexpr int kSfbBytes = kNvfp4 ? kBAtomRows * kKBlocksPerStage * kAtomBytes : 0;
-  static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
+  static constexpr int kHalves = BLOCK_N > 128 ? BLOCK_N / 128 : 1;
+  static constexpr int kHalfRows = BLOCK_N / kHalves;
+  static constexpr int kLBytes = kTileL * kStageRowBytes;
+  static constexpr int kCBytes = BLOCK_N * kStageRowBytes;
+  static constexpr int kSflBytes = kNvfp4 ? kKBlocksPerStage * kAtomBytes : 0;
+  static constexpr int kSfcBytes = kNvfp4 ? kHalves * kKBlocksPerStage * kAtomBytes : 0;
+  static constexpr int kStageBytes = kLBytes + kCBytes + kSflBytes + kSfcBytes;
   static constexpr int kMaxSmem = 227 * 1024 - 2048;   // leave room for barriers + alignment slack
   static constexpr int kStagesRaw = kMaxSmem / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
-  static constexpr int kSfbColsPerKb = 4 * kBAtomRows;
+  static constexpr int kSfcColsPerKb = 4 * kHalves;
   static constexpr int kAccCols = kAccStages * BLOCK_N;
-  static constexpr int kSfaCol = kAccCols;
-  static constexpr int kSfbCol = kSfaCol + (kNvfp4 ? 4 * kKBlocksPerStage : 0);
-  static constexpr int kUsedCols = kSfbCol + (kNvfp4 ? kSfbColsPerKb * kKBlocksPerStage : 0);
+  static constexpr int kSflCol = kAccCols;
+  static constexpr int kSfcCol = kSflCol + (kNvfp4 ? 4 * kKBlocksPerStage : 0);
+  static constexpr int kUsedCols = kSfcCol + (kNvfp4 ? kSfcColsPerKb * kKBlocksPerStage : 0);
   static constexpr int kTmemCols = kUsedCols <= 32 ? 32 : kUsedCols <= 64 ? 64 : kUsedCols <= 128 ? 128
                                    : kUsedCols <= 256 ? 256 : 512;
   static constexpr int kBarrierBytes = (2 * kStages + 2 * kAccStages) * 8 + 16;
@@ -57,15 +59,17 @@ struct Config {
 };
 
 struct WorkItem {
-  GemmGroup group;
-  int a_tile, b_tile;
-  int n_valid;   // valid B rows in this tile
-  int mma_n;     // n_valid rounded up to 16
+  GemmGroup g;
+  int l_tile, c_tile;
+  int l_valid;   // valid lanes (rows of L) in this tile
+  int c_valid;   // swap form: valid columns (tokens) in this tile
+  int halves;    // boxes of the C operand that hold valid rows in this tile
+  int mma_n;     // MMA N for this tile
 };
 
-template <int BLOCK_N>
-__device__ __forceinline__ bool decode_work(const GemmParams& p, int w, WorkItem& item) {
-  int gi = 0;
+template <int BLOCK_N, GemmEpilogue EPI>
+__device__ __forceinline__ void decode_work(const GemmParams& p, int w, WorkItem& item) {
+  using C = Config<true, BLOCK_N>;
   if (p.groups != nullptr) {
     // largest gi with groups[gi].work_begin <= w  (groups[num_groups] is the sentinel)
     int lo = 0, hi = p.num_groups;
@@ -73,18 +77,30 @@ __device__ __forceinline__ bool decode_work(const GemmParams& p, int w, WorkItem
       const int mid = (lo + hi) / 2;
       if (p.groups[mid].work_begin <= w) lo = mid; else hi = mid;
     }
-    gi = lo;
-    item.group = p.groups[gi];
+    item.g = p.groups[lo];
   } else {
-    item.group = p.single;
+    item.g = p.single;
   }
-  const int local = w - item.group.work_begin;
-  item.a_tile = local % item.group.a_tiles;
-  item.b_tile = local / item.group.a_tiles;
-  const int remaining = item.group.b_rows - item.b_tile * BLOCK_N;
-  item.n_valid = remaining < BLOCK_N ? remaining : BLOCK_N;
-  item.mma_n = (item.n_valid + 15) & ~15;
-  return item.n_valid > 0;
+  const int local = w - item.g.work_begin;
+  if constexpr (EPI == GemmEpilogue::swap_store) {
+    // consecutive work items share the token tile and sweep the weight tiles
+    item.l_tile = local % item.g.l_tiles;
+    item.c_tile = local / item.g.l_tiles;
+  } else {
+    // consecutive work items share the token tile (L) and sweep the weight tiles (C)
+    item.c_tile = local % item.g.c_tiles;
+    item.l_tile = local / item.g.c_tiles;
+  }
+  const int l_left = item.g.l_rows - item.l_tile * kTileL;
+  item.l_valid = l_left < kTileL ? l_left : kTileL;
+  const int c_left = item.g.c_rows - item.c_tile * p.c_rows_per_tile;
+  item.c_valid = c_left < C::kHalfRows ? c_left : C::kHalfRows;
+  // a dense projection whose row count is not a multiple of BLOCK_N leaves the
+  // second half of its last column tile empty
+  item.halves = C::kHalves;
+  if (C::kHalves == 2 && item.g.c_half_stride != 0 && c_left <= C::kHalfRows) item.halves = 1;
+  if constexpr (EPI == GemmEpilogue::swap_store) item.mma_n = (item.c_valid + 15) & ~15;   // kHalves == 1
+  else item.mma_n = item.halves * C::kHalfRows;
 }
 
 __device__ __forceinline__ void report(uint32_t* error, uint32_t code, volatile int* abort_flag) {
@@ -92,7 +108,12 @@ __device__ __forceinline__ void report(uint32_t* error, uint32_t code, volatile 
   if (error != nullptr) atomicCAS(error, 0u, code);
 }
 
-template <bool kNvfp4, int BLOCK_N>
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  const __nv_bfloat162 pair = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&pair);
+}
+
+template <bool kNvfp4, int BLOCK_N, GemmEpilogue EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ GemmParams p) {
   using C = Config<kNvfp4, BLOCK_N>;
@@ -110,7 +131,10 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) { ptx::mbar_init(full_bar + s, 1); ptx::mbar_init(empty_bar + s, 1); }
-    for (int a = 0; a < C::kAccStages; ++a) { ptx::mbar_init(acc_full_bar + a, 1); ptx::mbar_init(acc_empty_bar + a, 4); }
+    for (int a = 0; a < C::kAccStages; ++a) {
+      ptx::mbar_init(acc_full_bar + a, 1);
+      ptx::mbar_init(acc_empty_bar + a, kEpilogueWarps);
+    }
     *abort_flag = 0;
     ptx::fence_barrier_init();
     ptx::fence_proxy_async_smem();
@@ -130,10 +154,10 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
   const int k_stages = (total_kb + kKBlocksPerStage - 1) / kKBlocksPerStage;
   const int k_atoms = p.k / 64;                             // scale atoms per 128-row block (NVFP4)
 
-  auto stage_a = [&](int s) { return smem + s * C::kStageBytes; };
-  auto stage_b = [&](int s) { return smem + s * C::kStageBytes + C::kABytes; };
-  auto stage_sfa = [&](int s) { return smem + s * C::kStageBytes + C::kABytes + C::kBBytes; };
-  auto stage_sfb = [&](int s) { return smem + s * C::kStageBytes + C::kABytes + C::kBBytes + C::kSfaBytes; };
+  auto stage_l = [&](int s) { return smem + s * C::kStageBytes; };
+  auto stage_c = [&](int s) { return smem + s * C::kStageBytes + C::kLBytes; };
+  auto stage_sfl = [&](int s) { return smem + s * C::kStageBytes + C::kLBytes + C::kCBytes; };
+  auto stage_sfc = [&](int s) { return smem + s * C::kStageBytes + C::kLBytes + C::kCBytes + C::kSflBytes; };
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
@@ -141,12 +165,18 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
     uint32_t phase = 0;
     for (int w = blockIdx.x; w < total_work && !*abort_flag; w += gridDim.x) {
       WorkItem item;
-      if (!decode_work<BLOCK_N>(p, w, item)) continue;
-      const CUtensorMap* map_a = item.group.map_a >= 0 ? p.map_a_table + item.group.map_a : &p.map_a;
-      if (item.group.map_a >= 0 && lane == 0) ptx::tensormap_acquire(map_a);
-      const int b_row = item.group.b_row0 + item.b_tile * BLOCK_N;
-      const int sfb_row = item.group.sfb_row0 + item.b_tile * BLOCK_N;
-      const int b_atom_rows = (item.n_valid + 127) / 128;
+      decode_work<BLOCK_N, EPI>(p, w, item);
+      const CUtensorMap* map_l = item.g.map_l >= 0 ? p.map_table + item.g.map_l : &p.map_l;
+      const CUtensorMap* map_c[2];
+      for (int h = 0; h < C::kHalves; ++h) map_c[h] = item.g.map_c[h] >= 0 ? p.map_table + item.g.map_c[h] : &p.map_c;
+      if (lane == 0) {
+        if (item.g.map_l >= 0) ptx::tensormap_acquire(map_l);
+        for (int h = 0; h < C::kHalves; ++h)
+          if (item.g.map_c[h] >= 0) ptx::tensormap_acquire(map_c[h]);
+      }
+      const int l_row = item.g.l_row0 + item.l_tile * kTileL;
+      const int c_local = item.c_tile * p.c_rows_per_tile;   // row inside each matrix of the C operand
+      const int halves = item.halves;
       for (int ks = 0; ks < k_stages; ++ks) {
         if (!ptx::mbar_wait_bounded(empty_bar + stage, phase ^ 1)) {
           report(p.error, 0x10000000u | (blockIdx.x << 8) | stage, abort_flag);
@@ -155,20 +185,23 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
         if (*abort_flag) break;
         if (lane == 0) {
           const int nkb = min(kKBlocksPerStage, total_kb - ks * kKBlocksPerStage);
-          uint32_t bytes = C::kABytes + C::kBBytes;
-          if constexpr (kNvfp4) bytes += nkb * kAtomBytes * (1 + b_atom_rows);
+          uint32_t bytes = C::kLBytes + halves * C::kHalfRows * kStageRowBytes;
+          if constexpr (kNvfp4) bytes += nkb * kAtomBytes * (1 + halves);
           ptx::mbar_expect_tx(full_bar + stage, bytes);
-          ptx::tma_load_2d(stage_a(stage), map_a, ks * kStageRowBytes, item.a_tile * kTileA, full_bar + stage);
-          ptx::tma_load_2d(stage_b(stage), &p.map_b, ks * kStageRowBytes, b_row, full_bar + stage);
+          ptx::tma_load_2d(stage_l(stage), map_l, ks * kStageRowBytes, l_row, full_bar + stage);
+          for (int h = 0; h < halves; ++h)
+            ptx::tma_load_2d(stage_c(stage) + h * C::kHalfRows * kStageRowBytes, map_c[h], ks * kStageRowBytes,
+                             item.g.c_row0 + c_local + h * item.g.c_half_stride, full_bar + stage);
           if constexpr (kNvfp4) {
             const size_t atom0 = size_t(ks) * kKBlocksPerStage;
-            ptx::bulk_load(stage_sfa(stage),
-                           item.group.sf_a + (size_t(item.a_tile) * k_atoms + atom0) * kAtomBytes,
+            ptx::bulk_load(stage_sfl(stage), item.g.sf_l + (size_t(item.l_tile) * k_atoms + atom0) * kAtomBytes,
                            nkb * kAtomBytes, full_bar + stage);
-            for (int j = 0; j < b_atom_rows; ++j)
-              ptx::bulk_load(stage_sfb(stage) + j * kKBlocksPerStage * kAtomBytes,
-                             p.sf_b + (size_t(sfb_row / 128 + j) * k_atoms + atom0) * kAtomBytes,
-                             nkb * kAtomBytes, full_bar + stage);
+            for (int h = 0; h < halves; ++h) {
+              const size_t row_block = size_t(c_local + h * item.g.c_half_stride) / 128;
+              ptx::bulk_load(stage_sfc(stage) + h * kKBlocksPerStage * kAtomBytes,
+                             item.g.sf_c[h] + (row_block * k_atoms + atom0) * kAtomBytes, nkb * kAtomBytes,
+                             full_bar + stage);
+            }
           }
         }
         __syncwarp();
@@ -181,7 +214,7 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
     uint32_t phase = 0, acc_phase = 0;
     for (int w = blockIdx.x; w < total_work && !*abort_flag; w += gridDim.x) {
       WorkItem item;
-      if (!decode_work<BLOCK_N>(p, w, item)) continue;
+      decode_work<BLOCK_N, EPI>(p, w, item);
       if (!ptx::mbar_wait_bounded(acc_empty_bar + acc, acc_phase ^ 1)) {
         report(p.error, 0x20000000u | (blockIdx.x << 8) | acc, abort_flag);
         break;
@@ -189,9 +222,10 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
       ptx::tc_fence_after_sync();
       const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
       const uint32_t idesc = kNvfp4 ? ptx::idesc_nvfp4(item.mma_n) : ptx::idesc_fp8(item.mma_n);
-      const int sfb_row = item.group.sfb_row0 + item.b_tile * BLOCK_N;
-      const uint32_t sfb_sub = BLOCK_N < 128 ? (sfb_row % 128) / 32 : 0;
-      const int b_atom_rows = (item.n_valid + 127) / 128;
+      const int c_local = item.c_tile * p.c_rows_per_tile;
+      // swap form with BLOCK_N < 128: the tile starts part-way into a 128-row scale atom
+      const uint32_t sfc_sub = BLOCK_N < 128 ? (c_local % 128) / 32 : 0;
+      const int halves = item.halves;
       bool failed = false;
       for (int ks = 0; ks < k_stages; ++ks) {
         if (!ptx::mbar_wait_bounded(full_bar + stage, phase)) {
@@ -203,26 +237,25 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
         ptx::tc_fence_after_sync();
         if (lane == 0) {
           const int nkb = min(kKBlocksPerStage, total_kb - ks * kKBlocksPerStage);
-          if constexpr (kNvfp4) {
-            const uint32_t sfa_smem = ptx::smem_u32(stage_sfa(stage));
-            const uint32_t sfb_smem = ptx::smem_u32(stage_sfb(stage));
-            for (int kb = 0; kb < nkb; ++kb) {
-              ptx::tc_copy_sf_atom(tmem_base + C::kSfaCol + 4 * kb, ptx::smem_desc_sf_atom(sfa_smem + kb * kAtomBytes));
-              for (int j = 0; j < b_atom_rows; ++j)
-                ptx::tc_copy_sf_atom(tmem_base + C::kSfbCol + kb * C::kSfbColsPerKb + 4 * j,
-                                     ptx::smem_desc_sf_atom(sfb_smem + (j * kKBlocksPerStage + kb) * kAtomBytes));
-            }
-          }
-          const uint64_t a_desc = ptx::smem_desc_sw128(ptx::smem_u32(stage_a(stage)));
-          const uint64_t b_desc = ptx::smem_desc_sw128(ptx::smem_u32(stage_b(stage)));
+          const uint64_t l_desc = ptx::smem_desc_sw128(ptx::smem_u32(stage_l(stage)));
+          const uint64_t c_desc = ptx::smem_desc_sw128(ptx::smem_u32(stage_c(stage)));
+          const uint32_t sfl_smem = ptx::smem_u32(stage_sfl(stage));
+          const uint32_t sfc_smem = ptx::smem_u32(stage_sfc(stage));
           for (int kb = 0; kb < nkb; ++kb) {
+            if constexpr (kNvfp4) {
+              // scale atoms of this K-block; issued right before their MMA so that they
+              // execute under the previous MMA
+              ptx::tc_copy_sf_atom(tmem_base + C::kSflCol + 4 * kb, ptx::smem_desc_sf_atom(sfl_smem + kb * kAtomBytes));
+              for (int h = 0; h < halves; ++h)
+                ptx::tc_copy_sf_atom(tmem_base + C::kSfcCol + kb * C::kSfcColsPerKb + 4 * h,
+                                     ptx::smem_desc_sf_atom(sfc_smem + (h * kKBlocksPerStage + kb) * kAtomBytes));
+            }
             const uint32_t accumulate = (ks | kb) != 0;
             if constexpr (kNvfp4)
-              ptx::tc_mma_nvfp4(d_tmem, a_desc + 2 * kb, b_desc + 2 * kb, idesc,
-                                tmem_base + C::kSfaCol + 4 * kb,
-                                tmem_base + C::kSfbCol + kb * C::kSfbColsPerKb + sfb_sub, accumulate);
+              ptx::tc_mma_nvfp4(d_tmem, l_desc + 2 * kb, c_desc + 2 * kb, idesc, tmem_base + C::kSflCol + 4 * kb,
+                                tmem_base + C::kSfcCol + kb * C::kSfcColsPerKb + sfc_sub, accumulate);
             else
-              ptx::tc_mma_fp8(d_tmem, a_desc + 2 * kb, b_desc + 2 * kb, idesc, accumulate);
+              ptx::tc_mma_fp8(d_tmem, l_desc + 2 * kb, c_desc + 2 * kb, idesc, accumulate);
           }
           ptx::tc_commit(empty_bar + stage);
         }
@@ -236,34 +269,145 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
     }
   } else {
     // ------------------------------------------------------------------ epilogue
-    const int quad = warp % 4;   // TMEM lanes [32*quad, 32*quad+32) belong to this warp
+    const int quad = warp % 4;            // TMEM lanes [32*quad, 32*quad+32) belong to this warp
+    const int col_half = (warp - 2) / 4;  // which half of the accumulator columns this warp drains
     int acc = 0;
     uint32_t acc_phase = 0;
-    bf16* out = static_cast<bf16*>(p.out);
     for (int w = blockIdx.x; w < total_work && !*abort_flag; w += gridDim.x) {
       WorkItem item;
-      if (!decode_work<BLOCK_N>(p, w, item)) continue;
+      decode_work<BLOCK_N, EPI>(p, w, item);
       if (!ptx::mbar_wait_bounded(acc_full_bar + acc, acc_phase)) {
         report(p.error, 0x40000000u | (blockIdx.x << 8) | acc, abort_flag);
         break;
       }
       ptx::tc_fence_after_sync();
-      const int channel = item.a_tile * kTileA + quad * 32 + lane;
-      const bool channel_ok = channel < item.group.a_rows;
-      float alpha = item.group.alpha;
-      if (item.group.channel_alpha != nullptr && channel_ok) alpha = item.group.channel_alpha[channel];
-      bf16* dst = out + (size_t(item.group.out_row0) + size_t(item.b_tile) * BLOCK_N) * p.ld_out +
-                  item.group.out_col0 + channel;
       const uint32_t taddr = tmem_base + acc * BLOCK_N + (uint32_t(quad * 32) << 16);
-      for (int c0 = 0; c0 < item.mma_n; c0 += 16) {
-        uint32_t r[16];
-        ptx::tmem_load16(taddr + c0, r);
-        ptx::tmem_load_wait();
-        if (channel_ok) {
+      const int l_index = item.l_tile * kTileL + quad * 32 + lane;   // row of L inside the group
+      const bool l_ok = quad * 32 + lane < item.l_valid;
+
+      if constexpr (EPI == GemmEpilogue::swap_store) {
+        // lanes = output channels, columns = tokens: out[token][channel]
+        bf16* out = static_cast<bf16*>(p.out);
+        float alpha = item.g.alpha[0];
+        if (item.g.channel_alpha != nullptr && l_ok) alpha = item.g.channel_alpha[l_index];
+        bf16* dst = out + (size_t(item.g.out_row0) + size_t(item.c_tile) * BLOCK_N) * p.ld_out + item.g.out_col0 + l_index;
+        for (int c0 = col_half * 16; c0 < item.mma_n; c0 += 32) {
+          uint32_t r[16];
+          ptx::tmem_load16(taddr + c0, r);
+          ptx::tmem_load_wait();
+          if (l_ok) {
 #pragma unroll
-          for (int i = 0; i < 16; ++i)
-            if (c0 + i < item.n_valid)
-              dst[size_t(c0 + i) * p.ld_out] = __float2bfloat16_rn(__fmul_rn(__uint_as_float(r[i]), alpha));
+            for (int i = 0; i < 16; ++i)
+              if (c0 + i < item.c_valid)
+                dst[size_t(c0 + i) * p.ld_out] = __float2bfloat16_rn(__fmul_rn(__uint_as_float(r[i]), alpha));
+          }
+        }
+      } else if constexpr (EPI == GemmEpilogue::direct_store) {
+        // lanes = tokens, columns = output channels: out[token][channel], 16-byte stores
+        bf16* out = static_cast<bf16*>(p.out);
+        const int c_base = item.c_tile * p.c_rows_per_tile;           // first channel of the tile
+        const int c_end = item.g.c_rows;                              // valid channels of the matrix
+        bf16* dst = out + (size_t(item.g.out_row0) + l_index) * p.ld_out + item.g.out_col0 + c_base;
+        const float alpha = item.g.alpha[0];
+        constexpr int kColsPerWarp = BLOCK_N / 2;
+        for (int c0 = col_half * kColsPerWarp; c0 < (col_half + 1) * kColsPerWarp; c0 += 32) {
+          if (c_base + c0 >= c_end) break;                            // warp-uniform
+          uint32_t r[32];
+          ptx::tmem_load16(taddr + c0, r);
+          ptx::tmem_load16(taddr + c0 + 16, r + 16);
+          ptx::tmem_load_wait();
+          if (!l_ok) continue;
+          float v[32];
+          if (item.g.channel_alpha != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int c = c_base + c0 + i;
+              v[i] = __fmul_rn(__uint_as_float(r[i]), c < c_end ? item.g.channel_alpha[c] : 0.0F);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __fmul_rn(__uint_as_float(r[i]), alpha);
+          }
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int c = c_base + c0 + 8 * q;
+            if (c + 8 <= c_end) {
+              *reinterpret_cast<uint4*>(dst + c0 + 8 * q) =
+                  make_uint4(pack_bf16x2(v[8 * q], v[8 * q + 1]), pack_bf16x2(v[8 * q + 2], v[8 * q + 3]),
+                             pack_bf16x2(v[8 * q + 4], v[8 * q + 5]), pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
+            } else {
+              for (int i = 0; i < 8; ++i)
+                if (c + i < c_end) dst[c0 + 8 * q + i] = __float2bfloat16_rn(v[8 * q + i]);
+            }
+          }
+        }
+      } else {
+        // GeGLU + FP4 quantise: columns [0,128) = gate channels, [128,256) = up channels of
+        // the same 128 output channels; this warp owns 64 of them (4 K16 blocks).
+        const int channel0 = item.c_tile * 128 + col_half * 64;       // first channel of this warp
+        const int width = p.out_width;
+        if (channel0 < width) {
+          const size_t row = size_t(item.g.out_row0) + l_index;
+          uint32_t packed_words[8];
+          uint32_t scale_word = 0;
+          const float inverse_scale = item.g.quant_inverse_scale;
+          bf16* cap_gu = static_cast<bf16*>(p.capture_gate_up);
+          bf16* cap_act = static_cast<bf16*>(p.capture_activated);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint32_t g[16], u[16];
+            ptx::tmem_load16(taddr + col_half * 64 + 16 * j, g);
+            ptx::tmem_load16(taddr + 128 + col_half * 64 + 16 * j, u);
+            ptx::tmem_load_wait();
+            float act[16];
+            uint32_t gw[8], uw[8], aw[8];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float gate = __bfloat162float(__float2bfloat16_rn(__fmul_rn(__uint_as_float(g[i]), item.g.alpha[0])));
+              const float up = __bfloat162float(__float2bfloat16_rn(__fmul_rn(__uint_as_float(u[i]), item.g.alpha[1])));
+              act[i] = gelu_tanh_multiply_bf16(gate, up);
+              g[i] = __float_as_uint(gate);
+              u[i] = __float_as_uint(up);
+            }
+            float amax = 0.0F;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(act[i]));
+            const uint8_t code = float_to_e4m3(inverse_scale * (amax * rcp_approx_ftz(6.0F)));
+            const float block_scale = e4m3_to_float(code);
+            const float factor =
+                block_scale == 0.0F ? 0.0F : rcp_approx_ftz(block_scale * rcp_approx_ftz(inverse_scale));
+            scale_word |= uint32_t(code) << (8 * j);
+            uint32_t lo = 0, hi = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              lo |= uint32_t(float2_to_e2m1x2(act[2 * i] * factor, act[2 * i + 1] * factor)) << (8 * i);
+              hi |= uint32_t(float2_to_e2m1x2(act[8 + 2 * i] * factor, act[8 + 2 * i + 1] * factor)) << (8 * i);
+            }
+            packed_words[2 * j] = lo;
+            packed_words[2 * j + 1] = hi;
+            if (cap_gu != nullptr && l_ok) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                gw[i] = (g[2 * i] >> 16) | (g[2 * i + 1] & 0xFFFF0000u);
+                uw[i] = (u[2 * i] >> 16) | (u[2 * i + 1] & 0xFFFF0000u);
+                aw[i] = (__float_as_uint(act[2 * i]) >> 16) | (__float_as_uint(act[2 * i + 1]) & 0xFFFF0000u);
+              }
+              uint4* gdst = reinterpret_cast<uint4*>(cap_gu + row * (2 * size_t(width)) + channel0 + 16 * j);
+              uint4* udst = reinterpret_cast<uint4*>(cap_gu + row * (2 * size_t(width)) + width + channel0 + 16 * j);
+              uint4* adst = reinterpret_cast<uint4*>(cap_act + row * size_t(width) + channel0 + 16 * j);
+              gdst[0] = make_uint4(gw[0], gw[1], gw[2], gw[3]); gdst[1] = make_uint4(gw[4], gw[5], gw[6], gw[7]);
+              udst[0] = make_uint4(uw[0], uw[1], uw[2], uw[3]); udst[1] = make_uint4(uw[4], uw[5], uw[6], uw[7]);
+              adst[0] = make_uint4(aw[0], aw[1], aw[2], aw[3]); adst[1] = make_uint4(aw[4], aw[5], aw[6], aw[7]);
+            }
+          }
+          if (l_ok) {
+            uint8_t* packed_out = static_cast<uint8_t*>(p.out) + row * size_t(p.ld_out) + channel0 / 2;
+            uint4* dst = reinterpret_cast<uint4*>(packed_out);
+            dst[0] = make_uint4(packed_words[0], packed_words[1], packed_words[2], packed_words[3]);
+            dst[1] = make_uint4(packed_words[4], packed_words[5], packed_words[6], packed_words[7]);
+            const size_t region = size_t(item.g.sf_out_row0) * (width / 16);
+            *reinterpret_cast<uint32_t*>(p.out_scales + region + scale_offset(l_index, channel0 / 16, width)) = scale_word;
+          }
         }
       }
       ptx::tc_fence_before_sync();
@@ -281,42 +425,47 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
   }
 }
 
-template <bool kNvfp4, int BLOCK_N>
+template <bool kNvfp4, int BLOCK_N, GemmEpilogue EPI>
 cudaError_t launch(const GemmParams& params, int grid, cudaStream_t stream) {
   using C = Config<kNvfp4, BLOCK_N>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t status = cudaFuncSetAttribute(gemm_tc_kernel<kNvfp4, BLOCK_N>,
+    cudaError_t status = cudaFuncSetAttribute(gemm_tc_kernel<kNvfp4, BLOCK_N, EPI>,
                                               cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
     if (status != cudaSuccess) return status;
     configured = true;
   }
-  gemm_tc_kernel<kNvfp4, BLOCK_N><<<grid, kThreads, C::kSmemBytes, stream>>>(params);
+  gemm_tc_kernel<kNvfp4, BLOCK_N, EPI><<<grid, kThreads, C::kSmemBytes, stream>>>(params);
   return cudaGetLastError();
 }
 
 }  // namespace
 
-cudaError_t launch_gemm_tc(GemmKind kind, int block_n, const GemmParams& params, int grid, cudaStream_t stream) {
+cudaError_t launch_gemm_tc(GemmKind kind, GemmEpilogue epilogue, int block_n, const GemmParams& params, int grid,
+                           cudaStream_t stream) {
   const bool fp4 = kind == GemmKind::nvfp4;
-  switch (block_n) {
-    case 32: return fp4 ? launch<true, 32>(params, grid, stream) : launch<false, 32>(params, grid, stream);
-    case 64: return fp4 ? launch<true, 64>(params, grid, stream) : launch<false, 64>(params, grid, stream);
-    case 128: return fp4 ? launch<true, 128>(params, grid, stream) : launch<false, 128>(params, grid, stream);
-    case 256: return fp4 ? launch<true, 256>(params, grid, stream) : launch<false, 256>(params, grid, stream);
-    default: return cudaErrorInvalidValue;
+  if (epilogue == GemmEpilogue::swap_store) {
+    switch (block_n) {
+      case 32: return fp4 ? launch<true, 32, GemmEpilogue::swap_store>(params, grid, stream)
+                          : launch<false, 32, GemmEpilogue::swap_store>(params, grid, stream);
+      case 64: return fp4 ? launch<true, 64, GemmEpilogue::swap_store>(params, grid, stream)
+                          : launch<false, 64, GemmEpilogue::swap_store>(params, grid, stream);
+      case 128: return fp4 ? launch<true, 128, GemmEpilogue::swap_store>(params, grid, stream)
+                           : launch<false, 128, GemmEpilogue::swap_store>(params, grid, stream);
+      default: return cudaErrorInvalidValue;
+    }
   }
-}
-
-size_t gemm_tc_smem_bytes(GemmKind kind, int block_n) {
-  const bool fp4 = kind == GemmKind::nvfp4;
-  switch (block_n) {
-    case 32: return fp4 ? Config<true, 32>::kSmemBytes : Config<false, 32>::kSmemBytes;
-    case 64: return fp4 ? Config<true, 64>::kSmemBytes : Config<false, 64>::kSmemBytes;
-    case 128: return fp4 ? Config<true, 128>::kSmemBytes : Config<false, 128>::kSmemBytes;
-    case 256: return fp4 ? Config<true, 256>::kSmemBytes : Config<false, 256>::kSmemBytes;
-    default: return 0;
+  if (epilogue == GemmEpilogue::direct_store) {
+    switch (block_n) {
+      case 128: return fp4 ? launch<true, 128, GemmEpilogue::direct_store>(params, grid, stream)
+                           : launch<false, 128, GemmEpilogue::direct_store>(params, grid, stream);
+      case 256: return fp4 ? launch<true, 256, GemmEpilogue::direct_store>(params, grid, stream)
+                           : launch<false, 256, GemmEpilogue::direct_store>(params, grid, stream);
+      default: return cudaErrorInvalidValue;
+    }
   }
+  if (fp4 && block_n == 256) return launch<true, 256, GemmEpilogue::geglu_quant>(params, grid, stream);
+  return cudaErrorInvalidValue;
 }
 
 }  // namespace gw

@@ -1,14 +1,18 @@
 // Host-visible description of one launch of the tcgen05 GEMM kernel.
 //
-// The kernel computes, for every group g,
-//     D_g[a_row, b_row] = sum_k A_g[a_row, k] * B[b_row0_g + b_row, k]
-// with A on the 128-lane side of the tensor core (TMEM lanes = rows of A) and
-// B on the column side (TMEM columns = rows of B), and writes
-//     out[(out_row0_g + b_row) * ld_out + out_col0_g + a_row] = bf16(D * alpha).
-// Used with A = weights [N_out, K] and B = activations [tokens, K] this is the
-// "swap-AB" form Y = X W^T: the token count only has to be a multiple of 16
-// per tile (ragged expert groups and 1..64-row decode batches cost no padding
-// to 128) while weight rows stream through the 128-lane operand.
+// The tensor core sees two K-major operands:
+//   L  the "lane" operand: 128 rows per tile, one row per TMEM lane
+//   C  the "column" operand: BLOCK_N rows per tile, one row per TMEM column
+//      (loaded as 1 or 2 boxes of <=128 rows, which may come from two
+//      different matrices: the gate and up weights of an expert)
+// and accumulates D[l, c] = sum_k L[l, k] * C[c, k] in TMEM.  Which of weights /
+// activations plays which role is the caller's choice:
+//   * "swap" form (decode, small batches): L = weights, C = tokens.  The token
+//     tile only needs a multiple of 16 valid rows, so 1..64-row batches and
+//     ragged expert groups cost no padding to 128.
+//   * "direct" form (prefill): L = tokens, C = weights.  Every epilogue thread
+//     owns one token row and sees consecutive output channels, so stores are
+//     16-byte vectors and GeGLU + FP4 quantisation fuse into the epilogue.
 #pragma once
 
 #include <cuda.h>
@@ -19,43 +23,55 @@
 namespace gw {
 
 struct GemmGroup {
-  const uint8_t* sf_a;         // tiled E4M3 scales of this group's A matrix (NVFP4 only)
-  const float* channel_alpha;  // optional multiplier per A row (FP8 joined projections)
-  float alpha;                 // scalar multiplier (used when channel_alpha == nullptr)
-  int32_t map_a;               // index into GemmParams::map_a_table, or -1 for GemmParams::map_a
-  int32_t a_tiles;             // number of 128-row tiles of A
-  int32_t a_rows;              // valid rows of A (output channels)
-  int32_t b_row0;              // first row of the group inside the B tensor map
-  int32_t b_rows;              // valid rows of B (tokens) in the group
-  int32_t sfb_row0;            // first row of the group's region in B's scale storage (multiple of 128)
-  int32_t out_row0;            // first output row of the group
-  int32_t out_col0;            // first output column of the group
-  int32_t work_begin;          // index of the group's first work item (prefix sum)
-  int32_t pad_;
+  // lane operand
+  const uint8_t* sf_l;        // tiled E4M3 scales of L (NVFP4), row 0 = the group's first 128-row block
+  int32_t map_l;              // index into GemmParams::map_table, or -1 for GemmParams::map_l
+  int32_t l_row0;             // first row of the group inside the L tensor map
+  int32_t l_rows;             // valid rows (lanes beyond are masked in the epilogue)
+  int32_t l_tiles;            // number of 128-row tiles
+  // column operand: `halves` boxes of (BLOCK_N / halves) rows each
+  const uint8_t* sf_c[2];     // tiled scales of each half's matrix, row 0 = the group's first 128-row block
+  int32_t map_c[2];           // tensor maps of the halves (-1 = GemmParams::map_c)
+  int32_t c_row0;             // first row of the group inside the C tensor map(s)
+  int32_t c_rows;             // valid rows per matrix (columns beyond are masked)
+  int32_t c_tiles;            // number of column tiles
+  int32_t c_half_stride;      // row offset of half 1 relative to half 0 inside one matrix (0: separate matrices)
+  int32_t sf_c_sub;           // swap form, BLOCK_N < 128: the group's first C row modulo 128 (multiple of 32)
+  // epilogue
+  float alpha[2];             // multiplier of the accumulator (per half)
+  const float* channel_alpha; // optional per-output-channel multipliers (FP8 joined projections)
+  float quant_inverse_scale;  // GeGLU+quantise epilogue: 1 / input_scale of the consumer
+  int32_t out_row0;           // first output row
+  int32_t out_col0;           // first output column
+  int32_t sf_out_row0;        // GeGLU+quantise epilogue: first row of the group's output scale region
+  int32_t work_begin;         // index of the group's first work item (prefix sum)
 };
 
 struct GemmParams {
-  CUtensorMap map_a;               // A operand when the group says map_a == -1
-  CUtensorMap map_b;               // B operand (box height = BLOCK_N rows)
-  const CUtensorMap* map_a_table;  // per-group A operands in global memory (host written)
-  const GemmGroup* groups;         // num_groups + 1 entries in global memory, or nullptr
-  GemmGroup single;                // the only group when groups == nullptr
+  CUtensorMap map_l;              // used when a group says map_l == -1
+  CUtensorMap map_c;              // used when a group says map_c[h] == -1
+  const CUtensorMap* map_table;   // per-group operands in global memory (host written)
+  const GemmGroup* groups;        // num_groups + 1 entries in global memory, or nullptr
+  GemmGroup single;               // the only group when groups == nullptr
   int32_t num_groups;
-  int32_t total_work;              // work items when groups == nullptr
-  const uint8_t* sf_b;             // tiled E4M3 scales of B (NVFP4 only)
-  int32_t k;                       // reduction length in elements
-  void* out;                       // BF16
-  int64_t ld_out;                  // elements between output rows
-  uint32_t* error;                 // device error word (0 = fine)
+  int32_t total_work;             // work items when groups == nullptr
+  int32_t k;                      // reduction length in elements
+  int32_t c_rows_per_tile;        // rows of one matrix covered by one column tile
+  void* out;                      // BF16 output (swap/direct), packed E2M1 output (GeGLU+quantise)
+  int64_t ld_out;                 // elements (bytes for the packed output) between output rows
+  uint8_t* out_scales;            // GeGLU+quantise: tiled scale storage of the output
+  int32_t out_width;              // GeGLU+quantise: logical width (K of the consumer)
+  void* capture_gate_up;          // GeGLU+quantise: optional BF16 [rows, 2*out_width]
+  void* capture_activated;        // GeGLU+quantise: optional BF16 [rows, out_width]
+  uint32_t* error;                // device error word (0 = fine)
 };
 
 enum class GemmKind { nvfp4, fp8 };
+enum class GemmEpilogue { swap_store, direct_store, geglu_quant };
 
-// block_n in {32, 64, 128, 256}.  Returns cudaErrorInvalidValue for others.
-cudaError_t launch_gemm_tc(GemmKind kind, int block_n, const GemmParams& params, int grid,
+// swap_store: block_n in {32, 64, 128}; direct_store: {128, 256}; geglu_quant: 256 (NVFP4).
+cudaError_t launch_gemm_tc(GemmKind kind, GemmEpilogue epilogue, int block_n, const GemmParams& params, int grid,
                            cudaStream_t stream);
-// Dynamic shared memory the launch will request (for occupancy reasoning/tests).
-size_t gemm_tc_smem_bytes(GemmKind kind, int block_n);
 
 // Host helper: 2-D byte tensor map {inner = row_bytes, outer = rows} with a
 // 128-byte x box_rows box and the 128-byte swizzle.

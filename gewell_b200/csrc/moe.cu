@@ -49,6 +49,7 @@ struct gw_moe_workspace {
   int32_t *offsets = nullptr, *chunk_counts = nullptr, *local_offsets = nullptr;
   float* weights = nullptr;
   bool timing = false;
+  bool capture = false;   // materialise the BF16 gate/up and activated intermediates on the fused path too
   cudaEvent_t events[7] = {};
   ~gw_moe_workspace() { for (auto& e : events) if (e) cudaEventDestroy(e); }
   void mark(int i, cudaStream_t s) const { if (timing) cudaEventRecord(events[i], s); }
@@ -168,59 +169,102 @@ gw_status gw_moe_dispatch(gw_moe_workspace* w, const void* scores_bf16, const vo
 
 namespace {
 
+int env_int(const char* name, int fallback) {
+  const char* value = std::getenv(name);
+  return value ? std::atoi(value) : fallback;
+}
+
 // Expert MLP over rows sorted by expert: quantise -> gate/up GEMM -> GeGLU +
 // quantise -> down GEMM.  `gather_index` != nullptr reads input rows through
 // the permutation (token = index / 8); otherwise input row i is sorted row i.
+//
+// Three plans (see moe_prepare_groups_kernel): small batches put the weights on
+// the 128-lane operand and an expert's few tokens on the column operand; large
+// batches put tokens on the lanes, and when gate and up share their input scale
+// the first GEMM's epilogue applies GeGLU and quantises the down input itself.
 gw_status run_experts(gw_moe_workspace* w, const void* input, const int32_t* gather_index, const int32_t* offsets,
                       uint32_t n, const gw_expert_table* table, void* down_out, cudaStream_t s) {
   const auto* info = table->info.as<MoeExpertInfo>();
-  auto* gate_up_groups = w->groups.as<GemmGroup>();
-  auto* down_groups = gate_up_groups + 2 * kExperts + 1;
-  // Token-side tile: small batches leave most experts with a handful of rows.
-  int block_n = n <= 8 * 64 ? 32 : (n <= 8 * 1024 ? 128 : 256);
-  if (const char* forced = std::getenv("GW_MOE_BLOCK_N")) {   // tuning override
-    const int v = std::atoi(forced);
-    if (v == 32 || v == 64 || v == 128 || v == 256) block_n = v;
+  auto* first_groups = w->groups.as<GemmGroup>();
+  auto* down_groups = first_groups + 2 * kExperts + 1;
+  int form = n <= 8 * 512 ? kMoeFormSwap : (table->shared_gate_up ? kMoeFormFused : kMoeFormDirect);
+  if (const char* forced = std::getenv("GW_MOE_FORM")) {   // tuning override: swap / direct / fused
+    if (forced[0] == 's') form = kMoeFormSwap;
+    if (forced[0] == 'd') form = kMoeFormDirect;
+    if (forced[0] == 'f' && table->shared_gate_up) form = kMoeFormFused;
+  }
+  int block_n_first, block_n_down;
+  if (form == kMoeFormSwap) {
+    block_n_first = n <= 8 * 64 ? 32 : (n <= 8 * 256 ? 64 : 128);
+    block_n_first = block_n_down = env_int("GW_MOE_BLOCK_N", block_n_first);
+    if (block_n_first != 32 && block_n_first != 64 && block_n_first != 128) block_n_first = block_n_down = 128;
+  } else {
+    block_n_first = form == kMoeFormFused ? 256 : env_int("GW_MOE_BLOCK_N", 128);
+    block_n_down = env_int("GW_MOE_BLOCK_N_DOWN", 128);
+    if (block_n_first != 128 && block_n_first != 256) block_n_first = 128;
+    if (block_n_down != 128 && block_n_down != 256) block_n_down = 128;
   }
   const int parts = table->shared_gate_up ? 1 : 2;
+  MoeGroupPlan plan{offsets, info, w->scales_in.as<uint8_t>(), w->scales_act.as<uint8_t>(), n, w->scale_rows, form,
+                    block_n_first, block_n_down, table->shared_gate_up ? 1 : 0};
   w->mark(1, s);
-  GW_CUDA_CHECK(launch_moe_prepare_groups(offsets, info, n, w->scale_rows, block_n, table->shared_gate_up,
-                                          gate_up_groups, down_groups, s),
-                "MoE group descriptors");
+  GW_CUDA_CHECK(launch_moe_prepare_groups(plan, first_groups, down_groups, s), "MoE group descriptors");
   GW_CUDA_CHECK(launch_moe_quantize_input(input, gather_index, w->sorted_keys, offsets, info, n, w->scale_rows, parts,
                                           w->packed_in.as<uint8_t>(), w->scales_in.as<uint8_t>(), s),
                 "MoE gather + quantise");
   std::string error;
-  GemmParams params{};
-  if (!encode_tensor_map_2d(&params.map_b, w->packed_in.data, kHidden / 2, size_t(parts) * n, block_n, &error))
+  const bool swap = form == kMoeFormSwap;
+  GemmParams first{};
+  CUtensorMap token_map;
+  if (!encode_tensor_map_2d(&token_map, w->packed_in.data, kHidden / 2, size_t(parts) * n, swap ? block_n_first : 128,
+                            &error))
     return fail(GW_CUDA_ERROR, "MoE activation descriptor: " + error);
-  params.map_a_table = table->maps.as<CUtensorMap>();
-  params.groups = gate_up_groups;
-  params.num_groups = 2 * kExperts;
-  params.sf_b = w->scales_in.as<uint8_t>();
-  params.k = kHidden;
-  params.out = w->gate_up.data;
-  params.ld_out = 2 * kInter;
-  params.error = device_error_word();
+  (swap ? first.map_c : first.map_l) = token_map;
+  first.map_table = table->maps.as<CUtensorMap>();
+  first.groups = first_groups;
+  first.num_groups = form == kMoeFormFused ? kExperts : 2 * kExperts;
+  first.k = kHidden;
+  first.c_rows_per_tile = form == kMoeFormFused ? 128 : block_n_first;
+  first.error = device_error_word();
   w->mark(2, s);
-  GW_CUDA_CHECK(launch_gemm_tc(GemmKind::nvfp4, block_n, params, sm_count(), s), "MoE grouped gate/up GEMM");
-  w->mark(3, s);
-  GW_CUDA_CHECK(launch_moe_activate_quantize(w->gate_up.data, w->sorted_keys, offsets, info, n, w->scale_rows,
-                                             w->packed_act.as<uint8_t>(), w->scales_act.as<uint8_t>(), w->activated.data, s),
-                "MoE GeGLU + quantise");
+  if (form == kMoeFormFused) {
+    first.out = w->packed_act.data;
+    first.ld_out = kInter / 2;
+    first.out_scales = w->scales_act.as<uint8_t>();
+    first.out_width = kInter;
+    first.capture_gate_up = w->capture ? w->gate_up.data : nullptr;
+    first.capture_activated = w->capture ? w->activated.data : nullptr;
+    GW_CUDA_CHECK(launch_gemm_tc(GemmKind::nvfp4, GemmEpilogue::geglu_quant, 256, first, sm_count(), s),
+                  "MoE grouped gate/up GEMM with fused GeGLU + quantise");
+    w->mark(3, s);
+  } else {
+    first.out = w->gate_up.data;
+    first.ld_out = 2 * kInter;
+    GW_CUDA_CHECK(launch_gemm_tc(GemmKind::nvfp4, swap ? GemmEpilogue::swap_store : GemmEpilogue::direct_store,
+                                 block_n_first, first, sm_count(), s),
+                  "MoE grouped gate/up GEMM");
+    w->mark(3, s);
+    GW_CUDA_CHECK(launch_moe_activate_quantize(w->gate_up.data, w->sorted_keys, offsets, info, n, w->scale_rows,
+                                               w->packed_act.as<uint8_t>(), w->scales_act.as<uint8_t>(),
+                                               w->activated.data, s),
+                  "MoE GeGLU + quantise");
+  }
   GemmParams down{};
-  if (!encode_tensor_map_2d(&down.map_b, w->packed_act.data, kInter / 2, n, block_n, &error))
+  if (!encode_tensor_map_2d(&token_map, w->packed_act.data, kInter / 2, n, swap ? block_n_down : 128, &error))
     return fail(GW_CUDA_ERROR, "MoE activation descriptor: " + error);
-  down.map_a_table = table->maps.as<CUtensorMap>();
+  (swap ? down.map_c : down.map_l) = token_map;
+  down.map_table = table->maps.as<CUtensorMap>();
   down.groups = down_groups;
   down.num_groups = kExperts;
-  down.sf_b = w->scales_act.as<uint8_t>();
   down.k = kInter;
+  down.c_rows_per_tile = block_n_down;
   down.out = down_out;
   down.ld_out = kHidden;
   down.error = device_error_word();
   w->mark(4, s);
-  GW_CUDA_CHECK(launch_gemm_tc(GemmKind::nvfp4, block_n, down, sm_count(), s), "MoE grouped down GEMM");
+  GW_CUDA_CHECK(launch_gemm_tc(GemmKind::nvfp4, swap ? GemmEpilogue::swap_store : GemmEpilogue::direct_store,
+                               block_n_down, down, sm_count(), s),
+                "MoE grouped down GEMM");
   w->mark(5, s);
   return GW_OK;
 }
@@ -249,6 +293,13 @@ gw_status gw_moe_run(gw_moe_workspace* w, const void* input_bf16, const void* sc
   if (status != GW_OK) return status;
   GW_CUDA_CHECK(launch_moe_combine(w->down.data, w->inverse, w->weights, rows, kHidden, output_bf16, s), "MoE combine");
   w->mark(6, s);
+  return GW_OK;
+}
+
+gw_status gw_moe_capture(gw_moe_workspace* w, int enable) {
+  clear_error();
+  if (!w) return fail(GW_INVALID_ARGUMENT, "capture switch requires a workspace");
+  w->capture = enable != 0;
   return GW_OK;
 }
 

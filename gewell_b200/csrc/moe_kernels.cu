@@ -194,69 +194,143 @@ moe_keys_from_offsets_kernel(const int32_t* __restrict__ offsets, uint32_t first
 }
 
 // ---------------------------------------------------------------------------
-// 4. group descriptors of the two grouped GEMMs, from the offsets (the role of
-//    grouped_nvfp4::prepare, moe_nvfp4.cuh:51-78).
+// 4. group descriptors of the grouped GEMMs, from the offsets (the role of
+//    grouped_nvfp4::prepare, moe_nvfp4.cuh:51-78).  Three plans:
+//      swap    weights on the lane operand, an expert's tokens on the column operand
+//              (small batches): 256 gate/up groups + 128 down groups
+//      direct  tokens on the lane operand, weights on the column operand, plain BF16
+//              output: 256 gate/up groups + 128 down groups
+//      fused   direct form with gate and up as the two halves of the column operand
+//              and GeGLU + FP4 quantisation in the epilogue: 128 groups (+128 down)
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
-moe_prepare_groups_kernel(const int32_t* __restrict__ offsets, const MoeExpertInfo* __restrict__ experts,
-                          uint32_t n, uint32_t scale_rows, int block_n, int shared_gate_up,
-                          GemmGroup* __restrict__ gate_up_groups, GemmGroup* __restrict__ down_groups) {
-  __shared__ int32_t items_gu[2 * kExperts], items_dn[kExperts];
+moe_prepare_groups_kernel(MoeGroupPlan plan, GemmGroup* __restrict__ first_groups, GemmGroup* __restrict__ down_groups) {
+  __shared__ int32_t items_first[2 * kExperts], items_down[kExperts];
   const unsigned g = threadIdx.x;            // 0..255: expert = g/2, part = g%2
   const unsigned e = g / 2, part = g % 2;
-  const int32_t first = offsets[e], count = offsets[e + 1] - first;
-  const int32_t b_tiles = (count + block_n - 1) / block_n;
+  const int32_t first = plan.offsets[e], count = plan.offsets[e + 1] - first;
+  const int32_t token_tiles_swap = (count + plan.block_n_first - 1) / plan.block_n_first;
+  const int32_t token_tiles_direct = (count + 127) / 128;
   const int32_t padded_first = (first / 128 + int32_t(e)) * 128;
-  const MoeExpertInfo info = experts[e];
+  const MoeExpertInfo info = plan.experts[e];
+  const int src_part = plan.shared_gate_up ? 0 : int(part);
+  const uint8_t* in_scales = plan.scales_in + (size_t(src_part) * plan.scale_rows + padded_first) * (kHidden / 16);
+  const uint8_t* act_scales = plan.scales_act + size_t(padded_first) * (kInter / 16);
   {
     GemmGroup grp{};
-    const int proj = part;                   // 0 gate, 1 up
-    const int src_part = shared_gate_up ? 0 : int(part);
-    grp.sf_a = info.scales[proj];
-    grp.channel_alpha = nullptr;
-    grp.alpha = info.alpha[proj];
-    grp.map_a = int32_t(e) * 3 + proj;
-    grp.a_tiles = (kInter + 127) / 128;
-    grp.a_rows = kInter;
-    grp.b_row0 = src_part * int32_t(n) + first;
-    grp.b_rows = count;
-    grp.sfb_row0 = src_part * int32_t(scale_rows) + padded_first;
-    grp.out_row0 = first;
-    grp.out_col0 = proj * kInter;
-    items_gu[g] = grp.a_tiles * b_tiles;
-    gate_up_groups[g] = grp;
+    if (plan.form == kMoeFormFused) {
+      // one group per expert (threads with part == 1 write nothing)
+      grp.sf_l = in_scales;
+      grp.map_l = -1;
+      grp.l_row0 = first;
+      grp.l_rows = count;
+      grp.l_tiles = token_tiles_direct;
+      grp.sf_c[0] = info.scales[0];
+      grp.sf_c[1] = info.scales[1];
+      grp.map_c[0] = int32_t(e) * 3;
+      grp.map_c[1] = int32_t(e) * 3 + 1;
+      grp.c_row0 = 0;
+      grp.c_rows = kInter;
+      grp.c_tiles = (kInter + 127) / 128;
+      grp.c_half_stride = 0;
+      grp.alpha[0] = info.alpha[0];
+      grp.alpha[1] = info.alpha[1];
+      grp.quant_inverse_scale = info.inverse_input_scale[2];
+      grp.out_row0 = first;
+      grp.out_col0 = 0;
+      grp.sf_out_row0 = padded_first;
+      items_first[g] = part == 0 ? grp.l_tiles * grp.c_tiles : 0;
+      if (part == 0) first_groups[e] = grp;
+    } else if (plan.form == kMoeFormDirect) {
+      const int proj = part;
+      grp.sf_l = in_scales;
+      grp.map_l = -1;
+      grp.l_row0 = src_part * int32_t(plan.n) + first;
+      grp.l_rows = count;
+      grp.l_tiles = token_tiles_direct;
+      grp.sf_c[0] = grp.sf_c[1] = info.scales[proj];
+      grp.map_c[0] = grp.map_c[1] = int32_t(e) * 3 + proj;
+      grp.c_row0 = 0;
+      grp.c_rows = kInter;
+      grp.c_tiles = (kInter + plan.block_n_first - 1) / plan.block_n_first;
+      grp.c_half_stride = plan.block_n_first > 128 ? 128 : 0;
+      grp.alpha[0] = grp.alpha[1] = info.alpha[proj];
+      grp.out_row0 = first;
+      grp.out_col0 = proj * kInter;
+      items_first[g] = grp.l_tiles * grp.c_tiles;
+      first_groups[g] = grp;
+    } else {
+      const int proj = part;
+      grp.sf_l = info.scales[proj];
+      grp.map_l = int32_t(e) * 3 + proj;
+      grp.l_row0 = 0;
+      grp.l_rows = kInter;
+      grp.l_tiles = (kInter + 127) / 128;
+      grp.sf_c[0] = grp.sf_c[1] = in_scales;
+      grp.map_c[0] = grp.map_c[1] = -1;
+      grp.c_row0 = src_part * int32_t(plan.n) + first;
+      grp.c_rows = count;
+      grp.c_tiles = token_tiles_swap;
+      grp.c_half_stride = 0;
+      grp.alpha[0] = grp.alpha[1] = info.alpha[proj];
+      grp.out_row0 = first;
+      grp.out_col0 = proj * kInter;
+      items_first[g] = grp.l_tiles * grp.c_tiles;
+      first_groups[g] = grp;
+    }
   }
   if (part == 0) {
     GemmGroup grp{};
-    grp.sf_a = info.scales[2];
-    grp.channel_alpha = nullptr;
-    grp.alpha = info.alpha[2];
-    grp.map_a = int32_t(e) * 3 + 2;
-    grp.a_tiles = kHidden / 128;
-    grp.a_rows = kHidden;
-    grp.b_row0 = first;
-    grp.b_rows = count;
-    grp.sfb_row0 = padded_first;
+    if (plan.form == kMoeFormSwap) {
+      grp.sf_l = info.scales[2];
+      grp.map_l = int32_t(e) * 3 + 2;
+      grp.l_row0 = 0;
+      grp.l_rows = kHidden;
+      grp.l_tiles = kHidden / 128;
+      grp.sf_c[0] = grp.sf_c[1] = act_scales;
+      grp.map_c[0] = grp.map_c[1] = -1;
+      grp.c_row0 = first;
+      grp.c_rows = count;
+      grp.c_tiles = (count + plan.block_n_down - 1) / plan.block_n_down;
+      grp.c_half_stride = 0;
+    } else {
+      grp.sf_l = act_scales;
+      grp.map_l = -1;
+      grp.l_row0 = first;
+      grp.l_rows = count;
+      grp.l_tiles = token_tiles_direct;
+      grp.sf_c[0] = grp.sf_c[1] = info.scales[2];
+      grp.map_c[0] = grp.map_c[1] = int32_t(e) * 3 + 2;
+      grp.c_row0 = 0;
+      grp.c_rows = kHidden;
+      grp.c_tiles = kHidden / plan.block_n_down;
+      grp.c_half_stride = plan.block_n_down > 128 ? 128 : 0;
+    }
+    grp.alpha[0] = grp.alpha[1] = info.alpha[2];
     grp.out_row0 = first;
     grp.out_col0 = 0;
-    items_dn[e] = grp.a_tiles * b_tiles;
+    items_down[e] = grp.l_tiles * grp.c_tiles;
     down_groups[e] = grp;
   }
   __syncthreads();
   if (g == 0) {
+    const int count_first = plan.form == kMoeFormFused ? kExperts : 2 * kExperts;
     int32_t acc = 0;
-    for (int i = 0; i < 2 * kExperts; ++i) { gate_up_groups[i].work_begin = acc; acc += items_gu[i]; }
+    for (int i = 0; i < count_first; ++i) {
+      first_groups[i].work_begin = acc;
+      acc += plan.form == kMoeFormFused ? items_first[2 * i] : items_first[i];
+    }
     GemmGroup sentinel{};
     sentinel.work_begin = acc;
-    sentinel.a_tiles = 1;
-    gate_up_groups[2 * kExperts] = sentinel;
+    sentinel.l_tiles = sentinel.c_tiles = 1;
+    first_groups[count_first] = sentinel;
   }
   if (g == 1) {
     int32_t acc = 0;
-    for (int i = 0; i < kExperts; ++i) { down_groups[i].work_begin = acc; acc += items_dn[i]; }
+    for (int i = 0; i < kExperts; ++i) { down_groups[i].work_begin = acc; acc += items_down[i]; }
     GemmGroup sentinel{};
     sentinel.work_begin = acc;
-    sentinel.a_tiles = 1;
+    sentinel.l_tiles = sentinel.c_tiles = 1;
     down_groups[kExperts] = sentinel;
   }
 }
@@ -394,11 +468,9 @@ cudaError_t launch_moe_keys_from_offsets(const int32_t* offsets, uint32_t first_
   return cudaGetLastError();
 }
 
-cudaError_t launch_moe_prepare_groups(const int32_t* offsets, const MoeExpertInfo* experts, uint32_t n,
-                                      uint32_t scale_rows, int block_n, bool shared_gate_up, GemmGroup* gate_up_groups,
-                                      GemmGroup* down_groups, cudaStream_t stream) {
-  moe_prepare_groups_kernel<<<1, 256, 0, stream>>>(offsets, experts, n, scale_rows, block_n, shared_gate_up ? 1 : 0,
-                                                   gate_up_groups, down_groups);
+cudaError_t launch_moe_prepare_groups(const MoeGroupPlan& plan, GemmGroup* first_groups, GemmGroup* down_groups,
+                                      cudaStream_t stream) {
+  moe_prepare_groups_kernel<<<1, 256, 0, stream>>>(plan, first_groups, down_groups);
   return cudaGetLastError();
 }
 

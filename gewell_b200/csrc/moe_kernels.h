@@ -18,6 +18,22 @@ struct MoeExpertInfo {
   int32_t pad_;
 };
 
+enum { kMoeFormSwap = 0, kMoeFormDirect = 1, kMoeFormFused = 2 };
+
+// Everything the group-descriptor kernel needs (all pointers on the device).
+struct MoeGroupPlan {
+  const int32_t* offsets;          // [129]
+  const MoeExpertInfo* experts;    // [128]
+  const uint8_t* scales_in;        // scale storage of the packed gate/up input
+  const uint8_t* scales_act;       // scale storage of the packed down input
+  uint32_t n;                      // sorted rows (8 * tokens)
+  uint32_t scale_rows;             // rows of one part of the scale storage
+  int form;                        // kMoeForm*
+  int block_n_first;               // column tile of the gate/up GEMM
+  int block_n_down;                // column tile of the down GEMM
+  int shared_gate_up;              // gate and up read one quantised copy of the input
+};
+
 uint32_t moe_chunks(uint32_t rows);
 
 cudaError_t launch_moe_dispatch(const void* scores, const void* expert_scales, uint32_t rows, int32_t* keys,
@@ -27,9 +43,8 @@ cudaError_t launch_moe_dispatch(const void* scores, const void* expert_scales, u
 cudaError_t launch_moe_keys_from_offsets(const int32_t* offsets, uint32_t first_expert, uint32_t expert_count,
                                          uint32_t rows, int32_t* sorted_keys, int32_t* full_offsets,
                                          cudaStream_t stream);
-cudaError_t launch_moe_prepare_groups(const int32_t* offsets, const MoeExpertInfo* experts, uint32_t n,
-                                      uint32_t scale_rows, int block_n, bool shared_gate_up, GemmGroup* gate_up_groups,
-                                      GemmGroup* down_groups, cudaStream_t stream);
+cudaError_t launch_moe_prepare_groups(const MoeGroupPlan& plan, GemmGroup* first_groups, GemmGroup* down_groups,
+                                      cudaStream_t stream);
 cudaError_t launch_moe_quantize_input(const void* input, const int32_t* gather_index, const int32_t* sorted_keys,
                                       const int32_t* offsets, const MoeExpertInfo* experts, uint32_t n,
                                       uint32_t scale_rows, int parts, uint8_t* packed, uint8_t* scales,

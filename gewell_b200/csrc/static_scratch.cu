@@ -20,6 +20,7 @@
 #include <string>
 
 #include "common.cuh"
+#include "dense.h"
 #include "gemm_tc.cuh"
 #include "kernels.h"
 
@@ -108,33 +109,11 @@ gw_status gw_nvfp4_linear_static_scratch(const void* input_bf16, uint32_t rows, 
   GW_CUDA_CHECK(launch_nvfp4_quantize(input_bf16, rows, input_width, 1.0F / input_scale,
                                       transform == GW_TRANSFORM_GELU_TANH_MULTIPLY, packed, scales, s),
                 "static-scratch NVFP4 quantize activations");
-  const int block_n = rows <= 32 ? 32 : rows <= 64 ? 64 : rows <= 128 ? 128 : 256;
-  GemmParams params{};
-  std::string error;
-  if (!encode_tensor_map_2d(&params.map_a, weight_data, input_width / 2, output_width, 128, &error))
-    return fail(GW_CUDA_ERROR, "static-scratch NVFP4 weight descriptor: " + error);
-  if (!encode_tensor_map_2d(&params.map_b, packed, input_width / 2, rows, block_n, &error))
-    return fail(GW_CUDA_ERROR, "static-scratch NVFP4 activation descriptor: " + error);
-  params.groups = nullptr;
-  params.num_groups = 1;
-  GemmGroup& g = params.single;
-  g.sf_a = weight_scales;
-  g.channel_alpha = nullptr;
-  g.alpha = alpha;
-  g.map_a = -1;
-  g.a_tiles = int32_t(output_width / 128);
-  g.a_rows = int32_t(output_width);
-  g.b_rows = int32_t(rows);
-  const int b_tiles = (rows + block_n - 1) / block_n;
-  params.total_work = g.a_tiles * b_tiles;
-  params.sf_b = scales;
-  params.k = int32_t(input_width);
-  params.out = output_bf16;
-  params.ld_out = output_width;
-  params.error = slot->error;
-  const int grid = params.total_work < sm_count() ? params.total_work : sm_count();
-  GW_CUDA_CHECK(launch_gemm_tc(GemmKind::nvfp4, block_n, params, grid, s), "static-scratch NVFP4 tensor-core GEMM");
-  return GW_OK;
+  // descriptors live on this call's stack: nothing is cached, nothing allocated
+  DenseDescriptors descriptors;
+  DenseProblem problem{GemmKind::nvfp4, rows, input_width, output_width, weight_data, weight_scales, packed, scales,
+                       alpha, nullptr, output_bf16, slot->error};
+  return launch_dense(problem, &descriptors, s);
 }
 
 }  // extern "C"

@@ -362,6 +362,10 @@ class MoeWorkspace:
 
     STAGES = ("route_permute", "gather_quantise", "gate_up_gemm", "geglu_quantise", "down_gemm", "combine")
 
+    def capture(self, enable: bool = True):
+        """Also write the BF16 gate/up and activated intermediates when the fused path runs."""
+        _check(self._lib.gw_moe_capture(self._ws, int(enable)))
+
     def stage_timing(self, enable: bool = True):
         _check(self._lib.gw_moe_stage_timing(self._ws, int(enable)))
 

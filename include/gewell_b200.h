@@ -224,6 +224,13 @@ size_t gw_moe_routing_bytes(const gw_moe_workspace* workspace);
 size_t gw_moe_projection_bytes(const gw_moe_workspace* workspace);
 size_t gw_moe_reduction_bytes(const gw_moe_workspace* workspace);
 
+/* The reference always materialises the BF16 gate/up and activated
+ * intermediates that its capture accessors expose (moe.cuh:38-40).  Large
+ * batches here fuse GeGLU and the FP4 quantisation of the down input into the
+ * gate/up GEMM and skip those buffers; enable capture to have them written as
+ * well (the down capture is always valid).  Off by default. */
+gw_status gw_moe_capture(gw_moe_workspace* workspace, int enable);
+
 /* Optional per-stage timing of gw_moe_run (no counterpart in the reference;
  * its backends time whole steps with CUDA events, runtime/backend.h:127-129).
  * When enabled, run records CUDA events on its stream between the stages

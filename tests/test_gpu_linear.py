@@ -99,6 +99,20 @@ def test_nvfp4_shapes(gw, k, n, rows):
     assert_reference_tolerance(bits(y), exact, f"rows={rows} K={k} N={n}")
 
 
+@pytest.mark.parametrize("form", ["direct", "swap"])
+@pytest.mark.parametrize("rows", [5, 64, 128])
+def test_nvfp4_both_operand_roles(gw, form, rows, monkeypatch):
+    """Small row counts normally put the weights on the lane operand; the other
+    role assignment must give the same numbers."""
+    monkeypatch.setenv("GW_DENSE_FORM", form)
+    n, k = 384, 704
+    w = onv.pack_weights(to_f32(bf16_normal((n, k), 8, 0.05)), 0.0113)
+    x = bf16_normal((rows, k), 9)
+    y, packed, scales = run_nvfp4(gw, x.cuda(), oracle_weight_to_device(w), n, k)
+    exact = oracle_from_device_quantisation(packed, scales, rows, k, w)
+    assert_reference_tolerance(bits(y), exact, f"{form} rows={rows}")
+
+
 def test_nvfp4_gelu_input(gw):
     n, k, rows = 256, 704, 21
     w = onv.pack_weights(to_f32(bf16_normal((n, k), 3, 0.05)), 0.02)

@@ -1,5 +1,7 @@
 """GPU parity of the MoE layer (routing, permutation, grouped expert GEMMs,
 GeGLU, ordered combine) against the CPU oracle, through the C ABI."""
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -50,6 +52,33 @@ def experts(gw):
             onv.Weight(p.data.cpu().numpy(), p.scales.cpu().numpy(), p.input_scale, p.weight_scale,
                        p.data.shape[0], m.shape[1]) for p, m in zip(packs, mats)]))
     return gw.ExpertTable(device), host
+
+
+@pytest.fixture(scope="module")
+def experts_shared(gw, experts):
+    """The same matrices with one input scale for gate and up per expert (they
+    are one fused tensor in the checkpoint): enables the fused GeGLU epilogue."""
+    table, host = experts
+    device = []
+    shared_host = []
+    for (gate, up, down), h in zip(table._keep, host):
+        up2 = gw.Nvfp4Weight(up.data, up.scales, gate.input_scale, up.weight_scale)
+        device.append((gate, up2, down))
+        hu = onv.Weight(h.up.data, h.up.scales, h.gate.input_scale, h.up.weight_scale, h.up.rows, h.up.width)
+        shared_host.append(omoe.ExpertWeights(h.gate, hu, h.down))
+    return gw.ExpertTable(device), shared_host
+
+
+@pytest.fixture
+def moe_form():
+    """Sets / clears the tuning override that selects the grouped-GEMM plan."""
+    def choose(name):
+        if name is None:
+            os.environ.pop("GW_MOE_FORM", None)
+        else:
+            os.environ["GW_MOE_FORM"] = name
+    yield choose
+    os.environ.pop("GW_MOE_FORM", None)
 
 
 def make_scores(rows, mode, seed=0):
@@ -109,14 +138,23 @@ def test_combine_kernel_exact(gw):
     assert np.array_equal(bits(out), omoe.combine(to_f32(down), inverse, weights))
 
 
-@pytest.mark.parametrize("rows,mode", [(1, "hot"), (7, "normal"), (17, "distributed"), (33, "normal"),
-                                       (64, "normal"), (129, "uneven"), (300, "normal")])
-def test_moe_layer_vs_oracle(gw, experts, rows, mode):
-    table, host = experts
+@pytest.mark.parametrize("rows,mode,form", [
+    (1, "hot", None), (7, "normal", None), (17, "distributed", None), (33, "normal", None), (64, "normal", None),
+    (129, "uneven", None), (300, "normal", None),
+    (7, "normal", "direct"), (129, "uneven", "direct"), (300, "normal", "direct"),
+    (1, "hot", "fused"), (33, "normal", "fused"), (129, "uneven", "fused"), (300, "normal", "fused"),
+])
+def test_moe_layer_vs_oracle(gw, experts, experts_shared, moe_form, rows, mode, form):
+    """Whole layer against the faithful W4A4 oracle, for each grouped-GEMM plan:
+    swap (small batches), direct (tokens on the lane operand) and fused (GeGLU +
+    quantisation in the gate/up epilogue; needs one input scale for gate and up)."""
+    table, host = experts_shared if form == "fused" else experts
+    moe_form(form)
     x = bf16_normal((rows, H), 200 + rows)
     scores = make_scores(rows, mode, rows)
     scales = np.ones(E, dtype=np.float32)
     ws = gw.MoeWorkspace(max(rows, 64))
+    ws.capture(True)
     y = torch.full((rows * H + 64,), -3.0, dtype=torch.bfloat16, device="cuda")
     ws.run(x.cuda(), scores.cuda(), torch.ones(E, dtype=torch.bfloat16, device="cuda"), table, y, rows)
     torch.cuda.synchronize()
@@ -130,18 +168,42 @@ def test_moe_layer_vs_oracle(gw, experts, rows, mode):
     m_gu = assert_gemm_close(bits(ws.gate_up_capture()), C.bf16_bits(capture["gate_up"]), "gate/up capture")
     m_act = assert_gemm_close(bits(ws.activated_capture()), C.bf16_bits(capture["activated"]), "activated capture")
     m_dn = assert_gemm_close(bits(ws.down_capture()), C.bf16_bits(capture["down"]), "down capture")
-    m = assert_gemm_close(bits(y[:rows * H].reshape(rows, H)), expected, f"MoE rows={rows} {mode}")
+    m = assert_gemm_close(bits(y[:rows * H].reshape(rows, H)), expected, f"MoE rows={rows} {mode} {form}")
     host_path = omoe.forward(to_f32(x), to_f32(scores), scales, host, mode="w4a16")
-    print(f"rows={rows} {mode}: gate_up {m_gu['rel_fro']:.2e} act {m_act['rel_fro']:.2e} down {m_dn['rel_fro']:.2e} "
+    print(f"rows={rows} {mode} {form}: gate_up {m_gu['rel_fro']:.2e} act {m_act['rel_fro']:.2e} down {m_dn['rel_fro']:.2e} "
           f"out {m['rel_fro']:.2e} max_abs/max {m['max_abs'] / m['max_ref']:.2e}; vs W4A16 host path "
-          f"{error_metrics(bits(y[:rows * H].reshape(rows, H)), host_path)}")
+          f"rel_fro {error_metrics(bits(y[:rows * H].reshape(rows, H)), host_path)['rel_fro']:.3f}")
 
 
-def test_moe_layer_combine_consistency(gw, experts):
-    """The layer output is exactly the ordered BF16 fold of its own down
-    capture (moe.cu:446-456): checked at a size where the full oracle is slow."""
-    table, _ = experts
-    rows = 2048
+def test_moe_fused_without_capture_matches_captured_run(gw, experts_shared, moe_form):
+    """The fused plan skips the BF16 intermediates unless capture is on; the
+    layer output must not depend on that switch."""
+    table, _ = experts_shared
+    moe_form("fused")
+    rows = 257
+    x = bf16_normal((rows, H), 91).cuda()
+    scores = make_scores(rows, "normal", 9).cuda()
+    one = torch.ones(E, dtype=torch.bfloat16, device="cuda")
+    outs = []
+    for capture in (False, True):
+        ws = gw.MoeWorkspace(rows)
+        ws.capture(capture)
+        y = torch.empty((rows, H), dtype=torch.bfloat16, device="cuda")
+        ws.run(x, scores, one, table, y, rows)
+        torch.cuda.synchronize()
+        outs.append(y)
+    assert gw.kernel_error() == 0
+    assert torch.equal(outs[0], outs[1])
+
+
+@pytest.mark.parametrize("rows,form", [(2048, None), (2048, "fused"), (8192, "fused"), (8192, "direct")])
+def test_moe_layer_combine_consistency(gw, experts, experts_shared, moe_form, rows, form):
+    """Size-independent properties at sizes where the full oracle is slow: the
+    layer output is exactly the ordered BF16 fold of its own down capture
+    (moe.cu:446-456), offsets are the histogram of the selected ids, and the
+    plans agree with each other to GEMM tolerance."""
+    table, _ = experts_shared if form == "fused" else experts
+    moe_form(form)
     x = bf16_normal((rows, H), 77)
     scores = make_scores(rows, "normal", 5)
     ws = gw.MoeWorkspace(rows)
@@ -154,10 +216,18 @@ def test_moe_layer_combine_consistency(gw, experts):
     inverse[order] = np.arange(order.size, dtype=order.dtype)
     expected = omoe.combine(to_f32(ws.down_capture()), inverse, ws.routing_weights().cpu().numpy())
     assert np.array_equal(bits(y), expected)
-    # every expert's rows: spot-check one expert's gate/up tile against the oracle
     offsets = ws.offsets().cpu().numpy()
     ids = ws.selected_experts().cpu().numpy()
     assert offsets[-1] == rows * 8 and np.array_equal(np.bincount(ids.reshape(-1), minlength=E), np.diff(offsets))
+    if form is not None:
+        # same inputs through the small-batch plan: identical quantised operands, so the
+        # two results differ only by FP32 accumulation order inside the tensor core
+        moe_form("swap")
+        ws2 = gw.MoeWorkspace(rows)
+        y2 = torch.empty((rows, H), dtype=torch.bfloat16, device="cuda")
+        ws2.run(x.cuda(), scores.cuda(), torch.ones(E, dtype=torch.bfloat16, device="cuda"), table, y2, rows)
+        torch.cuda.synchronize()
+        assert_gemm_close(bits(y), bits(y2), f"{form} plan vs swap plan at rows={rows}")
 
 
 def test_moe_unsupported_modes(gw, experts):
