@@ -86,6 +86,7 @@ _SIGNATURES = {
     "gw_gather_rows_bf16": (c_int, [c_void_p, c_void_p, c_uint32, c_uint32, c_uint32, c_void_p, c_void_p]),
     "gw_moe_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_void_p, c_void_p]),
     "gw_debug_kernel_error": (c_uint32, []),
+    "gw_debug_gemm_profile": (c_int, [c_void_p]),
     "gw_debug_rcp_approx": (c_int, [c_void_p, c_void_p, c_uint64, c_void_p]),
     "gw_debug_geglu_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_uint64, c_void_p]),
 }

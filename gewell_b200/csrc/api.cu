@@ -85,6 +85,12 @@ uint32_t gw_debug_kernel_error(void) {
   return value;
 }
 
+gw_status gw_debug_gemm_profile(void* device_buffer) {
+  clear_error();
+  set_gemm_profile_buffer(static_cast<long long*>(device_buffer));
+  return GW_OK;
+}
+
 gw_status gw_debug_rcp_approx(const float* input, float* output, uint64_t count, void* stream) {
   clear_error();
   if (!input || !output) return fail(GW_INVALID_ARGUMENT, "rcp probe requires input and output buffers");

@@ -2,11 +2,16 @@
 //
 //   warp 0       TMA producer: operand tiles (cp.async.bulk.tensor, 128B swizzle)
 //                and scale-factor atoms (cp.async.bulk) into a ring of smem stages
-//   warp 1       MMA issuer: scale atoms smem->TMEM (tcgen05.cp) interleaved with
-//                the block-scaled tcgen05.mma (kind::mxf4nvf4, or kind::f8f6f4 for
-//                FP8) so that the copies hide behind the preceding MMA;
-//                tcgen05.commit frees stages / publishes accumulators
-//   warps 2..9   epilogue: two warps per TMEM lane quadrant, each draining half of
+//   warp 1       MMA issuer: block-scaled tcgen05.mma (kind::mxf4nvf4, or
+//                kind::f8f6f4 for FP8); tcgen05.commit frees stages / publishes
+//                accumulators.  Nothing else runs in the tensor pipe.
+//   warps 2..5   scale loaders (NVFP4): one warp per TMEM lane quadrant moves the
+//                stage's scale atoms smem -> registers -> TMEM (tcgen05.st) into a
+//                per-stage TMEM slot.  Measured on B200, a tcgen05.cp scale copy
+//                occupies the tensor pipe for ~40 cycles and never overlaps an MMA
+//                (12 copies per stage = 490 cycles next to 630 cycles of MMA);
+//                going through registers takes the copies out of that pipe.
+//   warps 6..13  epilogue: two warps per TMEM lane quadrant, each draining half of
 //                the accumulator columns with tcgen05.ld
 //
 // Operand roles and the three epilogues are described in gemm_tc.cuh.  Every
@@ -22,8 +27,10 @@
 namespace gw {
 namespace {
 
+constexpr int kScaleWarps = 4;
 constexpr int kEpilogueWarps = 8;
-constexpr int kThreads = 64 + 32 * kEpilogueWarps;
+constexpr int kFirstEpilogueWarp = 2 + kScaleWarps;
+constexpr int kThreads = 32 * (2 + kScaleWarps + kEpilogueWarps);
 constexpr int kTileL = 128;
 constexpr int kStageRowBytes = 128;   // bytes of K per stage row (= swizzle span)
 constexpr int kAtomBytes = 512;       // one scale atom: 128 rows x 4 K16 blocks
@@ -44,12 +51,14 @@ struct Config {
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
   static constexpr int kSfcColsPerKb = 4 * kHalves;
   static constexpr int kAccCols = kAccStages * BLOCK_N;
-  static constexpr int kSflCol = kAccCols;
-  static constexpr int kSfcCol = kSflCol + (kNvfp4 ? 4 * kKBlocksPerStage : 0);
-  static constexpr int kUsedCols = kSfcCol + (kNvfp4 ? kSfcColsPerKb * kKBlocksPerStage : 0);
+  // one scale slot per smem stage: [L scales: 4 columns per K-block][C scales]
+  static constexpr int kSfSlotCols = kNvfp4 ? kKBlocksPerStage * (4 + kSfcColsPerKb) : 0;
+  static constexpr int kSflCol = kAccCols;                               // + stage * kSfSlotCols
+  static constexpr int kSfcCol = kSflCol + 4 * kKBlocksPerStage;         // + stage * kSfSlotCols
+  static constexpr int kUsedCols = kAccCols + kStages * kSfSlotCols;
   static constexpr int kTmemCols = kUsedCols <= 32 ? 32 : kUsedCols <= 64 ? 64 : kUsedCols <= 128 ? 128
                                    : kUsedCols <= 256 ? 256 : 512;
-  static constexpr int kBarrierBytes = (2 * kStages + 2 * kAccStages) * 8 + 16;
+  static constexpr int kBarrierBytes = (3 * kStages + 2 * kAccStages) * 8 + 16;
   static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;  // +1024 alignment slack
   static_assert(kUsedCols <= 512, "TMEM over-subscribed");
   static_assert(kStages >= 2, "need at least two stages");
@@ -121,7 +130,8 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes);
   uint64_t* empty_bar = full_bar + C::kStages;
-  uint64_t* acc_full_bar = empty_bar + C::kStages;
+  uint64_t* sf_ready_bar = empty_bar + C::kStages;
+  uint64_t* acc_full_bar = sf_ready_bar + C::kStages;
   uint64_t* acc_empty_bar = acc_full_bar + C::kAccStages;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + C::kAccStages);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -130,7 +140,11 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
   const int lane = threadIdx.x % 32;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < C::kStages; ++s) { ptx::mbar_init(full_bar + s, 1); ptx::mbar_init(empty_bar + s, 1); }
+    for (int s = 0; s < C::kStages; ++s) {
+      ptx::mbar_init(full_bar + s, 1);
+      ptx::mbar_init(empty_bar + s, 1);
+      ptx::mbar_init(sf_ready_bar + s, kScaleWarps);
+    }
     for (int a = 0; a < C::kAccStages; ++a) {
       ptx::mbar_init(acc_full_bar + a, 1);
       ptx::mbar_init(acc_empty_bar + a, kEpilogueWarps);
@@ -154,11 +168,26 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
   const int k_stages = (total_kb + kKBlocksPerStage - 1) / kKBlocksPerStage;
   const int k_atoms = p.k / 64;                             // scale atoms per 128-row block (NVFP4)
 
+  // shared-memory descriptors: high words are constants, low word = address >> 4
+  constexpr uint32_t kDescHiSw128 = uint32_t(1024 >> 4) | (1u << 14) | (2u << 29);   // SBO 1024 B, version 1, SWIZZLE_128B
+  constexpr uint32_t kDescHiSf = uint32_t(128 >> 4) | (1u << 14);                    // SBO 128 B, version 1, no swizzle
+  constexpr uint32_t kCOff16 = C::kLBytes >> 4;
+  constexpr uint32_t kSflOff16 = (C::kLBytes + C::kCBytes) >> 4;
+  constexpr uint32_t kSfcOff16 = (C::kLBytes + C::kCBytes + C::kSflBytes) >> 4;
+  auto make_desc = [](uint32_t hi, uint32_t lo) { return (uint64_t(hi) << 32) | lo; };
+  const uint32_t smem_base16 = ptx::smem_u32(smem) >> 4;
+  const uint32_t sfl_tmem = tmem_base + C::kSflCol;
+  const uint32_t sfc_tmem = tmem_base + C::kSfcCol;
+
   auto stage_l = [&](int s) { return smem + s * C::kStageBytes; };
   auto stage_c = [&](int s) { return smem + s * C::kStageBytes + C::kLBytes; };
   auto stage_sfl = [&](int s) { return smem + s * C::kStageBytes + C::kLBytes + C::kCBytes; };
   auto stage_sfc = [&](int s) { return smem + s * C::kStageBytes + C::kLBytes + C::kCBytes + C::kSflBytes; };
 
+  // optional cycle counters (debug aid): [cta][8] = producer wait, mma wait for data, mma issue,
+  // mma wait for accumulator, epilogue wait, epilogue work, role total, items
+  long long prof_wait = 0, prof_work = 0, prof_wait2 = 0;
+  const long long prof_start = p.profile ? clock64() : 0;
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
     int stage = 0;
@@ -177,31 +206,42 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
       const int l_row = item.g.l_row0 + item.l_tile * kTileL;
       const int c_local = item.c_tile * p.c_rows_per_tile;   // row inside each matrix of the C operand
       const int halves = item.halves;
+      // per-item source addresses; per stage they advance by a constant
+      const uint8_t* sfl_src = nullptr;
+      const uint8_t* sfc_src[2] = {nullptr, nullptr};
+      int c_row[2] = {0, 0};
+      if constexpr (kNvfp4) sfl_src = item.g.sf_l + size_t(item.l_tile) * k_atoms * kAtomBytes;
+      for (int h = 0; h < C::kHalves; ++h) {
+        c_row[h] = item.g.c_row0 + c_local + h * item.g.c_half_stride;
+        if constexpr (kNvfp4)
+          sfc_src[h] = item.g.sf_c[h] + size_t((c_local + h * item.g.c_half_stride) / 128) * k_atoms * kAtomBytes;
+      }
+      const uint32_t full_stage_bytes =
+          C::kLBytes + halves * C::kHalfRows * kStageRowBytes + (kNvfp4 ? kKBlocksPerStage * kAtomBytes * (1 + halves) : 0);
       for (int ks = 0; ks < k_stages; ++ks) {
-        if (!ptx::mbar_wait_bounded(empty_bar + stage, phase ^ 1)) {
+        const long long t0 = p.profile ? clock64() : 0;
+        if (!ptx::mbar_wait_warp(empty_bar + stage, phase ^ 1)) {
           report(p.error, 0x10000000u | (blockIdx.x << 8) | stage, abort_flag);
           break;
         }
-        if (*abort_flag) break;
+        if (p.profile) prof_wait += clock64() - t0;
         if (lane == 0) {
           const int nkb = min(kKBlocksPerStage, total_kb - ks * kKBlocksPerStage);
-          uint32_t bytes = C::kLBytes + halves * C::kHalfRows * kStageRowBytes;
-          if constexpr (kNvfp4) bytes += nkb * kAtomBytes * (1 + halves);
-          ptx::mbar_expect_tx(full_bar + stage, bytes);
-          ptx::tma_load_2d(stage_l(stage), map_l, ks * kStageRowBytes, l_row, full_bar + stage);
+          uint32_t bytes = full_stage_bytes;
+          if (kNvfp4 && nkb != kKBlocksPerStage) bytes -= (kKBlocksPerStage - nkb) * kAtomBytes * (1 + halves);
+          uint8_t* base = smem + stage * C::kStageBytes;
+          uint64_t* bar = full_bar + stage;
+          ptx::mbar_expect_tx(bar, bytes);
+          ptx::tma_load_2d(base, map_l, ks * kStageRowBytes, l_row, bar);
           for (int h = 0; h < halves; ++h)
-            ptx::tma_load_2d(stage_c(stage) + h * C::kHalfRows * kStageRowBytes, map_c[h], ks * kStageRowBytes,
-                             item.g.c_row0 + c_local + h * item.g.c_half_stride, full_bar + stage);
+            ptx::tma_load_2d(base + C::kLBytes + h * C::kHalfRows * kStageRowBytes, map_c[h], ks * kStageRowBytes,
+                             c_row[h], bar);
           if constexpr (kNvfp4) {
-            const size_t atom0 = size_t(ks) * kKBlocksPerStage;
-            ptx::bulk_load(stage_sfl(stage), item.g.sf_l + (size_t(item.l_tile) * k_atoms + atom0) * kAtomBytes,
-                           nkb * kAtomBytes, full_bar + stage);
-            for (int h = 0; h < halves; ++h) {
-              const size_t row_block = size_t(c_local + h * item.g.c_half_stride) / 128;
-              ptx::bulk_load(stage_sfc(stage) + h * kKBlocksPerStage * kAtomBytes,
-                             item.g.sf_c[h] + (row_block * k_atoms + atom0) * kAtomBytes, nkb * kAtomBytes,
-                             full_bar + stage);
-            }
+            const size_t atom_offset = size_t(ks) * kKBlocksPerStage * kAtomBytes;
+            ptx::bulk_load(base + C::kLBytes + C::kCBytes, sfl_src + atom_offset, nkb * kAtomBytes, bar);
+            for (int h = 0; h < halves; ++h)
+              ptx::bulk_load(base + C::kLBytes + C::kCBytes + C::kSflBytes + h * kKBlocksPerStage * kAtomBytes,
+                             sfc_src[h] + atom_offset, nkb * kAtomBytes, bar);
           }
         }
         __syncwarp();
@@ -215,10 +255,12 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
     for (int w = blockIdx.x; w < total_work && !*abort_flag; w += gridDim.x) {
       WorkItem item;
       decode_work<BLOCK_N, EPI>(p, w, item);
-      if (!ptx::mbar_wait_bounded(acc_empty_bar + acc, acc_phase ^ 1)) {
+      const long long ta = p.profile ? clock64() : 0;
+      if (!ptx::mbar_wait_warp(acc_empty_bar + acc, acc_phase ^ 1)) {
         report(p.error, 0x20000000u | (blockIdx.x << 8) | acc, abort_flag);
         break;
       }
+      if (p.profile) prof_wait2 += clock64() - ta;
       ptx::tc_fence_after_sync();
       const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
       const uint32_t idesc = kNvfp4 ? ptx::idesc_nvfp4(item.mma_n) : ptx::idesc_fp8(item.mma_n);
@@ -228,38 +270,48 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
       const int halves = item.halves;
       bool failed = false;
       for (int ks = 0; ks < k_stages; ++ks) {
-        if (!ptx::mbar_wait_bounded(full_bar + stage, phase)) {
+        const long long t0 = p.profile ? clock64() : 0;
+        if (!ptx::mbar_wait_warp(full_bar + stage, phase)) {
           report(p.error, 0x30000000u | (blockIdx.x << 8) | stage, abort_flag);
           failed = true;
           break;
         }
-        if (*abort_flag) { failed = true; break; }
+        const long long t1 = p.profile ? clock64() : 0;
+        prof_wait += t1 - t0;
         ptx::tc_fence_after_sync();
+        if constexpr (kNvfp4) {
+          // this stage's scales are in its TMEM slot once the four loader warps have arrived
+          if (!ptx::mbar_wait_warp(sf_ready_bar + stage, phase)) {
+            report(p.error, 0x50000000u | (blockIdx.x << 8) | stage, abort_flag);
+            failed = true;
+            break;
+          }
+          ptx::tc_fence_after_sync();
+        }
         if (lane == 0) {
+          // Single in-order instruction stream: descriptors are a constant plus
+          // stage * (kStageBytes >> 4) in their low word, the loop is unrolled.
           const int nkb = min(kKBlocksPerStage, total_kb - ks * kKBlocksPerStage);
-          const uint64_t l_desc = ptx::smem_desc_sw128(ptx::smem_u32(stage_l(stage)));
-          const uint64_t c_desc = ptx::smem_desc_sw128(ptx::smem_u32(stage_c(stage)));
-          const uint32_t sfl_smem = ptx::smem_u32(stage_sfl(stage));
-          const uint32_t sfc_smem = ptx::smem_u32(stage_sfc(stage));
-          for (int kb = 0; kb < nkb; ++kb) {
-            if constexpr (kNvfp4) {
-              // scale atoms of this K-block; issued right before their MMA so that they
-              // execute under the previous MMA
-              ptx::tc_copy_sf_atom(tmem_base + C::kSflCol + 4 * kb, ptx::smem_desc_sf_atom(sfl_smem + kb * kAtomBytes));
-              for (int h = 0; h < halves; ++h)
-                ptx::tc_copy_sf_atom(tmem_base + C::kSfcCol + kb * C::kSfcColsPerKb + 4 * h,
-                                     ptx::smem_desc_sf_atom(sfc_smem + (h * kKBlocksPerStage + kb) * kAtomBytes));
+          const uint32_t base16 = smem_base16 + uint32_t(stage) * uint32_t(C::kStageBytes >> 4);
+          const uint32_t sfl_t = sfl_tmem + uint32_t(stage) * C::kSfSlotCols;
+          const uint32_t sfc_t = sfc_tmem + uint32_t(stage) * C::kSfSlotCols + sfc_sub;
+          const uint32_t first = ks == 0 ? 0u : 1u;
+#pragma unroll
+          for (int kb = 0; kb < kKBlocksPerStage; ++kb) {
+            if (kb < nkb) {
+              if constexpr (kNvfp4)
+                ptx::tc_mma_nvfp4(d_tmem, make_desc(kDescHiSw128, base16 + 2 * kb),
+                                  make_desc(kDescHiSw128, base16 + kCOff16 + 2 * kb), idesc, sfl_t + 4 * kb,
+                                  sfc_t + kb * C::kSfcColsPerKb, kb == 0 ? first : 1u);
+              else
+                ptx::tc_mma_fp8(d_tmem, make_desc(kDescHiSw128, base16 + 2 * kb),
+                                make_desc(kDescHiSw128, base16 + kCOff16 + 2 * kb), idesc, kb == 0 ? first : 1u);
             }
-            const uint32_t accumulate = (ks | kb) != 0;
-            if constexpr (kNvfp4)
-              ptx::tc_mma_nvfp4(d_tmem, l_desc + 2 * kb, c_desc + 2 * kb, idesc, tmem_base + C::kSflCol + 4 * kb,
-                                tmem_base + C::kSfcCol + kb * C::kSfcColsPerKb + sfc_sub, accumulate);
-            else
-              ptx::tc_mma_fp8(d_tmem, l_desc + 2 * kb, c_desc + 2 * kb, idesc, accumulate);
           }
           ptx::tc_commit(empty_bar + stage);
         }
         __syncwarp();
+        if (p.profile) prof_work += clock64() - t1;
         if (++stage == C::kStages) { stage = 0; phase ^= 1; }
       }
       if (failed) break;
@@ -267,19 +319,86 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
       __syncwarp();
       if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1; }
     }
+  } else if (warp < kFirstEpilogueWarp) {
+    // ------------------------------------------------------------------ scale loaders
+    // TMEM layout the MMA expects for a K-block: lane (row % 32) of every lane quadrant,
+    // 32-bit column (row / 32), byte (K16 block % 4) -- i.e. the 16 bytes of row (lane) of a
+    // 512-byte atom are four consecutive columns, identical in all four quadrants.  Each of
+    // the four warps writes its own quadrant: one 16-byte shared-memory load per atom and
+    // lane, then tcgen05.st of 16 columns at a time.
+    if constexpr (kNvfp4) {
+      const uint32_t quad_lane = uint32_t((warp % 4) * 32) << 16;
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int w = blockIdx.x; w < total_work && !*abort_flag; w += gridDim.x) {
+        WorkItem item;
+        decode_work<BLOCK_N, EPI>(p, w, item);
+        const int halves = item.halves;
+        bool failed = false;
+        for (int ks = 0; ks < k_stages; ++ks) {
+          if (!ptx::mbar_wait_warp(full_bar + stage, phase)) {
+            report(p.error, 0x60000000u | (blockIdx.x << 8) | stage, abort_flag);
+            failed = true;
+            break;
+          }
+          const uint32_t src = ptx::smem_u32(smem + stage * C::kStageBytes + C::kLBytes + C::kCBytes) + lane * 16;
+          const uint32_t slot = tmem_base + C::kSflCol + uint32_t(stage) * C::kSfSlotCols + quad_lane;
+          uint32_t r[16];
+#pragma unroll
+          for (int kb = 0; kb < kKBlocksPerStage; ++kb) {
+            const uint4 v = ptx::lds128(src + kb * kAtomBytes);
+            r[4 * kb] = v.x; r[4 * kb + 1] = v.y; r[4 * kb + 2] = v.z; r[4 * kb + 3] = v.w;
+          }
+          ptx::tmem_store16(slot, r);
+          // column operand scales: per K-block [half 0: 4 columns][half 1: 4 columns]
+          if constexpr (C::kHalves == 1) {
+#pragma unroll
+            for (int kb = 0; kb < kKBlocksPerStage; ++kb) {
+              const uint4 v = ptx::lds128(src + C::kSflBytes + kb * kAtomBytes);
+              r[4 * kb] = v.x; r[4 * kb + 1] = v.y; r[4 * kb + 2] = v.z; r[4 * kb + 3] = v.w;
+            }
+            ptx::tmem_store16(slot + 4 * kKBlocksPerStage, r);
+          } else {
+#pragma unroll
+            for (int pair = 0; pair < 2; ++pair) {      // two K-blocks (16 columns) per store
+#pragma unroll
+              for (int i = 0; i < 2; ++i) {
+                const int kb = 2 * pair + i;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                  uint4 v = make_uint4(0, 0, 0, 0);
+                  if (h < halves) v = ptx::lds128(src + C::kSflBytes + (h * kKBlocksPerStage + kb) * kAtomBytes);
+                  r[8 * i + 4 * h] = v.x; r[8 * i + 4 * h + 1] = v.y; r[8 * i + 4 * h + 2] = v.z; r[8 * i + 4 * h + 3] = v.w;
+                }
+              }
+              ptx::tmem_store16(slot + 4 * kKBlocksPerStage + 16 * pair, r);
+            }
+          }
+          ptx::tmem_store_wait();
+          ptx::tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(sf_ready_bar + stage);
+          if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+        }
+        if (failed) break;
+      }
+    }
   } else {
     // ------------------------------------------------------------------ epilogue
     const int quad = warp % 4;            // TMEM lanes [32*quad, 32*quad+32) belong to this warp
-    const int col_half = (warp - 2) / 4;  // which half of the accumulator columns this warp drains
+    const int col_half = (warp - kFirstEpilogueWarp) / 4;  // which half of the accumulator columns this warp drains
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int w = blockIdx.x; w < total_work && !*abort_flag; w += gridDim.x) {
       WorkItem item;
       decode_work<BLOCK_N, EPI>(p, w, item);
-      if (!ptx::mbar_wait_bounded(acc_full_bar + acc, acc_phase)) {
+      const long long te0 = p.profile ? clock64() : 0;
+      if (!ptx::mbar_wait_warp(acc_full_bar + acc, acc_phase)) {
         report(p.error, 0x40000000u | (blockIdx.x << 8) | acc, abort_flag);
         break;
       }
+      const long long te1 = p.profile ? clock64() : 0;
+      prof_wait += te1 - te0;
       ptx::tc_fence_after_sync();
       const uint32_t taddr = tmem_base + acc * BLOCK_N + (uint32_t(quad * 32) << 16);
       const int l_index = item.l_tile * kTileL + quad * 32 + lane;   // row of L inside the group
@@ -413,8 +532,16 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
       ptx::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(acc_empty_bar + acc);
+      if (p.profile) prof_work += clock64() - te1;
       if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1; }
     }
+  }
+  if (p.profile && lane == 0 && (warp <= 1 || warp == kFirstEpilogueWarp)) {
+    long long* row = p.profile + size_t(blockIdx.x) * 8;
+    const long long total = clock64() - prof_start;
+    if (warp == 0) { row[0] = prof_wait; }
+    if (warp == 1) { row[1] = prof_wait; row[2] = prof_work; row[3] = prof_wait2; row[6] = total; }
+    if (warp == kFirstEpilogueWarp) { row[4] = prof_wait; row[5] = prof_work; }
   }
 
   ptx::tc_fence_before_sync();
@@ -425,8 +552,12 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
   }
 }
 
+long long* g_profile_buffer = nullptr;
+
 template <bool kNvfp4, int BLOCK_N, GemmEpilogue EPI>
-cudaError_t launch(const GemmParams& params, int grid, cudaStream_t stream) {
+cudaError_t launch(const GemmParams& params_in, int grid, cudaStream_t stream) {
+  GemmParams params = params_in;
+  params.profile = g_profile_buffer;
   using C = Config<kNvfp4, BLOCK_N>;
   static bool configured = false;
   if (!configured) {
@@ -440,6 +571,8 @@ cudaError_t launch(const GemmParams& params, int grid, cudaStream_t stream) {
 }
 
 }  // namespace
+
+void set_gemm_profile_buffer(long long* device_buffer) { g_profile_buffer = device_buffer; }
 
 cudaError_t launch_gemm_tc(GemmKind kind, GemmEpilogue epilogue, int block_n, const GemmParams& params, int grid,
                            cudaStream_t stream) {

@@ -64,6 +64,7 @@ struct GemmParams {
   void* capture_gate_up;          // GeGLU+quantise: optional BF16 [rows, 2*out_width]
   void* capture_activated;        // GeGLU+quantise: optional BF16 [rows, out_width]
   uint32_t* error;                // device error word (0 = fine)
+  long long* profile;             // optional [grid][8] cycle counters (debug aid), normally nullptr
 };
 
 enum class GemmKind { nvfp4, fp8 };
@@ -72,6 +73,11 @@ enum class GemmEpilogue { swap_store, direct_store, geglu_quant };
 // swap_store: block_n in {32, 64, 128}; direct_store: {128, 256}; geglu_quant: 256 (NVFP4).
 cudaError_t launch_gemm_tc(GemmKind kind, GemmEpilogue epilogue, int block_n, const GemmParams& params, int grid,
                            cudaStream_t stream);
+
+// Debug aid: subsequent launches write per-CTA cycle counters ([grid][8] int64:
+// producer wait, MMA wait for data, MMA issue, MMA wait for accumulator, epilogue
+// wait, epilogue work, total, unused) into this device buffer; nullptr turns it off.
+void set_gemm_profile_buffer(long long* device_buffer);
 
 // Host helper: 2-D byte tensor map {inner = row_bytes, outer = rows} with a
 // 128-byte x box_rows box and the 128-byte swizzle.

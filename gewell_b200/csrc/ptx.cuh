@@ -64,6 +64,27 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   }
 }
 
+// Warp-level wait: one lane polls (backing off with nanosleep between polls so
+// that waiting warps leave the issue slots and the barrier unit to the warps
+// that are doing work), the outcome is broadcast.  All 32 lanes must call it.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, uint32_t backoff_ns = 0,
+                                               uint64_t limit_ns = 2000000000ull) {
+  uint32_t ok = 1;
+  if ((threadIdx.x & 31) == 0) {
+    if (!mbar_try_wait(bar, parity)) {
+      const uint64_t start = global_timer_ns();
+      for (uint32_t spin = 1;; ++spin) {
+        if (backoff_ns) __nanosleep(backoff_ns);
+        if (mbar_try_wait(bar, parity)) break;
+        if ((spin & 63u) == 0 && global_timer_ns() - start > limit_ns) { ok = 0; break; }
+      }
+    }
+  }
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  __syncwarp();   // orders the polling lane's acquire before the other lanes' accesses
+  return ok != 0;
+}
+
 // ----------------------------------------------------------------------------
 // TMA
 // ----------------------------------------------------------------------------
@@ -188,6 +209,23 @@ __device__ __forceinline__ void tmem_load16(uint32_t taddr, uint32_t* r) {
         "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
+}
+// 16 registers per thread -> 32 lanes x 16 consecutive 32-bit columns.
+__device__ __forceinline__ void tmem_store16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_store_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t smem_addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(smem_addr));
+  return v;
 }
 __device__ __forceinline__ void tmem_load_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");

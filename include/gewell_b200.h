@@ -263,6 +263,12 @@ gw_status gw_moe_combine(const void* down_bf16, const int32_t* inverse, const fl
  * bounded waits inside the tensor-core kernels.  Synchronises the device. */
 uint32_t gw_debug_kernel_error(void);
 
+/* Tuning aid: when `device_buffer` (148 x 8 int64 on the device) is not NULL,
+ * every later tensor-core GEMM launch writes per-CTA cycle counters into it
+ * (producer wait, MMA wait for data, MMA issue, MMA wait for the accumulator,
+ * epilogue wait, epilogue work, total); NULL switches it off again. */
+gw_status gw_debug_gemm_profile(void* device_buffer);
+
 /* Test aid: output[i] = rcp.approx.ftz.f32(input[i]) evaluated on the device.
  * The activation recipe (src/nvfp4_linear.cu:92-114) is defined in terms of
  * this instruction, whose last bit a CPU cannot predict; the parity tests feed
