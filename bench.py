@@ -91,13 +91,16 @@ def zipf_bias(alpha: float = 1.2):
     return (p / p.sum()).log()
 
 
-def build_experts(gw, torch, device, seed=4):
-    """128 experts ~ N(0, 0.02), packed to NVFP4 by the device packer; gate
-    and up share one input scale per expert (they are one fused tensor in the
-    checkpoint), so the layer quantises its input once."""
-    experts = []
-    g = torch.Generator(device=device).manual_seed(seed)
-    for e in range(E):
+def build_experts(gw, torch, device, seed=4, expert_ids=None):
+    """The layer's experts ~ N(0, 0.02), packed to NVFP4 by the device packer;
+    gate and up share one input scale per expert (they are one fused tensor in
+    the checkpoint), so the layer quantises its input once.  Every expert has
+    its own sub-seed, so a rank that owns only some experts (`expert_ids`)
+    builds exactly the tensors the single-GPU run builds; the other entries
+    of the returned 128-list are None."""
+    experts = [None] * E
+    for e in (range(E) if expert_ids is None else expert_ids):
+        g = torch.Generator(device=device).manual_seed(seed * 1000003 + e)
         mats = [(torch.randn((I, H), generator=g, device=device) * 0.02).bfloat16(),
                 (torch.randn((I, H), generator=g, device=device) * 0.02).bfloat16(),
                 (torch.randn((H, I), generator=g, device=device) * 0.02).bfloat16()]
@@ -111,7 +114,7 @@ def build_experts(gw, torch, device, seed=4):
                 data[:m.shape[0]] = w.data
                 w = gw.Nvfp4Weight(data, w.scales, w.input_scale, w.weight_scale)
             packs.append(w)
-        experts.append(tuple(packs))
+        experts[e] = tuple(packs)
     return experts
 
 
@@ -176,6 +179,147 @@ def workload_config(n_gpus: int) -> dict:
             "parallelism": "single GPU" if n_gpus == 1 else f"ep{n_gpus}"}
 
 
+def run_expert_parallel(args, world: int, rank: int, local_rank: int):
+    """N > 1: config 5, the layer sharded by expert over the ranks (T = 32768
+    tokens in total, T / N routed per rank, Zipf(1.2)-biased router logits)."""
+    import torch
+    import torch.distributed as dist
+    import gewell_b200 as gw
+    from gewell_b200 import expert_parallel as ep
+
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    dist.init_process_group("nccl", device_id=device)
+    config = workload_config(world)
+    tokens = args.tokens or config["tokens"]
+    config["tokens"] = tokens
+    local_tokens = tokens // world
+    g = torch.Generator(device=device).manual_seed(1000 + rank)
+    if args.placement == "balanced":
+        # load-aware placement from the routing histogram of a calibration batch
+        # (same distribution, other seed), as a serving system keeps from earlier steps
+        calibration = (torch.randn((local_tokens, E), generator=g, device=device) + zipf_bias().to(device)).bfloat16()
+        chosen = calibration.float().topk(TOPK, dim=1).indices.reshape(-1)
+        histogram = torch.bincount(chosen, minlength=E).float()
+        dist.all_reduce(histogram)
+        placement = ep.Placement.balanced(world, histogram.tolist())
+    else:
+        placement = getattr(ep.Placement, args.placement)(world)
+    config["placement"] = args.placement
+    mine = placement.local_experts(rank)
+    by_id = build_experts(gw, torch, device, expert_ids=mine)
+    by_position = [None] * E
+    for e in mine:
+        by_position[placement.physical[e]] = by_id[e]
+    capacity = TOPK * tokens          # worst case: every assignment lands on one rank
+    backend = ep.DeviceBackend(by_position, local_tokens, capacity)
+    layer = ep.ExpertParallelMoe(backend, rank, world, local_tokens, capacity, placement=placement)
+    x = torch.randn((local_tokens, H), generator=g, device=device).bfloat16()
+    logits = torch.randn((local_tokens, E), generator=g, device=device) + zipf_bias().to(device)
+    scores = logits.bfloat16()
+    expert_scales = torch.ones(E, dtype=torch.bfloat16, device=device)
+    y = torch.empty((local_tokens, H), dtype=torch.bfloat16, device=device)
+    stream = torch.cuda.current_stream()
+
+    def step():
+        layer.run(x, scores, expert_scales, local_tokens, out=y)
+
+    def timed(fn, steps):
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        dist.barrier()
+        torch.cuda.synchronize()
+        begin.record(stream)
+        for _ in range(steps):
+            fn()
+        end.record(stream)
+        torch.cuda.synchronize()
+        dist.barrier()
+        ms = torch.tensor([begin.elapsed_time(end) / steps], device=device)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    if gw.kernel_error() != 0:
+        raise SystemExit("tensor-core kernel reported an error during warm-up")
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    time.sleep(0.25)
+    t0 = time.time()
+    ms = timed(step, args.steps)
+    flops = tokens * TOPK * FLOPS_PER_ASSIGNMENT
+    value = flops / (ms * 1e-3) / 1e12
+
+    hx, hs = x.cpu().pin_memory(), scores.cpu().pin_memory()
+    hy = torch.empty((local_tokens, H), dtype=torch.bfloat16).pin_memory()
+    dx, ds = torch.empty_like(x), torch.empty_like(scores)
+
+    def e2e_step():
+        dx.copy_(hx, non_blocking=True)
+        ds.copy_(hs, non_blocking=True)
+        layer.run(dx, ds, expert_scales, local_tokens, out=y)
+        hy.copy_(y, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    e2e_ms = timed(e2e_step, args.steps)
+    clocks = sampler.stop(t0, time.time()) if sampler else None
+
+    # per-stage device times of this rank and the grouped GEMMs' roofline
+    marks = []
+    layer.timer = lambda name: marks.append((name, _record(torch, stream)))
+    backend.expert_ws.stage_timing(True)
+    stage_sum, gemm_sum = {}, 0.0
+    for _ in range(max(3, args.steps // 4)):
+        marks.clear()
+        first = _record(torch, stream)
+        step()
+        torch.cuda.synchronize()
+        previous = first
+        for name, event in marks:
+            stage_sum[name] = stage_sum.get(name, 0.0) + previous.elapsed_time(event)
+            previous = event
+        inner = backend.expert_ws.stage_elapsed_ms()
+        gemm_sum += inner["gate_up_gemm"] + inner["down_gemm"]
+    repeats = max(3, args.steps // 4)
+    layer.timer = None
+    backend.expert_ws.stage_timing(False)
+    stages = {k: v / repeats for k, v in stage_sum.items()}
+    received = torch.tensor([float(layer.last_layout.total), gemm_sum / repeats], device=device)
+    gathered = [torch.zeros_like(received) for _ in range(world)]
+    dist.all_gather(gathered, received)
+    rows_per_rank = [int(t[0].item()) for t in gathered]
+    gemm_ms_per_rank = [float(t[1].item()) for t in gathered]
+    if rank == 0:
+        peaks = measured_peaks()
+        fp4_peak = 4.0 * peaks["bf16_tflops"]
+        slowest = max(range(world), key=lambda r: gemm_ms_per_rank[r])
+        achieved = rows_per_rank[slowest] * FLOPS_PER_ASSIGNMENT / (gemm_ms_per_rank[slowest] * 1e-3) / 1e12
+        line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "nvfp4 (e2m1 x e2m1, fp32 accumulate)", "data": "synthetic",
+                "config": config,
+                "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                        "h2d_bytes_per_step": world * (hx.numel() + hs.numel()) * 2,
+                        "d2h_bytes_per_step": world * hy.numel() * 2, "ms_per_step": e2e_ms},
+                "gpu_launches": 13 * args.steps * world, "clocks": clocks,
+                "roofline": {"kernel": "gemm_tc_kernel<nvfp4> (grouped gate/up + grouped down) on the busiest rank",
+                             "bound": "tensor", "achieved": achieved, "peak": fp4_peak, "unit": "TFLOP/s",
+                             "frac": achieved / fp4_peak, "traffic": None,
+                             "peak_note": f"4 x the {peaks['source']} dense BF16 burst figure per GPU",
+                             "rows_received_per_rank": rows_per_rank, "gemm_ms_per_rank": gemm_ms_per_rank,
+                             "stage_ms_rank0": stages},
+                "cpu_baseline": None}
+        print(json.dumps(line))
+    dist.destroy_process_group()
+
+
+def _record(torch, stream):
+    event = torch.cuda.Event(enable_timing=True)
+    event.record(stream)
+    return event
+
+
 def main():
     parser = argparse.ArgumentParser(description=__doc__)
     parser.add_argument("--gpus", type=int, default=1)
@@ -184,6 +328,8 @@ def main():
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--tokens", type=int, default=0, help="override the token count (testing)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--placement", default="balanced", choices=["contiguous", "interleaved", "balanced"],
+                        help="expert placement of the expert-parallel run")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
@@ -196,9 +342,7 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if world > 1:
-        from gewell_b200 import expert_parallel
-        return expert_parallel.bench_main(args, world, rank, local_rank, workload_config(world), METRIC,
-                                          build_experts, ClockSampler, measured_peaks)
+        return run_expert_parallel(args, world, rank, local_rank)
 
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)

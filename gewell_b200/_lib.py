@@ -12,7 +12,7 @@ LIBRARY_PATH = Path(__file__).resolve().parent / "_C" / "libgewell_b200.so"
 GW_OK, GW_INVALID_ARGUMENT, GW_CUDA_ERROR, GW_KERNEL_ERROR, GW_UNSUPPORTED = range(5)
 TRANSFORM_IDENTITY, TRANSFORM_GELU_TANH_MULTIPLY = 0, 1
 QDQ_BF16, QDQ_FP8, QDQ_NVFP4 = 0, 1, 2
-STORAGE_BF16, STORAGE_NVFP4_W4A4, STORAGE_FP8_W8A8 = 0, 1, 2
+STORAGE_BF16, STORAGE_NVFP4_W4A4, STORAGE_FP8_W8A8, STORAGE_ABSENT = 0, 1, 2, 3
 
 
 class Projection(ctypes.Structure):
@@ -72,6 +72,7 @@ _SIGNATURES = {
     "gw_moe_routing_weights": (c_void_p, [c_void_p]),
     "gw_moe_offsets": (c_void_p, [c_void_p]),
     "gw_moe_sorted_assignments": (c_void_p, [c_void_p]),
+    "gw_moe_inverse": (c_void_p, [c_void_p]),
     "gw_moe_gate_up_capture": (c_void_p, [c_void_p]),
     "gw_moe_activated_capture": (c_void_p, [c_void_p]),
     "gw_moe_down_capture": (c_void_p, [c_void_p]),
@@ -82,7 +83,7 @@ _SIGNATURES = {
     "gw_moe_capture": (c_int, [c_void_p, c_int]),
     "gw_moe_stage_timing": (c_int, [c_void_p, c_int]),
     "gw_moe_stage_elapsed_ms": (c_int, [c_void_p, POINTER(c_float)]),
-    "gw_moe_run_sorted": (c_int, [c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_uint32, c_void_p, c_void_p, c_void_p]),
+    "gw_moe_run_sorted": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_uint32, c_void_p, c_void_p, c_void_p]),
     "gw_gather_rows_bf16": (c_int, [c_void_p, c_void_p, c_uint32, c_uint32, c_uint32, c_void_p, c_void_p]),
     "gw_moe_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_void_p, c_void_p]),
     "gw_debug_kernel_error": (c_uint32, []),

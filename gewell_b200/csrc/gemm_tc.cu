@@ -58,7 +58,8 @@ struct Config {
   static constexpr int kUsedCols = kAccCols + kStages * kSfSlotCols;
   static constexpr int kTmemCols = kUsedCols <= 32 ? 32 : kUsedCols <= 64 ? 64 : kUsedCols <= 128 ? 128
                                    : kUsedCols <= 256 ? 256 : 512;
-  static constexpr int kBarrierBytes = (3 * kStages + 2 * kAccStages) * 8 + 16;
+  static constexpr int kMaxGroups = 256;
+  static constexpr int kBarrierBytes = (3 * kStages + 2 * kAccStages) * 8 + 16 + (kMaxGroups + 4) * 4;
   static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;  // +1024 alignment slack
   static_assert(kUsedCols <= 512, "TMEM over-subscribed");
   static_assert(kStages >= 2, "need at least two stages");
@@ -77,14 +78,14 @@ struct WorkItem {
 };
 
 template <int BLOCK_N, GemmEpilogue EPI>
-__device__ __forceinline__ void decode_work(const GemmParams& p, int w, WorkItem& item) {
+__device__ __forceinline__ void decode_work(const GemmParams& p, const int32_t* prefix, int w, WorkItem& item) {
   using C = Config<true, BLOCK_N>;
   if (p.groups != nullptr) {
-    // largest gi with groups[gi].work_begin <= w  (groups[num_groups] is the sentinel)
+    // largest gi with work_begin[gi] <= w; the prefix sums were staged in shared memory
     int lo = 0, hi = p.num_groups;
     while (lo + 1 < hi) {
       const int mid = (lo + hi) / 2;
-      if (p.groups[mid].work_begin <= w) lo = mid; else hi = mid;
+      if (prefix[mid] <= w) lo = mid; else hi = mid;
     }
     item.g = p.groups[lo];
   } else {
@@ -135,6 +136,9 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
   uint64_t* acc_empty_bar = acc_full_bar + C::kAccStages;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + C::kAccStages);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int32_t* prefix = reinterpret_cast<int32_t*>(tmem_slot + 4);   // work_begin of every group (+ sentinel)
+  if (p.groups != nullptr)
+    for (int i = threadIdx.x; i <= p.num_groups; i += kThreads) prefix[i] = p.groups[i].work_begin;
 
   const int warp = threadIdx.x / 32;
   const int lane = threadIdx.x % 32;
@@ -162,7 +166,7 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int total_work = p.groups != nullptr ? p.groups[p.num_groups].work_begin : p.total_work;
+  const int total_work = p.groups != nullptr ? prefix[p.num_groups] : p.total_work;
   const int k_bytes = kNvfp4 ? p.k / 2 : p.k;
   const int total_kb = (k_bytes + 31) / 32;                 // MMA K-blocks (32 bytes of K each)
   const int k_stages = (total_kb + kKBlocksPerStage - 1) / kKBlocksPerStage;
@@ -192,9 +196,11 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
     // ------------------------------------------------------------------ producer
     int stage = 0;
     uint32_t phase = 0;
+    WorkItem item, next;
+    if (int(blockIdx.x) < total_work) decode_work<BLOCK_N, EPI>(p, prefix, blockIdx.x, next);
     for (int w = blockIdx.x; w < total_work && !*abort_flag; w += gridDim.x) {
-      WorkItem item;
-      decode_work<BLOCK_N, EPI>(p, w, item);
+      item = next;   // the next item's descriptor is fetched while this one is processed
+      if (w + int(gridDim.x) < total_work) decode_work<BLOCK_N, EPI>(p, prefix, w + gridDim.x, next);
       const CUtensorMap* map_l = item.g.map_l >= 0 ? p.map_table + item.g.map_l : &p.map_l;
       const CUtensorMap* map_c[2];
       for (int h = 0; h < C::kHalves; ++h) map_c[h] = item.g.map_c[h] >= 0 ? p.map_table + item.g.map_c[h] : &p.map_c;
@@ -252,9 +258,11 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
     // ------------------------------------------------------------------ MMA issuer
     int stage = 0, acc = 0;
     uint32_t phase = 0, acc_phase = 0;
+    WorkItem item, next;
+    if (int(blockIdx.x) < total_work) decode_work<BLOCK_N, EPI>(p, prefix, blockIdx.x, next);
     for (int w = blockIdx.x; w < total_work && !*abort_flag; w += gridDim.x) {
-      WorkItem item;
-      decode_work<BLOCK_N, EPI>(p, w, item);
+      item = next;   // the next item's descriptor is fetched while this one is processed
+      if (w + int(gridDim.x) < total_work) decode_work<BLOCK_N, EPI>(p, prefix, w + gridDim.x, next);
       const long long ta = p.profile ? clock64() : 0;
       if (!ptx::mbar_wait_warp(acc_empty_bar + acc, acc_phase ^ 1)) {
         report(p.error, 0x20000000u | (blockIdx.x << 8) | acc, abort_flag);
@@ -330,9 +338,11 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
       const uint32_t quad_lane = uint32_t((warp % 4) * 32) << 16;
       int stage = 0;
       uint32_t phase = 0;
+      WorkItem item, next;
+      if (int(blockIdx.x) < total_work) decode_work<BLOCK_N, EPI>(p, prefix, blockIdx.x, next);
       for (int w = blockIdx.x; w < total_work && !*abort_flag; w += gridDim.x) {
-        WorkItem item;
-        decode_work<BLOCK_N, EPI>(p, w, item);
+        item = next;
+        if (w + int(gridDim.x) < total_work) decode_work<BLOCK_N, EPI>(p, prefix, w + gridDim.x, next);
         const int halves = item.halves;
         bool failed = false;
         for (int ks = 0; ks < k_stages; ++ks) {
@@ -389,9 +399,11 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
     const int col_half = (warp - kFirstEpilogueWarp) / 4;  // which half of the accumulator columns this warp drains
     int acc = 0;
     uint32_t acc_phase = 0;
+    WorkItem item, next;
+    if (int(blockIdx.x) < total_work) decode_work<BLOCK_N, EPI>(p, prefix, blockIdx.x, next);
     for (int w = blockIdx.x; w < total_work && !*abort_flag; w += gridDim.x) {
-      WorkItem item;
-      decode_work<BLOCK_N, EPI>(p, w, item);
+      item = next;   // the next item's descriptor is fetched while this one is processed
+      if (w + int(gridDim.x) < total_work) decode_work<BLOCK_N, EPI>(p, prefix, w + gridDim.x, next);
       const long long te0 = p.profile ? clock64() : 0;
       if (!ptx::mbar_wait_warp(acc_full_bar + acc, acc_phase)) {
         report(p.error, 0x40000000u | (blockIdx.x << 8) | acc, abort_flag);

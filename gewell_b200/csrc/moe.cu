@@ -67,6 +67,11 @@ gw_status gw_moe_expert_table_create(const gw_expert_weights* experts, uint32_t 
   std::string error;
   for (uint32_t e = 0; e < kExperts; ++e) {
     const gw_projection* proj[3] = {&experts[e].gate, &experts[e].up, &experts[e].down};
+    if (proj[0]->storage == GW_STORAGE_ABSENT && proj[1]->storage == GW_STORAGE_ABSENT &&
+        proj[2]->storage == GW_STORAGE_ABSENT) {
+      info[e] = MoeExpertInfo{};   // lives on another rank: no rows may be routed to it here
+      continue;
+    }
     for (int i = 0; i < 3; ++i) {
       const gw_projection& p = *proj[i];
       const uint32_t want_in = i < 2 ? kHidden : kInter, want_out = i < 2 ? kInter : kHidden;
@@ -176,14 +181,15 @@ int env_int(const char* name, int fallback) {
 
 // Expert MLP over rows sorted by expert: quantise -> gate/up GEMM -> GeGLU +
 // quantise -> down GEMM.  `gather_index` != nullptr reads input rows through
-// the permutation (token = index / 8); otherwise input row i is sorted row i.
+// the permutation (input row = index / gather_divisor); otherwise input row i
+// is sorted row i.
 //
 // Three plans (see moe_prepare_groups_kernel): small batches put the weights on
 // the 128-lane operand and an expert's few tokens on the column operand; large
 // batches put tokens on the lanes, and when gate and up share their input scale
 // the first GEMM's epilogue applies GeGLU and quantises the down input itself.
-gw_status run_experts(gw_moe_workspace* w, const void* input, const int32_t* gather_index, const int32_t* offsets,
-                      uint32_t n, const gw_expert_table* table, void* down_out, cudaStream_t s) {
+gw_status run_experts(gw_moe_workspace* w, const void* input, const int32_t* gather_index, uint32_t gather_divisor,
+                      const int32_t* offsets, uint32_t n, const gw_expert_table* table, void* down_out, cudaStream_t s) {
   const auto* info = table->info.as<MoeExpertInfo>();
   auto* first_groups = w->groups.as<GemmGroup>();
   auto* down_groups = first_groups + 2 * kExperts + 1;
@@ -209,7 +215,7 @@ gw_status run_experts(gw_moe_workspace* w, const void* input, const int32_t* gat
                     block_n_first, block_n_down, table->shared_gate_up ? 1 : 0};
   w->mark(1, s);
   GW_CUDA_CHECK(launch_moe_prepare_groups(plan, first_groups, down_groups, s), "MoE group descriptors");
-  GW_CUDA_CHECK(launch_moe_quantize_input(input, gather_index, w->sorted_keys, offsets, info, n, w->scale_rows, parts,
+  GW_CUDA_CHECK(launch_moe_quantize_input(input, gather_index, gather_divisor, w->sorted_keys, offsets, info, n, w->scale_rows, parts,
                                           w->packed_in.as<uint8_t>(), w->scales_in.as<uint8_t>(), s),
                 "MoE gather + quantise");
   std::string error;
@@ -289,7 +295,7 @@ gw_status gw_moe_run(gw_moe_workspace* w, const void* input_bf16, const void* sc
   w->mark(0, s);
   gw_status status = gw_moe_dispatch(w, scores_bf16, expert_scales_bf16, rows, stream);
   if (status != GW_OK) return status;
-  status = run_experts(w, input_bf16, w->sorted_assignments, w->offsets, 8 * rows, table, w->down.data, s);
+  status = run_experts(w, input_bf16, w->sorted_assignments, 8, w->offsets, 8 * rows, table, w->down.data, s);
   if (status != GW_OK) return status;
   GW_CUDA_CHECK(launch_moe_combine(w->down.data, w->inverse, w->weights, rows, kHidden, output_bf16, s), "MoE combine");
   w->mark(6, s);
@@ -321,9 +327,9 @@ gw_status gw_moe_stage_elapsed_ms(gw_moe_workspace* w, float* milliseconds) {
   return GW_OK;
 }
 
-gw_status gw_moe_run_sorted(gw_moe_workspace* w, const void* input_bf16, const int32_t* offsets, uint32_t first_expert,
-                            uint32_t expert_count, uint32_t total_rows, const gw_expert_table* table, void* output_bf16,
-                            void* stream) {
+gw_status gw_moe_run_sorted(gw_moe_workspace* w, const void* input_bf16, const int32_t* row_index,
+                            const int32_t* offsets, uint32_t first_expert, uint32_t expert_count, uint32_t total_rows,
+                            const gw_expert_table* table, void* output_bf16, void* stream) {
   clear_error();
   if (!w || !table) return fail(GW_INVALID_ARGUMENT, "sorted MoE run requires a workspace and an expert table");
   if (total_rows > w->n) return fail(GW_INVALID_ARGUMENT, "sorted MoE rows exceed workspace (8 x max_rows)");
@@ -332,10 +338,13 @@ gw_status gw_moe_run_sorted(gw_moe_workspace* w, const void* input_bf16, const i
       reinterpret_cast<uintptr_t>(input_bf16) % 16 || reinterpret_cast<uintptr_t>(output_bf16) % 16)
     return fail(GW_INVALID_ARGUMENT, "sorted MoE run requires aligned buffers and an expert range inside 0..128");
   cudaStream_t s = as_stream(stream);
+  w->mark(0, s);
   GW_CUDA_CHECK(launch_moe_keys_from_offsets(offsets, first_expert, expert_count, total_rows, w->sorted_keys,
                                              w->local_offsets, s),
                 "MoE keys from offsets");
-  return run_experts(w, input_bf16, nullptr, w->local_offsets, total_rows, table, output_bf16, s);
+  const gw_status status = run_experts(w, input_bf16, row_index, 1, w->local_offsets, total_rows, table, output_bf16, s);
+  w->mark(6, s);
+  return status;
 }
 
 gw_status gw_gather_rows_bf16(const void* input_bf16, const int32_t* index, uint32_t divisor, uint32_t rows,
@@ -363,6 +372,7 @@ gw_status gw_moe_combine(const void* down_bf16, const int32_t* inverse, const fl
 const int32_t* gw_moe_selected_experts(const gw_moe_workspace* w) { return w ? w->keys : nullptr; }
 const float* gw_moe_routing_weights(const gw_moe_workspace* w) { return w ? w->weights : nullptr; }
 const int32_t* gw_moe_offsets(const gw_moe_workspace* w) { return w ? w->offsets : nullptr; }
+const int32_t* gw_moe_inverse(const gw_moe_workspace* w) { return w ? w->inverse : nullptr; }
 const int32_t* gw_moe_sorted_assignments(const gw_moe_workspace* w) { return w ? w->sorted_assignments : nullptr; }
 const void* gw_moe_gate_up_capture(const gw_moe_workspace* w) { return w ? w->gate_up.data : nullptr; }
 const void* gw_moe_activated_capture(const gw_moe_workspace* w) { return w ? w->activated.data : nullptr; }

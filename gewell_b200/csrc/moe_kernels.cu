@@ -349,7 +349,8 @@ __global__ void __launch_bounds__(256)
 moe_quantize_kernel(const uint4* __restrict__ input, const int32_t* __restrict__ gather_index,
                     const int32_t* __restrict__ sorted_keys, const int32_t* __restrict__ offsets,
                     const MoeExpertInfo* __restrict__ experts, uint32_t n, uint32_t scale_rows, int projection,
-                    uint2* __restrict__ packed, uint8_t* __restrict__ scales, uint4* __restrict__ activated) {
+                    uint32_t gather_divisor, uint2* __restrict__ packed, uint8_t* __restrict__ scales,
+                    uint4* __restrict__ activated) {
   constexpr uint32_t kBlocks = K / 16;
   const size_t index = size_t(blockIdx.x) * 256 + threadIdx.x;
   const uint32_t part = blockIdx.y;             // gate/up copy (0 unless the scales differ)
@@ -377,7 +378,7 @@ moe_quantize_kernel(const uint4* __restrict__ input, const int32_t* __restrict__
       activated[2 * index + 1] = make_uint4(words[4], words[5], words[6], words[7]);
     }
   } else {
-    const size_t source_row = gather_index ? size_t(gather_index[row]) / kTopK : row;
+    const size_t source_row = gather_index ? size_t(uint32_t(gather_index[row]) / gather_divisor) : row;
     const size_t block = source_row * kBlocks + kb;
     unpack8(input[2 * block], values);
     unpack8(input[2 * block + 1], values + 8);
@@ -474,14 +475,14 @@ cudaError_t launch_moe_prepare_groups(const MoeGroupPlan& plan, GemmGroup* first
   return cudaGetLastError();
 }
 
-cudaError_t launch_moe_quantize_input(const void* input, const int32_t* gather_index, const int32_t* sorted_keys,
-                                      const int32_t* offsets, const MoeExpertInfo* experts, uint32_t n,
-                                      uint32_t scale_rows, int parts, uint8_t* packed, uint8_t* scales,
-                                      cudaStream_t stream) {
+cudaError_t launch_moe_quantize_input(const void* input, const int32_t* gather_index, uint32_t gather_divisor,
+                                      const int32_t* sorted_keys, const int32_t* offsets,
+                                      const MoeExpertInfo* experts, uint32_t n, uint32_t scale_rows, int parts,
+                                      uint8_t* packed, uint8_t* scales, cudaStream_t stream) {
   const dim3 grid(blocks_for(size_t(n) * (kHidden / 16)), parts);
   moe_quantize_kernel<kHidden, false><<<grid, 256, 0, stream>>>(
       static_cast<const uint4*>(input), gather_index, sorted_keys, offsets, experts, n, scale_rows, 0,
-      reinterpret_cast<uint2*>(packed), scales, nullptr);
+      gather_divisor ? gather_divisor : 1, reinterpret_cast<uint2*>(packed), scales, nullptr);
   return cudaGetLastError();
 }
 
@@ -490,7 +491,7 @@ cudaError_t launch_moe_activate_quantize(const void* gate_up, const int32_t* sor
                                          uint8_t* scales, void* activated, cudaStream_t stream) {
   const dim3 grid(blocks_for(size_t(n) * (kInter / 16)), 1);
   moe_quantize_kernel<kInter, true><<<grid, 256, 0, stream>>>(
-      static_cast<const uint4*>(gate_up), nullptr, sorted_keys, offsets, experts, n, scale_rows, 2,
+      static_cast<const uint4*>(gate_up), nullptr, sorted_keys, offsets, experts, n, scale_rows, 2, 1,
       reinterpret_cast<uint2*>(packed), scales, static_cast<uint4*>(activated));
   return cudaGetLastError();
 }

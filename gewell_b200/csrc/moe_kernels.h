@@ -45,10 +45,11 @@ cudaError_t launch_moe_keys_from_offsets(const int32_t* offsets, uint32_t first_
                                          cudaStream_t stream);
 cudaError_t launch_moe_prepare_groups(const MoeGroupPlan& plan, GemmGroup* first_groups, GemmGroup* down_groups,
                                       cudaStream_t stream);
-cudaError_t launch_moe_quantize_input(const void* input, const int32_t* gather_index, const int32_t* sorted_keys,
-                                      const int32_t* offsets, const MoeExpertInfo* experts, uint32_t n,
-                                      uint32_t scale_rows, int parts, uint8_t* packed, uint8_t* scales,
-                                      cudaStream_t stream);
+// gather_index != nullptr: sorted row i reads input row gather_index[i] / gather_divisor.
+cudaError_t launch_moe_quantize_input(const void* input, const int32_t* gather_index, uint32_t gather_divisor,
+                                      const int32_t* sorted_keys, const int32_t* offsets,
+                                      const MoeExpertInfo* experts, uint32_t n, uint32_t scale_rows, int parts,
+                                      uint8_t* packed, uint8_t* scales, cudaStream_t stream);
 cudaError_t launch_moe_activate_quantize(const void* gate_up, const int32_t* sorted_keys, const int32_t* offsets,
                                          const MoeExpertInfo* experts, uint32_t n, uint32_t scale_rows, uint8_t* packed,
                                          uint8_t* scales, void* activated, cudaStream_t stream);

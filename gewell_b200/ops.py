@@ -276,11 +276,17 @@ class _RawDeviceBytes:
 class ExpertTable:
     """The 128-entry ExpertWeights table, bound once (keeps the tensors alive)."""
 
-    def __init__(self, experts: list[tuple[Nvfp4Weight, Nvfp4Weight, Nvfp4Weight]]):
+    def __init__(self, experts: list[tuple[Nvfp4Weight, Nvfp4Weight, Nvfp4Weight] | None]):
+        """`experts[i] is None` marks an expert whose weights live on another
+        rank (expert parallelism); no row may be routed to it on this rank."""
         self._lib = _library()
         self._keep = experts
         array = (_lib.ExpertWeights * len(experts))()
-        for i, (gate, up, down) in enumerate(experts):
+        for i, entry in enumerate(experts):
+            if entry is None:
+                array[i].gate.storage = array[i].up.storage = array[i].down.storage = _lib.STORAGE_ABSENT
+                continue
+            gate, up, down = entry
             array[i].gate = make_projection(gate, 2816, 704)
             array[i].up = make_projection(up, 2816, 704)
             array[i].down = make_projection(down, 704, 2816)
@@ -320,10 +326,31 @@ class MoeWorkspace:
         return y
 
     def run_sorted(self, x, offsets, first_expert: int, expert_count: int, total_rows: int, table: ExpertTable, y,
-                   stream=None):
-        _check(self._lib.gw_moe_run_sorted(self._ws, _ptr(x), _ptr(offsets), first_expert, expert_count, total_rows,
-                                           table.handle, _ptr(y), _stream(stream)))
+                   row_index=None, stream=None):
+        """Expert MLP over rows sorted by local expert; sorted row i is
+        x[row_index[i]] (x[i] when row_index is None)."""
+        _check(self._lib.gw_moe_run_sorted(self._ws, _ptr(x), _ptr(row_index), _ptr(offsets), first_expert,
+                                           expert_count, total_rows, table.handle, _ptr(y), _stream(stream)))
         return y
+
+    def _alias(self, pointer: int, shape, dtype):
+        """Zero-copy tensor over a workspace buffer (valid while the workspace lives)."""
+        count = 1
+        for s in shape:
+            count *= s
+        nbytes = count * torch.empty((), dtype=dtype).element_size()
+        raw = torch.as_tensor(_RawDeviceBytes(pointer, nbytes), device=self.device)
+        return raw.view(dtype).reshape(shape)
+
+    def routing_state(self, rows: int):
+        """Aliases (no copies) of the routing results of the last dispatch over
+        `rows` tokens: offsets [129], sorted_assignments [8*rows], inverse
+        [8*rows], weights [8*rows]."""
+        n = 8 * rows
+        return (self._alias(self._lib.gw_moe_offsets(self._ws), (129,), torch.int32),
+                self._alias(self._lib.gw_moe_sorted_assignments(self._ws), (n,), torch.int32),
+                self._alias(self._lib.gw_moe_inverse(self._ws), (n,), torch.int32),
+                self._alias(self._lib.gw_moe_routing_weights(self._ws), (n,), torch.float32))
 
     def _view(self, pointer: int, shape, dtype):
         """Copy of a workspace buffer as a tensor (the workspace owns the memory)."""

@@ -162,7 +162,10 @@ gw_status gw_weight_qdq_apply(int type, void* values_bf16, uint64_t elements, ui
 /* ------------------------------------------------------------------------- */
 /* MoE -- models/gemma4/26b_a4b/sm120/{projection.cuh:11-17, moe.cuh:11-48}   */
 /* ------------------------------------------------------------------------- */
-enum { GW_STORAGE_BF16 = 0, GW_STORAGE_NVFP4_W4A4 = 1, GW_STORAGE_FP8_W8A8 = 2 };
+enum { GW_STORAGE_BF16 = 0, GW_STORAGE_NVFP4_W4A4 = 1, GW_STORAGE_FP8_W8A8 = 2,
+       /* expert-parallel only (no counterpart in the reference): the expert's
+        * weights live on another rank; all three projections carry this tag */
+       GW_STORAGE_ABSENT = 3 };
 
 /* sm120::Projection (projection.cuh:11-17), flattened. */
 typedef struct gw_projection {
@@ -216,6 +219,9 @@ const int32_t* gw_moe_selected_experts(const gw_moe_workspace* workspace);   /* 
 const float* gw_moe_routing_weights(const gw_moe_workspace* workspace);      /* [8*rows] */
 const int32_t* gw_moe_offsets(const gw_moe_workspace* workspace);            /* [129] */
 const int32_t* gw_moe_sorted_assignments(const gw_moe_workspace* workspace); /* [8*rows] */
+/* inverse[8*t + slot] = sorted position of that assignment (moe.cu:158-182 `invert`);
+ * the reference keeps it private, the expert-parallel combine needs it. */
+const int32_t* gw_moe_inverse(const gw_moe_workspace* workspace);            /* [8*rows] */
 const void* gw_moe_gate_up_capture(const gw_moe_workspace* workspace);       /* BF16 [8*rows,1408] */
 const void* gw_moe_activated_capture(const gw_moe_workspace* workspace);     /* BF16 [8*rows,704] */
 const void* gw_moe_down_capture(const gw_moe_workspace* workspace);          /* BF16 [8*rows,2816] */
@@ -243,10 +249,11 @@ gw_status gw_moe_stage_elapsed_ms(gw_moe_workspace* workspace, float* millisecon
 /* Expert-parallel building blocks (no counterpart in the reference, which is
  * single GPU).  A rank that owns experts [first, first+count) runs the expert
  * MLP over rows that are already sorted by expert: `offsets` (device, int32,
- * count+1 entries) delimit each local expert's rows inside `input_bf16`
- * [total_rows, 2816]; output BF16 [total_rows, 2816], unweighted. */
+ * count+1 entries) delimit each local expert's rows; sorted row i is row
+ * row_index[i] of `input_bf16` (row i itself when row_index is NULL); output
+ * BF16 [total_rows, 2816] in sorted order, unweighted. */
 gw_status gw_moe_run_sorted(gw_moe_workspace* workspace, const void* input_bf16,
-                            const int32_t* offsets, uint32_t first_expert, uint32_t expert_count,
+                            const int32_t* row_index, const int32_t* offsets, uint32_t first_expert, uint32_t expert_count,
                             uint32_t total_rows, const gw_expert_table* table, void* output_bf16,
                             void* stream);
 
