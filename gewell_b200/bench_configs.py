@@ -33,6 +33,33 @@ def _time(fn, iters: int, warmup: int = 3) -> float:
     return start.elapsed_time(stop) / iters
 
 
+def _time_graph(fn, calls: int, replays: int = 10) -> float:
+    """Per-call time of `calls` consecutive calls (fn(i), i = 0..calls-1) captured
+    into one CUDA graph and replayed: the launch cost on the host drops out, the
+    dependencies between the kernels stay."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for i in range(calls):
+            fn(i)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(calls):
+            fn(i)
+    for _ in range(2):
+        graph.replay()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(replays):
+        graph.replay()
+    stop.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) / (replays * calls)
+
+
 def _copies(nbytes: int) -> int:
     return max(2, -(-2 * L2_BYTES // nbytes))
 
@@ -60,11 +87,14 @@ def bench_fp8_decode(rows_list=(1, 8, 32, 64), n=43008, k=5376, iters=20):
         def run(i=0):
             plan.run(x, ws[i % copies], y, scratch)
 
-        ms = _time(run, iters)
+        eager_ms = _time(run, iters)
+        ms = _time_graph(run, 2 * copies)
         algorithmic = n * k + 4 * n + rows * k * 2 + rows * n * 2
-        out.append({"config": "c2_fp8_decode", "rows": rows, "K": k, "N": n, "ms": ms,
+        out.append({"config": "c2_fp8_decode", "rows": rows, "K": k, "N": n, "ms": ms, "eager_ms": eager_ms,
+                    "timing": "CUDA-graph replay of plan.run (quantise + GEMM); eager_ms = the same calls issued one by one",
                     "algorithmic_bytes": algorithmic, "GBps": algorithmic / ms / 1e6,
-                    "TFLOPs": 2.0 * rows * n * k / ms / 1e9, "weight_copies_rotated": copies})
+                    "TFLOPs": 2.0 * rows * n * k / ms / 1e9, "weight_copies_rotated": copies,
+                    "kernel_error": gw.kernel_error()})
     return out
 
 
@@ -97,6 +127,9 @@ def bench_nvfp4_linear(rows, n, k, name, iters=20, seed=3):
 
     ms = _time(run, iters)
     qms = _time(quantise_only, iters)
+    if rows <= 128:     # decode-shaped: launch cost on the host would dominate an eager loop
+        ms = _time_graph(run, 2 * copies)
+        qms = _time_graph(quantise_only, 2 * copies)
     algorithmic = wbytes + rows * k * 2 + rows * n * 2
     flops = 2.0 * rows * n * k
     return {"config": name, "rows": rows, "K": k, "N": n, "ms": ms, "quantise_ms": qms, "gemm_ms": ms - qms,

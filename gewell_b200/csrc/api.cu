@@ -176,7 +176,7 @@ gw_status gw_nvfp4_gemv_w4a16(const void* input_bf16, uint32_t rows, const uint8
 
 struct gw_nvfp4_plan {
   uint32_t rows, input_width, output_width;
-  size_t scale_offset, total_bytes;
+  size_t scale_offset, split_offset, total_bytes;
   DenseDescriptors descriptors;
 };
 
@@ -192,7 +192,15 @@ gw_status gw_nvfp4_plan_create(uint32_t rows, uint32_t input_width, uint32_t out
   p->output_width = output_width;
   // scratch = packed activations | tiled activation scales   (each 256-byte aligned)
   p->scale_offset = align_up(size_t(rows) * input_width / 2, 256);
-  p->total_bytes = p->scale_offset + align_up(scale_storage_bytes(rows, input_width), 256);
+  p->split_offset = p->scale_offset + align_up(scale_storage_bytes(rows, input_width), 256);
+  // Decode shapes split the K loop evenly over the SMs; that needs per-tile counters owned
+  // by the plan and room for FP32 partial tiles in the scratch.  Without a usable device
+  // (or memory for the counters) the plan falls back to whole tiles per CTA.
+  p->total_bytes = p->split_offset;
+  if (p->descriptors.allocate_split_counters(rows, output_width) == cudaSuccess && p->descriptors.split_counters)
+    p->total_bytes += align_up(dense_split_bytes(rows, output_width), 256);
+  else
+    (void)cudaGetLastError();
   *plan = p;
   return GW_OK;
 }
@@ -223,6 +231,7 @@ gw_status gw_nvfp4_plan_run(gw_nvfp4_plan* plan, const void* input_bf16, const u
                 "NVFP4 quantize activations");
   DenseProblem problem{GemmKind::nvfp4, plan->rows, plan->input_width, plan->output_width, weight_data, weight_scales,
                        packed, scales, alpha, nullptr, output_bf16, device_error_word()};
+  if (plan->total_bytes != plan->split_offset) problem.split_workspace = packed + plan->split_offset;
   return launch_dense(problem, &plan->descriptors, s);
 }
 
@@ -256,7 +265,7 @@ gw_status gw_fp8_pack_weights(const void* weights_bf16, uint32_t output_width, u
 struct gw_fp8_plan {
   uint32_t rows, input_width, output_width;
   bool channel_scales;
-  size_t total_bytes;
+  size_t split_offset, total_bytes;
   DenseDescriptors descriptors;
 };
 
@@ -274,7 +283,15 @@ gw_status gw_fp8_plan_create(uint32_t rows, uint32_t input_width, uint32_t outpu
   p->input_width = input_width;
   p->output_width = output_width;
   p->channel_scales = channel_scales != 0;
-  p->total_bytes = align_up(size_t(rows) * input_width, 256);
+  p->split_offset = align_up(size_t(rows) * input_width, 256);
+  // Decode shapes split the K loop evenly over the SMs; that needs per-tile counters owned
+  // by the plan and room for FP32 partial tiles in the scratch.  Without a usable device
+  // (or memory for the counters) the plan falls back to whole tiles per CTA.
+  p->total_bytes = p->split_offset;
+  if (p->descriptors.allocate_split_counters(rows, output_width) == cudaSuccess && p->descriptors.split_counters)
+    p->total_bytes += align_up(dense_split_bytes(rows, output_width), 256);
+  else
+    (void)cudaGetLastError();
   *plan = p;
   return GW_OK;
 }
@@ -305,6 +322,7 @@ gw_status gw_fp8_plan_run(gw_fp8_plan* plan, const void* input_bf16, const uint8
   DenseProblem problem{GemmKind::fp8, plan->rows, plan->input_width, plan->output_width, weight_data, nullptr,
                        packed, nullptr, alpha, plan->channel_scales ? channel_scales : nullptr, output_bf16,
                        device_error_word()};
+  if (plan->total_bytes != plan->split_offset) problem.split_workspace = packed + plan->split_offset;
   return launch_dense(problem, &plan->descriptors, s);
 }
 

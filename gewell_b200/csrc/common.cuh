@@ -52,6 +52,16 @@ __host__ __device__ __forceinline__ size_t scale_offset(size_t row, size_t block
 }
 
 #ifdef __CUDACC__
+// Programmatic dependent launch.  A kernel launched with the programmatic-
+// serialisation attribute may start while its predecessor in the stream still
+// runs; griddep_wait() blocks until that predecessor has completed and its
+// writes are visible (no-op for a normal launch).  griddep_launch() lets the
+// successor start being scheduled.  Every kernel that can be launched that way
+// calls griddep_wait() in all threads before touching global memory, so the
+// usual stream order still holds transitively.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ float rcp_approx_ftz(float value) {
   float result;
   asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(result) : "f"(value));

@@ -22,6 +22,32 @@ int dense_block_n(uint32_t rows) {
   return 256;
 }
 
+namespace {
+size_t split_counter_bytes(uint32_t rows, uint32_t n) {
+  const int block_n = dense_block_n(rows);
+  const size_t tiles = size_t((n + 127) / 128) * ((rows + block_n - 1) / block_n);
+  return align_up(tiles * sizeof(int32_t), 256);
+}
+}  // namespace
+
+size_t dense_split_bytes(uint32_t rows, uint32_t n) {
+  (void)n;
+  if (!dense_uses_swap_form(rows) || std::getenv("GW_DENSE_NO_SPLIT")) return 0;
+  return size_t(2) * sm_count() * 128 * dense_block_n(rows) * sizeof(float);
+}
+
+cudaError_t DenseDescriptors::allocate_split_counters(uint32_t rows, uint32_t n) {
+  if (dense_split_bytes(rows, n) == 0) return cudaSuccess;
+  const size_t bytes = split_counter_bytes(rows, n);
+  cudaError_t status = cudaMalloc(&split_counters, bytes);
+  if (status == cudaSuccess) status = cudaMemset(split_counters, 0, bytes);
+  return status;
+}
+
+DenseDescriptors::~DenseDescriptors() {
+  if (split_counters != nullptr) cudaFree(split_counters);
+}
+
 gw_status launch_dense(const DenseProblem& q, DenseDescriptors* cache, cudaStream_t stream) {
   const bool swap = dense_uses_swap_form(q.rows);
   const int block_n = dense_block_n(q.rows);
@@ -74,7 +100,13 @@ gw_status launch_dense(const DenseProblem& q, DenseDescriptors* cache, cudaStrea
     g.c_half_stride = block_n > 128 ? 128 : 0;
   }
   params.total_work = g.l_tiles * g.c_tiles;
-  const int grid = params.total_work < sm_count() ? params.total_work : sm_count();
+  int grid = params.total_work < sm_count() ? params.total_work : sm_count();
+  if (swap && q.split_workspace != nullptr && cache->split_counters != nullptr) {
+    params.split_counters = cache->split_counters;
+    params.split_partials = static_cast<float*>(q.split_workspace);
+    const long long stages = (long long)((row_bytes + 127) / 128) * params.total_work;
+    grid = stages < sm_count() ? int(stages) : sm_count();
+  }
   GW_CUDA_CHECK(launch_gemm_tc(q.kind, swap ? GemmEpilogue::swap_store : GemmEpilogue::direct_store, block_n, params,
                                grid, stream),
                 fp4 ? "NVFP4 tensor-core GEMM" : "FP8 tensor-core GEMM");

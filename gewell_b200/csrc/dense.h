@@ -12,6 +12,11 @@ struct DenseDescriptors {          // re-encoded only when a pointer changes
   const void* weight = nullptr;
   const void* activations = nullptr;
   CUtensorMap weight_map{}, activation_map{};
+  // Split mode: one arrival counter per weight tile, owned by the plan (device memory,
+  // zeroed at creation; the kernel leaves every counter at zero again).
+  int32_t* split_counters = nullptr;
+  cudaError_t allocate_split_counters(uint32_t rows, uint32_t n);
+  ~DenseDescriptors();
 };
 
 struct DenseProblem {
@@ -25,11 +30,18 @@ struct DenseProblem {
   const float* channel_alpha;
   void* output;
   uint32_t* error;
+  // Optional, decode shapes only: dense_split_bytes() bytes, 256-byte aligned, for FP32
+  // partial tiles.  With it (and the plan's counters) the K loop of the weight tiles is
+  // divided evenly over the SMs (see GemmParams).
+  void* split_workspace = nullptr;
 };
 
 // true: weights on the 128-lane operand and tokens on the column operand.
 bool dense_uses_swap_form(uint32_t rows);
 int dense_block_n(uint32_t rows);
+
+// Bytes of split workspace a projection of this shape can use (0: none).
+size_t dense_split_bytes(uint32_t rows, uint32_t n);
 
 gw_status launch_dense(const DenseProblem& problem, DenseDescriptors* cache, cudaStream_t stream);
 

@@ -48,7 +48,7 @@ struct Config {
   static constexpr int kStageBytes = kLBytes + kCBytes + kSflBytes + kSfcBytes;
   static constexpr int kMaxSmem = 227 * 1024 - 2048;   // leave room for barriers + alignment slack
   static constexpr int kStagesRaw = kMaxSmem / kStageBytes;
-  static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+  static constexpr int kStages = kStagesRaw > 12 ? 12 : kStagesRaw;
   static constexpr int kSfcColsPerKb = 4 * kHalves;
   static constexpr int kAccCols = kAccStages * BLOCK_N;
   // one scale slot per smem stage: [L scales: 4 columns per K-block][C scales]
@@ -113,6 +113,47 @@ __device__ __forceinline__ void decode_work(const GemmParams& p, const int32_t* 
   else item.mma_n = item.halves * C::kHalfRows;
 }
 
+// Walks the work of one CTA.  Normal mode: whole work items blockIdx.x,
+// blockIdx.x + gridDim.x, ...  Split mode (decode shapes): the launch's
+// (item, K-stage) units are cut into gridDim.x equal contiguous ranges, so a CTA
+// may start and end in the middle of an item's K loop; every SM then streams
+// the same number of weight bytes whatever the number of tiles.
+struct SegmentWalk {
+  bool split;
+  int w, step, total_work, k_stages;
+  long long u, u_begin, u_end, total_units;
+  __device__ SegmentWalk(bool split_, int total_work_, int k_stages_)
+      : split(split_), w(blockIdx.x), step(gridDim.x), total_work(total_work_), k_stages(k_stages_) {
+    total_units = (long long)total_work * k_stages;
+    u_begin = u = total_units * blockIdx.x / gridDim.x;
+    u_end = total_units * (blockIdx.x + 1) / gridDim.x;
+  }
+  // next segment: work item `tile`, K stages [ks0, ks1)
+  __device__ bool next(int& tile, int& ks0, int& ks1, bool& at_range_start) {
+    if (!split) {
+      if (w >= total_work) return false;
+      tile = w; ks0 = 0; ks1 = k_stages; at_range_start = false;
+      w += step;
+      return true;
+    }
+    if (u >= u_end) return false;
+    tile = int(u / k_stages);
+    ks0 = int(u % k_stages);
+    const long long left = u_end - u;
+    ks1 = left < (long long)(k_stages - ks0) ? ks0 + int(left) : k_stages;
+    at_range_start = u == u_begin;
+    u += ks1 - ks0;
+    return true;
+  }
+  // CTA whose range holds unit x
+  __device__ int cta_of(long long x) const { return int(((x + 1) * step + total_units - 1) / total_units) - 1; }
+  __device__ long long range_begin(int cta) const { return total_units * cta / step; }
+};
+
+__device__ __forceinline__ void named_barrier_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
 __device__ __forceinline__ void report(uint32_t* error, uint32_t code, volatile int* abort_flag) {
   *abort_flag = 1;
   if (error != nullptr) atomicCAS(error, 0u, code);
@@ -136,9 +177,9 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
   uint64_t* acc_empty_bar = acc_full_bar + C::kAccStages;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + C::kAccStages);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* split_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
   int32_t* prefix = reinterpret_cast<int32_t*>(tmem_slot + 4);   // work_begin of every group (+ sentinel)
-  if (p.groups != nullptr)
-    for (int i = threadIdx.x; i <= p.num_groups; i += kThreads) prefix[i] = p.groups[i].work_begin;
+  griddep_launch();
 
   const int warp = threadIdx.x / 32;
   const int lane = threadIdx.x % 32;
@@ -165,12 +206,20 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
   __syncthreads();
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // Everything above is independent of earlier kernels in the stream and may overlap
+  // them (programmatic dependent launch); from here on their results are read.
+  griddep_wait();
+  if (p.groups != nullptr) {
+    for (int i = threadIdx.x; i <= p.num_groups; i += kThreads) prefix[i] = p.groups[i].work_begin;
+    __syncthreads();
+  }
 
   const int total_work = p.groups != nullptr ? prefix[p.num_groups] : p.total_work;
   const int k_bytes = kNvfp4 ? p.k / 2 : p.k;
   const int total_kb = (k_bytes + 31) / 32;                 // MMA K-blocks (32 bytes of K each)
   const int k_stages = (total_kb + kKBlocksPerStage - 1) / kKBlocksPerStage;
   const int k_atoms = p.k / 64;                             // scale atoms per 128-row block (NVFP4)
+  const bool split = p.split_partials != nullptr;
 
   // shared-memory descriptors: high words are constants, low word = address >> 4
   constexpr uint32_t kDescHiSw128 = uint32_t(1024 >> 4) | (1u << 14) | (2u << 29);   // SBO 1024 B, version 1, SWIZZLE_128B
@@ -197,15 +246,24 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
     int stage = 0;
     uint32_t phase = 0;
     WorkItem item, next;
-    if (int(blockIdx.x) < total_work) decode_work<BLOCK_N, EPI>(p, prefix, blockIdx.x, next);
-    for (int w = blockIdx.x; w < total_work && !*abort_flag; w += gridDim.x) {
-      item = next;   // the next item's descriptor is fetched while this one is processed
-      if (w + int(gridDim.x) < total_work) decode_work<BLOCK_N, EPI>(p, prefix, w + gridDim.x, next);
+    SegmentWalk walk(split, total_work, k_stages);
+    int tile, ks0, ks1, next_tile, next_ks0, next_ks1;
+    bool at_start, next_at_start;
+    bool more = walk.next(next_tile, next_ks0, next_ks1, next_at_start);
+    if (more) decode_work<BLOCK_N, EPI>(p, prefix, next_tile, next);
+    while (more && !*abort_flag) {
+      item = next; tile = next_tile; ks0 = next_ks0; ks1 = next_ks1; at_start = next_at_start;
+      // the next item's descriptor is fetched while this one is processed
+      more = walk.next(next_tile, next_ks0, next_ks1, next_at_start);
+      if (more) decode_work<BLOCK_N, EPI>(p, prefix, next_tile, next);
+      (void)tile; (void)at_start;
       const CUtensorMap* map_l = item.g.map_l >= 0 ? p.map_table + item.g.map_l : &p.map_l;
       const CUtensorMap* map_c[2];
+#pragma unroll
       for (int h = 0; h < C::kHalves; ++h) map_c[h] = item.g.map_c[h] >= 0 ? p.map_table + item.g.map_c[h] : &p.map_c;
       if (lane == 0) {
         if (item.g.map_l >= 0) ptx::tensormap_acquire(map_l);
+#pragma unroll
         for (int h = 0; h < C::kHalves; ++h)
           if (item.g.map_c[h] >= 0) ptx::tensormap_acquire(map_c[h]);
       }
@@ -217,6 +275,7 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
       const uint8_t* sfc_src[2] = {nullptr, nullptr};
       int c_row[2] = {0, 0};
       if constexpr (kNvfp4) sfl_src = item.g.sf_l + size_t(item.l_tile) * k_atoms * kAtomBytes;
+#pragma unroll
       for (int h = 0; h < C::kHalves; ++h) {
         c_row[h] = item.g.c_row0 + c_local + h * item.g.c_half_stride;
         if constexpr (kNvfp4)
@@ -224,7 +283,7 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
       }
       const uint32_t full_stage_bytes =
           C::kLBytes + halves * C::kHalfRows * kStageRowBytes + (kNvfp4 ? kKBlocksPerStage * kAtomBytes * (1 + halves) : 0);
-      for (int ks = 0; ks < k_stages; ++ks) {
+      for (int ks = ks0; ks < ks1; ++ks) {
         const long long t0 = p.profile ? clock64() : 0;
         if (!ptx::mbar_wait_warp(empty_bar + stage, phase ^ 1)) {
           report(p.error, 0x10000000u | (blockIdx.x << 8) | stage, abort_flag);
@@ -239,15 +298,19 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
           uint64_t* bar = full_bar + stage;
           ptx::mbar_expect_tx(bar, bytes);
           ptx::tma_load_2d(base, map_l, ks * kStageRowBytes, l_row, bar);
-          for (int h = 0; h < halves; ++h)
-            ptx::tma_load_2d(base + C::kLBytes + h * C::kHalfRows * kStageRowBytes, map_c[h], ks * kStageRowBytes,
-                             c_row[h], bar);
+#pragma unroll
+          for (int h = 0; h < C::kHalves; ++h)     // compile-time bound: map_c / c_row stay in registers
+            if (h < halves)
+              ptx::tma_load_2d(base + C::kLBytes + h * C::kHalfRows * kStageRowBytes, map_c[h], ks * kStageRowBytes,
+                               c_row[h], bar);
           if constexpr (kNvfp4) {
             const size_t atom_offset = size_t(ks) * kKBlocksPerStage * kAtomBytes;
             ptx::bulk_load(base + C::kLBytes + C::kCBytes, sfl_src + atom_offset, nkb * kAtomBytes, bar);
-            for (int h = 0; h < halves; ++h)
-              ptx::bulk_load(base + C::kLBytes + C::kCBytes + C::kSflBytes + h * kKBlocksPerStage * kAtomBytes,
-                             sfc_src[h] + atom_offset, nkb * kAtomBytes, bar);
+#pragma unroll
+            for (int h = 0; h < C::kHalves; ++h)
+              if (h < halves)
+                ptx::bulk_load(base + C::kLBytes + C::kCBytes + C::kSflBytes + h * kKBlocksPerStage * kAtomBytes,
+                               sfc_src[h] + atom_offset, nkb * kAtomBytes, bar);
           }
         }
         __syncwarp();
@@ -259,10 +322,16 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
     int stage = 0, acc = 0;
     uint32_t phase = 0, acc_phase = 0;
     WorkItem item, next;
-    if (int(blockIdx.x) < total_work) decode_work<BLOCK_N, EPI>(p, prefix, blockIdx.x, next);
-    for (int w = blockIdx.x; w < total_work && !*abort_flag; w += gridDim.x) {
-      item = next;   // the next item's descriptor is fetched while this one is processed
-      if (w + int(gridDim.x) < total_work) decode_work<BLOCK_N, EPI>(p, prefix, w + gridDim.x, next);
+    SegmentWalk walk(split, total_work, k_stages);
+    int tile, ks0, ks1, next_tile, next_ks0, next_ks1;
+    bool at_start, next_at_start;
+    bool more = walk.next(next_tile, next_ks0, next_ks1, next_at_start);
+    if (more) decode_work<BLOCK_N, EPI>(p, prefix, next_tile, next);
+    while (more && !*abort_flag) {
+      item = next; tile = next_tile; ks0 = next_ks0; ks1 = next_ks1; at_start = next_at_start;
+      more = walk.next(next_tile, next_ks0, next_ks1, next_at_start);
+      if (more) decode_work<BLOCK_N, EPI>(p, prefix, next_tile, next);
+      (void)tile; (void)at_start;
       const long long ta = p.profile ? clock64() : 0;
       if (!ptx::mbar_wait_warp(acc_empty_bar + acc, acc_phase ^ 1)) {
         report(p.error, 0x20000000u | (blockIdx.x << 8) | acc, abort_flag);
@@ -277,7 +346,7 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
       const uint32_t sfc_sub = BLOCK_N < 128 ? (c_local % 128) / 32 : 0;
       const int halves = item.halves;
       bool failed = false;
-      for (int ks = 0; ks < k_stages; ++ks) {
+      for (int ks = ks0; ks < ks1; ++ks) {
         const long long t0 = p.profile ? clock64() : 0;
         if (!ptx::mbar_wait_warp(full_bar + stage, phase)) {
           report(p.error, 0x30000000u | (blockIdx.x << 8) | stage, abort_flag);
@@ -303,7 +372,7 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
           const uint32_t base16 = smem_base16 + uint32_t(stage) * uint32_t(C::kStageBytes >> 4);
           const uint32_t sfl_t = sfl_tmem + uint32_t(stage) * C::kSfSlotCols;
           const uint32_t sfc_t = sfc_tmem + uint32_t(stage) * C::kSfSlotCols + sfc_sub;
-          const uint32_t first = ks == 0 ? 0u : 1u;
+          const uint32_t first = ks == ks0 ? 0u : 1u;
 #pragma unroll
           for (int kb = 0; kb < kKBlocksPerStage; ++kb) {
             if (kb < nkb) {
@@ -339,13 +408,19 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
       int stage = 0;
       uint32_t phase = 0;
       WorkItem item, next;
-      if (int(blockIdx.x) < total_work) decode_work<BLOCK_N, EPI>(p, prefix, blockIdx.x, next);
-      for (int w = blockIdx.x; w < total_work && !*abort_flag; w += gridDim.x) {
-        item = next;
-        if (w + int(gridDim.x) < total_work) decode_work<BLOCK_N, EPI>(p, prefix, w + gridDim.x, next);
+      SegmentWalk walk(split, total_work, k_stages);
+      int tile, ks0, ks1, next_tile, next_ks0, next_ks1;
+      bool at_start, next_at_start;
+      bool more = walk.next(next_tile, next_ks0, next_ks1, next_at_start);
+      if (more) decode_work<BLOCK_N, EPI>(p, prefix, next_tile, next);
+      while (more && !*abort_flag) {
+        item = next; tile = next_tile; ks0 = next_ks0; ks1 = next_ks1; at_start = next_at_start;
+        more = walk.next(next_tile, next_ks0, next_ks1, next_at_start);
+        if (more) decode_work<BLOCK_N, EPI>(p, prefix, next_tile, next);
+        (void)tile; (void)at_start;
         const int halves = item.halves;
         bool failed = false;
-        for (int ks = 0; ks < k_stages; ++ks) {
+        for (int ks = ks0; ks < ks1; ++ks) {
           if (!ptx::mbar_wait_warp(full_bar + stage, phase)) {
             report(p.error, 0x60000000u | (blockIdx.x << 8) | stage, abort_flag);
             failed = true;
@@ -400,10 +475,16 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
     int acc = 0;
     uint32_t acc_phase = 0;
     WorkItem item, next;
-    if (int(blockIdx.x) < total_work) decode_work<BLOCK_N, EPI>(p, prefix, blockIdx.x, next);
-    for (int w = blockIdx.x; w < total_work && !*abort_flag; w += gridDim.x) {
-      item = next;   // the next item's descriptor is fetched while this one is processed
-      if (w + int(gridDim.x) < total_work) decode_work<BLOCK_N, EPI>(p, prefix, w + gridDim.x, next);
+    SegmentWalk walk(split, total_work, k_stages);
+    int tile, ks0, ks1, next_tile, next_ks0, next_ks1;
+    bool at_start, next_at_start;
+    bool more = walk.next(next_tile, next_ks0, next_ks1, next_at_start);
+    if (more) decode_work<BLOCK_N, EPI>(p, prefix, next_tile, next);
+    while (more && !*abort_flag) {
+      item = next; tile = next_tile; ks0 = next_ks0; ks1 = next_ks1; at_start = next_at_start;
+      more = walk.next(next_tile, next_ks0, next_ks1, next_at_start);
+      if (more) decode_work<BLOCK_N, EPI>(p, prefix, next_tile, next);
+      (void)tile; (void)at_start;
       const long long te0 = p.profile ? clock64() : 0;
       if (!ptx::mbar_wait_warp(acc_full_bar + acc, acc_phase)) {
         report(p.error, 0x40000000u | (blockIdx.x << 8) | acc, abort_flag);
@@ -422,15 +503,65 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
         float alpha = item.g.alpha[0];
         if (item.g.channel_alpha != nullptr && l_ok) alpha = item.g.channel_alpha[l_index];
         bf16* dst = out + (size_t(item.g.out_row0) + size_t(item.c_tile) * BLOCK_N) * p.ld_out + item.g.out_col0 + l_index;
-        for (int c0 = col_half * 16; c0 < item.mma_n; c0 += 32) {
-          uint32_t r[16];
-          ptx::tmem_load16(taddr + c0, r);
-          ptx::tmem_load_wait();
-          if (l_ok) {
+        const bool partial = ks1 - ks0 < k_stages;      // only in split mode
+        if (!partial) {
+          for (int c0 = col_half * 16; c0 < item.mma_n; c0 += 32) {
+            uint32_t r[16];
+            ptx::tmem_load16(taddr + c0, r);
+            ptx::tmem_load_wait();
+            if (l_ok) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i)
-              if (c0 + i < item.c_valid)
-                dst[size_t(c0 + i) * p.ld_out] = __float2bfloat16_rn(__fmul_rn(__uint_as_float(r[i]), alpha));
+              for (int i = 0; i < 16; ++i)
+                if (c0 + i < item.c_valid)
+                  dst[size_t(c0 + i) * p.ld_out] = __float2bfloat16_rn(__fmul_rn(__uint_as_float(r[i]), alpha));
+            }
+          }
+        } else {
+          // This CTA covered only K stages [ks0, ks1) of the tile.  Its FP32 partial goes to
+          // this CTA's slot ([column][lane], so a warp writes 128 contiguous bytes); the CTA
+          // that arrives last at the tile's counter adds the slots in CTA order -- a fixed
+          // order, so the result does not depend on which CTA that was -- and stores.
+          const int row = quad * 32 + lane;
+          float* mine = p.split_partials + (size_t(blockIdx.x) * 2 + (at_start ? 0 : 1)) * size_t(kTileL * BLOCK_N);
+          for (int c0 = col_half * 16; c0 < item.mma_n; c0 += 32) {
+            uint32_t r[16];
+            ptx::tmem_load16(taddr + c0, r);
+            ptx::tmem_load_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) __stcg(mine + (c0 + i) * kTileL + row, __uint_as_float(r[i]));
+          }
+          __threadfence();
+          named_barrier_sync(1, kEpilogueWarps * 32);
+          const long long tile_first_unit = (long long)tile * k_stages;
+          const int cta_first = walk.cta_of(tile_first_unit);
+          const int cta_last = walk.cta_of(tile_first_unit + k_stages - 1);
+          if (threadIdx.x == kFirstEpilogueWarp * 32) {
+            const int arrived = atomicAdd(p.split_counters + tile, 1);
+            const int last = arrived == cta_last - cta_first;
+            if (last) p.split_counters[tile] = 0;         // ready for the next launch
+            *split_flag = last;
+          }
+          named_barrier_sync(1, kEpilogueWarps * 32);
+          if (*split_flag) {
+            __threadfence();
+            for (int c0 = col_half * 16; c0 < item.mma_n; c0 += 32) {
+              float sum[16];
+#pragma unroll
+              for (int i = 0; i < 16; ++i) sum[i] = 0.0F;
+              for (int cta = cta_first; cta <= cta_last; ++cta) {
+                // the tile is the first segment of every CTA but (possibly) the first one
+                const int which = (cta == cta_first && walk.range_begin(cta) < tile_first_unit) ? 1 : 0;
+                const float* theirs = p.split_partials + (size_t(cta) * 2 + which) * size_t(kTileL * BLOCK_N);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) sum[i] += __ldcg(theirs + (c0 + i) * kTileL + row);
+              }
+              if (l_ok) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                  if (c0 + i < item.c_valid)
+                    dst[size_t(c0 + i) * p.ld_out] = __float2bfloat16_rn(__fmul_rn(sum[i], alpha));
+              }
+            }
           }
         }
       } else if constexpr (EPI == GemmEpilogue::direct_store) {
@@ -578,8 +709,17 @@ cudaError_t launch(const GemmParams& params_in, int grid, cudaStream_t stream) {
     if (status != cudaSuccess) return status;
     configured = true;
   }
-  gemm_tc_kernel<kNvfp4, BLOCK_N, EPI><<<grid, kThreads, C::kSmemBytes, stream>>>(params);
-  return cudaGetLastError();
+  cudaLaunchConfig_t config{};
+  config.gridDim = dim3(grid);
+  config.blockDim = dim3(kThreads);
+  config.dynamicSmemBytes = C::kSmemBytes;
+  config.stream = stream;
+  cudaLaunchAttribute attribute{};
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, gemm_tc_kernel<kNvfp4, BLOCK_N, EPI>, params);
 }
 
 }  // namespace

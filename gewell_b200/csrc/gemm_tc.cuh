@@ -63,6 +63,10 @@ struct GemmParams {
   int32_t out_width;              // GeGLU+quantise: logical width (K of the consumer)
   void* capture_gate_up;          // GeGLU+quantise: optional BF16 [rows, 2*out_width]
   void* capture_activated;        // GeGLU+quantise: optional BF16 [rows, out_width]
+  // Split mode (swap form, groups == nullptr): work is divided into equal ranges of
+  // (tile, K stage) units; partial tiles are summed through these buffers.
+  float* split_partials;          // [2 * grid][128 * BLOCK_N] FP32, or nullptr (whole tiles per CTA)
+  int32_t* split_counters;        // [work items], zero at launch; left zero by the kernel
   uint32_t* error;                // device error word (0 = fine)
   long long* profile;             // optional [grid][8] cycle counters (debug aid), normally nullptr
 };

@@ -105,6 +105,7 @@ nvfp4_quantize_kernel(const uint4* __restrict__ input, uint32_t rows, uint32_t w
                       float inverse_global_scale, uint2* __restrict__ packed,
                       uint8_t* __restrict__ scales, size_t padded_blocks,
                       uint32_t padded_blocks_per_row) {
+  griddep_launch();   // the GEMM that follows may set itself up while this kernel runs
   const size_t index = size_t(blockIdx.x) * kThreads + threadIdx.x;
   if (index >= padded_blocks) return;
   const size_t row = index / padded_blocks_per_row;
@@ -156,6 +157,7 @@ template <bool Gelu, bool Vector>
 __global__ void __launch_bounds__(kThreads)
 fp8_quantize_kernel(const bf16* __restrict__ input, size_t groups, uint32_t width, float inverse_scale,
                     uint2* __restrict__ packed) {
+  griddep_launch();   // the GEMM that follows may set itself up while this kernel runs
   for (size_t group = size_t(blockIdx.x) * kThreads + threadIdx.x; group < groups;
        group += size_t(gridDim.x) * kThreads) {
     const size_t row = group / (width / 8);
