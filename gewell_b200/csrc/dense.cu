@@ -54,10 +54,16 @@ gw_status launch_dense(const DenseProblem& q, DenseDescriptors* cache, cudaStrea
   const bool fp4 = q.kind == GemmKind::nvfp4;
   const uint64_t row_bytes = fp4 ? q.k / 2 : q.k;
   std::string error;
+  const bool single_box = !swap && block_n == 256;   // both column halves come from the one weight matrix
   if (cache->weight != q.weight) {
-    if (!encode_tensor_map_2d(&cache->weight_map, q.weight, row_bytes, q.n, 128, &error))
+    if (!encode_tensor_map_2d(&cache->weight_map, q.weight, row_bytes, q.n, single_box ? 256 : 128, &error))
       return fail(GW_CUDA_ERROR, "weight descriptor: " + error);
     cache->weight = q.weight;
+  }
+  if (single_box && fp4 && cache->weight_scales != q.weight_scales) {
+    if (!encode_tensor_map_scales(&cache->weight_scale_map, q.weight_scales, q.k / 64, (q.n + 127) / 128, 2, &error))
+      return fail(GW_CUDA_ERROR, "weight scale descriptor: " + error);
+    cache->weight_scales = q.weight_scales;
   }
   if (cache->activations != q.activations) {
     if (!encode_tensor_map_2d(&cache->activation_map, q.activations, row_bytes, q.rows, swap ? block_n : 128, &error))
@@ -98,6 +104,10 @@ gw_status launch_dense(const DenseProblem& q, DenseDescriptors* cache, cudaStrea
     g.c_rows = int32_t(q.n);
     g.c_tiles = int32_t((q.n + block_n - 1) / block_n);
     g.c_half_stride = block_n > 128 ? 128 : 0;
+    if (single_box) {
+      params.c_single_box = 1;
+      if (fp4) params.map_sfc = cache->weight_scale_map;
+    }
   }
   params.total_work = g.l_tiles * g.c_tiles;
   int grid = params.total_work < sm_count() ? params.total_work : sm_count();

@@ -11,7 +11,8 @@ namespace gw {
 struct DenseDescriptors {          // re-encoded only when a pointer changes
   const void* weight = nullptr;
   const void* activations = nullptr;
-  CUtensorMap weight_map{}, activation_map{};
+  const void* weight_scales = nullptr;
+  CUtensorMap weight_map{}, activation_map{}, weight_scale_map{};
   // Split mode: one arrival counter per weight tile, owned by the plan (device memory,
   // zeroed at creation; the kernel leaves every counter at zero again).
   int32_t* split_counters = nullptr;

@@ -164,6 +164,11 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&pair);
 }
 
+__device__ __forceinline__ uint4 shfl_xor_u4(const uint4& v, int mask) {
+  return make_uint4(__shfl_xor_sync(0xffffffffu, v.x, mask), __shfl_xor_sync(0xffffffffu, v.y, mask),
+                    __shfl_xor_sync(0xffffffffu, v.z, mask), __shfl_xor_sync(0xffffffffu, v.w, mask));
+}
+
 template <bool kNvfp4, int BLOCK_N, GemmEpilogue EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ GemmParams p) {
@@ -281,8 +286,11 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
         if constexpr (kNvfp4)
           sfc_src[h] = item.g.sf_c[h] + size_t((c_local + h * item.g.c_half_stride) / 128) * k_atoms * kAtomBytes;
       }
-      const uint32_t full_stage_bytes =
-          C::kLBytes + halves * C::kHalfRows * kStageRowBytes + (kNvfp4 ? kKBlocksPerStage * kAtomBytes * (1 + halves) : 0);
+      // dense direct form: both column halves are consecutive rows of one matrix, so one
+      // 256-row box and one two-row box of scale atoms replace four copies (the copy
+      // engine's cost per operation, not per byte, is what limits the fill rate)
+      const bool single_box = C::kHalves == 2 && p.c_single_box != 0;
+      const uint32_t c_bytes = single_box ? uint32_t(C::kCBytes) : uint32_t(halves * C::kHalfRows * kStageRowBytes);
       for (int ks = ks0; ks < ks1; ++ks) {
         const long long t0 = p.profile ? clock64() : 0;
         if (!ptx::mbar_wait_warp(empty_bar + stage, phase ^ 1)) {
@@ -292,25 +300,35 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
         if (p.profile) prof_wait += clock64() - t0;
         if (lane == 0) {
           const int nkb = min(kKBlocksPerStage, total_kb - ks * kKBlocksPerStage);
-          uint32_t bytes = full_stage_bytes;
-          if (kNvfp4 && nkb != kKBlocksPerStage) bytes -= (kKBlocksPerStage - nkb) * kAtomBytes * (1 + halves);
+          uint32_t bytes = C::kLBytes + c_bytes;
+          if constexpr (kNvfp4)
+            bytes += nkb * kAtomBytes + (single_box ? uint32_t(C::kSfcBytes) : uint32_t(nkb * kAtomBytes * halves));
           uint8_t* base = smem + stage * C::kStageBytes;
           uint64_t* bar = full_bar + stage;
           ptx::mbar_expect_tx(bar, bytes);
           ptx::tma_load_2d(base, map_l, ks * kStageRowBytes, l_row, bar);
+          if (single_box) {
+            ptx::tma_load_2d(base + C::kLBytes, &p.map_c, ks * kStageRowBytes, c_row[0], bar);
+          } else {
 #pragma unroll
-          for (int h = 0; h < C::kHalves; ++h)     // compile-time bound: map_c / c_row stay in registers
-            if (h < halves)
-              ptx::tma_load_2d(base + C::kLBytes + h * C::kHalfRows * kStageRowBytes, map_c[h], ks * kStageRowBytes,
-                               c_row[h], bar);
+            for (int h = 0; h < C::kHalves; ++h)     // compile-time bound: map_c / c_row stay in registers
+              if (h < halves)
+                ptx::tma_load_2d(base + C::kLBytes + h * C::kHalfRows * kStageRowBytes, map_c[h], ks * kStageRowBytes,
+                                 c_row[h], bar);
+          }
           if constexpr (kNvfp4) {
             const size_t atom_offset = size_t(ks) * kKBlocksPerStage * kAtomBytes;
             ptx::bulk_load(base + C::kLBytes + C::kCBytes, sfl_src + atom_offset, nkb * kAtomBytes, bar);
+            if (single_box) {
+              // scale storage seen as [row blocks][K/64 atoms] of 8-byte words: 256 words = 4 atoms
+              ptx::tma_load_2d(base + C::kLBytes + C::kCBytes + C::kSflBytes, &p.map_sfc, ks * 256, c_local / 128, bar);
+            } else {
 #pragma unroll
-            for (int h = 0; h < C::kHalves; ++h)
-              if (h < halves)
-                ptx::bulk_load(base + C::kLBytes + C::kCBytes + C::kSflBytes + h * kKBlocksPerStage * kAtomBytes,
-                               sfc_src[h] + atom_offset, nkb * kAtomBytes, bar);
+              for (int h = 0; h < C::kHalves; ++h)
+                if (h < halves)
+                  ptx::bulk_load(base + C::kLBytes + C::kCBytes + C::kSflBytes + h * kKBlocksPerStage * kAtomBytes,
+                                 sfc_src[h] + atom_offset, nkb * kAtomBytes, bar);
+            }
           }
         }
         __syncwarp();
@@ -565,12 +583,18 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
           }
         }
       } else if constexpr (EPI == GemmEpilogue::direct_store) {
-        // lanes = tokens, columns = output channels: out[token][channel], 16-byte stores
+        // lanes = tokens, columns = output channels: out[token][channel].  A thread reads
+        // 32 consecutive channels of its own row from TMEM; a 4x4 transpose of 16-byte
+        // units inside every group of four lanes then lets four neighbouring lanes write
+        // 64 contiguous bytes of one row (8 cache lines per store instruction, not 32).
         bf16* out = static_cast<bf16*>(p.out);
         const int c_base = item.c_tile * p.c_rows_per_tile;           // first channel of the tile
         const int c_end = item.g.c_rows;                              // valid channels of the matrix
-        bf16* dst = out + (size_t(item.g.out_row0) + l_index) * p.ld_out + item.g.out_col0 + c_base;
+        const int group_row = item.l_tile * kTileL + quad * 32 + (lane & ~3);   // first row of this lane group
+        bf16* dst = out + (size_t(item.g.out_row0) + group_row) * p.ld_out + item.g.out_col0 + c_base + 8 * (lane & 3);
+        const int rows_left = item.l_valid - (quad * 32 + (lane & ~3));          // valid rows from group_row on
         const float alpha = item.g.alpha[0];
+        const bool hi = (lane & 2) != 0, lo = (lane & 1) != 0;
         constexpr int kColsPerWarp = BLOCK_N / 2;
         for (int c0 = col_half * kColsPerWarp; c0 < (col_half + 1) * kColsPerWarp; c0 += 32) {
           if (c_base + c0 >= c_end) break;                            // warp-uniform
@@ -578,7 +602,6 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
           ptx::tmem_load16(taddr + c0, r);
           ptx::tmem_load16(taddr + c0 + 16, r + 16);
           ptx::tmem_load_wait();
-          if (!l_ok) continue;
           float v[32];
           if (item.g.channel_alpha != nullptr) {
 #pragma unroll
@@ -590,16 +613,35 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = __fmul_rn(__uint_as_float(r[i]), alpha);
           }
+          uint4 unit[4];                                              // unit q = channels c0 + 8q .. + 7
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const int c = c_base + c0 + 8 * q;
+          for (int q = 0; q < 4; ++q)
+            unit[q] = make_uint4(pack_bf16x2(v[8 * q], v[8 * q + 1]), pack_bf16x2(v[8 * q + 2], v[8 * q + 3]),
+                                 pack_bf16x2(v[8 * q + 4], v[8 * q + 5]), pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
+          // exchange bit 1 of (lane, unit), then bit 0: afterwards unit[i] of lane 4j+k is
+          // unit k of row 4j+i
+          {
+            const uint4 send_a = hi ? unit[0] : unit[2], send_b = hi ? unit[1] : unit[3];
+            const uint4 got_a = shfl_xor_u4(send_a, 2), got_b = shfl_xor_u4(send_b, 2);
+            if (hi) { unit[0] = got_a; unit[1] = got_b; } else { unit[2] = got_a; unit[3] = got_b; }
+          }
+          {
+            const uint4 send_a = lo ? unit[0] : unit[1], send_b = lo ? unit[2] : unit[3];
+            const uint4 got_a = shfl_xor_u4(send_a, 1), got_b = shfl_xor_u4(send_b, 1);
+            if (lo) { unit[0] = got_a; unit[2] = got_b; } else { unit[1] = got_a; unit[3] = got_b; }
+          }
+          const int c = c_base + c0 + 8 * (lane & 3);                 // first channel of this lane's units
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            if (i >= rows_left) continue;
+            bf16* row_dst = dst + size_t(i) * p.ld_out + c0;
             if (c + 8 <= c_end) {
-              *reinterpret_cast<uint4*>(dst + c0 + 8 * q) =
-                  make_uint4(pack_bf16x2(v[8 * q], v[8 * q + 1]), pack_bf16x2(v[8 * q + 2], v[8 * q + 3]),
-                             pack_bf16x2(v[8 * q + 4], v[8 * q + 5]), pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
+              *reinterpret_cast<uint4*>(row_dst) = unit[i];
             } else {
-              for (int i = 0; i < 8; ++i)
-                if (c + i < c_end) dst[c0 + 8 * q + i] = __float2bfloat16_rn(v[8 * q + i]);
+              const uint32_t words[4] = {unit[i].x, unit[i].y, unit[i].z, unit[i].w};
+              for (int e = 0; e < 8; ++e)
+                if (c + e < c_end)
+                  reinterpret_cast<uint16_t*>(row_dst)[e] = uint16_t(words[e / 2] >> (16 * (e % 2)));
             }
           }
         }
@@ -696,11 +738,14 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
 }
 
 long long* g_profile_buffer = nullptr;
+unsigned g_profile_launches = 0;
 
 template <bool kNvfp4, int BLOCK_N, GemmEpilogue EPI>
 cudaError_t launch(const GemmParams& params_in, int grid, cudaStream_t stream) {
   GemmParams params = params_in;
-  params.profile = g_profile_buffer;
+  // debug aid: consecutive launches alternate between the two halves of the buffer, so the
+  // two grouped GEMMs of one MoE pass can be told apart
+  params.profile = g_profile_buffer ? g_profile_buffer + size_t(g_profile_launches++ % 2) * 148 * 8 : nullptr;
   using C = Config<kNvfp4, BLOCK_N>;
   static bool configured = false;
   if (!configured) {
@@ -724,7 +769,10 @@ cudaError_t launch(const GemmParams& params_in, int grid, cudaStream_t stream) {
 
 }  // namespace
 
-void set_gemm_profile_buffer(long long* device_buffer) { g_profile_buffer = device_buffer; }
+void set_gemm_profile_buffer(long long* device_buffer) {
+  g_profile_buffer = device_buffer;
+  g_profile_launches = 0;
+}
 
 cudaError_t launch_gemm_tc(GemmKind kind, GemmEpilogue epilogue, int block_n, const GemmParams& params, int grid,
                            cudaStream_t stream) {

@@ -50,6 +50,8 @@ struct GemmGroup {
 struct GemmParams {
   CUtensorMap map_l;              // used when a group says map_l == -1
   CUtensorMap map_c;              // used when a group says map_c[h] == -1
+  CUtensorMap map_sfc;            // c_single_box: scale atoms of the C operand's matrix (NVFP4)
+  int32_t c_single_box;           // BLOCK_N 256, groups == nullptr: map_c has a 256-row box over one matrix
   const CUtensorMap* map_table;   // per-group operands in global memory (host written)
   const GemmGroup* groups;        // num_groups + 1 entries in global memory, or nullptr
   GemmGroup single;               // the only group when groups == nullptr
@@ -78,7 +80,7 @@ enum class GemmEpilogue { swap_store, direct_store, geglu_quant };
 cudaError_t launch_gemm_tc(GemmKind kind, GemmEpilogue epilogue, int block_n, const GemmParams& params, int grid,
                            cudaStream_t stream);
 
-// Debug aid: subsequent launches write per-CTA cycle counters ([grid][8] int64:
+// Debug aid: subsequent launches write per-CTA cycle counters ([2][148][8] int64:
 // producer wait, MMA wait for data, MMA issue, MMA wait for accumulator, epilogue
 // wait, epilogue work, total, unused) into this device buffer; nullptr turns it off.
 void set_gemm_profile_buffer(long long* device_buffer);
@@ -87,5 +89,10 @@ void set_gemm_profile_buffer(long long* device_buffer);
 // 128-byte x box_rows box and the 128-byte swizzle.
 bool encode_tensor_map_2d(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_t rows,
                           uint32_t box_rows, std::string* error);
+
+// Host helper: tiled NVFP4 scale storage ([row blocks][K/64 atoms of 512 bytes]) as a 2-D map of
+// 8-byte words with a box of 4 atoms x box_row_blocks.
+bool encode_tensor_map_scales(CUtensorMap* map, const void* base, uint64_t k_atoms, uint64_t row_blocks,
+                              uint32_t box_row_blocks, std::string* error);
 
 }  // namespace gw

@@ -53,4 +53,29 @@ bool encode_tensor_map_2d(CUtensorMap* map, const void* base, uint64_t row_bytes
   return true;
 }
 
+bool encode_tensor_map_scales(CUtensorMap* map, const void* base, uint64_t k_atoms, uint64_t row_blocks,
+                              uint32_t box_row_blocks, std::string* error) {
+  auto fn = encode_fn();
+  if (fn == nullptr) {
+    if (error) *error = "cuTensorMapEncodeTiled is not available from this driver";
+    return false;
+  }
+  if (reinterpret_cast<uintptr_t>(base) % 16 != 0 || k_atoms == 0 || row_blocks == 0 || box_row_blocks == 0) {
+    if (error) *error = "scale tensor map needs a 16-byte aligned base and positive extents";
+    return false;
+  }
+  const cuuint64_t dims[2] = {k_atoms * 64, row_blocks};          // 8-byte words per row block, row blocks
+  const cuuint64_t strides[1] = {k_atoms * 512};
+  const cuuint32_t box[2] = {256, box_row_blocks};                // 4 atoms of 512 bytes
+  const cuuint32_t element_strides[2] = {1, 1};
+  const CUresult status = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<void*>(base), dims, strides, box,
+                             element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (status != CUDA_SUCCESS) {
+    if (error) *error = "cuTensorMapEncodeTiled (scales) failed with CUresult " + std::to_string(int(status));
+    return false;
+  }
+  return true;
+}
+
 }  // namespace gw

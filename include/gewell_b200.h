@@ -270,7 +270,7 @@ gw_status gw_moe_combine(const void* down_bf16, const int32_t* inverse, const fl
  * bounded waits inside the tensor-core kernels.  Synchronises the device. */
 uint32_t gw_debug_kernel_error(void);
 
-/* Tuning aid: when `device_buffer` (148 x 8 int64 on the device) is not NULL,
+/* Tuning aid: when `device_buffer` (2 x 148 x 8 int64 on the device; consecutive launches alternate between the halves) is not NULL,
  * every later tensor-core GEMM launch writes per-CTA cycle counters into it
  * (producer wait, MMA wait for data, MMA issue, MMA wait for the accumulator,
  * epilogue wait, epilogue work, total); NULL switches it off again. */
