@@ -212,8 +212,15 @@ def run_expert_parallel(args, world: int, rank: int, local_rank: int):
     for e in mine:
         by_position[placement.physical[e]] = by_id[e]
     capacity = TOPK * tokens          # worst case: every assignment lands on one rank
-    backend = ep.DeviceBackend(by_position, local_tokens, capacity)
-    layer = ep.ExpertParallelMoe(backend, rank, world, local_tokens, capacity, placement=placement)
+    config["exchange"] = args.exchange
+    if args.exchange == "peer":
+        layer = ep.PeerMemoryExpertParallelMoe(by_position, [6.0 / 2688] * E, rank, world, local_tokens, capacity,
+                                               placement=placement)
+        expert_ws = layer.expert_ws
+    else:
+        backend = ep.DeviceBackend(by_position, local_tokens, capacity)
+        layer = ep.ExpertParallelMoe(backend, rank, world, local_tokens, capacity, placement=placement)
+        expert_ws = backend.expert_ws
     x = torch.randn((local_tokens, H), generator=g, device=device).bfloat16()
     logits = torch.randn((local_tokens, E), generator=g, device=device) + zipf_bias().to(device)
     scores = logits.bfloat16()
@@ -268,7 +275,7 @@ def run_expert_parallel(args, world: int, rank: int, local_rank: int):
     # per-stage device times of this rank and the grouped GEMMs' roofline
     marks = []
     layer.timer = lambda name: marks.append((name, _record(torch, stream)))
-    backend.expert_ws.stage_timing(True)
+    expert_ws.stage_timing(True)
     stage_sum, gemm_sum = {}, 0.0
     for _ in range(max(3, args.steps // 4)):
         marks.clear()
@@ -279,13 +286,14 @@ def run_expert_parallel(args, world: int, rank: int, local_rank: int):
         for name, event in marks:
             stage_sum[name] = stage_sum.get(name, 0.0) + previous.elapsed_time(event)
             previous = event
-        inner = backend.expert_ws.stage_elapsed_ms()
+        inner = expert_ws.stage_elapsed_ms()
         gemm_sum += inner["gate_up_gemm"] + inner["down_gemm"]
     repeats = max(3, args.steps // 4)
     layer.timer = None
-    backend.expert_ws.stage_timing(False)
+    expert_ws.stage_timing(False)
     stages = {k: v / repeats for k, v in stage_sum.items()}
-    received = torch.tensor([float(layer.last_layout.total), gemm_sum / repeats], device=device)
+    rows_received = layer.rows_received() if args.exchange == "peer" else layer.last_layout.total
+    received = torch.tensor([float(rows_received), gemm_sum / repeats], device=device)
     gathered = [torch.zeros_like(received) for _ in range(world)]
     dist.all_gather(gathered, received)
     rows_per_rank = [int(t[0].item()) for t in gathered]
@@ -311,6 +319,8 @@ def run_expert_parallel(args, world: int, rank: int, local_rank: int):
                              "stage_ms_rank0": stages},
                 "cpu_baseline": None}
         print(json.dumps(line))
+    if args.exchange == "peer":
+        layer.close()
     dist.destroy_process_group()
 
 
@@ -328,6 +338,9 @@ def main():
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--tokens", type=int, default=0, help="override the token count (testing)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                        help="expert-parallel run: rows cross NVLink inside the dispatch/combine kernels (peer "
+                             "memory) or through NCCL all-to-all")
     parser.add_argument("--placement", default="balanced", choices=["contiguous", "interleaved", "balanced"],
                         help="expert placement of the expert-parallel run")
     args = parser.parse_args()

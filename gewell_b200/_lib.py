@@ -86,6 +86,16 @@ _SIGNATURES = {
     "gw_moe_run_sorted": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_uint32, c_void_p, c_void_p, c_void_p]),
     "gw_gather_rows_bf16": (c_int, [c_void_p, c_void_p, c_uint32, c_uint32, c_uint32, c_void_p, c_void_p]),
     "gw_moe_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_void_p, c_void_p]),
+    "gw_ipc_alloc": (c_int, [c_size_t, POINTER(c_void_p), c_void_p]),
+    "gw_ipc_open": (c_int, [c_void_p, POINTER(c_void_p)]),
+    "gw_ipc_close": (c_int, [c_void_p]),
+    "gw_ipc_free": (c_int, [c_void_p]),
+    "gw_moe_ep_dispatch": (c_int, [c_void_p, c_void_p, c_uint32, c_void_p, c_void_p, c_void_p, c_void_p, c_uint32,
+                                   c_void_p]),
+    "gw_moe_ep_tables": (c_int, [c_void_p, c_void_p, c_uint32, c_uint32, c_void_p, c_void_p, c_void_p]),
+    "gw_moe_ep_run_experts": (c_int, [c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_uint32, c_void_p, c_void_p,
+                                      c_void_p]),
+    "gw_moe_ep_combine": (c_int, [c_void_p, c_uint32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "gw_debug_kernel_error": (c_uint32, []),
     "gw_debug_gemm_profile": (c_int, [c_void_p]),
     "gw_debug_rcp_approx": (c_int, [c_void_p, c_void_p, c_uint64, c_void_p]),

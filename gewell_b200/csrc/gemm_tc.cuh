@@ -86,9 +86,10 @@ cudaError_t launch_gemm_tc(GemmKind kind, GemmEpilogue epilogue, int block_n, co
 void set_gemm_profile_buffer(long long* device_buffer);
 
 // Host helper: 2-D byte tensor map {inner = row_bytes, outer = rows} with a
-// 128-byte x box_rows box and the 128-byte swizzle.
+// 128-byte x box_rows box and the 128-byte swizzle.  pitch_bytes (0 = row_bytes)
+// is the distance between rows in memory.
 bool encode_tensor_map_2d(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_t rows,
-                          uint32_t box_rows, std::string* error);
+                          uint32_t box_rows, std::string* error, uint64_t pitch_bytes = 0);
 
 // Host helper: tiled NVFP4 scale storage ([row blocks][K/64 atoms of 512 bytes]) as a 2-D map of
 // 8-byte words with a box of 4 atoms x box_row_blocks.

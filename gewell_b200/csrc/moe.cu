@@ -4,6 +4,7 @@
 // (models/gemma4/26b_a4b/sm120/moe.cuh:20-48, moe.cu:462-545).
 #include <cmath>
 #include <cstdlib>
+#include <cstring>
 #include <new>
 #include <string>
 #include <vector>
@@ -188,8 +189,13 @@ int env_int(const char* name, int fallback) {
 // the 128-lane operand and an expert's few tokens on the column operand; large
 // batches put tokens on the lanes, and when gate and up share their input scale
 // the first GEMM's epilogue applies GeGLU and quantises the down input itself.
+//
+// `records` != nullptr (expert parallelism): the rows arrive already quantised as 1584-byte
+// records (packed E2M1 + K-ordered scale bytes) written by the ranks that routed them; the
+// GEMM reads the packed part in place and only the scale bytes are re-tiled here.
 gw_status run_experts(gw_moe_workspace* w, const void* input, const int32_t* gather_index, uint32_t gather_divisor,
-                      const int32_t* offsets, uint32_t n, const gw_expert_table* table, void* down_out, cudaStream_t s) {
+                      const int32_t* offsets, uint32_t n, const gw_expert_table* table, void* down_out, cudaStream_t s,
+                      const void* records = nullptr) {
   const auto* info = table->info.as<MoeExpertInfo>();
   auto* first_groups = w->groups.as<GemmGroup>();
   auto* down_groups = first_groups + 2 * kExperts + 1;
@@ -215,15 +221,20 @@ gw_status run_experts(gw_moe_workspace* w, const void* input, const int32_t* gat
                     block_n_first, block_n_down, table->shared_gate_up ? 1 : 0};
   w->mark(1, s);
   GW_CUDA_CHECK(launch_moe_prepare_groups(plan, first_groups, down_groups, s), "MoE group descriptors");
-  GW_CUDA_CHECK(launch_moe_quantize_input(input, gather_index, gather_divisor, w->sorted_keys, offsets, info, n, w->scale_rows, parts,
-                                          w->packed_in.as<uint8_t>(), w->scales_in.as<uint8_t>(), s),
-                "MoE gather + quantise");
+  if (records != nullptr) {
+    GW_CUDA_CHECK(launch_ep_retile_scales(records, w->sorted_keys, offsets, n, w->scales_in.as<uint8_t>(), s),
+                  "MoE scale re-tiling of received rows");
+  } else {
+    GW_CUDA_CHECK(launch_moe_quantize_input(input, gather_index, gather_divisor, w->sorted_keys, offsets, info, n,
+                                            w->scale_rows, parts, w->packed_in.as<uint8_t>(), w->scales_in.as<uint8_t>(), s),
+                  "MoE gather + quantise");
+  }
   std::string error;
   const bool swap = form == kMoeFormSwap;
   GemmParams first{};
   CUtensorMap token_map;
-  if (!encode_tensor_map_2d(&token_map, w->packed_in.data, kHidden / 2, size_t(parts) * n, swap ? block_n_first : 128,
-                            &error))
+  if (!encode_tensor_map_2d(&token_map, records ? records : w->packed_in.data, kHidden / 2, size_t(parts) * n,
+                            swap ? block_n_first : 128, &error, records ? kEpRecordBytes : 0))
     return fail(GW_CUDA_ERROR, "MoE activation descriptor: " + error);
   (swap ? first.map_c : first.map_l) = token_map;
   first.map_table = table->maps.as<CUtensorMap>();
@@ -366,6 +377,109 @@ gw_status gw_moe_combine(const void* down_bf16, const int32_t* inverse, const fl
       reinterpret_cast<uintptr_t>(down_bf16) % 16 || reinterpret_cast<uintptr_t>(output_bf16) % 16)
     return fail(GW_INVALID_ARGUMENT, "MoE combine requires 16-byte aligned buffers and a width divisible by 8");
   GW_CUDA_CHECK(launch_moe_combine(down_bf16, inverse, weights, rows, width, output_bf16, as_stream(stream)), "MoE combine");
+  return GW_OK;
+}
+
+// --------------------------------------------------------------------------- expert parallelism over peer memory
+
+gw_status gw_ipc_alloc(size_t bytes, void** pointer, uint8_t* handle) {
+  clear_error();
+  if (!pointer || !handle || bytes == 0) return fail(GW_INVALID_ARGUMENT, "shared buffer needs a size, a pointer slot and a 64-byte handle slot");
+  static_assert(sizeof(cudaIpcMemHandle_t) == GW_IPC_HANDLE_BYTES, "handle size");
+  void* p = nullptr;
+  GW_CUDA_CHECK(cudaMalloc(&p, bytes), "allocate shared buffer");
+  cudaIpcMemHandle_t h;
+  const cudaError_t status = cudaIpcGetMemHandle(&h, p);
+  if (status != cudaSuccess) {
+    cudaFree(p);
+    return fail(GW_CUDA_ERROR, std::string("export shared buffer: ") + cudaGetErrorString(status));
+  }
+  std::memcpy(handle, &h, sizeof(h));
+  *pointer = p;
+  return GW_OK;
+}
+
+gw_status gw_ipc_open(const uint8_t* handle, void** pointer) {
+  clear_error();
+  if (!handle || !pointer) return fail(GW_INVALID_ARGUMENT, "opening a shared buffer needs its handle and a pointer slot");
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle, sizeof(h));
+  GW_CUDA_CHECK(cudaIpcOpenMemHandle(pointer, h, cudaIpcMemLazyEnablePeerAccess), "open a peer's shared buffer");
+  return GW_OK;
+}
+
+gw_status gw_ipc_close(void* pointer) {
+  clear_error();
+  if (pointer) GW_CUDA_CHECK(cudaIpcCloseMemHandle(pointer), "close a peer's shared buffer");
+  return GW_OK;
+}
+
+gw_status gw_ipc_free(void* pointer) {
+  clear_error();
+  if (pointer) GW_CUDA_CHECK(cudaFree(pointer), "free shared buffer");
+  return GW_OK;
+}
+
+gw_status gw_moe_ep_tables(const int32_t* counts, const int32_t* physical, uint32_t rank, uint32_t world,
+                           int32_t* dest_row0, int32_t* local_offsets, void* stream) {
+  clear_error();
+  if (!counts || !physical || !dest_row0 || !local_offsets || world == 0 || kExperts % world || rank >= world)
+    return fail(GW_INVALID_ARGUMENT, "destination tables need the gathered histogram, the placement and a rank count that divides 128");
+  GW_CUDA_CHECK(launch_ep_tables(counts, physical, rank, world, dest_row0, local_offsets, as_stream(stream)),
+                "expert-parallel destination tables");
+  return GW_OK;
+}
+
+gw_status gw_moe_ep_dispatch(gw_moe_workspace* w, const void* input_bf16, uint32_t rows,
+                             const float* inverse_input_scales, const int32_t* dest_rank, const int32_t* dest_row0,
+                             void* const* peer_records, uint32_t capacity_rows, void* stream) {
+  clear_error();
+  if (!w) return fail(GW_INVALID_ARGUMENT, "expert-parallel dispatch requires the workspace that routed the rows");
+  if (rows > w->max_rows) return fail(GW_INVALID_ARGUMENT, "MoE rows exceed workspace");
+  if (!rows) return GW_OK;
+  if (!input_bf16 || !inverse_input_scales || !dest_rank || !dest_row0 || !peer_records ||
+      reinterpret_cast<uintptr_t>(input_bf16) % 16)
+    return fail(GW_INVALID_ARGUMENT, "expert-parallel dispatch requires a 16-byte aligned input and the destination tables");
+  GW_CUDA_CHECK(launch_ep_dispatch(input_bf16, w->sorted_assignments, w->sorted_keys, w->offsets, inverse_input_scales,
+                                   dest_rank, dest_row0, peer_records, 8 * rows, capacity_rows, device_error_word(),
+                                   as_stream(stream)),
+                "expert-parallel dispatch");
+  return GW_OK;
+}
+
+gw_status gw_moe_ep_run_experts(gw_moe_workspace* w, const void* records, const int32_t* offsets, uint32_t first_expert,
+                                uint32_t expert_count, uint32_t total_rows, const gw_expert_table* table,
+                                void* down_bf16, void* stream) {
+  clear_error();
+  if (!w || !table) return fail(GW_INVALID_ARGUMENT, "expert run requires a workspace and an expert table");
+  if (!table->shared_gate_up)
+    return fail(GW_UNSUPPORTED, "records carry one quantised copy of a row: gate and up must share their input scale");
+  if (total_rows > w->n) return fail(GW_INVALID_ARGUMENT, "received rows exceed workspace (8 x max_rows)");
+  if (!total_rows) return GW_OK;
+  if (!records || !offsets || !down_bf16 || expert_count == 0 || first_expert + expert_count > kExperts ||
+      reinterpret_cast<uintptr_t>(records) % 16 || reinterpret_cast<uintptr_t>(down_bf16) % 16)
+    return fail(GW_INVALID_ARGUMENT, "expert run requires aligned buffers and an expert range inside 0..128");
+  cudaStream_t s = as_stream(stream);
+  w->mark(0, s);
+  GW_CUDA_CHECK(launch_moe_keys_from_offsets(offsets, first_expert, expert_count, total_rows, w->sorted_keys,
+                                             w->local_offsets, s),
+                "MoE keys from offsets");
+  const gw_status status = run_experts(w, nullptr, nullptr, 1, w->local_offsets, total_rows, table, down_bf16, s, records);
+  w->mark(6, s);
+  return status;
+}
+
+gw_status gw_moe_ep_combine(gw_moe_workspace* w, uint32_t rows, const int32_t* dest_rank, const int32_t* dest_row0,
+                            void* const* peer_down, void* output_bf16, void* stream) {
+  clear_error();
+  if (!w) return fail(GW_INVALID_ARGUMENT, "expert-parallel combine requires the workspace that routed the rows");
+  if (rows > w->max_rows) return fail(GW_INVALID_ARGUMENT, "MoE rows exceed workspace");
+  if (!rows) return GW_OK;
+  if (!dest_rank || !dest_row0 || !peer_down || !output_bf16 || reinterpret_cast<uintptr_t>(output_bf16) % 16)
+    return fail(GW_INVALID_ARGUMENT, "expert-parallel combine requires the destination tables and a 16-byte aligned output");
+  GW_CUDA_CHECK(launch_ep_combine(w->keys, w->inverse, w->weights, w->offsets, dest_rank, dest_row0, peer_down, rows,
+                                  output_bf16, as_stream(stream)),
+                "expert-parallel combine");
   return GW_OK;
 }
 

@@ -184,7 +184,7 @@ moe_keys_from_offsets_kernel(const int32_t* __restrict__ offsets, uint32_t first
     else v = offsets[expert_count];
     full_offsets[e] = v;
   }
-  if (i >= rows) return;
+  if (i >= rows || i >= uint32_t(offsets[expert_count])) return;   // `rows` may be an upper bound
   uint32_t lo = 0, hi = expert_count;   // largest e with offsets[e] <= i
   while (lo + 1 < hi) {
     const uint32_t mid = (lo + hi) / 2;
@@ -356,6 +356,7 @@ moe_quantize_kernel(const uint4* __restrict__ input, const int32_t* __restrict__
   const uint32_t part = blockIdx.y;             // gate/up copy (0 unless the scales differ)
   if (index >= size_t(n) * kBlocks) return;
   const uint32_t row = index / kBlocks, kb = index % kBlocks;
+  if (row >= uint32_t(offsets[kExperts])) return;       // n may be an upper bound (expert parallelism)
   const int32_t e = sorted_keys[row];
   const int32_t first = offsets[e];
   const float inverse_scale = experts[e].inverse_input_scale[projection + part];
@@ -442,6 +443,137 @@ gather_rows_kernel(const uint4* __restrict__ input, const int32_t* __restrict__ 
   output[i] = input[size_t(uint32_t(index[row]) / divisor) * vectors + v];
 }
 
+// ---------------------------------------------------------------------------
+// 7. Expert parallelism over peer memory (no counterpart in the reference, which
+//    is single GPU).  A travelling row is a 1584-byte record: 1408 bytes of
+//    packed E2M1 (K = 2816) followed by its 176 E4M3 block scales in K order.
+//    The dispatch kernel quantises a routed row with the destination expert's
+//    input scale (same arithmetic as kernel 5) and stores the record straight
+//    into the owning rank's buffer; the owner re-tiles the scale bytes locally
+//    and runs the grouped GEMMs on the records in place; the combine kernel
+//    reads the eight result rows of a token from their owners' buffers and folds
+//    them as kernel 6 does.  All remote accesses are plain loads and stores.
+// ---------------------------------------------------------------------------
+constexpr uint32_t kRecordBytes = kHidden / 2 + kHidden / 16;   // 1584
+
+__global__ void __launch_bounds__(256)
+ep_dispatch_kernel(const uint4* __restrict__ input, const int32_t* __restrict__ sorted_assignments,
+                   const int32_t* __restrict__ sorted_keys, const int32_t* __restrict__ offsets,
+                   const float* __restrict__ inverse_input_scale, const int32_t* __restrict__ dest_rank,
+                   const int32_t* __restrict__ dest_row0, uint8_t* const* __restrict__ peer_records, uint32_t n,
+                   uint32_t capacity_rows, uint32_t* __restrict__ error) {
+  constexpr uint32_t kBlocks = kHidden / 16;
+  const size_t index = size_t(blockIdx.x) * 256 + threadIdx.x;
+  if (index >= size_t(n) * kBlocks) return;
+  const uint32_t row = index / kBlocks, kb = index % kBlocks;
+  const int32_t e = sorted_keys[row];
+  const float inverse_scale = inverse_input_scale[e];
+  const size_t source_row = size_t(uint32_t(sorted_assignments[row]) / kTopK);
+  float values[16];
+  unpack8(input[2 * (source_row * kBlocks + kb)], values);
+  unpack8(input[2 * (source_row * kBlocks + kb) + 1], values + 8);
+  float amax = 0.0F;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(values[i]));
+  const uint8_t scale_code = float_to_e4m3(inverse_scale * (amax * rcp_approx_ftz(6.0F)));
+  const float block_scale = e4m3_to_float(scale_code);
+  const float factor =
+      block_scale == 0.0F ? 0.0F : rcp_approx_ftz(block_scale * rcp_approx_ftz(inverse_scale));
+  uint32_t out[2] = {0, 0};
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    out[i / 4] |= uint32_t(float2_to_e2m1x2(values[2 * i] * factor, values[2 * i + 1] * factor)) << (8 * (i % 4));
+  const uint32_t dest_row = uint32_t(dest_row0[e] + int32_t(row) - offsets[e]);
+  if (dest_row >= capacity_rows) {          // the owner's buffer is too small: report, never write outside it
+    if (kb == 0 && error != nullptr) atomicCAS(error, 0u, 0x70000000u | uint32_t(e));
+    return;
+  }
+  uint8_t* record = peer_records[dest_rank[e]] + size_t(dest_row) * kRecordBytes;
+  *reinterpret_cast<uint2*>(record + kb * 8) = make_uint2(out[0], out[1]);
+  record[kHidden / 2 + kb] = scale_code;
+}
+
+// Where every rank's rows of every expert go, from the all-gathered histogram
+// counts[source rank][expert id]: experts are laid out expert-major in physical order on
+// their owner, source ranks in rank order inside an expert.  One block of 128 threads.
+__global__ void __launch_bounds__(kExperts)
+ep_tables_kernel(const int32_t* __restrict__ counts, const int32_t* __restrict__ physical, uint32_t rank,
+                 uint32_t world, int32_t* __restrict__ dest_row0, int32_t* __restrict__ local_offsets) {
+  __shared__ int32_t total_at[kExperts];       // rows of the expert at a physical position, over all sources
+  const uint32_t e = threadIdx.x, per_rank = kExperts / world;
+  int32_t total = 0, before_me = 0;
+  for (uint32_t s = 0; s < world; ++s) {
+    const int32_t c = counts[s * kExperts + e];
+    total += c;
+    if (s < rank) before_me += c;
+  }
+  const uint32_t position = uint32_t(physical[e]);
+  total_at[position] = total;
+  __syncthreads();
+  int32_t first = 0;                            // rows of the owner's experts placed before this one
+  for (uint32_t q = position / per_rank * per_rank; q < position; ++q) first += total_at[q];
+  dest_row0[e] = first + before_me;
+  if (position / per_rank == rank) {
+    local_offsets[position % per_rank] = first;
+    if (position % per_rank == per_rank - 1) local_offsets[per_rank] = first + total;
+  }
+}
+
+// scale bytes of the local records -> the tiled per-expert regions the GEMM reads
+__global__ void __launch_bounds__(256)
+ep_retile_scales_kernel(const uint8_t* __restrict__ records, const int32_t* __restrict__ sorted_keys,
+                        const int32_t* __restrict__ offsets, uint32_t n, uint8_t* __restrict__ scales) {
+  constexpr uint32_t kWords = kHidden / 64;        // 44 four-byte words of scales per row
+  const size_t index = size_t(blockIdx.x) * 256 + threadIdx.x;
+  if (index >= size_t(n) * kWords) return;
+  const uint32_t row = index / kWords, word = index % kWords;
+  if (row >= uint32_t(offsets[kExperts])) return;       // n may be an upper bound
+  const int32_t e = sorted_keys[row];
+  const int32_t first = offsets[e];
+  const uint32_t value = *reinterpret_cast<const uint32_t*>(records + size_t(row) * kRecordBytes + kHidden / 2 + word * 4);
+  const size_t region = size_t(first / 128 + e) * 128 * (kHidden / 16);
+  *reinterpret_cast<uint32_t*>(scales + region + scale_offset(row - first, word * 4, kHidden)) = value;
+}
+
+__global__ void __launch_bounds__(256)
+ep_combine_kernel(const int32_t* __restrict__ keys, const int32_t* __restrict__ inverse,
+                  const float* __restrict__ weights, const int32_t* __restrict__ offsets,
+                  const int32_t* __restrict__ dest_rank, const int32_t* __restrict__ dest_row0,
+                  const uint4* const* __restrict__ peer_down, uint32_t rows, uint4* __restrict__ output) {
+  constexpr uint32_t kVectors = kHidden / 8;
+  const size_t index = size_t(blockIdx.x) * 256 + threadIdx.x;
+  if (index >= size_t(rows) * kVectors) return;
+  const uint32_t row = index / kVectors, v = index % kVectors;
+  uint4 raw[kTopK];
+  float w[kTopK];
+#pragma unroll
+  for (int j = 0; j < kTopK; ++j) {      // all eight remote loads are in flight before the fold starts
+    const uint32_t assignment = row * kTopK + j;
+    const int32_t e = keys[assignment];
+    const size_t remote_row = size_t(dest_row0[e] + inverse[assignment] - offsets[e]);
+    raw[j] = peer_down[dest_rank[e]][remote_row * kVectors + v];
+    w[j] = weights[assignment];
+  }
+  float sum[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) sum[i] = 0.0F;
+#pragma unroll
+  for (int j = 0; j < kTopK; ++j) {
+    float x[8];
+    unpack8(raw[j], x);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float product = __bfloat162float(__float2bfloat16_rn(__fmul_rn(x[i], w[j])));
+      sum[i] = __bfloat162float(__float2bfloat16_rn(__fadd_rn(sum[i], product)));
+    }
+  }
+  uint32_t words[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    words[i] = (__float_as_uint(sum[2 * i]) >> 16) | (__float_as_uint(sum[2 * i + 1]) & 0xFFFF0000u);
+  output[index] = make_uint4(words[0], words[1], words[2], words[3]);
+}
+
 unsigned blocks_for(size_t items) { return unsigned((items + 255) / 256); }
 
 }  // namespace
@@ -507,6 +639,38 @@ cudaError_t launch_gather_rows(const void* input, const int32_t* index, uint32_t
                                uint32_t width, void* output, cudaStream_t stream) {
   gather_rows_kernel<<<blocks_for(size_t(rows) * (width / 8)), 256, 0, stream>>>(
       static_cast<const uint4*>(input), index, divisor, rows, width / 8, static_cast<uint4*>(output));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ep_dispatch(const void* input, const int32_t* sorted_assignments, const int32_t* sorted_keys,
+                               const int32_t* offsets, const float* inverse_input_scale, const int32_t* dest_rank,
+                               const int32_t* dest_row0, void* const* peer_records, uint32_t n,
+                               uint32_t capacity_rows, uint32_t* error, cudaStream_t stream) {
+  ep_dispatch_kernel<<<blocks_for(size_t(n) * (kHidden / 16)), 256, 0, stream>>>(
+      static_cast<const uint4*>(input), sorted_assignments, sorted_keys, offsets, inverse_input_scale, dest_rank,
+      dest_row0, reinterpret_cast<uint8_t* const*>(peer_records), n, capacity_rows, error);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ep_tables(const int32_t* counts, const int32_t* physical, uint32_t rank, uint32_t world,
+                             int32_t* dest_row0, int32_t* local_offsets, cudaStream_t stream) {
+  ep_tables_kernel<<<1, kExperts, 0, stream>>>(counts, physical, rank, world, dest_row0, local_offsets);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ep_retile_scales(const void* records, const int32_t* sorted_keys, const int32_t* offsets,
+                                    uint32_t n, uint8_t* scales, cudaStream_t stream) {
+  ep_retile_scales_kernel<<<blocks_for(size_t(n) * (kHidden / 64)), 256, 0, stream>>>(
+      static_cast<const uint8_t*>(records), sorted_keys, offsets, n, scales);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ep_combine(const int32_t* keys, const int32_t* inverse, const float* weights,
+                              const int32_t* offsets, const int32_t* dest_rank, const int32_t* dest_row0,
+                              void* const* peer_down, uint32_t rows, void* output, cudaStream_t stream) {
+  ep_combine_kernel<<<blocks_for(size_t(rows) * (kHidden / 8)), 256, 0, stream>>>(
+      keys, inverse, weights, offsets, dest_rank, dest_row0, reinterpret_cast<const uint4* const*>(peer_down), rows,
+      static_cast<uint4*>(output));
   return cudaGetLastError();
 }
 

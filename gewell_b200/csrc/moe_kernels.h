@@ -58,4 +58,19 @@ cudaError_t launch_moe_combine(const void* down, const int32_t* inverse, const f
 cudaError_t launch_gather_rows(const void* input, const int32_t* index, uint32_t divisor, uint32_t rows,
                                uint32_t width, void* output, cudaStream_t stream);
 
+
+// Expert parallelism over peer memory: 1584-byte records (1408 B packed E2M1 + 176 scale bytes).
+constexpr uint32_t kEpRecordBytes = 1584;
+cudaError_t launch_ep_dispatch(const void* input, const int32_t* sorted_assignments, const int32_t* sorted_keys,
+                               const int32_t* offsets, const float* inverse_input_scale, const int32_t* dest_rank,
+                               const int32_t* dest_row0, void* const* peer_records, uint32_t n,
+                               uint32_t capacity_rows, uint32_t* error, cudaStream_t stream);
+cudaError_t launch_ep_tables(const int32_t* counts, const int32_t* physical, uint32_t rank, uint32_t world,
+                             int32_t* dest_row0, int32_t* local_offsets, cudaStream_t stream);
+cudaError_t launch_ep_retile_scales(const void* records, const int32_t* sorted_keys, const int32_t* offsets,
+                                    uint32_t n, uint8_t* scales, cudaStream_t stream);
+cudaError_t launch_ep_combine(const int32_t* keys, const int32_t* inverse, const float* weights,
+                              const int32_t* offsets, const int32_t* dest_rank, const int32_t* dest_row0,
+                              void* const* peer_down, uint32_t rows, void* output, cudaStream_t stream);
+
 }  // namespace gw

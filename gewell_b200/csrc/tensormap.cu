@@ -28,19 +28,20 @@ PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
 }  // namespace
 
 bool encode_tensor_map_2d(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_t rows,
-                          uint32_t box_rows, std::string* error) {
+                          uint32_t box_rows, std::string* error, uint64_t pitch_bytes) {
+  if (pitch_bytes == 0) pitch_bytes = row_bytes;
   auto fn = encode_fn();
   if (fn == nullptr) {
     if (error) *error = "cuTensorMapEncodeTiled is not available from this driver";
     return false;
   }
-  if (reinterpret_cast<uintptr_t>(base) % 16 != 0 || row_bytes % 16 != 0 || rows == 0 || box_rows == 0 ||
-      box_rows > 256) {
+  if (reinterpret_cast<uintptr_t>(base) % 16 != 0 || row_bytes % 16 != 0 || pitch_bytes % 16 != 0 ||
+      pitch_bytes < row_bytes || rows == 0 || box_rows == 0 || box_rows > 256) {
     if (error) *error = "tensor map needs a 16-byte aligned base, a row pitch divisible by 16 and 1..256 box rows";
     return false;
   }
   const cuuint64_t dims[2] = {row_bytes, rows};
-  const cuuint64_t strides[1] = {row_bytes};
+  const cuuint64_t strides[1] = {pitch_bytes};
   const cuuint32_t box[2] = {128, box_rows};
   const cuuint32_t element_strides[2] = {1, 1};
   const CUresult status = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,

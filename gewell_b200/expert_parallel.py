@@ -258,3 +258,137 @@ class ExpertParallelMoe:
         b.combine(self.returned_rows, home, weights, rows, out)
         self._mark("combine")
         return out
+
+
+class SharedBuffer:
+    """Device memory that every rank of the node can address: each rank
+    allocates its own buffer (gw_ipc_alloc), the 64-byte handles are exchanged
+    through the process group, and every rank maps the others' buffers
+    (gw_ipc_open).  `pointers[r]` is rank r's buffer as seen from this process."""
+
+    def __init__(self, nbytes: int, rank: int, world: int, group=None):
+        import ctypes
+        import gewell_b200 as gw
+        self._gw, self.rank, self.world, self.nbytes = gw, rank, world, nbytes
+        pointer, handle = ctypes.c_void_p(), (ctypes.c_uint8 * 64)()
+        gw.ops._check(gw.lib.gw_ipc_alloc(nbytes, ctypes.byref(pointer), handle))
+        self.local = pointer.value
+        handles = [None] * world
+        dist.all_gather_object(handles, bytes(handle), group=group)
+        self.pointers = []
+        for r in range(world):
+            if r == rank:
+                self.pointers.append(self.local)
+                continue
+            peer = ctypes.c_void_p()
+            raw = (ctypes.c_uint8 * 64).from_buffer_copy(handles[r])
+            gw.ops._check(gw.lib.gw_ipc_open(raw, ctypes.byref(peer)))
+            self.pointers.append(peer.value)
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        self.pointer_table = torch.tensor(self.pointers, dtype=torch.int64, device=self.device)
+
+    def close(self, group=None):
+        """Unmap the peers' buffers, wait for everybody, then free the own one."""
+        if self.local is None:
+            return
+        for r, p in enumerate(self.pointers):
+            if r != self.rank:
+                self._gw.lib.gw_ipc_close(p)
+        torch.cuda.synchronize()
+        dist.barrier(group=group)
+        self._gw.lib.gw_ipc_free(self.local)
+        self.local = None
+
+
+class PeerMemoryExpertParallelMoe:
+    """The expert-parallel layer with the exchange fused into the kernels on
+    either side of it.  Instead of gather -> all-to-all -> regroup, the dispatch
+    kernel quantises each routed row to NVFP4 with its expert's input scale and
+    stores the 1584-byte record (1408 B of E2M1 + 176 scale bytes, against 5632 B
+    of BF16) directly into the owning GPU's memory over NVLink, already at its
+    expert-major position; the owner's grouped GEMMs read the records in place;
+    the combine kernel reads each token's eight result rows from their owners'
+    memory and folds them in expert order.  Collectives are only used for the
+    128-integer histogram (all-gather) and for the two barriers of a step.
+
+    Needs experts whose gate and up projections share their input scale (one
+    quantised copy of a row serves both), as the fused checkpoint tensors do.
+    """
+
+    STAGES = ("route", "counts", "dispatch", "barrier_1", "experts", "barrier_2", "combine")
+    RECORD_BYTES = 1584
+
+    def __init__(self, experts_by_position, input_scales, rank: int, world: int, local_tokens: int,
+                 receive_capacity_rows: int, placement: Placement | None = None, group=None):
+        """experts_by_position: 128 entries indexed by physical position, None for
+        experts of other ranks.  input_scales: the gate/up input scale of all 128
+        experts by expert id (every rank quantises rows for every expert)."""
+        import gewell_b200 as gw
+        self.gw = gw
+        self.placement = placement or Placement.contiguous(world)
+        self.rank, self.world, self.group = rank, world, group
+        self.per_rank = EXPERTS // world
+        self.local_tokens, self.capacity = local_tokens, receive_capacity_rows
+        self.table = gw.ExpertTable(experts_by_position)
+        self.route_ws = gw.MoeWorkspace(local_tokens)
+        self.expert_ws = gw.MoeWorkspace((receive_capacity_rows + 7) // 8)
+        self.device = self.route_ws.device
+        self.records = SharedBuffer(receive_capacity_rows * self.RECORD_BYTES, rank, world, group)
+        self.down = SharedBuffer(receive_capacity_rows * HIDDEN * 2, rank, world, group)
+        scales = torch.tensor(list(input_scales), dtype=torch.float32)
+        self.inverse_scales = (torch.ones_like(scales) / scales).to(self.device)      # IEEE FP32 division
+        self.dest_rank = torch.tensor(self.placement.owner, dtype=torch.int32, device=self.device)
+        self.physical = torch.tensor(self.placement.physical, dtype=torch.int32, device=self.device)
+        self.counts_all = torch.zeros((world, EXPERTS), dtype=torch.int32, device=self.device)
+        self.dest_row0 = torch.zeros(EXPERTS, dtype=torch.int32, device=self.device)
+        self.local_offsets = torch.zeros(self.per_rank + 1, dtype=torch.int32, device=self.device)
+        self.flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.timer = None
+
+    def _mark(self, name: str):
+        if self.timer is not None:
+            self.timer(name)
+
+    def _barrier(self):
+        # stream-ordered: completes on this rank only after every rank's earlier kernels have
+        dist.all_reduce(self.flag, group=self.group)
+
+    def rows_received(self) -> int:
+        """Rows this rank's experts processed in the last step (reads back one integer)."""
+        return int(self.local_offsets[-1].item())
+
+    def run(self, x, scores, expert_scales, rows: int, out=None):
+        """One step; nothing is read back to the host, so the step can be
+        enqueued ahead of the GPU (or captured)."""
+        lib, check = self.gw.lib, self.gw.ops._check
+        stream = torch.cuda.current_stream().cuda_stream
+        self.route_ws.dispatch(scores, expert_scales, rows)
+        offsets, _, _, _ = self.route_ws.routing_state(rows)
+        self._mark("route")
+        counts = (offsets[1:] - offsets[:-1]).contiguous()
+        dist.all_gather_into_tensor(self.counts_all, counts, group=self.group)
+        check(lib.gw_moe_ep_tables(self.counts_all.data_ptr(), self.physical.data_ptr(), self.rank, self.world,
+                                   self.dest_row0.data_ptr(), self.local_offsets.data_ptr(), stream))
+        self._mark("counts")
+        check(lib.gw_moe_ep_dispatch(self.route_ws._ws, x.data_ptr(), rows, self.inverse_scales.data_ptr(),
+                                     self.dest_rank.data_ptr(), self.dest_row0.data_ptr(),
+                                     self.records.pointer_table.data_ptr(), self.capacity, stream))
+        self._mark("dispatch")
+        self._barrier()
+        self._mark("barrier_1")
+        check(lib.gw_moe_ep_run_experts(self.expert_ws._ws, self.records.local, self.local_offsets.data_ptr(),
+                                        self.rank * self.per_rank, self.per_rank, self.capacity, self.table.handle,
+                                        self.down.local, stream))
+        self._mark("experts")
+        self._barrier()
+        self._mark("barrier_2")
+        if out is None:
+            out = torch.empty((rows, HIDDEN), dtype=torch.bfloat16, device=self.device)
+        check(lib.gw_moe_ep_combine(self.route_ws._ws, rows, self.dest_rank.data_ptr(), self.dest_row0.data_ptr(),
+                                    self.down.pointer_table.data_ptr(), out.data_ptr(), stream))
+        self._mark("combine")
+        return out
+
+    def close(self):
+        self.records.close(self.group)
+        self.down.close(self.group)

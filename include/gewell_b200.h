@@ -266,6 +266,58 @@ gw_status gw_gather_rows_bf16(const void* input_bf16, const int32_t* index, uint
 gw_status gw_moe_combine(const void* down_bf16, const int32_t* inverse, const float* weights,
                          uint32_t rows, uint32_t width, void* output_bf16, void* stream);
 
+/* Expert parallelism over peer memory (no counterpart in the reference).  Rows
+ * travel as 1584-byte records: 1408 bytes of packed E2M1 followed by the row's
+ * 176 E4M3 block scales in K order.
+ *
+ * Buffers that other ranks (processes) of the same node write or read are
+ * allocated with gw_ipc_alloc, which also returns a 64-byte handle; a peer turns
+ * the handle into a pointer valid in its own process with gw_ipc_open.  Neither
+ * call is capturable; both belong to set-up. */
+#define GW_IPC_HANDLE_BYTES 64
+gw_status gw_ipc_alloc(size_t bytes, void** pointer, uint8_t* handle);
+gw_status gw_ipc_open(const uint8_t* handle, void** pointer);
+gw_status gw_ipc_close(void* pointer);
+gw_status gw_ipc_free(void* pointer);
+
+/* After gw_moe_dispatch on `workspace`: quantise every routed row with its
+ * expert's input scale (inverse_input_scales[e] = 1 / input_scale of expert e,
+ * 128 floats on the device) and store its record at row
+ *   dest_row0[e] + (position of the row among this rank's rows of expert e)
+ * of peer_records[dest_rank[e]].  dest_rank / dest_row0: 128 int32 each on the
+ * device; peer_records: one device pointer per rank, in device memory.  The
+ * caller orders this against the owners' reads (a barrier over the ranks). */
+gw_status gw_moe_ep_dispatch(gw_moe_workspace* workspace, const void* input_bf16, uint32_t rows,
+                             const float* inverse_input_scales, const int32_t* dest_rank,
+                             const int32_t* dest_row0, void* const* peer_records,
+                             uint32_t capacity_rows, void* stream);
+
+/* The destination tables on the device, without a host round trip: from
+ * counts[source rank][expert id] (world x 128 int32, the all-gathered routing
+ * histograms) and physical[expert id] (position of the expert in (owner, id)
+ * order) compute dest_row0[128] for this rank and its own group boundaries
+ * local_offsets[128 / world + 1].  Rows of an expert sit expert-major on the
+ * owner, source ranks in rank order.  A record that would fall outside
+ * capacity_rows is dropped by the dispatch and reported through the kernel
+ * error word. */
+gw_status gw_moe_ep_tables(const int32_t* counts, const int32_t* physical, uint32_t rank, uint32_t world,
+                           int32_t* dest_row0, int32_t* local_offsets, void* stream);
+
+/* Owner side: grouped gate/up GEMM + GeGLU + grouped down GEMM over the
+ * records this rank received, grouped by expert as `offsets` (expert_count + 1
+ * entries, on the device) says; `total_rows` is an upper bound known to the host
+ * (the true count is offsets[expert_count]), so no read-back is needed; BF16 results [total_rows, 2816] in the same
+ * order go to `down_bf16` (a gw_ipc_alloc buffer when peers read it). */
+gw_status gw_moe_ep_run_experts(gw_moe_workspace* workspace, const void* records, const int32_t* offsets,
+                                uint32_t first_expert, uint32_t expert_count, uint32_t total_rows,
+                                const gw_expert_table* table, void* down_bf16, void* stream);
+
+/* Ordered BF16 fold (moe.cu:446-456) of each token's eight result rows, read
+ * from their owners: row dest_row0[e] + position of peer_down[dest_rank[e]]. */
+gw_status gw_moe_ep_combine(gw_moe_workspace* workspace, uint32_t rows, const int32_t* dest_rank,
+                            const int32_t* dest_row0, void* const* peer_down, void* output_bf16,
+                            void* stream);
+
 /* Last kernel-reported error word of this process's device (0 = none); set by
  * bounded waits inside the tensor-core kernels.  Synchronises the device. */
 uint32_t gw_debug_kernel_error(void);

@@ -91,13 +91,91 @@ def test_absent_experts_are_accepted_and_validated(layer):
         ws.run_sorted(rows, offsets.cuda(), 100, 64, n, table, out)     # range leaves 0..128
 
 
+def test_destination_tables_match_numpy(layer):
+    gw, _, _ = layer
+    from gewell_b200 import expert_parallel as ep
+    rng = np.random.default_rng(3)
+    for world in (1, 2, 8):
+        owner = np.repeat(np.arange(world), E // world)
+        rng.shuffle(owner)
+        placement = ep.Placement(owner.tolist(), world)
+        counts = rng.integers(0, 50, size=(world, E)).astype(np.int32)
+        counts[rng.random(counts.shape) < 0.2] = 0
+        per_rank = E // world
+        totals = counts.sum(0)
+        first = np.zeros(E, dtype=np.int64)
+        for r in range(world):
+            running = 0
+            for e in placement.local_experts(r):
+                first[e] = running
+                running += totals[e]
+        for rank in range(world):
+            want_row0 = first + counts[:rank].sum(0)
+            mine = placement.local_experts(rank)
+            want_offsets = np.concatenate([[0], np.cumsum(totals[mine])])
+            row0 = torch.zeros(E, dtype=torch.int32, device="cuda")
+            offsets = torch.zeros(per_rank + 1, dtype=torch.int32, device="cuda")
+            device_counts = torch.from_numpy(counts).cuda()
+            device_physical = torch.tensor(placement.physical, dtype=torch.int32).cuda()
+            gw.ops._check(gw.lib.gw_moe_ep_tables(device_counts.data_ptr(), device_physical.data_ptr(), rank, world,
+                                                  row0.data_ptr(), offsets.data_ptr(),
+                                                  torch.cuda.current_stream().cuda_stream))
+            torch.cuda.synchronize()
+            assert np.array_equal(row0.cpu().numpy(), want_row0)
+            assert np.array_equal(offsets.cpu().numpy(), want_offsets)
+
+
+@pytest.mark.parametrize("tokens", [40, 900])
+def test_record_path_on_one_rank_equals_layer(layer, tokens):
+    """Dispatch into records, grouped GEMMs on the records, combine through the
+    pointer table -- with this GPU as the only rank -- give the layer's output."""
+    import ctypes
+    gw, _, table = layer
+    lib, check = gw.lib, gw.ops._check
+    stream = torch.cuda.current_stream().cuda_stream
+    x, scores, scales = (t.cuda() for t in _inputs(tokens, 60, True))
+    ws = gw.MoeWorkspace(tokens)
+    y = torch.empty((tokens, H), dtype=torch.bfloat16, device="cuda")
+    ws.run(x, scores, scales, table, y, tokens)
+    route_ws, expert_ws = gw.MoeWorkspace(tokens), gw.MoeWorkspace(tokens + 16)
+    capacity = 8 * (tokens + 16)
+    records = torch.full((capacity * 1584,), 0xFF, dtype=torch.uint8, device="cuda")    # stale bytes must not matter
+    down = torch.empty((capacity, H), dtype=torch.bfloat16, device="cuda")
+    route_ws.dispatch(scores, scales, tokens)
+    offsets, _, _, _ = route_ws.routing_state(tokens)
+    counts = (offsets[1:] - offsets[:-1]).contiguous()
+    physical = torch.arange(E, dtype=torch.int32, device="cuda")
+    dest_rank = torch.zeros(E, dtype=torch.int32, device="cuda")
+    row0 = torch.zeros(E, dtype=torch.int32, device="cuda")
+    local_offsets = torch.zeros(E + 1, dtype=torch.int32, device="cuda")
+    check(lib.gw_moe_ep_tables(counts.data_ptr(), physical.data_ptr(), 0, 1, row0.data_ptr(), local_offsets.data_ptr(), stream))
+    inverse_scales = (torch.ones(E) / torch.full((E,), 6.0 / 2688)).cuda()
+    record_table = torch.tensor([records.data_ptr()], dtype=torch.int64, device="cuda")
+    down_table = torch.tensor([down.data_ptr()], dtype=torch.int64, device="cuda")
+    check(lib.gw_moe_ep_dispatch(route_ws._ws, x.data_ptr(), tokens, inverse_scales.data_ptr(), dest_rank.data_ptr(),
+                                 row0.data_ptr(), record_table.data_ptr(), capacity, stream))
+    check(lib.gw_moe_ep_run_experts(expert_ws._ws, records.data_ptr(), local_offsets.data_ptr(), 0, E, capacity,
+                                    table.handle, down.data_ptr(), stream))
+    out = torch.empty((tokens, H), dtype=torch.bfloat16, device="cuda")
+    check(lib.gw_moe_ep_combine(route_ws._ws, tokens, dest_rank.data_ptr(), row0.data_ptr(), down_table.data_ptr(),
+                                out.data_ptr(), stream))
+    torch.cuda.synchronize()
+    assert gw.kernel_error() == 0
+    assert np.array_equal(local_offsets.cpu().numpy(), offsets.cpu().numpy())
+    assert np.array_equal(bits(out), bits(y))
+    # a buffer that is too small is reported, not overrun
+    check(lib.gw_moe_ep_dispatch(route_ws._ws, x.data_ptr(), tokens, inverse_scales.data_ptr(), dest_rank.data_ptr(),
+                                 row0.data_ptr(), record_table.data_ptr(), 8, stream))
+    assert gw.kernel_error() >> 28 == 7
+
+
 def _free_port() -> int:
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         return s.getsockname()[1]
 
 
-def _worker(rank: int, world: int, port: int, placement_name: str, tokens: int, out_dir: str):
+def _worker(rank: int, world: int, port: int, placement_name: str, exchange: str, tokens: int, out_dir: str):
     import torch.distributed as dist
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -120,26 +198,34 @@ def _worker(rank: int, world: int, port: int, placement_name: str, tokens: int, 
         for e in mine:
             by_position[placement.physical[e]] = by_id[e]
         local = tokens // world
-        backend = ep.DeviceBackend(by_position, local, 8 * tokens)
-        moe = ep.ExpertParallelMoe(backend, rank, world, local, 8 * tokens, placement=placement)
+        if exchange == "peer":
+            moe = ep.PeerMemoryExpertParallelMoe(by_position, [6.0 / 2688] * E, rank, world, local, 8 * tokens,
+                                                 placement=placement)
+        else:
+            backend = ep.DeviceBackend(by_position, local, 8 * tokens)
+            moe = ep.ExpertParallelMoe(backend, rank, world, local, 8 * tokens, placement=placement)
         begin = rank * local
         for _ in range(2):
             y = moe.run(x[begin:begin + local], scores[begin:begin + local], scales, local)
         torch.cuda.synchronize()
         assert gw.kernel_error() == 0
         np.save(os.path.join(out_dir, f"y{rank}.npy"), bits(y))
+        if exchange == "peer":
+            moe.close()
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("placement_name", ["contiguous", "balanced"])
-def test_two_ranks_equal_single_gpu(layer, tmp_path, placement_name):
+@pytest.mark.parametrize("placement_name,exchange", [("contiguous", "nccl"), ("balanced", "nccl"),
+                                                     ("contiguous", "peer"), ("balanced", "peer")])
+def test_two_ranks_equal_single_gpu(layer, tmp_path, placement_name, exchange):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
     gw, _, table = layer
     tokens, world = 1536, 2
-    mp.spawn(_worker, args=(world, _free_port(), placement_name, tokens, str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), placement_name, exchange, tokens, str(tmp_path)), nprocs=world,
+             join=True)
     x, scores, scales = (t.cuda() for t in _inputs(tokens, 50, True))
     ws = gw.MoeWorkspace(tokens)
     y = torch.empty((tokens, H), dtype=torch.bfloat16, device="cuda")
