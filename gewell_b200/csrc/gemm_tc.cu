@@ -360,8 +360,7 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
       const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
       const uint32_t idesc = kNvfp4 ? ptx::idesc_nvfp4(item.mma_n) : ptx::idesc_fp8(item.mma_n);
       const int c_local = item.c_tile * p.c_rows_per_tile;
-      // swap form with BLOCK_N < 128: the tile starts part-way into a 128-row scale atom
-      const uint32_t sfc_sub = BLOCK_N < 128 ? (c_local % 128) / 32 : 0;
+      (void)c_local;
       const int halves = item.halves;
       bool failed = false;
       for (int ks = ks0; ks < ks1; ++ks) {
@@ -389,7 +388,7 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
           const int nkb = min(kKBlocksPerStage, total_kb - ks * kKBlocksPerStage);
           const uint32_t base16 = smem_base16 + uint32_t(stage) * uint32_t(C::kStageBytes >> 4);
           const uint32_t sfl_t = sfl_tmem + uint32_t(stage) * C::kSfSlotCols;
-          const uint32_t sfc_t = sfc_tmem + uint32_t(stage) * C::kSfSlotCols + sfc_sub;
+          const uint32_t sfc_t = sfc_tmem + uint32_t(stage) * C::kSfSlotCols;
           const uint32_t first = ks == ks0 ? 0u : 1u;
 #pragma unroll
           for (int kb = 0; kb < kKBlocksPerStage; ++kb) {
@@ -437,6 +436,7 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
         if (more) decode_work<BLOCK_N, EPI>(p, prefix, next_tile, next);
         (void)tile; (void)at_start;
         const int halves = item.halves;
+        const uint32_t sfc_sub = BLOCK_N < 128 ? uint32_t((item.c_tile * p.c_rows_per_tile) % 128) / 32 : 0;
         bool failed = false;
         for (int ks = ks0; ks < ks1; ++ks) {
           if (!ptx::mbar_wait_warp(full_bar + stage, phase)) {
@@ -455,10 +455,17 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
           ptx::tmem_store16(slot, r);
           // column operand scales: per K-block [half 0: 4 columns][half 1: 4 columns]
           if constexpr (C::kHalves == 1) {
+            // A column tile narrower than 128 rows may start part-way into its 128-row scale
+            // atom (32-row steps).  The four words of a lane are the atom's four 32-row
+            // groups: rotate them so that the tile's first group lands in the slot's first
+            // column -- the MMA wants its scale address aligned to the whole four-column group.
 #pragma unroll
             for (int kb = 0; kb < kKBlocksPerStage; ++kb) {
               const uint4 v = ptx::lds128(src + C::kSflBytes + kb * kAtomBytes);
-              r[4 * kb] = v.x; r[4 * kb + 1] = v.y; r[4 * kb + 2] = v.z; r[4 * kb + 3] = v.w;
+              uint32_t a = v.x, b = v.y, c = v.z, d = v.w;
+              if (sfc_sub & 1) { const uint32_t t = a; a = b; b = c; c = d; d = t; }
+              if (sfc_sub & 2) { uint32_t t = a; a = c; c = t; t = b; b = d; d = t; }
+              r[4 * kb] = a; r[4 * kb + 1] = b; r[4 * kb + 2] = c; r[4 * kb + 3] = d;
             }
             ptx::tmem_store16(slot + 4 * kKBlocksPerStage, r);
           } else {

@@ -141,6 +141,9 @@ def test_combine_kernel_exact(gw):
 @pytest.mark.parametrize("rows,mode,form", [
     (1, "hot", None), (7, "normal", None), (17, "distributed", None), (33, "normal", None), (64, "normal", None),
     (129, "uneven", None), (300, "normal", None),
+    # an expert with 33..64 rows and a 32-row column tile: the second tile starts 32 rows into
+    # its scale atom; 200 hot tokens walk a 64-row tile through all of an atom's offsets
+    (40, "hot", None), (64, "hot", None), (200, "hot", None),
     (7, "normal", "direct"), (129, "uneven", "direct"), (300, "normal", "direct"),
     (1, "hot", "fused"), (33, "normal", "fused"), (129, "uneven", "fused"), (300, "normal", "fused"),
 ])
