@@ -213,9 +213,9 @@ def run_expert_parallel(args, world: int, rank: int, local_rank: int):
         by_position[placement.physical[e]] = by_id[e]
     capacity = TOPK * tokens          # worst case: every assignment lands on one rank
     config["exchange"] = args.exchange
-    if args.exchange == "peer":
+    if args.exchange in ("peer", "peer_pull"):
         layer = ep.PeerMemoryExpertParallelMoe(by_position, [6.0 / 2688] * E, rank, world, local_tokens, capacity,
-                                               placement=placement)
+                                               placement=placement, send_home=args.exchange == "peer")
         expert_ws = layer.expert_ws
     else:
         backend = ep.DeviceBackend(by_position, local_tokens, capacity)
@@ -292,7 +292,7 @@ def run_expert_parallel(args, world: int, rank: int, local_rank: int):
     layer.timer = None
     expert_ws.stage_timing(False)
     stages = {k: v / repeats for k, v in stage_sum.items()}
-    rows_received = layer.rows_received() if args.exchange == "peer" else layer.last_layout.total
+    rows_received = layer.rows_received() if args.exchange != "nccl" else layer.last_layout.total
     received = torch.tensor([float(rows_received), gemm_sum / repeats], device=device)
     gathered = [torch.zeros_like(received) for _ in range(world)]
     dist.all_gather(gathered, received)
@@ -319,7 +319,7 @@ def run_expert_parallel(args, world: int, rank: int, local_rank: int):
                              "stage_ms_rank0": stages},
                 "cpu_baseline": None}
         print(json.dumps(line))
-    if args.exchange == "peer":
+    if args.exchange != "nccl":
         layer.close()
     dist.destroy_process_group()
 
@@ -338,7 +338,7 @@ def main():
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--tokens", type=int, default=0, help="override the token count (testing)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
-    parser.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+    parser.add_argument("--exchange", default="peer", choices=["peer", "peer_pull", "nccl"],
                         help="expert-parallel run: rows cross NVLink inside the dispatch/combine kernels (peer "
                              "memory) or through NCCL all-to-all")
     parser.add_argument("--placement", default="balanced", choices=["contiguous", "interleaved", "balanced"],

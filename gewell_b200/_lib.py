@@ -92,9 +92,10 @@ _SIGNATURES = {
     "gw_ipc_free": (c_int, [c_void_p]),
     "gw_moe_ep_dispatch": (c_int, [c_void_p, c_void_p, c_uint32, c_void_p, c_void_p, c_void_p, c_void_p, c_uint32,
                                    c_void_p]),
-    "gw_moe_ep_tables": (c_int, [c_void_p, c_void_p, c_uint32, c_uint32, c_void_p, c_void_p, c_void_p]),
+    "gw_moe_ep_tables": (c_int, [c_void_p, c_void_p, c_uint32, c_uint32, c_void_p, c_void_p, c_void_p, c_void_p,
+                                 c_void_p]),
     "gw_moe_ep_run_experts": (c_int, [c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_uint32, c_void_p, c_void_p,
-                                      c_void_p]),
+                                      c_void_p, c_void_p, c_void_p, c_uint32, c_void_p]),
     "gw_moe_ep_combine": (c_int, [c_void_p, c_uint32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "gw_debug_kernel_error": (c_uint32, []),
     "gw_debug_gemm_profile": (c_int, [c_void_p]),

@@ -170,6 +170,7 @@ __device__ __forceinline__ uint4 shfl_xor_u4(const uint4& v, int mask) {
 }
 
 template <bool kNvfp4, int BLOCK_N, GemmEpilogue EPI>
+// 14 warps are allocated as 16: 128 registers per thread is the most one CTA can have.
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ GemmParams p) {
   using C = Config<kNvfp4, BLOCK_N>;
@@ -537,8 +538,13 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
             if (l_ok) {
 #pragma unroll
               for (int i = 0; i < 16; ++i)
-                if (c0 + i < item.c_valid)
-                  dst[size_t(c0 + i) * p.ld_out] = __float2bfloat16_rn(__fmul_rn(__uint_as_float(r[i]), alpha));
+                if (c0 + i < item.c_valid) {
+                  bf16* token_dst = dst + size_t(c0 + i) * p.ld_out;
+                  if (p.row_dest != nullptr)     // per-row destinations: the token's row may live on another GPU
+                    token_dst = reinterpret_cast<bf16*>(p.row_dest[size_t(item.g.out_row0) + item.c_tile * BLOCK_N + c0 + i]) +
+                                item.g.out_col0 + l_index;
+                  *token_dst = __float2bfloat16_rn(__fmul_rn(__uint_as_float(r[i]), alpha));
+                }
             }
           }
         } else {
@@ -600,11 +606,22 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
         const int group_row = item.l_tile * kTileL + quad * 32 + (lane & ~3);   // first row of this lane group
         bf16* dst = out + (size_t(item.g.out_row0) + group_row) * p.ld_out + item.g.out_col0 + c_base + 8 * (lane & 3);
         const int rows_left = item.l_valid - (quad * 32 + (lane & ~3));          // valid rows from group_row on
+        // optional per-row destinations (expert parallelism: a row goes straight to its home)
+        uint64_t my_row_dest = 0;
+        if (p.row_dest != nullptr && l_ok) my_row_dest = p.row_dest[size_t(item.g.out_row0) + l_index];
+        uint64_t group_dest[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) group_dest[i] = __shfl_sync(0xffffffffu, my_row_dest, (lane & ~3) + i);
         const float alpha = item.g.alpha[0];
         const bool hi = (lane & 2) != 0, lo = (lane & 1) != 0;
         constexpr int kColsPerWarp = BLOCK_N / 2;
-        for (int c0 = col_half * kColsPerWarp; c0 < (col_half + 1) * kColsPerWarp; c0 += 32) {
-          if (c_base + c0 >= c_end) break;                            // warp-uniform
+        constexpr int kChunks = kColsPerWarp / 32;
+        // With a single accumulator stage (256 columns) the warp drains all of its columns
+        // into registers as packed BF16 first and returns the accumulator before it stores,
+        // so the stores overlap the next tile's MMAs; with two stages it goes chunk by chunk.
+        constexpr bool kEarlyRelease = C::kAccStages == 1;
+        uint4 unit[kEarlyRelease ? kChunks : 1][4];                  // unit q of a chunk = channels c0 + 8q .. + 7
+        auto drain = [&](int c0, uint4* out_units) {
           uint32_t r[32];
           ptx::tmem_load16(taddr + c0, r);
           ptx::tmem_load16(taddr + c0 + 16, r + 16);
@@ -620,44 +637,95 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = __fmul_rn(__uint_as_float(r[i]), alpha);
           }
-          uint4 unit[4];                                              // unit q = channels c0 + 8q .. + 7
 #pragma unroll
           for (int q = 0; q < 4; ++q)
-            unit[q] = make_uint4(pack_bf16x2(v[8 * q], v[8 * q + 1]), pack_bf16x2(v[8 * q + 2], v[8 * q + 3]),
-                                 pack_bf16x2(v[8 * q + 4], v[8 * q + 5]), pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
-          // exchange bit 1 of (lane, unit), then bit 0: afterwards unit[i] of lane 4j+k is
+            out_units[q] = make_uint4(pack_bf16x2(v[8 * q], v[8 * q + 1]), pack_bf16x2(v[8 * q + 2], v[8 * q + 3]),
+                                      pack_bf16x2(v[8 * q + 4], v[8 * q + 5]), pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
+        };
+        auto store = [&](int c0, uint4* u) {
+          // exchange bit 1 of (lane, unit), then bit 0: afterwards u[i] of lane 4j+k is
           // unit k of row 4j+i
           {
-            const uint4 send_a = hi ? unit[0] : unit[2], send_b = hi ? unit[1] : unit[3];
+            const uint4 send_a = hi ? u[0] : u[2], send_b = hi ? u[1] : u[3];
             const uint4 got_a = shfl_xor_u4(send_a, 2), got_b = shfl_xor_u4(send_b, 2);
-            if (hi) { unit[0] = got_a; unit[1] = got_b; } else { unit[2] = got_a; unit[3] = got_b; }
+            if (hi) { u[0] = got_a; u[1] = got_b; } else { u[2] = got_a; u[3] = got_b; }
           }
           {
-            const uint4 send_a = lo ? unit[0] : unit[1], send_b = lo ? unit[2] : unit[3];
+            const uint4 send_a = lo ? u[0] : u[1], send_b = lo ? u[2] : u[3];
             const uint4 got_a = shfl_xor_u4(send_a, 1), got_b = shfl_xor_u4(send_b, 1);
-            if (lo) { unit[0] = got_a; unit[2] = got_b; } else { unit[1] = got_a; unit[3] = got_b; }
+            if (lo) { u[0] = got_a; u[2] = got_b; } else { u[1] = got_a; u[3] = got_b; }
           }
           const int c = c_base + c0 + 8 * (lane & 3);                 // first channel of this lane's units
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             if (i >= rows_left) continue;
-            bf16* row_dst = dst + size_t(i) * p.ld_out + c0;
+            bf16* row_dst = p.row_dest == nullptr
+                                ? dst + size_t(i) * p.ld_out + c0
+                                : reinterpret_cast<bf16*>(group_dest[i]) + item.g.out_col0 + c_base + 8 * (lane & 3) + c0;
             if (c + 8 <= c_end) {
-              *reinterpret_cast<uint4*>(row_dst) = unit[i];
+              *reinterpret_cast<uint4*>(row_dst) = u[i];
             } else {
-              const uint32_t words[4] = {unit[i].x, unit[i].y, unit[i].z, unit[i].w};
+              const uint32_t words[4] = {u[i].x, u[i].y, u[i].z, u[i].w};
               for (int e = 0; e < 8; ++e)
                 if (c + e < c_end)
                   reinterpret_cast<uint16_t*>(row_dst)[e] = uint16_t(words[e / 2] >> (16 * (e % 2)));
             }
           }
+        };
+        if constexpr (kEarlyRelease) {
+#pragma unroll
+          for (int ch = 0; ch < kChunks; ++ch) {
+            const int c0 = col_half * kColsPerWarp + 32 * ch;
+            if (c_base + c0 < c_end) drain(c0, unit[ch]);             // warp-uniform
+          }
+          ptx::tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(acc_empty_bar + acc);      // the next tile's MMAs may start
+#pragma unroll
+          for (int ch = 0; ch < kChunks; ++ch) {
+            const int c0 = col_half * kColsPerWarp + 32 * ch;
+            if (c_base + c0 < c_end) store(c0, unit[ch]);
+          }
+        } else {
+          for (int c0 = col_half * kColsPerWarp; c0 < (col_half + 1) * kColsPerWarp; c0 += 32) {
+            if (c_base + c0 >= c_end) break;                          // warp-uniform
+            drain(c0, unit[0]);
+            store(c0, unit[0]);
+          }
         }
       } else {
         // GeGLU + FP4 quantise: columns [0,128) = gate channels, [128,256) = up channels of
         // the same 128 output channels; this warp owns 64 of them (4 K16 blocks).
+        //
+        // The 256-column accumulator has no second stage (tensor memory is full), so the
+        // warp first drains its share into registers -- scaled and rounded to BF16, which is
+        // what GeGLU consumes anyway, two values per register -- and hands the accumulator
+        // back to the MMA issuer at once; the transcendental math and the stores then
+        // overlap the next tile's MMAs.
         const int channel0 = item.c_tile * 128 + col_half * 64;       // first channel of this warp
         const int width = p.out_width;
-        if (channel0 < width) {
+        const bool active = channel0 < width;
+        uint32_t gate_words[32], up_words[32];                        // BF16 pairs: channels channel0 + 2i, + 2i + 1
+        if (active) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint32_t g[16], u[16];
+            ptx::tmem_load16(taddr + col_half * 64 + 16 * j, g);
+            ptx::tmem_load16(taddr + 128 + col_half * 64 + 16 * j, u);
+            ptx::tmem_load_wait();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              gate_words[8 * j + i] = pack_bf16x2(__fmul_rn(__uint_as_float(g[2 * i]), item.g.alpha[0]),
+                                                  __fmul_rn(__uint_as_float(g[2 * i + 1]), item.g.alpha[0]));
+              up_words[8 * j + i] = pack_bf16x2(__fmul_rn(__uint_as_float(u[2 * i]), item.g.alpha[1]),
+                                                __fmul_rn(__uint_as_float(u[2 * i + 1]), item.g.alpha[1]));
+            }
+          }
+        }
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(acc_empty_bar + acc);        // the next tile's MMAs may start
+        if (active) {
           const size_t row = size_t(item.g.out_row0) + l_index;
           uint32_t packed_words[8];
           uint32_t scale_word = 0;
@@ -666,19 +734,12 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
           bf16* cap_act = static_cast<bf16*>(p.capture_activated);
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            uint32_t g[16], u[16];
-            ptx::tmem_load16(taddr + col_half * 64 + 16 * j, g);
-            ptx::tmem_load16(taddr + 128 + col_half * 64 + 16 * j, u);
-            ptx::tmem_load_wait();
             float act[16];
-            uint32_t gw[8], uw[8], aw[8];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const float gate = __bfloat162float(__float2bfloat16_rn(__fmul_rn(__uint_as_float(g[i]), item.g.alpha[0])));
-              const float up = __bfloat162float(__float2bfloat16_rn(__fmul_rn(__uint_as_float(u[i]), item.g.alpha[1])));
-              act[i] = gelu_tanh_multiply_bf16(gate, up);
-              g[i] = __float_as_uint(gate);
-              u[i] = __float_as_uint(up);
+            for (int i = 0; i < 8; ++i) {
+              const uint32_t gw = gate_words[8 * j + i], uw = up_words[8 * j + i];
+              act[2 * i] = gelu_tanh_multiply_bf16(__uint_as_float(gw << 16), __uint_as_float(uw << 16));
+              act[2 * i + 1] = gelu_tanh_multiply_bf16(__uint_as_float(gw & 0xFFFF0000u), __uint_as_float(uw & 0xFFFF0000u));
             }
             float amax = 0.0F;
 #pragma unroll
@@ -697,15 +758,15 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
             packed_words[2 * j] = lo;
             packed_words[2 * j + 1] = hi;
             if (cap_gu != nullptr && l_ok) {
+              uint32_t aw[8];
 #pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                gw[i] = (g[2 * i] >> 16) | (g[2 * i + 1] & 0xFFFF0000u);
-                uw[i] = (u[2 * i] >> 16) | (u[2 * i + 1] & 0xFFFF0000u);
+              for (int i = 0; i < 8; ++i)
                 aw[i] = (__float_as_uint(act[2 * i]) >> 16) | (__float_as_uint(act[2 * i + 1]) & 0xFFFF0000u);
-              }
               uint4* gdst = reinterpret_cast<uint4*>(cap_gu + row * (2 * size_t(width)) + channel0 + 16 * j);
               uint4* udst = reinterpret_cast<uint4*>(cap_gu + row * (2 * size_t(width)) + width + channel0 + 16 * j);
               uint4* adst = reinterpret_cast<uint4*>(cap_act + row * size_t(width) + channel0 + 16 * j);
+              const uint32_t* gw = gate_words + 8 * j;
+              const uint32_t* uw = up_words + 8 * j;
               gdst[0] = make_uint4(gw[0], gw[1], gw[2], gw[3]); gdst[1] = make_uint4(gw[4], gw[5], gw[6], gw[7]);
               udst[0] = make_uint4(uw[0], uw[1], uw[2], uw[3]); udst[1] = make_uint4(uw[4], uw[5], uw[6], uw[7]);
               adst[0] = make_uint4(aw[0], aw[1], aw[2], aw[3]); adst[1] = make_uint4(aw[4], aw[5], aw[6], aw[7]);
@@ -721,9 +782,11 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
           }
         }
       }
-      ptx::tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(acc_empty_bar + acc);
+      if constexpr (EPI == GemmEpilogue::swap_store || (EPI == GemmEpilogue::direct_store && C::kAccStages > 1)) {
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(acc_empty_bar + acc);
+      }
       if (p.profile) prof_work += clock64() - te1;
       if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1; }
     }

@@ -61,6 +61,8 @@ struct GemmParams {
   int32_t c_rows_per_tile;        // rows of one matrix covered by one column tile
   void* out;                      // BF16 output (swap/direct), packed E2M1 output (GeGLU+quantise)
   int64_t ld_out;                 // elements (bytes for the packed output) between output rows
+  const uint64_t* row_dest;       // direct store, optional: byte address of the start of every output row
+                                  // (indexed like rows of `out`); rows may live in other GPUs' memory
   uint8_t* out_scales;            // GeGLU+quantise: tiled scale storage of the output
   int32_t out_width;              // GeGLU+quantise: logical width (K of the consumer)
   void* capture_gate_up;          // GeGLU+quantise: optional BF16 [rows, 2*out_width]

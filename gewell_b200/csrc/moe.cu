@@ -46,6 +46,7 @@ struct gw_expert_table {
 struct gw_moe_workspace {
   uint32_t max_rows = 0, n = 0, scale_rows = 0, chunks = 0;
   DeviceBuffer metadata, bitmaps, groups, packed_in, scales_in, gate_up, activated, packed_act, scales_act, down;
+  DeviceBuffer row_home;   // expert parallelism: address of every produced row's home in its source rank
   int32_t *keys = nullptr, *sorted_keys = nullptr, *sorted_assignments = nullptr, *inverse = nullptr;
   int32_t *offsets = nullptr, *chunk_counts = nullptr, *local_offsets = nullptr;
   float* weights = nullptr;
@@ -134,6 +135,7 @@ gw_status gw_moe_create(uint32_t max_rows, gw_moe_workspace** workspace) {
   if (status == cudaSuccess) status = w->packed_act.allocate(n * (kInter / 2));
   if (status == cudaSuccess) status = w->scales_act.allocate(size_t(w->scale_rows) * (kInter / 16));
   if (status == cudaSuccess) status = w->down.allocate(n * kHidden * sizeof(bf16));
+  if (status == cudaSuccess) status = w->row_home.allocate(n * sizeof(uint64_t));
   // Scale regions contain rows no kernel writes (tile padding); start from zero so
   // that they never hold NaN patterns.
   if (status == cudaSuccess) status = cudaMemset(w->scales_in.data, 0, w->scales_in.bytes);
@@ -195,7 +197,7 @@ int env_int(const char* name, int fallback) {
 // GEMM reads the packed part in place and only the scale bytes are re-tiled here.
 gw_status run_experts(gw_moe_workspace* w, const void* input, const int32_t* gather_index, uint32_t gather_divisor,
                       const int32_t* offsets, uint32_t n, const gw_expert_table* table, void* down_out, cudaStream_t s,
-                      const void* records = nullptr) {
+                      const void* records = nullptr, const uint64_t* row_home = nullptr) {
   const auto* info = table->info.as<MoeExpertInfo>();
   auto* first_groups = w->groups.as<GemmGroup>();
   auto* down_groups = first_groups + 2 * kExperts + 1;
@@ -277,6 +279,7 @@ gw_status run_experts(gw_moe_workspace* w, const void* input, const int32_t* gat
   down.c_rows_per_tile = block_n_down;
   down.out = down_out;
   down.ld_out = kHidden;
+  down.row_dest = row_home;   // rows go to their homes (possibly on other GPUs) instead of down_out
   down.error = device_error_word();
   w->mark(4, s);
   GW_CUDA_CHECK(launch_gemm_tc(GemmKind::nvfp4, swap ? GemmEpilogue::swap_store : GemmEpilogue::direct_store,
@@ -421,11 +424,16 @@ gw_status gw_ipc_free(void* pointer) {
 }
 
 gw_status gw_moe_ep_tables(const int32_t* counts, const int32_t* physical, uint32_t rank, uint32_t world,
-                           int32_t* dest_row0, int32_t* local_offsets, void* stream) {
+                           int32_t* dest_row0, int32_t* local_offsets, int32_t* segment_start, int32_t* home_base,
+                           void* stream) {
   clear_error();
-  if (!counts || !physical || !dest_row0 || !local_offsets || world == 0 || kExperts % world || rank >= world)
+  if (!counts || !physical || !dest_row0 || !local_offsets || world == 0 || kExperts % world || rank >= world ||
+      (segment_start == nullptr) != (home_base == nullptr))
     return fail(GW_INVALID_ARGUMENT, "destination tables need the gathered histogram, the placement and a rank count that divides 128");
-  GW_CUDA_CHECK(launch_ep_tables(counts, physical, rank, world, dest_row0, local_offsets, as_stream(stream)),
+  if (segment_start != nullptr && world > 8)
+    return fail(GW_UNSUPPORTED, "the way-home tables are built for at most 8 ranks (one node)");
+  GW_CUDA_CHECK(launch_ep_tables(counts, physical, rank, world, dest_row0, local_offsets, segment_start, home_base,
+                                 as_stream(stream)),
                 "expert-parallel destination tables");
   return GW_OK;
 }
@@ -449,22 +457,32 @@ gw_status gw_moe_ep_dispatch(gw_moe_workspace* w, const void* input_bf16, uint32
 
 gw_status gw_moe_ep_run_experts(gw_moe_workspace* w, const void* records, const int32_t* offsets, uint32_t first_expert,
                                 uint32_t expert_count, uint32_t total_rows, const gw_expert_table* table,
-                                void* down_bf16, void* stream) {
+                                void* down_bf16, const int32_t* segment_start, const int32_t* home_base,
+                                void* const* peer_returned, uint32_t world, void* stream) {
   clear_error();
   if (!w || !table) return fail(GW_INVALID_ARGUMENT, "expert run requires a workspace and an expert table");
   if (!table->shared_gate_up)
     return fail(GW_UNSUPPORTED, "records carry one quantised copy of a row: gate and up must share their input scale");
   if (total_rows > w->n) return fail(GW_INVALID_ARGUMENT, "received rows exceed workspace (8 x max_rows)");
   if (!total_rows) return GW_OK;
-  if (!records || !offsets || !down_bf16 || expert_count == 0 || first_expert + expert_count > kExperts ||
+  const bool push = peer_returned != nullptr;
+  if (!records || !offsets || (!down_bf16 && !push) || expert_count == 0 || first_expert + expert_count > kExperts ||
       reinterpret_cast<uintptr_t>(records) % 16 || reinterpret_cast<uintptr_t>(down_bf16) % 16)
     return fail(GW_INVALID_ARGUMENT, "expert run requires aligned buffers and an expert range inside 0..128");
+  if (push && (!segment_start || !home_base || world == 0 || world > 8 || expert_count * world != kExperts))
+    return fail(GW_INVALID_ARGUMENT, "sending rows home requires the way-home tables of gw_moe_ep_tables and 128 / world experts");
   cudaStream_t s = as_stream(stream);
   w->mark(0, s);
   GW_CUDA_CHECK(launch_moe_keys_from_offsets(offsets, first_expert, expert_count, total_rows, w->sorted_keys,
                                              w->local_offsets, s),
                 "MoE keys from offsets");
-  const gw_status status = run_experts(w, nullptr, nullptr, 1, w->local_offsets, total_rows, table, down_bf16, s, records);
+  if (push)
+    GW_CUDA_CHECK(launch_ep_row_home(w->sorted_keys, w->local_offsets, segment_start, home_base, peer_returned,
+                                     first_expert, expert_count, world, total_rows, w->row_home.as<uint64_t>(), s),
+                  "addresses of the rows' homes");
+  const gw_status status = run_experts(w, nullptr, nullptr, 1, w->local_offsets, total_rows, table,
+                                       push ? w->down.data : down_bf16, s, records,
+                                       push ? w->row_home.as<uint64_t>() : nullptr);
   w->mark(6, s);
   return status;
 }

@@ -498,8 +498,10 @@ ep_dispatch_kernel(const uint4* __restrict__ input, const int32_t* __restrict__ 
 // their owner, source ranks in rank order inside an expert.  One block of 128 threads.
 __global__ void __launch_bounds__(kExperts)
 ep_tables_kernel(const int32_t* __restrict__ counts, const int32_t* __restrict__ physical, uint32_t rank,
-                 uint32_t world, int32_t* __restrict__ dest_row0, int32_t* __restrict__ local_offsets) {
+                 uint32_t world, int32_t* __restrict__ dest_row0, int32_t* __restrict__ local_offsets,
+                 int32_t* __restrict__ segment_start, int32_t* __restrict__ home_base) {
   __shared__ int32_t total_at[kExperts];       // rows of the expert at a physical position, over all sources
+  __shared__ int32_t sorted_base[8][kExperts]; // a source rank's own offsets: rows of experts with a lower id
   const uint32_t e = threadIdx.x, per_rank = kExperts / world;
   int32_t total = 0, before_me = 0;
   for (uint32_t s = 0; s < world; ++s) {
@@ -509,14 +511,46 @@ ep_tables_kernel(const int32_t* __restrict__ counts, const int32_t* __restrict__
   }
   const uint32_t position = uint32_t(physical[e]);
   total_at[position] = total;
+  if (e < world && world <= 8) {               // thread s scans source s's histogram
+    int32_t running = 0;
+    for (uint32_t x = 0; x < kExperts; ++x) { sorted_base[e][x] = running; running += counts[e * kExperts + x]; }
+  }
   __syncthreads();
   int32_t first = 0;                            // rows of the owner's experts placed before this one
   for (uint32_t q = position / per_rank * per_rank; q < position; ++q) first += total_at[q];
   dest_row0[e] = first + before_me;
   if (position / per_rank == rank) {
-    local_offsets[position % per_rank] = first;
-    if (position % per_rank == per_rank - 1) local_offsets[per_rank] = first + total;
+    const uint32_t slot = position % per_rank;
+    local_offsets[slot] = first;
+    if (slot == per_rank - 1) local_offsets[per_rank] = first + total;
+    if (segment_start != nullptr && world <= 8) {
+      // the way home: rows [segment_start[s][slot], +counts[s][e]) of this rank's buffers came
+      // from source s, where they are rows home_base[s][slot].. of its expert-sorted order
+      int32_t running = first;
+      for (uint32_t s = 0; s < world; ++s) {
+        segment_start[s * per_rank + slot] = running;
+        home_base[s * per_rank + slot] = sorted_base[s][e];
+        running += counts[s * kExperts + e];
+      }
+    }
   }
+}
+
+// Byte address, in its source rank's memory, of the home of every row this rank's experts
+// produce: the down GEMM's epilogue stores its rows there directly.
+__global__ void __launch_bounds__(256)
+ep_row_home_kernel(const int32_t* __restrict__ sorted_keys, const int32_t* __restrict__ offsets,
+                   const int32_t* __restrict__ segment_start, const int32_t* __restrict__ home_base,
+                   uint8_t* const* __restrict__ peer_returned, uint32_t first_expert, uint32_t per_rank,
+                   uint32_t world, uint32_t n, uint64_t* __restrict__ row_home) {
+  const uint32_t row = blockIdx.x * 256 + threadIdx.x;
+  if (row >= n || row >= uint32_t(offsets[kExperts])) return;
+  const uint32_t slot = uint32_t(sorted_keys[row]) - first_expert;
+  uint32_t source = 0;
+  for (uint32_t s = 1; s < world; ++s)
+    if (uint32_t(segment_start[s * per_rank + slot]) <= row) source = s;     // starts are non-decreasing in s
+  const uint32_t home_row = uint32_t(home_base[source * per_rank + slot]) + row - uint32_t(segment_start[source * per_rank + slot]);
+  row_home[row] = reinterpret_cast<uint64_t>(peer_returned[source]) + uint64_t(home_row) * (kHidden * 2);
 }
 
 // scale bytes of the local records -> the tiled per-expert regions the GEMM reads
@@ -653,8 +687,19 @@ cudaError_t launch_ep_dispatch(const void* input, const int32_t* sorted_assignme
 }
 
 cudaError_t launch_ep_tables(const int32_t* counts, const int32_t* physical, uint32_t rank, uint32_t world,
-                             int32_t* dest_row0, int32_t* local_offsets, cudaStream_t stream) {
-  ep_tables_kernel<<<1, kExperts, 0, stream>>>(counts, physical, rank, world, dest_row0, local_offsets);
+                             int32_t* dest_row0, int32_t* local_offsets, int32_t* segment_start, int32_t* home_base,
+                             cudaStream_t stream) {
+  ep_tables_kernel<<<1, kExperts, 0, stream>>>(counts, physical, rank, world, dest_row0, local_offsets, segment_start,
+                                               home_base);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ep_row_home(const int32_t* sorted_keys, const int32_t* offsets, const int32_t* segment_start,
+                               const int32_t* home_base, void* const* peer_returned, uint32_t first_expert,
+                               uint32_t per_rank, uint32_t world, uint32_t n, uint64_t* row_home, cudaStream_t stream) {
+  ep_row_home_kernel<<<blocks_for(n), 256, 0, stream>>>(sorted_keys, offsets, segment_start, home_base,
+                                                        reinterpret_cast<uint8_t* const*>(peer_returned), first_expert,
+                                                        per_rank, world, n, row_home);
   return cudaGetLastError();
 }
 

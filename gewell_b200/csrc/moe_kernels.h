@@ -66,7 +66,11 @@ cudaError_t launch_ep_dispatch(const void* input, const int32_t* sorted_assignme
                                const int32_t* dest_row0, void* const* peer_records, uint32_t n,
                                uint32_t capacity_rows, uint32_t* error, cudaStream_t stream);
 cudaError_t launch_ep_tables(const int32_t* counts, const int32_t* physical, uint32_t rank, uint32_t world,
-                             int32_t* dest_row0, int32_t* local_offsets, cudaStream_t stream);
+                             int32_t* dest_row0, int32_t* local_offsets, int32_t* segment_start, int32_t* home_base,
+                             cudaStream_t stream);
+cudaError_t launch_ep_row_home(const int32_t* sorted_keys, const int32_t* offsets, const int32_t* segment_start,
+                               const int32_t* home_base, void* const* peer_returned, uint32_t first_expert,
+                               uint32_t per_rank, uint32_t world, uint32_t n, uint64_t* row_home, cudaStream_t stream);
 cudaError_t launch_ep_retile_scales(const void* records, const int32_t* sorted_keys, const int32_t* offsets,
                                     uint32_t n, uint8_t* scales, cudaStream_t stream);
 cudaError_t launch_ep_combine(const int32_t* keys, const int32_t* inverse, const float* weights,

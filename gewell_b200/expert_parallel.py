@@ -319,10 +319,15 @@ class PeerMemoryExpertParallelMoe:
     RECORD_BYTES = 1584
 
     def __init__(self, experts_by_position, input_scales, rank: int, world: int, local_tokens: int,
-                 receive_capacity_rows: int, placement: Placement | None = None, group=None):
+                 receive_capacity_rows: int, placement: Placement | None = None, group=None,
+                 send_home: bool = True):
         """experts_by_position: 128 entries indexed by physical position, None for
         experts of other ranks.  input_scales: the gate/up input scale of all 128
-        experts by expert id (every rank quantises rows for every expert)."""
+        experts by expert id (every rank quantises rows for every expert).
+        send_home: the down GEMM's epilogue stores each result row into its source
+        rank's memory (the way home overlaps the GEMM) and the source folds local
+        rows; otherwise results stay with the owner and the combine kernel pulls
+        them over NVLink."""
         import gewell_b200 as gw
         self.gw = gw
         self.placement = placement or Placement.contiguous(world)
@@ -334,7 +339,15 @@ class PeerMemoryExpertParallelMoe:
         self.expert_ws = gw.MoeWorkspace((receive_capacity_rows + 7) // 8)
         self.device = self.route_ws.device
         self.records = SharedBuffer(receive_capacity_rows * self.RECORD_BYTES, rank, world, group)
-        self.down = SharedBuffer(receive_capacity_rows * HIDDEN * 2, rank, world, group)
+        self.send_home = send_home and world <= 8
+        if self.send_home:
+            self.returned = SharedBuffer(TOPK * local_tokens * HIDDEN * 2, rank, world, group)
+            self.down = None
+        else:
+            self.returned = None
+            self.down = SharedBuffer(receive_capacity_rows * HIDDEN * 2, rank, world, group)
+        self.segment_start = torch.zeros(world * self.per_rank, dtype=torch.int32, device=self.device)
+        self.home_base = torch.zeros(world * self.per_rank, dtype=torch.int32, device=self.device)
         scales = torch.tensor(list(input_scales), dtype=torch.float32)
         self.inverse_scales = (torch.ones_like(scales) / scales).to(self.device)      # IEEE FP32 division
         self.dest_rank = torch.tensor(self.placement.owner, dtype=torch.int32, device=self.device)
@@ -367,8 +380,11 @@ class PeerMemoryExpertParallelMoe:
         self._mark("route")
         counts = (offsets[1:] - offsets[:-1]).contiguous()
         dist.all_gather_into_tensor(self.counts_all, counts, group=self.group)
+        home = self.send_home
         check(lib.gw_moe_ep_tables(self.counts_all.data_ptr(), self.physical.data_ptr(), self.rank, self.world,
-                                   self.dest_row0.data_ptr(), self.local_offsets.data_ptr(), stream))
+                                   self.dest_row0.data_ptr(), self.local_offsets.data_ptr(),
+                                   self.segment_start.data_ptr() if home else None,
+                                   self.home_base.data_ptr() if home else None, stream))
         self._mark("counts")
         check(lib.gw_moe_ep_dispatch(self.route_ws._ws, x.data_ptr(), rows, self.inverse_scales.data_ptr(),
                                      self.dest_rank.data_ptr(), self.dest_row0.data_ptr(),
@@ -378,17 +394,27 @@ class PeerMemoryExpertParallelMoe:
         self._mark("barrier_1")
         check(lib.gw_moe_ep_run_experts(self.expert_ws._ws, self.records.local, self.local_offsets.data_ptr(),
                                         self.rank * self.per_rank, self.per_rank, self.capacity, self.table.handle,
-                                        self.down.local, stream))
+                                        None if home else self.down.local,
+                                        self.segment_start.data_ptr() if home else None,
+                                        self.home_base.data_ptr() if home else None,
+                                        self.returned.pointer_table.data_ptr() if home else None, self.world, stream))
         self._mark("experts")
         self._barrier()
         self._mark("barrier_2")
         if out is None:
             out = torch.empty((rows, HIDDEN), dtype=torch.bfloat16, device=self.device)
-        check(lib.gw_moe_ep_combine(self.route_ws._ws, rows, self.dest_rank.data_ptr(), self.dest_row0.data_ptr(),
-                                    self.down.pointer_table.data_ptr(), out.data_ptr(), stream))
+        if home:
+            _, _, inverse, weights = self.route_ws.routing_state(rows)
+            check(lib.gw_moe_combine(self.returned.local, inverse.data_ptr(), weights.data_ptr(), rows, HIDDEN,
+                                     out.data_ptr(), stream))
+        else:
+            check(lib.gw_moe_ep_combine(self.route_ws._ws, rows, self.dest_rank.data_ptr(), self.dest_row0.data_ptr(),
+                                        self.down.pointer_table.data_ptr(), out.data_ptr(), stream))
         self._mark("combine")
         return out
 
     def close(self):
         self.records.close(self.group)
-        self.down.close(self.group)
+        for buffer in (self.down, self.returned):
+            if buffer is not None:
+                buffer.close(self.group)

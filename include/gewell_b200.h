@@ -301,7 +301,12 @@ gw_status gw_moe_ep_dispatch(gw_moe_workspace* workspace, const void* input_bf16
  * capacity_rows is dropped by the dispatch and reported through the kernel
  * error word. */
 gw_status gw_moe_ep_tables(const int32_t* counts, const int32_t* physical, uint32_t rank, uint32_t world,
-                           int32_t* dest_row0, int32_t* local_offsets, void* stream);
+                           int32_t* dest_row0, int32_t* local_offsets, int32_t* segment_start,
+                           int32_t* home_base, void* stream);
+/* segment_start / home_base (both NULL, or world x 128/world int32 each, world <= 8)
+ * describe the way home for gw_moe_ep_run_experts: rows [segment_start[s][j], ...)
+ * of this rank's j-th expert came from rank s, where they are rows home_base[s][j]..
+ * of its expert-sorted order. */
 
 /* Owner side: grouped gate/up GEMM + GeGLU + grouped down GEMM over the
  * records this rank received, grouped by expert as `offsets` (expert_count + 1
@@ -310,7 +315,16 @@ gw_status gw_moe_ep_tables(const int32_t* counts, const int32_t* physical, uint3
  * order go to `down_bf16` (a gw_ipc_alloc buffer when peers read it). */
 gw_status gw_moe_ep_run_experts(gw_moe_workspace* workspace, const void* records, const int32_t* offsets,
                                 uint32_t first_expert, uint32_t expert_count, uint32_t total_rows,
-                                const gw_expert_table* table, void* down_bf16, void* stream);
+                                const gw_expert_table* table, void* down_bf16,
+                                const int32_t* segment_start, const int32_t* home_base,
+                                void* const* peer_returned, uint32_t world, void* stream);
+/* With peer_returned != NULL (one [8 * tokens, 2816] BF16 gw_ipc_alloc buffer per
+ * rank, pointers in device memory) the down GEMM's epilogue stores every result row
+ * straight into its source rank's buffer, at the row's position in that rank's
+ * expert-sorted order, so the transfer home overlaps the GEMM; down_bf16 is then
+ * unused and the source folds its rows with gw_moe_combine after a barrier.
+ * With peer_returned == NULL the rows stay in down_bf16 and gw_moe_ep_combine pulls
+ * them. */
 
 /* Ordered BF16 fold (moe.cu:446-456) of each token's eight result rows, read
  * from their owners: row dest_row0[e] + position of peer_down[dest_rank[e]]. */

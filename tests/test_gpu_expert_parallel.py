@@ -117,16 +117,26 @@ def test_destination_tables_match_numpy(layer):
             offsets = torch.zeros(per_rank + 1, dtype=torch.int32, device="cuda")
             device_counts = torch.from_numpy(counts).cuda()
             device_physical = torch.tensor(placement.physical, dtype=torch.int32).cuda()
+            segment_start = torch.zeros(world * per_rank, dtype=torch.int32, device="cuda")
+            home_base = torch.zeros(world * per_rank, dtype=torch.int32, device="cuda")
             gw.ops._check(gw.lib.gw_moe_ep_tables(device_counts.data_ptr(), device_physical.data_ptr(), rank, world,
-                                                  row0.data_ptr(), offsets.data_ptr(),
-                                                  torch.cuda.current_stream().cuda_stream))
+                                                  row0.data_ptr(), offsets.data_ptr(), segment_start.data_ptr(),
+                                                  home_base.data_ptr(), torch.cuda.current_stream().cuda_stream))
             torch.cuda.synchronize()
+            # the way home: segment of source s inside local expert j, and s's own sorted offset of that expert
+            want_start = np.zeros((world, per_rank), dtype=np.int64)
+            want_home = np.zeros((world, per_rank), dtype=np.int64)
+            for j, e in enumerate(mine):
+                want_start[:, j] = want_offsets[j] + np.concatenate([[0], np.cumsum(counts[:-1, e])])
+                want_home[:, j] = [counts[s_, :e].sum() for s_ in range(world)]
+            assert np.array_equal(segment_start.cpu().numpy().reshape(world, per_rank), want_start)
+            assert np.array_equal(home_base.cpu().numpy().reshape(world, per_rank), want_home)
             assert np.array_equal(row0.cpu().numpy(), want_row0)
             assert np.array_equal(offsets.cpu().numpy(), want_offsets)
 
 
-@pytest.mark.parametrize("tokens", [40, 900])
-def test_record_path_on_one_rank_equals_layer(layer, tokens):
+@pytest.mark.parametrize("tokens,send_home", [(40, False), (900, False), (40, True), (900, True)])
+def test_record_path_on_one_rank_equals_layer(layer, tokens, send_home):
     """Dispatch into records, grouped GEMMs on the records, combine through the
     pointer table -- with this GPU as the only rank -- give the layer's output."""
     import ctypes
@@ -148,17 +158,30 @@ def test_record_path_on_one_rank_equals_layer(layer, tokens):
     dest_rank = torch.zeros(E, dtype=torch.int32, device="cuda")
     row0 = torch.zeros(E, dtype=torch.int32, device="cuda")
     local_offsets = torch.zeros(E + 1, dtype=torch.int32, device="cuda")
-    check(lib.gw_moe_ep_tables(counts.data_ptr(), physical.data_ptr(), 0, 1, row0.data_ptr(), local_offsets.data_ptr(), stream))
+    segment_start = torch.zeros(E, dtype=torch.int32, device="cuda")
+    home_base = torch.zeros(E, dtype=torch.int32, device="cuda")
+    check(lib.gw_moe_ep_tables(counts.data_ptr(), physical.data_ptr(), 0, 1, row0.data_ptr(), local_offsets.data_ptr(),
+                               segment_start.data_ptr(), home_base.data_ptr(), stream))
     inverse_scales = (torch.ones(E) / torch.full((E,), 6.0 / 2688)).cuda()
     record_table = torch.tensor([records.data_ptr()], dtype=torch.int64, device="cuda")
     down_table = torch.tensor([down.data_ptr()], dtype=torch.int64, device="cuda")
     check(lib.gw_moe_ep_dispatch(route_ws._ws, x.data_ptr(), tokens, inverse_scales.data_ptr(), dest_rank.data_ptr(),
                                  row0.data_ptr(), record_table.data_ptr(), capacity, stream))
-    check(lib.gw_moe_ep_run_experts(expert_ws._ws, records.data_ptr(), local_offsets.data_ptr(), 0, E, capacity,
-                                    table.handle, down.data_ptr(), stream))
     out = torch.empty((tokens, H), dtype=torch.bfloat16, device="cuda")
-    check(lib.gw_moe_ep_combine(route_ws._ws, tokens, dest_rank.data_ptr(), row0.data_ptr(), down_table.data_ptr(),
-                                out.data_ptr(), stream))
+    if send_home:
+        returned = torch.full((8 * tokens, H), float("nan"), dtype=torch.bfloat16, device="cuda")
+        returned_table = torch.tensor([returned.data_ptr()], dtype=torch.int64, device="cuda")
+        check(lib.gw_moe_ep_run_experts(expert_ws._ws, records.data_ptr(), local_offsets.data_ptr(), 0, E, capacity,
+                                        table.handle, None, segment_start.data_ptr(), home_base.data_ptr(),
+                                        returned_table.data_ptr(), 1, stream))
+        _, _, inverse, weights = route_ws.routing_state(tokens)
+        check(lib.gw_moe_combine(returned.data_ptr(), inverse.data_ptr(), weights.data_ptr(), tokens, H, out.data_ptr(),
+                                 stream))
+    else:
+        check(lib.gw_moe_ep_run_experts(expert_ws._ws, records.data_ptr(), local_offsets.data_ptr(), 0, E, capacity,
+                                        table.handle, down.data_ptr(), None, None, None, 1, stream))
+        check(lib.gw_moe_ep_combine(route_ws._ws, tokens, dest_rank.data_ptr(), row0.data_ptr(), down_table.data_ptr(),
+                                    out.data_ptr(), stream))
     torch.cuda.synchronize()
     assert gw.kernel_error() == 0
     assert np.array_equal(local_offsets.cpu().numpy(), offsets.cpu().numpy())
@@ -198,9 +221,9 @@ def _worker(rank: int, world: int, port: int, placement_name: str, exchange: str
         for e in mine:
             by_position[placement.physical[e]] = by_id[e]
         local = tokens // world
-        if exchange == "peer":
+        if exchange in ("peer", "peer_pull"):
             moe = ep.PeerMemoryExpertParallelMoe(by_position, [6.0 / 2688] * E, rank, world, local, 8 * tokens,
-                                                 placement=placement)
+                                                 placement=placement, send_home=exchange == "peer")
         else:
             backend = ep.DeviceBackend(by_position, local, 8 * tokens)
             moe = ep.ExpertParallelMoe(backend, rank, world, local, 8 * tokens, placement=placement)
@@ -210,14 +233,15 @@ def _worker(rank: int, world: int, port: int, placement_name: str, exchange: str
         torch.cuda.synchronize()
         assert gw.kernel_error() == 0
         np.save(os.path.join(out_dir, f"y{rank}.npy"), bits(y))
-        if exchange == "peer":
+        if exchange in ("peer", "peer_pull"):
             moe.close()
     finally:
         dist.destroy_process_group()
 
 
 @pytest.mark.parametrize("placement_name,exchange", [("contiguous", "nccl"), ("balanced", "nccl"),
-                                                     ("contiguous", "peer"), ("balanced", "peer")])
+                                                     ("contiguous", "peer"), ("balanced", "peer"),
+                                                     ("balanced", "peer_pull")])
 def test_two_ranks_equal_single_gpu(layer, tmp_path, placement_name, exchange):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
