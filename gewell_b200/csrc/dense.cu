@@ -83,6 +83,7 @@ gw_status launch_dense(const DenseProblem& q, DenseDescriptors* cache, cudaStrea
   g.map_l = -1;
   g.map_c[0] = g.map_c[1] = -1;
   if (swap) {
+    params.early_weights = 1;   // weights are never written by the activation-quantise kernel before this launch
     params.map_l = cache->weight_map;
     params.map_c = cache->activation_map;
     params.c_rows_per_tile = block_n;

@@ -214,7 +214,8 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
   const uint32_t tmem_base = *tmem_slot;
   // Everything above is independent of earlier kernels in the stream and may overlap
   // them (programmatic dependent launch); from here on their results are read.
-  griddep_wait();
+  const bool early_weights = EPI == GemmEpilogue::swap_store && p.groups == nullptr && p.early_weights != 0;
+  if (!(early_weights && warp == 0)) griddep_wait();
   if (p.groups != nullptr) {
     for (int i = threadIdx.x; i <= p.num_groups; i += kThreads) prefix[i] = p.groups[i].work_begin;
     __syncthreads();
@@ -251,6 +252,7 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
     // ------------------------------------------------------------------ producer
     int stage = 0;
     uint32_t phase = 0;
+    bool waited = !early_weights;        // this warp defers its wait for the previous kernel (see below)
     WorkItem item, next;
     SegmentWalk walk(split, total_work, k_stages);
     int tile, ks0, ks1, next_tile, next_ks0, next_ks1;
@@ -267,12 +269,10 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
       const CUtensorMap* map_c[2];
 #pragma unroll
       for (int h = 0; h < C::kHalves; ++h) map_c[h] = item.g.map_c[h] >= 0 ? p.map_table + item.g.map_c[h] : &p.map_c;
-      if (lane == 0) {
-        if (item.g.map_l >= 0) ptx::tensormap_acquire(map_l);
-#pragma unroll
-        for (int h = 0; h < C::kHalves; ++h)
-          if (item.g.map_c[h] >= 0) ptx::tensormap_acquire(map_c[h]);
-      }
+      // The descriptors in map_table were written by the host before any launch that uses
+      // them (expert table creation), so ordinary launch ordering makes them visible to the
+      // copy engine; no proxy fence is needed per use (one system-scope fence per work item
+      // cost more than the item's copies).
       const int l_row = item.g.l_row0 + item.l_tile * kTileL;
       const int c_local = item.c_tile * p.c_rows_per_tile;   // row inside each matrix of the C operand
       const int halves = item.halves;
@@ -292,22 +292,22 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
       // engine's cost per operation, not per byte, is what limits the fill rate)
       const bool single_box = C::kHalves == 2 && p.c_single_box != 0;
       const uint32_t c_bytes = single_box ? uint32_t(C::kCBytes) : uint32_t(halves * C::kHalfRows * kStageRowBytes);
-      for (int ks = ks0; ks < ks1; ++ks) {
-        const long long t0 = p.profile ? clock64() : 0;
-        if (!ptx::mbar_wait_warp(empty_bar + stage, phase ^ 1)) {
-          report(p.error, 0x10000000u | (blockIdx.x << 8) | stage, abort_flag);
-          break;
-        }
-        if (p.profile) prof_wait += clock64() - t0;
-        if (lane == 0) {
-          const int nkb = min(kKBlocksPerStage, total_kb - ks * kKBlocksPerStage);
+      // one stage's copies; `weights` / `tokens` select the L-side and the C-side copies
+      auto issue = [&](int ks, int st, bool l_side, bool c_side) {
+        const int nkb = min(kKBlocksPerStage, total_kb - ks * kKBlocksPerStage);
+        uint8_t* base = smem + st * C::kStageBytes;
+        uint64_t* bar = full_bar + st;
+        if (l_side) {                      // the stage's byte count is announced with its first copies
           uint32_t bytes = C::kLBytes + c_bytes;
           if constexpr (kNvfp4)
             bytes += nkb * kAtomBytes + (single_box ? uint32_t(C::kSfcBytes) : uint32_t(nkb * kAtomBytes * halves));
-          uint8_t* base = smem + stage * C::kStageBytes;
-          uint64_t* bar = full_bar + stage;
           ptx::mbar_expect_tx(bar, bytes);
           ptx::tma_load_2d(base, map_l, ks * kStageRowBytes, l_row, bar);
+          if constexpr (kNvfp4)
+            ptx::bulk_load(base + C::kLBytes + C::kCBytes, sfl_src + size_t(ks) * kKBlocksPerStage * kAtomBytes,
+                           nkb * kAtomBytes, bar);
+        }
+        if (c_side) {
           if (single_box) {
             ptx::tma_load_2d(base + C::kLBytes, &p.map_c, ks * kStageRowBytes, c_row[0], bar);
           } else {
@@ -319,7 +319,6 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
           }
           if constexpr (kNvfp4) {
             const size_t atom_offset = size_t(ks) * kKBlocksPerStage * kAtomBytes;
-            ptx::bulk_load(base + C::kLBytes + C::kCBytes, sfl_src + atom_offset, nkb * kAtomBytes, bar);
             if (single_box) {
               // scale storage seen as [row blocks][K/64 atoms] of 8-byte words: 256 words = 4 atoms
               ptx::tma_load_2d(base + C::kLBytes + C::kCBytes + C::kSflBytes, &p.map_sfc, ks * 256, c_local / 128, bar);
@@ -332,10 +331,38 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
             }
           }
         }
+      };
+      int ks_begin = ks0;
+      if (early_weights && !waited) {
+        // Decode shapes: the weights (L side) do not depend on the kernel that quantises the
+        // activations, so the first ring of weight copies is issued before waiting for it;
+        // the token-side copies of those stages follow once it has finished.
+        const int ahead = min(C::kStages, ks1 - ks0);
+        if (lane == 0)
+          for (int i = 0; i < ahead; ++i) issue(ks0 + i, i, true, false);
+        __syncwarp();
+        griddep_wait();
+        waited = true;
+        if (lane == 0)
+          for (int i = 0; i < ahead; ++i) issue(ks0 + i, i, false, true);
+        __syncwarp();
+        stage = ahead == C::kStages ? 0 : ahead;
+        phase = ahead == C::kStages ? 1 : 0;
+        ks_begin = ks0 + ahead;
+      }
+      for (int ks = ks_begin; ks < ks1; ++ks) {
+        const long long t0 = p.profile ? clock64() : 0;
+        if (!ptx::mbar_wait_warp(empty_bar + stage, phase ^ 1)) {
+          report(p.error, 0x10000000u | (blockIdx.x << 8) | stage, abort_flag);
+          break;
+        }
+        if (p.profile) prof_wait += clock64() - t0;
+        if (lane == 0) issue(ks, stage, true, true);
         __syncwarp();
         if (++stage == C::kStages) { stage = 0; phase ^= 1; }
       }
     }
+    if (!waited) griddep_wait();
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     int stage = 0, acc = 0;

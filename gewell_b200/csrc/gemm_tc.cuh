@@ -71,6 +71,9 @@ struct GemmParams {
   // (tile, K stage) units; partial tiles are summed through these buffers.
   float* split_partials;          // [2 * grid][128 * BLOCK_N] FP32, or nullptr (whole tiles per CTA)
   int32_t* split_counters;        // [work items], zero at launch; left zero by the kernel
+  int32_t early_weights;          // swap form, groups == nullptr: the L operand (weights, weight scales) does not
+                                  // depend on the previous kernel in the stream, so its first copies may be
+                                  // issued before that kernel has finished (programmatic dependent launch)
   uint32_t* error;                // device error word (0 = fine)
   long long* profile;             // optional [grid][8] cycle counters (debug aid), normally nullptr
 };
