@@ -441,7 +441,10 @@ def main():
     achieved = flops / (gemm_ms * 1e-3) / 1e12
     roofline = {"kernel": "gemm_tc_kernel<nvfp4> (grouped gate/up + grouped down)", "bound": "tensor",
                 "achieved": achieved, "peak": fp4_peak, "unit": "TFLOP/s", "frac": achieved / fp4_peak,
-                "traffic": None,
+                # dram__bytes_read.sum + dram__bytes_write.sum of the two launches at this size, from the one-pass
+                # ncu capture summarised in profiles/bench_moe_T8192_launch_list.md (gate/up 440.9 MB, down 484.7 MB)
+                "traffic": 925.6e6 if tokens == 8192 else None, "traffic_unit": "bytes per layer pass (both launches)",
+                "algorithmic_bytes": 979.0e6 if tokens == 8192 else None,
                 "peak_note": f"4 x the {peaks['source']} dense BF16 burst figure ({peaks['bf16_tflops']} TFLOP/s); "
                              "no FP4 GEMM peak was measured on this pool (nominal dense FP4: 9000 TFLOP/s)",
                 "frac_of_nominal_fp4": achieved / 9000.0,
