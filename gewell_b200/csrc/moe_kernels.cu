@@ -412,18 +412,24 @@ moe_combine_kernel(const uint4* __restrict__ down, const int32_t* __restrict__ i
   const size_t index = size_t(blockIdx.x) * 256 + threadIdx.x;
   if (index >= size_t(rows) * vectors) return;
   const uint32_t row = index / vectors, v = index % vectors;
+  uint4 raw[kTopK];
+  float w[kTopK];
+#pragma unroll
+  for (int j = 0; j < kTopK; ++j) {        // all eight gathered loads are in flight before the fold starts
+    const uint32_t assignment = row * kTopK + j;
+    raw[j] = down[size_t(inverse[assignment]) * vectors + v];
+    w[j] = weights[assignment];
+  }
   float sum[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) sum[i] = 0.0F;
 #pragma unroll
   for (int j = 0; j < kTopK; ++j) {
-    const uint32_t assignment = row * kTopK + j;
-    const float w = weights[assignment];
     float x[8];
-    unpack8(down[size_t(inverse[assignment]) * vectors + v], x);
+    unpack8(raw[j], x);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const float product = __bfloat162float(__float2bfloat16_rn(__fmul_rn(x[i], w)));
+      const float product = __bfloat162float(__float2bfloat16_rn(__fmul_rn(x[i], w[j])));
       sum[i] = __bfloat162float(__float2bfloat16_rn(__fadd_rn(sum[i], product)));
     }
   }
