@@ -226,6 +226,11 @@ gw_status run_experts(gw_moe_workspace* w, const void* input, const int32_t* gat
   if (records != nullptr) {
     GW_CUDA_CHECK(launch_ep_retile_scales(records, w->sorted_keys, offsets, n, w->scales_in.as<uint8_t>(), s),
                   "MoE scale re-tiling of received rows");
+  } else if (gather_index == w->sorted_assignments && gather_divisor == 8 && n % 8 == 0) {
+    // whole-layer path: rows are the routed copies of n / 8 tokens
+    GW_CUDA_CHECK(launch_moe_quantize_tokens(input, w->keys, w->inverse, offsets, info, n / 8, w->scale_rows, parts,
+                                             w->packed_in.as<uint8_t>(), w->scales_in.as<uint8_t>(), s),
+                  "MoE quantise (token-major)");
   } else {
     GW_CUDA_CHECK(launch_moe_quantize_input(input, gather_index, gather_divisor, w->sorted_keys, offsets, info, n,
                                             w->scale_rows, parts, w->packed_in.as<uint8_t>(), w->scales_in.as<uint8_t>(), s),
@@ -448,9 +453,8 @@ gw_status gw_moe_ep_dispatch(gw_moe_workspace* w, const void* input_bf16, uint32
   if (!input_bf16 || !inverse_input_scales || !dest_rank || !dest_row0 || !peer_records ||
       reinterpret_cast<uintptr_t>(input_bf16) % 16)
     return fail(GW_INVALID_ARGUMENT, "expert-parallel dispatch requires a 16-byte aligned input and the destination tables");
-  GW_CUDA_CHECK(launch_ep_dispatch(input_bf16, w->sorted_assignments, w->sorted_keys, w->offsets, inverse_input_scales,
-                                   dest_rank, dest_row0, peer_records, 8 * rows, capacity_rows, device_error_word(),
-                                   as_stream(stream)),
+  GW_CUDA_CHECK(launch_ep_dispatch(input_bf16, w->keys, w->inverse, w->offsets, inverse_input_scales, dest_rank,
+                                   dest_row0, peer_records, rows, capacity_rows, device_error_word(), as_stream(stream)),
                 "expert-parallel dispatch");
   return GW_OK;
 }

@@ -401,6 +401,69 @@ moe_quantize_kernel(const uint4* __restrict__ input, const int32_t* __restrict__
 }
 
 // ---------------------------------------------------------------------------
+// 5b. The same quantisation, token-major: one warp reads a token's row once
+//     (a lane keeps six K16 blocks as packed BF16 and their maxima) and writes
+//     the token's eight quantised copies, one per chosen expert, each with that
+//     expert's input scale, at the copy's sorted position.  Arithmetic per
+//     value is that of kernel 5, so the bytes are identical; the input is read
+//     from memory once instead of eight times.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+moe_quantize_tokens_kernel(const uint4* __restrict__ input, const int32_t* __restrict__ keys,
+                           const int32_t* __restrict__ inverse, const int32_t* __restrict__ offsets,
+                           const MoeExpertInfo* __restrict__ experts, uint32_t tokens, uint32_t scale_rows, int parts,
+                           uint2* __restrict__ packed, uint8_t* __restrict__ scales) {
+  constexpr uint32_t kBlocks = kHidden / 16;            // 176
+  constexpr int kPerLane = (kBlocks + 31) / 32;         // 6
+  const uint32_t token = (blockIdx.x * 256 + threadIdx.x) / 32, lane = threadIdx.x % 32;
+  if (token >= tokens) return;
+  const uint32_t n = tokens * kTopK;
+  uint32_t raw[kPerLane][8];
+  float amax[kPerLane];
+#pragma unroll
+  for (int i = 0; i < kPerLane; ++i) {
+    const uint32_t kb = lane + 32 * i;
+    amax[i] = 0.0F;
+    if (kb < kBlocks) {
+      const uint4 a = input[2 * (size_t(token) * kBlocks + kb)], b = input[2 * (size_t(token) * kBlocks + kb) + 1];
+      raw[i][0] = a.x; raw[i][1] = a.y; raw[i][2] = a.z; raw[i][3] = a.w;
+      raw[i][4] = b.x; raw[i][5] = b.y; raw[i][6] = b.z; raw[i][7] = b.w;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        amax[i] = fmaxf(amax[i], fabsf(__uint_as_float(raw[i][k] << 16)));
+        amax[i] = fmaxf(amax[i], fabsf(__uint_as_float(raw[i][k] & 0xFFFF0000u)));
+      }
+    }
+  }
+  for (int j = 0; j < kTopK; ++j) {
+    const uint32_t assignment = token * kTopK + j;
+    const int32_t e = keys[assignment];
+    const uint32_t row = uint32_t(inverse[assignment]);
+    const int32_t first = offsets[e];
+    for (int part = 0; part < parts; ++part) {
+      const float inverse_scale = experts[e].inverse_input_scale[part];
+      const size_t region = (size_t(part) * scale_rows + size_t(first / 128 + e) * 128) * kBlocks;
+#pragma unroll
+      for (int i = 0; i < kPerLane; ++i) {
+        const uint32_t kb = lane + 32 * i;
+        if (kb >= kBlocks) continue;
+        const uint8_t scale_code = float_to_e4m3(inverse_scale * (amax[i] * rcp_approx_ftz(6.0F)));
+        const float block_scale = e4m3_to_float(scale_code);
+        const float factor =
+            block_scale == 0.0F ? 0.0F : rcp_approx_ftz(block_scale * rcp_approx_ftz(inverse_scale));
+        uint32_t out[2] = {0, 0};
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          out[k / 4] |= uint32_t(float2_to_e2m1x2(__uint_as_float(raw[i][k] << 16) * factor,
+                                                  __uint_as_float(raw[i][k] & 0xFFFF0000u) * factor)) << (8 * (k % 4));
+        packed[(size_t(part) * n + row) * kBlocks + kb] = make_uint2(out[0], out[1]);
+        scales[region + scale_offset(row - first, kb, kHidden)] = scale_code;
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
 // 6. combine: out[t,:] = ordered BF16 fold over the token's eight slots
 //    (ascending expert id) of bf16(down[inverse[8t+j],:] * w[8t+j])
 //    (moe.cu:446-456).  Eight columns per thread.
@@ -463,40 +526,60 @@ gather_rows_kernel(const uint4* __restrict__ input, const int32_t* __restrict__ 
 constexpr uint32_t kRecordBytes = kHidden / 2 + kHidden / 16;   // 1584
 
 __global__ void __launch_bounds__(256)
-ep_dispatch_kernel(const uint4* __restrict__ input, const int32_t* __restrict__ sorted_assignments,
-                   const int32_t* __restrict__ sorted_keys, const int32_t* __restrict__ offsets,
+ep_dispatch_kernel(const uint4* __restrict__ input, const int32_t* __restrict__ keys,
+                   const int32_t* __restrict__ inverse, const int32_t* __restrict__ offsets,
                    const float* __restrict__ inverse_input_scale, const int32_t* __restrict__ dest_rank,
-                   const int32_t* __restrict__ dest_row0, uint8_t* const* __restrict__ peer_records, uint32_t n,
+                   const int32_t* __restrict__ dest_row0, uint8_t* const* __restrict__ peer_records, uint32_t tokens,
                    uint32_t capacity_rows, uint32_t* __restrict__ error) {
+  // token-major like kernel 5b: one warp reads a token once and writes its eight records
   constexpr uint32_t kBlocks = kHidden / 16;
-  const size_t index = size_t(blockIdx.x) * 256 + threadIdx.x;
-  if (index >= size_t(n) * kBlocks) return;
-  const uint32_t row = index / kBlocks, kb = index % kBlocks;
-  const int32_t e = sorted_keys[row];
-  const float inverse_scale = inverse_input_scale[e];
-  const size_t source_row = size_t(uint32_t(sorted_assignments[row]) / kTopK);
-  float values[16];
-  unpack8(input[2 * (source_row * kBlocks + kb)], values);
-  unpack8(input[2 * (source_row * kBlocks + kb) + 1], values + 8);
-  float amax = 0.0F;
+  constexpr int kPerLane = (kBlocks + 31) / 32;
+  const uint32_t token = (blockIdx.x * 256 + threadIdx.x) / 32, lane = threadIdx.x % 32;
+  if (token >= tokens) return;
+  uint32_t raw[kPerLane][8];
+  float amax[kPerLane];
 #pragma unroll
-  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(values[i]));
-  const uint8_t scale_code = float_to_e4m3(inverse_scale * (amax * rcp_approx_ftz(6.0F)));
-  const float block_scale = e4m3_to_float(scale_code);
-  const float factor =
-      block_scale == 0.0F ? 0.0F : rcp_approx_ftz(block_scale * rcp_approx_ftz(inverse_scale));
-  uint32_t out[2] = {0, 0};
+  for (int i = 0; i < kPerLane; ++i) {
+    const uint32_t kb = lane + 32 * i;
+    amax[i] = 0.0F;
+    if (kb < kBlocks) {
+      const uint4 a = input[2 * (size_t(token) * kBlocks + kb)], b = input[2 * (size_t(token) * kBlocks + kb) + 1];
+      raw[i][0] = a.x; raw[i][1] = a.y; raw[i][2] = a.z; raw[i][3] = a.w;
+      raw[i][4] = b.x; raw[i][5] = b.y; raw[i][6] = b.z; raw[i][7] = b.w;
 #pragma unroll
-  for (int i = 0; i < 8; ++i)
-    out[i / 4] |= uint32_t(float2_to_e2m1x2(values[2 * i] * factor, values[2 * i + 1] * factor)) << (8 * (i % 4));
-  const uint32_t dest_row = uint32_t(dest_row0[e] + int32_t(row) - offsets[e]);
-  if (dest_row >= capacity_rows) {          // the owner's buffer is too small: report, never write outside it
-    if (kb == 0 && error != nullptr) atomicCAS(error, 0u, 0x70000000u | uint32_t(e));
-    return;
+      for (int k = 0; k < 8; ++k) {
+        amax[i] = fmaxf(amax[i], fabsf(__uint_as_float(raw[i][k] << 16)));
+        amax[i] = fmaxf(amax[i], fabsf(__uint_as_float(raw[i][k] & 0xFFFF0000u)));
+      }
+    }
   }
-  uint8_t* record = peer_records[dest_rank[e]] + size_t(dest_row) * kRecordBytes;
-  *reinterpret_cast<uint2*>(record + kb * 8) = make_uint2(out[0], out[1]);
-  record[kHidden / 2 + kb] = scale_code;
+  for (int j = 0; j < kTopK; ++j) {
+    const uint32_t assignment = token * kTopK + j;
+    const int32_t e = keys[assignment];
+    const float inverse_scale = inverse_input_scale[e];
+    const uint32_t dest_row = uint32_t(dest_row0[e] + inverse[assignment] - offsets[e]);
+    if (dest_row >= capacity_rows) {          // the owner's buffer is too small: report, never write outside it
+      if (lane == 0 && error != nullptr) atomicCAS(error, 0u, 0x70000000u | uint32_t(e));
+      continue;
+    }
+    uint8_t* record = peer_records[dest_rank[e]] + size_t(dest_row) * kRecordBytes;
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) {
+      const uint32_t kb = lane + 32 * i;
+      if (kb >= kBlocks) continue;
+      const uint8_t scale_code = float_to_e4m3(inverse_scale * (amax[i] * rcp_approx_ftz(6.0F)));
+      const float block_scale = e4m3_to_float(scale_code);
+      const float factor =
+          block_scale == 0.0F ? 0.0F : rcp_approx_ftz(block_scale * rcp_approx_ftz(inverse_scale));
+      uint32_t out[2] = {0, 0};
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        out[k / 4] |= uint32_t(float2_to_e2m1x2(__uint_as_float(raw[i][k] << 16) * factor,
+                                                __uint_as_float(raw[i][k] & 0xFFFF0000u) * factor)) << (8 * (k % 4));
+      *reinterpret_cast<uint2*>(record + kb * 8) = make_uint2(out[0], out[1]);
+      record[kHidden / 2 + kb] = scale_code;
+    }
+  }
 }
 
 // Where every rank's rows of every expert go, from the all-gathered histogram
@@ -575,13 +658,15 @@ ep_retile_scales_kernel(const uint8_t* __restrict__ records, const int32_t* __re
   *reinterpret_cast<uint32_t*>(scales + region + scale_offset(row - first, word * 4, kHidden)) = value;
 }
 
-__global__ void __launch_bounds__(256)
+// Small blocks (128 threads, at most 64 registers): many independent blocks keep enough
+// remote loads in flight to cover the NVLink latency.
+__global__ void __launch_bounds__(128, 8)
 ep_combine_kernel(const int32_t* __restrict__ keys, const int32_t* __restrict__ inverse,
                   const float* __restrict__ weights, const int32_t* __restrict__ offsets,
                   const int32_t* __restrict__ dest_rank, const int32_t* __restrict__ dest_row0,
                   const uint4* const* __restrict__ peer_down, uint32_t rows, uint4* __restrict__ output) {
   constexpr uint32_t kVectors = kHidden / 8;
-  const size_t index = size_t(blockIdx.x) * 256 + threadIdx.x;
+  const size_t index = size_t(blockIdx.x) * 128 + threadIdx.x;
   if (index >= size_t(rows) * kVectors) return;
   const uint32_t row = index / kVectors, v = index % kVectors;
   uint4 raw[kTopK];
@@ -658,6 +743,16 @@ cudaError_t launch_moe_quantize_input(const void* input, const int32_t* gather_i
   return cudaGetLastError();
 }
 
+cudaError_t launch_moe_quantize_tokens(const void* input, const int32_t* keys, const int32_t* inverse,
+                                       const int32_t* offsets, const MoeExpertInfo* experts, uint32_t tokens,
+                                       uint32_t scale_rows, int parts, uint8_t* packed, uint8_t* scales,
+                                       cudaStream_t stream) {
+  moe_quantize_tokens_kernel<<<blocks_for(size_t(tokens) * 32), 256, 0, stream>>>(
+      static_cast<const uint4*>(input), keys, inverse, offsets, experts, tokens, scale_rows, parts,
+      reinterpret_cast<uint2*>(packed), scales);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_moe_activate_quantize(const void* gate_up, const int32_t* sorted_keys, const int32_t* offsets,
                                          const MoeExpertInfo* experts, uint32_t n, uint32_t scale_rows, uint8_t* packed,
                                          uint8_t* scales, void* activated, cudaStream_t stream) {
@@ -682,13 +777,13 @@ cudaError_t launch_gather_rows(const void* input, const int32_t* index, uint32_t
   return cudaGetLastError();
 }
 
-cudaError_t launch_ep_dispatch(const void* input, const int32_t* sorted_assignments, const int32_t* sorted_keys,
-                               const int32_t* offsets, const float* inverse_input_scale, const int32_t* dest_rank,
-                               const int32_t* dest_row0, void* const* peer_records, uint32_t n,
-                               uint32_t capacity_rows, uint32_t* error, cudaStream_t stream) {
-  ep_dispatch_kernel<<<blocks_for(size_t(n) * (kHidden / 16)), 256, 0, stream>>>(
-      static_cast<const uint4*>(input), sorted_assignments, sorted_keys, offsets, inverse_input_scale, dest_rank,
-      dest_row0, reinterpret_cast<uint8_t* const*>(peer_records), n, capacity_rows, error);
+cudaError_t launch_ep_dispatch(const void* input, const int32_t* keys, const int32_t* inverse, const int32_t* offsets,
+                               const float* inverse_input_scale, const int32_t* dest_rank, const int32_t* dest_row0,
+                               void* const* peer_records, uint32_t tokens, uint32_t capacity_rows, uint32_t* error,
+                               cudaStream_t stream) {
+  ep_dispatch_kernel<<<blocks_for(size_t(tokens) * 32), 256, 0, stream>>>(
+      static_cast<const uint4*>(input), keys, inverse, offsets, inverse_input_scale, dest_rank, dest_row0,
+      reinterpret_cast<uint8_t* const*>(peer_records), tokens, capacity_rows, error);
   return cudaGetLastError();
 }
 
@@ -719,7 +814,7 @@ cudaError_t launch_ep_retile_scales(const void* records, const int32_t* sorted_k
 cudaError_t launch_ep_combine(const int32_t* keys, const int32_t* inverse, const float* weights,
                               const int32_t* offsets, const int32_t* dest_rank, const int32_t* dest_row0,
                               void* const* peer_down, uint32_t rows, void* output, cudaStream_t stream) {
-  ep_combine_kernel<<<blocks_for(size_t(rows) * (kHidden / 8)), 256, 0, stream>>>(
+  ep_combine_kernel<<<unsigned((size_t(rows) * (kHidden / 8) + 127) / 128), 128, 0, stream>>>(
       keys, inverse, weights, offsets, dest_rank, dest_row0, reinterpret_cast<const uint4* const*>(peer_down), rows,
       static_cast<uint4*>(output));
   return cudaGetLastError();

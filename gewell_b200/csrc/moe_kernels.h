@@ -50,6 +50,12 @@ cudaError_t launch_moe_quantize_input(const void* input, const int32_t* gather_i
                                       const int32_t* sorted_keys, const int32_t* offsets,
                                       const MoeExpertInfo* experts, uint32_t n, uint32_t scale_rows, int parts,
                                       uint8_t* packed, uint8_t* scales, cudaStream_t stream);
+// Token-major form of the same quantisation for the whole-layer path: reads each token once and
+// writes its eight copies at inverse[8 t + slot].
+cudaError_t launch_moe_quantize_tokens(const void* input, const int32_t* keys, const int32_t* inverse,
+                                       const int32_t* offsets, const MoeExpertInfo* experts, uint32_t tokens,
+                                       uint32_t scale_rows, int parts, uint8_t* packed, uint8_t* scales,
+                                       cudaStream_t stream);
 cudaError_t launch_moe_activate_quantize(const void* gate_up, const int32_t* sorted_keys, const int32_t* offsets,
                                          const MoeExpertInfo* experts, uint32_t n, uint32_t scale_rows, uint8_t* packed,
                                          uint8_t* scales, void* activated, cudaStream_t stream);
@@ -61,10 +67,10 @@ cudaError_t launch_gather_rows(const void* input, const int32_t* index, uint32_t
 
 // Expert parallelism over peer memory: 1584-byte records (1408 B packed E2M1 + 176 scale bytes).
 constexpr uint32_t kEpRecordBytes = 1584;
-cudaError_t launch_ep_dispatch(const void* input, const int32_t* sorted_assignments, const int32_t* sorted_keys,
-                               const int32_t* offsets, const float* inverse_input_scale, const int32_t* dest_rank,
-                               const int32_t* dest_row0, void* const* peer_records, uint32_t n,
-                               uint32_t capacity_rows, uint32_t* error, cudaStream_t stream);
+cudaError_t launch_ep_dispatch(const void* input, const int32_t* keys, const int32_t* inverse, const int32_t* offsets,
+                               const float* inverse_input_scale, const int32_t* dest_rank, const int32_t* dest_row0,
+                               void* const* peer_records, uint32_t tokens, uint32_t capacity_rows, uint32_t* error,
+                               cudaStream_t stream);
 cudaError_t launch_ep_tables(const int32_t* counts, const int32_t* physical, uint32_t rank, uint32_t world,
                              int32_t* dest_row0, int32_t* local_offsets, int32_t* segment_start, int32_t* home_base,
                              cudaStream_t stream);

@@ -373,12 +373,21 @@ class PeerMemoryExpertParallelMoe:
     def run(self, x, scores, expert_scales, rows: int, out=None):
         """One step; nothing is read back to the host, so the step can be
         enqueued ahead of the GPU (or captured)."""
+        self.send(x, scores, expert_scales, rows)
+        self.compute()
+        return self.receive(rows, out)
+
+    def send(self, x, scores, expert_scales, rows: int):
+        """Routing, histogram exchange, destination tables, dispatch into the owners' memory."""
         lib, check = self.gw.lib, self.gw.ops._check
         stream = torch.cuda.current_stream().cuda_stream
-        self.route_ws.dispatch(scores, expert_scales, rows)
-        offsets, _, _, _ = self.route_ws.routing_state(rows)
+        if rows > 0:
+            self.route_ws.dispatch(scores, expert_scales, rows)
+            offsets, _, _, _ = self.route_ws.routing_state(rows)
+            counts = (offsets[1:] - offsets[:-1]).contiguous()
+        else:                                  # a rank without tokens still serves its experts
+            counts = torch.zeros(EXPERTS, dtype=torch.int32, device=self.device)
         self._mark("route")
-        counts = (offsets[1:] - offsets[:-1]).contiguous()
         dist.all_gather_into_tensor(self.counts_all, counts, group=self.group)
         home = self.send_home
         check(lib.gw_moe_ep_tables(self.counts_all.data_ptr(), self.physical.data_ptr(), self.rank, self.world,
@@ -386,12 +395,20 @@ class PeerMemoryExpertParallelMoe:
                                    self.segment_start.data_ptr() if home else None,
                                    self.home_base.data_ptr() if home else None, stream))
         self._mark("counts")
-        check(lib.gw_moe_ep_dispatch(self.route_ws._ws, x.data_ptr(), rows, self.inverse_scales.data_ptr(),
-                                     self.dest_rank.data_ptr(), self.dest_row0.data_ptr(),
-                                     self.records.pointer_table.data_ptr(), self.capacity, stream))
+        if rows > 0:
+            check(lib.gw_moe_ep_dispatch(self.route_ws._ws, x.data_ptr(), rows, self.inverse_scales.data_ptr(),
+                                         self.dest_rank.data_ptr(), self.dest_row0.data_ptr(),
+                                         self.records.pointer_table.data_ptr(), self.capacity, stream))
         self._mark("dispatch")
         self._barrier()
         self._mark("barrier_1")
+
+    def compute(self, barrier: bool = True):
+        """Grouped expert GEMMs over the records this rank received (and the barrier that
+        tells every rank the results are ready)."""
+        lib, check = self.gw.lib, self.gw.ops._check
+        stream = torch.cuda.current_stream().cuda_stream
+        home = self.send_home
         check(lib.gw_moe_ep_run_experts(self.expert_ws._ws, self.records.local, self.local_offsets.data_ptr(),
                                         self.rank * self.per_rank, self.per_rank, self.capacity, self.table.handle,
                                         None if home else self.down.local,
@@ -399,11 +416,22 @@ class PeerMemoryExpertParallelMoe:
                                         self.home_base.data_ptr() if home else None,
                                         self.returned.pointer_table.data_ptr() if home else None, self.world, stream))
         self._mark("experts")
+        if barrier:
+            self.results_barrier()
+
+    def results_barrier(self):
         self._barrier()
         self._mark("barrier_2")
+
+    def receive(self, rows: int, out=None):
+        """Ordered fold of each token's eight result rows (pulled from their owners, or local when sent home)."""
+        lib, check = self.gw.lib, self.gw.ops._check
+        stream = torch.cuda.current_stream().cuda_stream
         if out is None:
             out = torch.empty((rows, HIDDEN), dtype=torch.bfloat16, device=self.device)
-        if home:
+        if rows == 0:
+            pass
+        elif self.send_home:
             _, _, inverse, weights = self.route_ws.routing_state(rows)
             check(lib.gw_moe_combine(self.returned.local, inverse.data_ptr(), weights.data_ptr(), rows, HIDDEN,
                                      out.data_ptr(), stream))

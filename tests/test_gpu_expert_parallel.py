@@ -233,7 +233,7 @@ def _worker(rank: int, world: int, port: int, placement_name: str, exchange: str
         torch.cuda.synchronize()
         assert gw.kernel_error() == 0
         np.save(os.path.join(out_dir, f"y{rank}.npy"), bits(y))
-        if exchange in ("peer", "peer_pull"):
+        if exchange != "nccl":
             moe.close()
     finally:
         dist.destroy_process_group()
