@@ -20,8 +20,13 @@
 
 #include <cstddef>
 #include <cstdint>
+#include <map>
+#include <memory>
+#include <set>
 #include <stdexcept>
 #include <string>
+#include <tuple>
+#include <type_traits>
 #include <vector>
 
 #include "gewell_b200.h"
@@ -102,6 +107,82 @@ class Plan {
   gw_nvfp4_plan* plan_{};
 };
 
+// Join rule of the reference loader (31b/sm120/nvfp4_projections.h:21-33, there
+// fixed to the gate/up pair): two projections with the same input can run as
+// one GEMM when the second one's packed rows and scale tiles follow the first
+// one's in memory (first_rows a multiple of 128) and their global scales are
+// equal.  Returns `first` (now covering both) or an empty Weight.
+inline Weight joined(Weight first, Weight second, std::size_t first_rows, std::size_t input_width) {
+  const auto address = [](const void* p) { return reinterpret_cast<std::uintptr_t>(p); };
+  if (!first.data || !second.data || !first.scales || !second.scales || first_rows % 128 != 0 ||
+      first.input_scale != second.input_scale || first.weight_scale != second.weight_scale ||
+      address(second.data) != address(first.data) + first_rows * input_width / 2 ||
+      address(second.scales) != address(first.scales) + scale_storage_bytes(first_rows, input_width))
+    return {};
+  return first;
+}
+
+}  // namespace nvfp4
+
+namespace detail {
+// Plans per (rows, K, N, flag) sharing one scratch buffer, as the reference's
+// ProjectionPlans classes do (31b/sm120/nvfp4_projections.h:35-120,
+// fp8_projections.h:53-113): prepare() creates the plans of every registered
+// shape for a row count and grows the scratch (allocates: call it outside
+// capture); run() only enqueues work.
+template <typename PlanT, typename WeightT, typename TransformT>
+class PlanCache {
+ public:
+  PlanCache() = default;
+  ~PlanCache() { if (scratch_) cudaFree(scratch_); }
+  PlanCache(const PlanCache&) = delete;
+  PlanCache& operator=(const PlanCache&) = delete;
+
+  void add_shape(std::uint32_t input_width, std::uint32_t output_width, bool flag = false) {
+    shapes_.emplace(input_width, output_width, flag);
+  }
+  void prepare(std::uint32_t rows) {
+    for (const auto& [input_width, output_width, flag] : shapes_) {
+      const auto key = std::make_tuple(rows, input_width, output_width, flag);
+      if (plans_.count(key)) continue;
+      auto plan = make(rows, input_width, output_width, flag);
+      const std::size_t needed = plan->scratch_bytes();
+      if (needed > scratch_bytes_) {
+        void* replacement = nullptr;
+        const cudaError_t status = cudaMalloc(&replacement, needed);
+        if (status != cudaSuccess)
+          throw std::runtime_error(std::string("projection workspace: ") + cudaGetErrorString(status));
+        if (scratch_) cudaFree(scratch_);
+        scratch_ = replacement;
+        scratch_bytes_ = needed;
+      }
+      plans_.emplace(key, std::move(plan));
+    }
+  }
+  std::size_t scratch_bytes() const { return scratch_bytes_; }
+  void run(std::uint32_t rows, std::uint32_t input_width, std::uint32_t output_width, const __nv_bfloat16* input,
+           WeightT weight, __nv_bfloat16* output, cudaStream_t stream, TransformT transform = TransformT::identity,
+           bool flag = false) {
+    plans_.at(std::make_tuple(rows, input_width, output_width, flag))
+        ->run(input, weight, output, scratch_, scratch_bytes_, stream, transform);
+  }
+
+ private:
+  static std::unique_ptr<PlanT> make(std::uint32_t rows, std::uint32_t k, std::uint32_t n, bool flag) {
+    if constexpr (std::is_constructible_v<PlanT, std::uint32_t, std::uint32_t, std::uint32_t, bool>)
+      return std::make_unique<PlanT>(rows, k, n, flag);
+    else
+      return std::make_unique<PlanT>(rows, k, n);
+  }
+  std::set<std::tuple<std::uint32_t, std::uint32_t, bool>> shapes_;
+  std::map<std::tuple<std::uint32_t, std::uint32_t, std::uint32_t, bool>, std::unique_ptr<PlanT>> plans_;
+  void* scratch_{};
+  std::size_t scratch_bytes_{};
+};
+}  // namespace detail
+
+namespace nvfp4 {
+using ProjectionPlans = detail::PlanCache<Plan, Weight, InputTransform>;
 }  // namespace nvfp4
 
 namespace fp8 {
@@ -148,6 +229,21 @@ class Plan {
  private:
   gw_fp8_plan* plan_{};
 };
+
+// Join rules of the reference loader (31b/sm120/fp8_projections.h:20-50): the
+// second matrix starts `elements` bytes after the first and quantises its
+// input with the same scale; a joined projection needs per-channel scales
+// (they carry each part's own weight scale).
+inline bool adjacent(Weight first, Weight second, std::size_t elements) {
+  return first.data && second.data && first.input_scale == second.input_scale &&
+         reinterpret_cast<std::uintptr_t>(second.data) == reinterpret_cast<std::uintptr_t>(first.data) + elements;
+}
+inline Weight joined(Weight first, Weight second, std::size_t first_rows, std::size_t input_width) {
+  return first.channel_scales && adjacent(first, second, first_rows * input_width) ? first : Weight{};
+}
+
+// flag = the plan uses per-channel scales (joined projections)
+using ProjectionPlans = detail::PlanCache<Plan, Weight, InputTransform>;
 
 }  // namespace fp8
 

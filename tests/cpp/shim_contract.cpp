@@ -30,6 +30,25 @@ int main() {
     nvfp4::Plan moved(std::move(plan));
     expect(moved.scratch_bytes() == 512 + 2048, "moved plan keeps its state");
   }
+  {
+    // join rules: contiguous data and scale tiles with equal global scales join, anything else does not
+    alignas(16) static std::uint8_t data[2 * 128 * 128], scales[2 * 1024];
+    const nvfp4::Weight gate{data, scales, 0.5F, 0.25F}, up{data + 128 * 256 / 2, scales + nvfp4::scale_storage_bytes(128, 256), 0.5F, 0.25F};
+    expect(nvfp4::joined(gate, up, 128, 256).data == data, "nvfp4 gate/up join");
+    nvfp4::Weight other = up; other.weight_scale = 0.5F;
+    expect(nvfp4::joined(gate, other, 128, 256).data == nullptr, "nvfp4 join needs equal scales");
+    other = up; other.data += 16;
+    expect(nvfp4::joined(gate, other, 128, 256).data == nullptr, "nvfp4 join needs contiguous rows");
+    static float channel[4];
+    const fp8::Weight q{data, 0.5F, 1.0F, channel}, k{data + 64 * 128, 0.5F, 2.0F, channel};
+    expect(fp8::joined(q, k, 64, 128).data == data, "fp8 join");
+    expect(fp8::joined(fp8::Weight{data, 0.5F, 1.0F, nullptr}, k, 64, 128).data == nullptr, "fp8 join needs channel scales");
+    expect(!fp8::adjacent(q, fp8::Weight{data + 64 * 128, 0.25F, 2.0F, channel}, 64 * 128), "fp8 adjacency needs one input scale");
+    nvfp4::ProjectionPlans plans;
+    plans.add_shape(256, 256);
+    expect(plans.scratch_bytes() == 0, "no scratch before prepare");
+    expect(rejects([&] { plans.add_shape(250, 256); plans.prepare(4); }), "plan cache forwards validation");
+  }
   expect(nvfp4::scale_offset(130, 5, 256) == gw_nvfp4_scale_offset(130, 5, 256), "scale_offset");
   expect(nvfp4::scale_storage_bytes(768, 2816) == gw_nvfp4_scale_storage_bytes(768, 2816), "scale_storage_bytes");
   expect(fp8::scratch_upper_bound_bytes(33, 256) == gw_fp8_scratch_upper_bound_bytes(33, 256), "fp8 bound");
