@@ -250,6 +250,9 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
   const long long prof_start = p.profile ? clock64() : 0;
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
+    // One thread runs the whole role (no per-stage warp votes or shuffles); the other lanes
+    // wait at the end of the branch.
+    if (lane == 0) {
     int stage = 0;
     uint32_t phase = 0;
     bool waited = !early_weights;        // this warp defers its wait for the previous kernel (see below)
@@ -340,31 +343,31 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
         const int ahead = min(C::kStages, ks1 - ks0);
         if (lane == 0)
           for (int i = 0; i < ahead; ++i) issue(ks0 + i, i, true, false);
-        __syncwarp();
         griddep_wait();
         waited = true;
         if (lane == 0)
           for (int i = 0; i < ahead; ++i) issue(ks0 + i, i, false, true);
-        __syncwarp();
         stage = ahead == C::kStages ? 0 : ahead;
         phase = ahead == C::kStages ? 1 : 0;
         ks_begin = ks0 + ahead;
       }
       for (int ks = ks_begin; ks < ks1; ++ks) {
         const long long t0 = p.profile ? clock64() : 0;
-        if (!ptx::mbar_wait_warp(empty_bar + stage, phase ^ 1)) {
+        if (!ptx::mbar_wait_bounded(empty_bar + stage, phase ^ 1)) {
           report(p.error, 0x10000000u | (blockIdx.x << 8) | stage, abort_flag);
           break;
         }
         if (p.profile) prof_wait += clock64() - t0;
         if (lane == 0) issue(ks, stage, true, true);
-        __syncwarp();
         if (++stage == C::kStages) { stage = 0; phase ^= 1; }
       }
     }
     if (!waited) griddep_wait();
+    }
+    __syncwarp();
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
+    // ------------------------------------------------------------------ MMA issuer (one thread, as above)
+    if (lane == 0) {
     int stage = 0, acc = 0;
     uint32_t phase = 0, acc_phase = 0;
     WorkItem item, next;
@@ -379,7 +382,7 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
       if (more) decode_work<BLOCK_N, EPI>(p, prefix, next_tile, next);
       (void)tile; (void)at_start;
       const long long ta = p.profile ? clock64() : 0;
-      if (!ptx::mbar_wait_warp(acc_empty_bar + acc, acc_phase ^ 1)) {
+      if (!ptx::mbar_wait_bounded(acc_empty_bar + acc, acc_phase ^ 1)) {
         report(p.error, 0x20000000u | (blockIdx.x << 8) | acc, abort_flag);
         break;
       }
@@ -393,7 +396,7 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
       bool failed = false;
       for (int ks = ks0; ks < ks1; ++ks) {
         const long long t0 = p.profile ? clock64() : 0;
-        if (!ptx::mbar_wait_warp(full_bar + stage, phase)) {
+        if (!ptx::mbar_wait_bounded(full_bar + stage, phase)) {
           report(p.error, 0x30000000u | (blockIdx.x << 8) | stage, abort_flag);
           failed = true;
           break;
@@ -403,7 +406,7 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
         ptx::tc_fence_after_sync();
         if constexpr (kNvfp4) {
           // this stage's scales are in its TMEM slot once the four loader warps have arrived
-          if (!ptx::mbar_wait_warp(sf_ready_bar + stage, phase)) {
+          if (!ptx::mbar_wait_bounded(sf_ready_bar + stage, phase)) {
             report(p.error, 0x50000000u | (blockIdx.x << 8) | stage, abort_flag);
             failed = true;
             break;
@@ -432,15 +435,15 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
           }
           ptx::tc_commit(empty_bar + stage);
         }
-        __syncwarp();
         if (p.profile) prof_work += clock64() - t1;
         if (++stage == C::kStages) { stage = 0; phase ^= 1; }
       }
       if (failed) break;
       if (lane == 0) ptx::tc_commit(acc_full_bar + acc);
-      __syncwarp();
       if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1; }
     }
+    }
+    __syncwarp();
   } else if (warp < kFirstEpilogueWarp) {
     // ------------------------------------------------------------------ scale loaders
     // TMEM layout the MMA expects for a K-block: lane (row % 32) of every lane quadrant,
