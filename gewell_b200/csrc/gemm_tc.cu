@@ -470,7 +470,9 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
         const uint32_t sfc_sub = BLOCK_N < 128 ? uint32_t((item.c_tile * p.c_rows_per_tile) % 128) / 32 : 0;
         bool failed = false;
         for (int ks = ks0; ks < ks1; ++ks) {
-          if (!ptx::mbar_wait_warp(full_bar + stage, phase)) {
+          // every lane polls the barrier itself: no vote or shuffle between the data's arrival
+          // and the first shared-memory load (this latency is in front of every MMA)
+          if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(full_bar + stage, phase))) {
             report(p.error, 0x60000000u | (blockIdx.x << 8) | stage, abort_flag);
             failed = true;
             break;

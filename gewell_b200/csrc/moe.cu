@@ -226,8 +226,9 @@ gw_status run_experts(gw_moe_workspace* w, const void* input, const int32_t* gat
   if (records != nullptr) {
     GW_CUDA_CHECK(launch_ep_retile_scales(records, w->sorted_keys, offsets, n, w->scales_in.as<uint8_t>(), s),
                   "MoE scale re-tiling of received rows");
-  } else if (gather_index == w->sorted_assignments && gather_divisor == 8 && n % 8 == 0) {
-    // whole-layer path: rows are the routed copies of n / 8 tokens
+  } else if (gather_index == w->sorted_assignments && gather_divisor == 8 && n % 8 == 0 && n >= 8 * 512) {
+    // whole-layer path with enough tokens to fill the GPU with one warp per token: rows are the
+    // routed copies of n / 8 tokens
     GW_CUDA_CHECK(launch_moe_quantize_tokens(input, w->keys, w->inverse, offsets, info, n / 8, w->scale_rows, parts,
                                              w->packed_in.as<uint8_t>(), w->scales_in.as<uint8_t>(), s),
                   "MoE quantise (token-major)");
