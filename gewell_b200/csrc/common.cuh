@@ -62,6 +62,27 @@ __host__ __device__ __forceinline__ size_t scale_offset(size_t row, size_t block
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+#endif  // __CUDACC__
+
+// Launch with the programmatic-serialisation attribute: the kernel may be scheduled while
+// its predecessor in the stream drains; it must call griddep_wait() before it touches global
+// memory (every kernel launched through this helper does so first thing).
+template <typename... Params, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(Params...), dim3 grid, dim3 block, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t config{};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = 0;
+  config.stream = stream;
+  cudaLaunchAttribute attribute{};
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
+#ifdef __CUDACC__
 __device__ __forceinline__ float rcp_approx_ftz(float value) {
   float result;
   asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(result) : "f"(value));

@@ -40,6 +40,8 @@ __global__ void __launch_bounds__(256)
 moe_route_kernel(const bf16* __restrict__ scores, const bf16* __restrict__ expert_scales, uint32_t rows,
                  int32_t* __restrict__ keys, float* __restrict__ weights, uint32_t* __restrict__ bitmaps,
                  int32_t* __restrict__ chunk_counts) {
+  griddep_launch();
+  griddep_wait();     // results of earlier kernels in the stream are read from here on
   __shared__ uint32_t bitmap[kExperts][2];
   const unsigned lane = threadIdx.x % 32, warp = threadIdx.x / 32;
   if (threadIdx.x < kExperts) { bitmap[threadIdx.x][0] = 0; bitmap[threadIdx.x][1] = 0; }
@@ -118,6 +120,8 @@ moe_route_kernel(const bf16* __restrict__ scores, const bf16* __restrict__ exper
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(kExperts)
 moe_scan_kernel(int32_t* __restrict__ chunk_counts, uint32_t chunks, int32_t* __restrict__ offsets) {
+  griddep_launch();
+  griddep_wait();     // results of earlier kernels in the stream are read from here on
   __shared__ int32_t totals[kExperts];
   const unsigned e = threadIdx.x;
   int32_t running = 0;
@@ -145,6 +149,8 @@ moe_scatter_kernel(const int32_t* __restrict__ keys, const uint32_t* __restrict_
                    const int32_t* __restrict__ chunk_base, const int32_t* __restrict__ offsets, uint32_t rows,
                    int32_t* __restrict__ sorted_assignments, int32_t* __restrict__ sorted_keys,
                    int32_t* __restrict__ inverse) {
+  griddep_launch();
+  griddep_wait();     // results of earlier kernels in the stream are read from here on
   __shared__ uint32_t bitmap[kExperts][2];
   __shared__ int32_t base[kExperts];
   const uint32_t chunk = blockIdx.x;
@@ -174,6 +180,8 @@ moe_scatter_kernel(const int32_t* __restrict__ keys, const uint32_t* __restrict_
 __global__ void __launch_bounds__(256)
 moe_keys_from_offsets_kernel(const int32_t* __restrict__ offsets, uint32_t first_expert, uint32_t expert_count,
                              uint32_t rows, int32_t* __restrict__ sorted_keys, int32_t* __restrict__ full_offsets) {
+  griddep_launch();
+  griddep_wait();     // results of earlier kernels in the stream are read from here on
   const uint32_t i = blockIdx.x * 256 + threadIdx.x;
   if (blockIdx.x == 0 && threadIdx.x <= kExperts) {
     // offsets over all 128 experts: empty outside [first, first+count)
@@ -205,6 +213,8 @@ moe_keys_from_offsets_kernel(const int32_t* __restrict__ offsets, uint32_t first
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 moe_prepare_groups_kernel(MoeGroupPlan plan, GemmGroup* __restrict__ first_groups, GemmGroup* __restrict__ down_groups) {
+  griddep_launch();
+  griddep_wait();     // results of earlier kernels in the stream are read from here on
   __shared__ int32_t items_first[2 * kExperts], items_down[kExperts];
   const unsigned g = threadIdx.x;            // 0..255: expert = g/2, part = g%2
   const unsigned e = g / 2, part = g % 2;
@@ -351,6 +361,8 @@ moe_quantize_kernel(const uint4* __restrict__ input, const int32_t* __restrict__
                     const MoeExpertInfo* __restrict__ experts, uint32_t n, uint32_t scale_rows, int projection,
                     uint32_t gather_divisor, uint2* __restrict__ packed, uint8_t* __restrict__ scales,
                     uint4* __restrict__ activated) {
+  griddep_launch();
+  griddep_wait();     // results of earlier kernels in the stream are read from here on
   constexpr uint32_t kBlocks = K / 16;
   const size_t index = size_t(blockIdx.x) * 256 + threadIdx.x;
   const uint32_t part = blockIdx.y;             // gate/up copy (0 unless the scales differ)
@@ -413,6 +425,8 @@ moe_quantize_tokens_kernel(const uint4* __restrict__ input, const int32_t* __res
                            const int32_t* __restrict__ inverse, const int32_t* __restrict__ offsets,
                            const MoeExpertInfo* __restrict__ experts, uint32_t tokens, uint32_t scale_rows, int parts,
                            uint2* __restrict__ packed, uint8_t* __restrict__ scales) {
+  griddep_launch();
+  griddep_wait();     // results of earlier kernels in the stream are read from here on
   constexpr uint32_t kBlocks = kHidden / 16;            // 176
   constexpr int kPerLane = (kBlocks + 31) / 32;         // 6
   const uint32_t token = (blockIdx.x * 256 + threadIdx.x) / 32, lane = threadIdx.x % 32;
@@ -471,6 +485,8 @@ moe_quantize_tokens_kernel(const uint4* __restrict__ input, const int32_t* __res
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const uint4* __restrict__ down, const int32_t* __restrict__ inverse,
                    const float* __restrict__ weights, uint32_t rows, uint32_t width, uint4* __restrict__ output) {
+  griddep_launch();
+  griddep_wait();     // results of earlier kernels in the stream are read from here on
   const uint32_t vectors = width / 8;
   const size_t index = size_t(blockIdx.x) * 256 + threadIdx.x;
   if (index >= size_t(rows) * vectors) return;
@@ -506,6 +522,8 @@ moe_combine_kernel(const uint4* __restrict__ down, const int32_t* __restrict__ i
 __global__ void __launch_bounds__(256)
 gather_rows_kernel(const uint4* __restrict__ input, const int32_t* __restrict__ index, uint32_t divisor,
                    uint32_t rows, uint32_t vectors, uint4* __restrict__ output) {
+  griddep_launch();
+  griddep_wait();     // results of earlier kernels in the stream are read from here on
   const size_t i = size_t(blockIdx.x) * 256 + threadIdx.x;
   if (i >= size_t(rows) * vectors) return;
   const uint32_t row = i / vectors, v = i % vectors;
@@ -531,6 +549,8 @@ ep_dispatch_kernel(const uint4* __restrict__ input, const int32_t* __restrict__ 
                    const float* __restrict__ inverse_input_scale, const int32_t* __restrict__ dest_rank,
                    const int32_t* __restrict__ dest_row0, uint8_t* const* __restrict__ peer_records, uint32_t tokens,
                    uint32_t capacity_rows, uint32_t* __restrict__ error) {
+  griddep_launch();
+  griddep_wait();     // results of earlier kernels in the stream are read from here on
   // token-major like kernel 5b: one warp reads a token once and writes its eight records
   constexpr uint32_t kBlocks = kHidden / 16;
   constexpr int kPerLane = (kBlocks + 31) / 32;
@@ -589,6 +609,8 @@ __global__ void __launch_bounds__(kExperts)
 ep_tables_kernel(const int32_t* __restrict__ counts, const int32_t* __restrict__ physical, uint32_t rank,
                  uint32_t world, int32_t* __restrict__ dest_row0, int32_t* __restrict__ local_offsets,
                  int32_t* __restrict__ segment_start, int32_t* __restrict__ home_base) {
+  griddep_launch();
+  griddep_wait();     // results of earlier kernels in the stream are read from here on
   __shared__ int32_t total_at[kExperts];       // rows of the expert at a physical position, over all sources
   __shared__ int32_t sorted_base[8][kExperts]; // a source rank's own offsets: rows of experts with a lower id
   const uint32_t e = threadIdx.x, per_rank = kExperts / world;
@@ -632,6 +654,8 @@ ep_row_home_kernel(const int32_t* __restrict__ sorted_keys, const int32_t* __res
                    const int32_t* __restrict__ segment_start, const int32_t* __restrict__ home_base,
                    uint8_t* const* __restrict__ peer_returned, uint32_t first_expert, uint32_t per_rank,
                    uint32_t world, uint32_t n, uint64_t* __restrict__ row_home) {
+  griddep_launch();
+  griddep_wait();     // results of earlier kernels in the stream are read from here on
   const uint32_t row = blockIdx.x * 256 + threadIdx.x;
   if (row >= n || row >= uint32_t(offsets[kExperts])) return;
   const uint32_t slot = uint32_t(sorted_keys[row]) - first_expert;
@@ -646,6 +670,8 @@ ep_row_home_kernel(const int32_t* __restrict__ sorted_keys, const int32_t* __res
 __global__ void __launch_bounds__(256)
 ep_retile_scales_kernel(const uint8_t* __restrict__ records, const int32_t* __restrict__ sorted_keys,
                         const int32_t* __restrict__ offsets, uint32_t n, uint8_t* __restrict__ scales) {
+  griddep_launch();
+  griddep_wait();     // results of earlier kernels in the stream are read from here on
   constexpr uint32_t kWords = kHidden / 64;        // 44 four-byte words of scales per row
   const size_t index = size_t(blockIdx.x) * 256 + threadIdx.x;
   if (index >= size_t(n) * kWords) return;
@@ -665,6 +691,8 @@ ep_combine_kernel(const int32_t* __restrict__ keys, const int32_t* __restrict__ 
                   const float* __restrict__ weights, const int32_t* __restrict__ offsets,
                   const int32_t* __restrict__ dest_rank, const int32_t* __restrict__ dest_row0,
                   const uint4* const* __restrict__ peer_down, uint32_t rows, uint4* __restrict__ output) {
+  griddep_launch();
+  griddep_wait();     // results of earlier kernels in the stream are read from here on
   constexpr uint32_t kVectors = kHidden / 8;
   const size_t index = size_t(blockIdx.x) * 128 + threadIdx.x;
   if (index >= size_t(rows) * kVectors) return;
@@ -710,10 +738,10 @@ cudaError_t launch_moe_dispatch(const void* scores, const void* expert_scales, u
                                 int32_t* sorted_assignments, int32_t* sorted_keys, int32_t* inverse,
                                 cudaStream_t stream) {
   const uint32_t chunks = moe_chunks(rows);
-  moe_route_kernel<<<chunks, 256, 0, stream>>>(static_cast<const bf16*>(scores), static_cast<const bf16*>(expert_scales),
+  launch_pdl(moe_route_kernel, chunks, 256, stream, static_cast<const bf16*>(scores), static_cast<const bf16*>(expert_scales),
                                                rows, keys, weights, bitmaps, chunk_counts);
-  moe_scan_kernel<<<1, kExperts, 0, stream>>>(chunk_counts, chunks, offsets);
-  moe_scatter_kernel<<<chunks, 256, 0, stream>>>(keys, bitmaps, chunk_counts, offsets, rows, sorted_assignments,
+  launch_pdl(moe_scan_kernel, 1, kExperts, stream, chunk_counts, chunks, offsets);
+  launch_pdl(moe_scatter_kernel, chunks, 256, stream, keys, bitmaps, chunk_counts, offsets, rows, sorted_assignments,
                                                  sorted_keys, inverse);
   return cudaGetLastError();
 }
@@ -721,14 +749,14 @@ cudaError_t launch_moe_dispatch(const void* scores, const void* expert_scales, u
 cudaError_t launch_moe_keys_from_offsets(const int32_t* offsets, uint32_t first_expert, uint32_t expert_count,
                                          uint32_t rows, int32_t* sorted_keys, int32_t* full_offsets,
                                          cudaStream_t stream) {
-  moe_keys_from_offsets_kernel<<<blocks_for(rows > 256 ? rows : 256), 256, 0, stream>>>(
+  launch_pdl(moe_keys_from_offsets_kernel, blocks_for(rows > 256 ? rows : 256), 256, stream, 
       offsets, first_expert, expert_count, rows, sorted_keys, full_offsets);
   return cudaGetLastError();
 }
 
 cudaError_t launch_moe_prepare_groups(const MoeGroupPlan& plan, GemmGroup* first_groups, GemmGroup* down_groups,
                                       cudaStream_t stream) {
-  moe_prepare_groups_kernel<<<1, 256, 0, stream>>>(plan, first_groups, down_groups);
+  launch_pdl(moe_prepare_groups_kernel, 1, 256, stream, plan, first_groups, down_groups);
   return cudaGetLastError();
 }
 
@@ -737,7 +765,7 @@ cudaError_t launch_moe_quantize_input(const void* input, const int32_t* gather_i
                                       const MoeExpertInfo* experts, uint32_t n, uint32_t scale_rows, int parts,
                                       uint8_t* packed, uint8_t* scales, cudaStream_t stream) {
   const dim3 grid(blocks_for(size_t(n) * (kHidden / 16)), parts);
-  moe_quantize_kernel<kHidden, false><<<grid, 256, 0, stream>>>(
+  launch_pdl(moe_quantize_kernel<kHidden, false>, grid, 256, stream, 
       static_cast<const uint4*>(input), gather_index, sorted_keys, offsets, experts, n, scale_rows, 0,
       gather_divisor ? gather_divisor : 1, reinterpret_cast<uint2*>(packed), scales, nullptr);
   return cudaGetLastError();
@@ -747,7 +775,7 @@ cudaError_t launch_moe_quantize_tokens(const void* input, const int32_t* keys, c
                                        const int32_t* offsets, const MoeExpertInfo* experts, uint32_t tokens,
                                        uint32_t scale_rows, int parts, uint8_t* packed, uint8_t* scales,
                                        cudaStream_t stream) {
-  moe_quantize_tokens_kernel<<<blocks_for(size_t(tokens) * 32), 256, 0, stream>>>(
+  launch_pdl(moe_quantize_tokens_kernel, blocks_for(size_t(tokens) * 32), 256, stream, 
       static_cast<const uint4*>(input), keys, inverse, offsets, experts, tokens, scale_rows, parts,
       reinterpret_cast<uint2*>(packed), scales);
   return cudaGetLastError();
@@ -757,7 +785,7 @@ cudaError_t launch_moe_activate_quantize(const void* gate_up, const int32_t* sor
                                          const MoeExpertInfo* experts, uint32_t n, uint32_t scale_rows, uint8_t* packed,
                                          uint8_t* scales, void* activated, cudaStream_t stream) {
   const dim3 grid(blocks_for(size_t(n) * (kInter / 16)), 1);
-  moe_quantize_kernel<kInter, true><<<grid, 256, 0, stream>>>(
+  launch_pdl(moe_quantize_kernel<kInter, true>, grid, 256, stream, 
       static_cast<const uint4*>(gate_up), nullptr, sorted_keys, offsets, experts, n, scale_rows, 2, 1,
       reinterpret_cast<uint2*>(packed), scales, static_cast<uint4*>(activated));
   return cudaGetLastError();
@@ -765,14 +793,14 @@ cudaError_t launch_moe_activate_quantize(const void* gate_up, const int32_t* sor
 
 cudaError_t launch_moe_combine(const void* down, const int32_t* inverse, const float* weights, uint32_t rows,
                                uint32_t width, void* output, cudaStream_t stream) {
-  moe_combine_kernel<<<blocks_for(size_t(rows) * (width / 8)), 256, 0, stream>>>(
+  launch_pdl(moe_combine_kernel, blocks_for(size_t(rows) * (width / 8)), 256, stream, 
       static_cast<const uint4*>(down), inverse, weights, rows, width, static_cast<uint4*>(output));
   return cudaGetLastError();
 }
 
 cudaError_t launch_gather_rows(const void* input, const int32_t* index, uint32_t divisor, uint32_t rows,
                                uint32_t width, void* output, cudaStream_t stream) {
-  gather_rows_kernel<<<blocks_for(size_t(rows) * (width / 8)), 256, 0, stream>>>(
+  launch_pdl(gather_rows_kernel, blocks_for(size_t(rows) * (width / 8)), 256, stream, 
       static_cast<const uint4*>(input), index, divisor, rows, width / 8, static_cast<uint4*>(output));
   return cudaGetLastError();
 }
@@ -781,7 +809,7 @@ cudaError_t launch_ep_dispatch(const void* input, const int32_t* keys, const int
                                const float* inverse_input_scale, const int32_t* dest_rank, const int32_t* dest_row0,
                                void* const* peer_records, uint32_t tokens, uint32_t capacity_rows, uint32_t* error,
                                cudaStream_t stream) {
-  ep_dispatch_kernel<<<blocks_for(size_t(tokens) * 32), 256, 0, stream>>>(
+  launch_pdl(ep_dispatch_kernel, blocks_for(size_t(tokens) * 32), 256, stream, 
       static_cast<const uint4*>(input), keys, inverse, offsets, inverse_input_scale, dest_rank, dest_row0,
       reinterpret_cast<uint8_t* const*>(peer_records), tokens, capacity_rows, error);
   return cudaGetLastError();
@@ -790,7 +818,7 @@ cudaError_t launch_ep_dispatch(const void* input, const int32_t* keys, const int
 cudaError_t launch_ep_tables(const int32_t* counts, const int32_t* physical, uint32_t rank, uint32_t world,
                              int32_t* dest_row0, int32_t* local_offsets, int32_t* segment_start, int32_t* home_base,
                              cudaStream_t stream) {
-  ep_tables_kernel<<<1, kExperts, 0, stream>>>(counts, physical, rank, world, dest_row0, local_offsets, segment_start,
+  launch_pdl(ep_tables_kernel, 1, kExperts, stream, counts, physical, rank, world, dest_row0, local_offsets, segment_start,
                                                home_base);
   return cudaGetLastError();
 }
@@ -798,7 +826,7 @@ cudaError_t launch_ep_tables(const int32_t* counts, const int32_t* physical, uin
 cudaError_t launch_ep_row_home(const int32_t* sorted_keys, const int32_t* offsets, const int32_t* segment_start,
                                const int32_t* home_base, void* const* peer_returned, uint32_t first_expert,
                                uint32_t per_rank, uint32_t world, uint32_t n, uint64_t* row_home, cudaStream_t stream) {
-  ep_row_home_kernel<<<blocks_for(n), 256, 0, stream>>>(sorted_keys, offsets, segment_start, home_base,
+  launch_pdl(ep_row_home_kernel, blocks_for(n), 256, stream, sorted_keys, offsets, segment_start, home_base,
                                                         reinterpret_cast<uint8_t* const*>(peer_returned), first_expert,
                                                         per_rank, world, n, row_home);
   return cudaGetLastError();
@@ -806,7 +834,7 @@ cudaError_t launch_ep_row_home(const int32_t* sorted_keys, const int32_t* offset
 
 cudaError_t launch_ep_retile_scales(const void* records, const int32_t* sorted_keys, const int32_t* offsets,
                                     uint32_t n, uint8_t* scales, cudaStream_t stream) {
-  ep_retile_scales_kernel<<<blocks_for(size_t(n) * (kHidden / 64)), 256, 0, stream>>>(
+  launch_pdl(ep_retile_scales_kernel, blocks_for(size_t(n) * (kHidden / 64)), 256, stream, 
       static_cast<const uint8_t*>(records), sorted_keys, offsets, n, scales);
   return cudaGetLastError();
 }
@@ -814,7 +842,7 @@ cudaError_t launch_ep_retile_scales(const void* records, const int32_t* sorted_k
 cudaError_t launch_ep_combine(const int32_t* keys, const int32_t* inverse, const float* weights,
                               const int32_t* offsets, const int32_t* dest_rank, const int32_t* dest_row0,
                               void* const* peer_down, uint32_t rows, void* output, cudaStream_t stream) {
-  ep_combine_kernel<<<unsigned((size_t(rows) * (kHidden / 8) + 127) / 128), 128, 0, stream>>>(
+  launch_pdl(ep_combine_kernel, unsigned((size_t(rows) * (kHidden / 8) + 127) / 128), 128, stream, 
       keys, inverse, weights, offsets, dest_rank, dest_row0, reinterpret_cast<const uint4* const*>(peer_down), rows,
       static_cast<uint4*>(output));
   return cudaGetLastError();
