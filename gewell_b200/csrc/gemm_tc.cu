@@ -655,9 +655,11 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
         uint4 unit[kEarlyRelease ? kChunks : 1][4];                  // unit q of a chunk = channels c0 + 8q .. + 7
         auto drain = [&](int c0, uint4* out_units) {
           uint32_t r[32];
+          const long long td0 = p.profile ? clock64() : 0;
           ptx::tmem_load16(taddr + c0, r);
           ptx::tmem_load16(taddr + c0 + 16, r + 16);
           ptx::tmem_load_wait();
+          if (p.profile) prof_wait2 += clock64() - td0;
           float v[32];
           if (item.g.channel_alpha != nullptr) {
 #pragma unroll
@@ -828,7 +830,7 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
     const long long total = clock64() - prof_start;
     if (warp == 0) { row[0] = prof_wait; }
     if (warp == 1) { row[1] = prof_wait; row[2] = prof_work; row[3] = prof_wait2; row[6] = total; }
-    if (warp == kFirstEpilogueWarp) { row[4] = prof_wait; row[5] = prof_work; }
+    if (warp == kFirstEpilogueWarp) { row[4] = prof_wait; row[5] = prof_work; row[7] = prof_wait2; }
   }
 
   ptx::tc_fence_before_sync();

@@ -87,7 +87,7 @@ cudaError_t launch_gemm_tc(GemmKind kind, GemmEpilogue epilogue, int block_n, co
 
 // Debug aid: subsequent launches write per-CTA cycle counters ([2][148][8] int64:
 // producer wait, MMA wait for data, MMA issue, MMA wait for accumulator, epilogue
-// wait, epilogue work, total, unused) into this device buffer; nullptr turns it off.
+// wait, epilogue work, total, epilogue TMEM-load time) into this device buffer; nullptr turns it off.
 void set_gemm_profile_buffer(long long* device_buffer);
 
 // Host helper: 2-D byte tensor map {inner = row_bytes, outer = rows} with a

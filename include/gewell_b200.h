@@ -339,7 +339,8 @@ uint32_t gw_debug_kernel_error(void);
 /* Tuning aid: when `device_buffer` (2 x 148 x 8 int64 on the device; consecutive launches alternate between the halves) is not NULL,
  * every later tensor-core GEMM launch writes per-CTA cycle counters into it
  * (producer wait, MMA wait for data, MMA issue, MMA wait for the accumulator,
- * epilogue wait, epilogue work, total); NULL switches it off again. */
+ * epilogue wait, epilogue work, total, time the direct-store epilogue spends in
+ * tensor-memory loads); NULL switches it off again. */
 gw_status gw_debug_gemm_profile(void* device_buffer);
 
 /* Test aid: output[i] = rcp.approx.ftz.f32(input[i]) evaluated on the device.
