@@ -339,9 +339,10 @@ def main():
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--tokens", type=int, default=0, help="override the token count (testing)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
-    parser.add_argument("--exchange", default="peer", choices=["peer", "peer_pull", "nccl"],
-                        help="expert-parallel run: rows cross NVLink inside the dispatch/combine kernels (peer "
-                             "memory) or through NCCL all-to-all")
+    parser.add_argument("--exchange", default="peer_pull", choices=["peer", "peer_pull", "nccl"],
+                        help="expert-parallel run: rows cross NVLink inside the dispatch/combine kernels over peer "
+                             "memory (peer_pull: the combine kernel pulls result rows; peer: the down GEMM's epilogue "
+                             "stores them into the source rank) or through NCCL all-to-all")
     parser.add_argument("--placement", default="balanced", choices=["contiguous", "interleaved", "balanced"],
                         help="expert placement of the expert-parallel run")
     args = parser.parse_args()

@@ -320,14 +320,15 @@ class PeerMemoryExpertParallelMoe:
 
     def __init__(self, experts_by_position, input_scales, rank: int, world: int, local_tokens: int,
                  receive_capacity_rows: int, placement: Placement | None = None, group=None,
-                 send_home: bool = True):
+                 send_home: bool = False):
         """experts_by_position: 128 entries indexed by physical position, None for
         experts of other ranks.  input_scales: the gate/up input scale of all 128
         experts by expert id (every rank quantises rows for every expert).
         send_home: the down GEMM's epilogue stores each result row into its source
-        rank's memory (the way home overlaps the GEMM) and the source folds local
-        rows; otherwise results stay with the owner and the combine kernel pulls
-        them over NVLink."""
+        rank's memory and the source folds local rows; otherwise (default, faster
+        in every measured configuration: the remote stores slow the GEMM down more
+        than the pull costs) results stay with the owner and the combine kernel
+        pulls them over NVLink."""
         import gewell_b200 as gw
         self.gw = gw
         self.placement = placement or Placement.contiguous(world)
