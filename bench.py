@@ -310,8 +310,9 @@ def run_expert_parallel(args, world: int, rank: int, local_rank: int):
                 "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                         "h2d_bytes_per_step": world * (hx.numel() + hs.numel()) * 2,
                         "d2h_bytes_per_step": world * hy.numel() * 2, "ms_per_step": e2e_ms},
-                "gpu_launches": 12 * args.steps * world,   # per rank: 3 routing, tables, dispatch, keys, row homes, group descriptors,
-                # scale re-tiling, 2 GEMMs, combine (the collectives are NCCL's) "clocks": clocks,
+                # per rank: 3 routing, tables, dispatch, keys, group descriptors, scale re-tiling, 2 GEMMs,
+                # combine (the collectives are NCCL's)
+                "gpu_launches": 11 * args.steps * world, "clocks": clocks,
                 "roofline": {"kernel": "gemm_tc_kernel<nvfp4> (grouped gate/up + grouped down) on the busiest rank",
                              "bound": "tensor", "achieved": achieved, "peak": fp4_peak, "unit": "TFLOP/s",
                              "frac": achieved / fp4_peak, "traffic": None,
@@ -443,8 +444,8 @@ def main():
     roofline = {"kernel": "gemm_tc_kernel<nvfp4> (grouped gate/up + grouped down)", "bound": "tensor",
                 "achieved": achieved, "peak": fp4_peak, "unit": "TFLOP/s", "frac": achieved / fp4_peak,
                 # dram__bytes_read.sum + dram__bytes_write.sum of the two launches at this size, from the one-pass
-                # ncu capture summarised in profiles/bench_moe_T8192_launch_list.md (gate/up 440.9 MB, down 484.7 MB)
-                "traffic": 925.6e6 if tokens == 8192 else None, "traffic_unit": "bytes per layer pass (both launches)",
+                # ncu capture summarised in profiles/bench_moe_T8192_launch_list.md (gate/up 441.3 MB, down 486.1 MB)
+                "traffic": 927.4e6 if tokens == 8192 else None, "traffic_unit": "bytes per layer pass (both launches)",
                 "algorithmic_bytes": 979.0e6 if tokens == 8192 else None,
                 "peak_note": f"4 x the {peaks['source']} dense BF16 burst figure ({peaks['bf16_tflops']} TFLOP/s); "
                              "no FP4 GEMM peak was measured on this pool (nominal dense FP4: 9000 TFLOP/s)",
@@ -459,7 +460,8 @@ def main():
     line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "nvfp4 (e2m1 x e2m1, fp32 accumulate)", "data": "synthetic",
-            "config": config, "e2e": e2e, "gpu_launches": 8 * args.steps,   # route, scan, scatter, group descriptors, gather+quantise, 2 GEMMs, combine "clocks": clocks,
+            # launches per step: route, scan, scatter, group descriptors, gather+quantise, 2 GEMMs, combine
+            "config": config, "e2e": e2e, "gpu_launches": 8 * args.steps, "clocks": clocks,
             "roofline": roofline, "cpu_baseline": cpu}
     print(json.dumps(line))
 
