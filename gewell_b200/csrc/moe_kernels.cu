@@ -36,10 +36,14 @@ __device__ __forceinline__ void unpack8(const uint4& raw, float* out) {
 //    (models/gemma4/26b_a4b/sm120/moe.cu:104-157) so ids and FP32 weights match
 //    it bit for bit.  One warp per token, eight tokens per warp.
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(256)
+//    With at most 64 tokens there is one block: it then also does the work of kernels 2
+//    and 3 (`offsets` != nullptr), which saves two dependent launches on the decode path.
+__global__ void __launch_bounds__(1024)
 moe_route_kernel(const bf16* __restrict__ scores, const bf16* __restrict__ expert_scales, uint32_t rows,
                  int32_t* __restrict__ keys, float* __restrict__ weights, uint32_t* __restrict__ bitmaps,
-                 int32_t* __restrict__ chunk_counts) {
+                 int32_t* __restrict__ chunk_counts, int32_t* __restrict__ offsets,
+                 int32_t* __restrict__ sorted_assignments, int32_t* __restrict__ sorted_keys,
+                 int32_t* __restrict__ inverse) {
   griddep_launch();
   griddep_wait();     // results of earlier kernels in the stream are read from here on
   __shared__ uint32_t bitmap[kExperts][2];
@@ -47,8 +51,9 @@ moe_route_kernel(const bf16* __restrict__ scores, const bf16* __restrict__ exper
   if (threadIdx.x < kExperts) { bitmap[threadIdx.x][0] = 0; bitmap[threadIdx.x][1] = 0; }
   __syncthreads();
   const uint32_t chunk = blockIdx.x;
-  for (int t = 0; t < kChunkTokens / 8; ++t) {
-    const uint32_t local = warp * (kChunkTokens / 8) + t;
+  const int tokens_per_warp = kChunkTokens / int(blockDim.x / 32);     // 8 warps: 8 tokens each; 32 warps: 2
+  for (int t = 0; t < tokens_per_warp; ++t) {
+    const uint32_t local = warp * tokens_per_warp + t;
     const uint32_t row = chunk * kChunkTokens + local;
     if (row >= rows) break;
     float elements[4], maximum = -INFINITY;
@@ -110,7 +115,33 @@ moe_route_kernel(const bf16* __restrict__ scores, const bf16* __restrict__ exper
     const uint32_t w0 = bitmap[threadIdx.x][0], w1 = bitmap[threadIdx.x][1];
     bitmaps[(size_t(chunk) * kExperts + threadIdx.x) * 2] = w0;
     bitmaps[(size_t(chunk) * kExperts + threadIdx.x) * 2 + 1] = w1;
-    chunk_counts[size_t(chunk) * kExperts + threadIdx.x] = __popc(w0) + __popc(w1);
+    chunk_counts[size_t(chunk) * kExperts + threadIdx.x] = offsets != nullptr ? 0 : __popc(w0) + __popc(w1);
+  }
+  if (offsets == nullptr) return;
+  // single block: offsets, positions, inverse (the scan and scatter steps of kernels 2 and 3)
+  __shared__ int32_t base[kExperts];
+  if (threadIdx.x == 0) {
+    int32_t acc = 0;
+    for (int i = 0; i < kExperts; ++i) {
+      base[i] = acc;
+      offsets[i] = acc;
+      acc += __popc(bitmap[i][0]) + __popc(bitmap[i][1]);
+    }
+    offsets[kExperts] = acc;
+  }
+  __syncthreads();                       // also orders this block's writes of `keys` before the reads below
+  for (uint32_t i = threadIdx.x; i < kChunkTokens * kTopK; i += blockDim.x) {
+    const uint32_t local = i / kTopK;
+    if (local >= rows) continue;
+    const uint32_t assignment = local * kTopK + i % kTopK;
+    const int32_t e = keys[assignment];
+    const uint32_t w0 = bitmap[e][0], w1 = bitmap[e][1];
+    const int rank = local < 32 ? __popc(w0 & ((1u << local) - 1u))
+                                : __popc(w0) + __popc(w1 & ((1u << (local - 32)) - 1u));
+    const int32_t position = base[e] + rank;
+    sorted_assignments[position] = int32_t(assignment);
+    sorted_keys[position] = e;
+    inverse[assignment] = position;
   }
 }
 
@@ -738,11 +769,19 @@ cudaError_t launch_moe_dispatch(const void* scores, const void* expert_scales, u
                                 int32_t* sorted_assignments, int32_t* sorted_keys, int32_t* inverse,
                                 cudaStream_t stream) {
   const uint32_t chunks = moe_chunks(rows);
-  launch_pdl(moe_route_kernel, chunks, 256, stream, static_cast<const bf16*>(scores), static_cast<const bf16*>(expert_scales),
-                                               rows, keys, weights, bitmaps, chunk_counts);
+  if (chunks == 1) {     // decode sizes: one block (32 warps, two tokens each) routes, scans and scatters
+    launch_pdl(moe_route_kernel, chunks, 1024, stream, static_cast<const bf16*>(scores),
+               static_cast<const bf16*>(expert_scales), rows, keys, weights, bitmaps, chunk_counts, offsets,
+               sorted_assignments, sorted_keys, inverse);
+    return cudaGetLastError();
+  }
+  launch_pdl(moe_route_kernel, chunks, 256, stream, static_cast<const bf16*>(scores),
+             static_cast<const bf16*>(expert_scales), rows, keys, weights, bitmaps, chunk_counts,
+             static_cast<int32_t*>(nullptr), static_cast<int32_t*>(nullptr), static_cast<int32_t*>(nullptr),
+             static_cast<int32_t*>(nullptr));
   launch_pdl(moe_scan_kernel, 1, kExperts, stream, chunk_counts, chunks, offsets);
   launch_pdl(moe_scatter_kernel, chunks, 256, stream, keys, bitmaps, chunk_counts, offsets, rows, sorted_assignments,
-                                                 sorted_keys, inverse);
+             sorted_keys, inverse);
   return cudaGetLastError();
 }
 

@@ -346,11 +346,16 @@ class MoeWorkspace:
         """Aliases (no copies) of the routing results of the last dispatch over
         `rows` tokens: offsets [129], sorted_assignments [8*rows], inverse
         [8*rows], weights [8*rows]."""
+        cached = getattr(self, "_routing_aliases", None)
+        if cached is not None and cached[0] == rows:
+            return cached[1]
         n = 8 * rows
-        return (self._alias(self._lib.gw_moe_offsets(self._ws), (129,), torch.int32),
+        state = (self._alias(self._lib.gw_moe_offsets(self._ws), (129,), torch.int32),
                 self._alias(self._lib.gw_moe_sorted_assignments(self._ws), (n,), torch.int32),
                 self._alias(self._lib.gw_moe_inverse(self._ws), (n,), torch.int32),
                 self._alias(self._lib.gw_moe_routing_weights(self._ws), (n,), torch.float32))
+        self._routing_aliases = (rows, state)      # the buffers never move: build the views once per row count
+        return state
 
     def _view(self, pointer: int, shape, dtype):
         """Copy of a workspace buffer as a tensor (the workspace owns the memory)."""

@@ -99,6 +99,31 @@ def test_nvfp4_shapes(gw, k, n, rows):
     assert_reference_tolerance(bits(y), exact, f"rows={rows} K={k} N={n}")
 
 
+@pytest.mark.parametrize("rows,k,n", [(640, 512, 8192), (520, 1024, 8192 + 128)])
+def test_nvfp4_prefill_tiles_that_do_not_fill_whole_waves(gw, rows, k, n):
+    """More 128x256 tiles than SMs but not a multiple of them (the last wave is ragged), wide N,
+    two launches on one plan must agree bit for bit."""
+    w = onv.pack_weights(to_f32(bf16_normal((n, k), 21, 0.05)), 0.0113)
+    x = bf16_normal((rows, k), 22)
+    dev = oracle_weight_to_device(w)
+    plan = gw.Nvfp4Plan(rows, k, n)
+    scratch = torch.empty(plan.scratch_bytes(), dtype=torch.uint8, device="cuda")
+    assert plan.scratch_bytes() <= gw.lib.gw_nvfp4_scratch_upper_bound_bytes(rows, k, n)
+    y = torch.empty((rows, n), dtype=torch.bfloat16, device="cuda")
+    results = []
+    for _ in range(2):
+        y.fill_(float("nan"))
+        plan.run(x.cuda(), dev, y, scratch)
+        torch.cuda.synchronize()
+        assert gw.kernel_error() == 0
+        results.append(bits(y).copy())
+    assert np.array_equal(results[0], results[1])
+    packed = scratch[:rows * k // 2].cpu().numpy().reshape(rows, k // 2)
+    scales = scratch[(rows * k // 2 + 255) // 256 * 256:][:onv.scale_storage_bytes(rows, k)].cpu().numpy()
+    exact = oracle_from_device_quantisation(packed, scales, rows, k, w)
+    assert_reference_tolerance(results[0], exact, f"prefill rows={rows} K={k} N={n}")
+
+
 @pytest.mark.parametrize("form", ["direct", "swap"])
 @pytest.mark.parametrize("rows", [5, 64, 128])
 def test_nvfp4_both_operand_roles(gw, form, rows, monkeypatch):
