@@ -64,7 +64,7 @@ def _copies(nbytes: int) -> int:
     return max(2, -(-2 * L2_BYTES // nbytes))
 
 
-def bench_fp8_decode(rows_list=(1, 8, 32, 64), n=43008, k=5376, iters=20):
+def bench_fp8_decode(rows_list=(1, 2, 8, 32, 64), n=43008, k=5376, iters=20):
     """Config 2: joined gate+up projection, E4M3 weights with per-channel scales."""
     dev = torch.device("cuda")
     g = torch.Generator(device=dev).manual_seed(2)

@@ -316,6 +316,20 @@ gw_status gw_fp8_plan_run(gw_fp8_plan* plan, const void* input_bf16, const uint8
                 "scales with a finite positive product and finite input-scale reciprocal");
   cudaStream_t s = as_stream(stream);
   auto* packed = static_cast<uint8_t*>(scratch);
+  // Optional CUDA-core path for 1..4 rows (weight streaming with warp reductions, activations
+  // quantised inside the kernel).  Measured on B200 it is slower than the tensor-core path
+  // (55 us against 50 us for one row of the 43008 x 5376 projection, 82 us for two), so it is
+  // off unless GW_FP8_GEMV_ROWS names a row limit.
+  const char* gemv_env = std::getenv("GW_FP8_GEMV_ROWS");
+  const int gemv_rows = gemv_env ? std::atoi(gemv_env) : 0;
+  if (transform == GW_TRANSFORM_IDENTITY && int(plan->rows) <= gemv_rows && gemv_fp8_supports(plan->rows, plan->input_width) &&
+      aligned(input_bf16, 2)) {
+    GW_CUDA_CHECK(launch_gemv_fp8(input_bf16, plan->rows, weight_data, 1.0F / input_scale, alpha,
+                                  plan->channel_scales ? channel_scales : nullptr, plan->input_width, plan->output_width,
+                                  output_bf16, sm_count(), s),
+                  "FP8 weight-streaming projection");
+    return GW_OK;
+  }
   GW_CUDA_CHECK(launch_fp8_quantize(input_bf16, plan->rows, plan->input_width, 1.0F / input_scale,
                                     transform == GW_TRANSFORM_GELU_TANH_MULTIPLY, packed, s),
                 "FP8 quantize activations");

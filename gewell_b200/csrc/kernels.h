@@ -29,4 +29,10 @@ cudaError_t launch_gemv_w4a16(const void* input, uint32_t rows, const uint8_t* d
                               float weight_scale, uint32_t width, uint32_t out_width, void* output,
                               cudaStream_t stream);
 
+// FP8 W8A8 projection for 1..4 rows on the CUDA cores (quantises the activations itself).
+bool gemv_fp8_supports(uint32_t rows, uint32_t width);
+cudaError_t launch_gemv_fp8(const void* input, uint32_t rows, const uint8_t* weights, float inverse_input_scale,
+                            float alpha, const float* channel_alpha, uint32_t width, uint32_t out_width, void* output,
+                            int sm_count, cudaStream_t stream);
+
 }  // namespace gw

@@ -254,8 +254,22 @@ def test_fp8_rounding_boundaries_exact(gw):
     assert torch.all(y == 0)
 
 
+@pytest.mark.parametrize("rows", [1, 2, 3, 4])
+@pytest.mark.parametrize("channel", [False, True])
+def test_fp8_cuda_core_weight_streaming(gw, rows, channel, monkeypatch):
+    """The optional CUDA-core decode path (GW_FP8_GEMV_ROWS) quantises the activations itself
+    and must agree with the W8A8 oracle like the tensor-core path."""
+    monkeypatch.setenv("GW_FP8_GEMV_ROWS", "4")
+    n, k = 640, 5376
+    wv = to_f32(bf16_normal((n, k), 43, 0.05))
+    x = bf16_normal((rows, k), 44)
+    w = ofp8.pack_weights_per_channel(wv, 0.02) if channel else ofp8.pack_weights(wv, 0.02)
+    y = run_fp8(gw, x.cuda(), fp8_weight_to_device(gw, w), n, k, channel=channel)
+    assert_reference_tolerance(bits(y), ofp8.linear_w8a8(to_f32(x), w), f"FP8 CUDA-core rows={rows}")
+
+
 @pytest.mark.parametrize("k,n", [(16, 16), (256, 272), (5376, 512)])
-@pytest.mark.parametrize("rows", [1, 15, 17, 33, 65, 129, 257])
+@pytest.mark.parametrize("rows", [1, 2, 3, 15, 17, 33, 65, 129, 257])
 def test_fp8_shapes(gw, k, n, rows):
     wv = to_f32(bf16_normal((n, k), 40, 0.05))
     x = bf16_normal((rows, k), 41)
