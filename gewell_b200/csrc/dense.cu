@@ -1,4 +1,5 @@
 #include "dense.h"
+#include "gemm_pair.h"
 
 #include <cstdlib>
 #include <string>
@@ -69,6 +70,31 @@ gw_status launch_dense(const DenseProblem& q, DenseDescriptors* cache, cudaStrea
     if (!encode_tensor_map_2d(&cache->activation_map, q.activations, row_bytes, q.rows, swap ? block_n : 128, &error))
       return fail(GW_CUDA_ERROR, "activation descriptor: " + error);
     cache->activations = q.activations;
+  }
+  // NVFP4 prefill: the CTA-pair kernel (each CTA stages half of the weight tile) unless disabled
+  if (fp4 && single_box && q.rows >= 256 && !std::getenv("GW_DENSE_NO_PAIR")) {
+    if (cache->weight_half != q.weight) {
+      if (!encode_tensor_map_2d(&cache->weight_half_map, q.weight, row_bytes, q.n, 128, &error))
+        return fail(GW_CUDA_ERROR, "weight descriptor: " + error);
+      cache->weight_half = q.weight;
+    }
+    PairGemmParams pair{};
+    pair.map_tokens = cache->activation_map;
+    pair.map_weights = cache->weight_half_map;
+    pair.map_weight_scales = cache->weight_scale_map;
+    pair.sf_tokens = q.activation_scales;
+    pair.token_row_blocks = int32_t((q.rows + 127) / 128);
+    pair.k = int32_t(q.k);
+    pair.rows = int32_t(q.rows);
+    pair.n = int32_t(q.n);
+    pair.l_tiles = int32_t((q.rows + 255) / 256);
+    pair.c_tiles = int32_t((q.n + 255) / 256);
+    pair.out = q.output;
+    pair.ld_out = q.n;
+    pair.alpha = q.alpha;
+    pair.error = q.error;
+    GW_CUDA_CHECK(launch_gemm_pair(pair, sm_count(), stream), "NVFP4 CTA-pair tensor-core GEMM");
+    return GW_OK;
   }
   GemmParams params{};
   GemmGroup& g = params.single;

@@ -13,6 +13,8 @@ struct DenseDescriptors {          // re-encoded only when a pointer changes
   const void* activations = nullptr;
   const void* weight_scales = nullptr;
   CUtensorMap weight_map{}, activation_map{}, weight_scale_map{};
+  const void* weight_half = nullptr;
+  CUtensorMap weight_half_map{};     // 128-row box over the weights (CTA-pair kernel: each CTA stages half a tile)
   // Split mode: one arrival counter per weight tile, owned by the plan (device memory,
   // zeroed at creation; the kernel leaves every counter at zero again).
   int32_t* split_counters = nullptr;
