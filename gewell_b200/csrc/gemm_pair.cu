@@ -11,11 +11,12 @@
 //
 // Cross-CTA protocol (all mbarriers sit at the same shared-memory offsets in both
 // CTAs):
-//   full[s]      local; the CTA's own TMA copies complete on it
+//   sf_full[s]   local; the stage's scale atoms (copied first) complete on it
+//   full[s]      local; the stage's operand tiles complete on it
 //   sf_ready[s]  in the leader, 8 arrivals: the loader warps of BOTH CTAs arrive
-//                (the peer's remotely) after their CTA's stage landed and its
-//                scales are in tensor memory -- so it also tells the leader that
-//                the peer's operands are in shared memory
+//                (the peer's remotely) once their CTA's scales are in tensor
+//                memory AND its operand tiles have landed -- the only barrier the
+//                MMA lane waits on per stage
 //   empty[s], acc_full   local; signalled in both CTAs at once by the leader's
 //                tcgen05.commit with the pair mask
 //   acc_empty    in the leader, 16 arrivals (epilogue warps of both CTAs)
@@ -43,7 +44,7 @@ constexpr int kAccCols = 256;
 constexpr int kSfSlotCols = kKBlocks * (4 + 8);   // per stage: token scales 4 columns per K block, weight scales 8
 constexpr int kTmemCols = 512;
 static_assert(kAccCols + kStages * kSfSlotCols <= kTmemCols, "tensor memory over-subscribed");
-constexpr int kBarrierBytes = (3 * kStages + 2) * 8 + 16;
+constexpr int kBarrierBytes = (4 * kStages + 2) * 8 + 16;
 constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -66,25 +67,6 @@ __device__ __forceinline__ uint32_t leader_address(const void* local) {
 // written by tcgen05.st, which tcgen05.wait::st and the tcgen05 fences on both sides order.
 __device__ __forceinline__ void arrive_cluster(uint32_t cluster_address) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_address) : "memory");
-}
-// bounded wait that acquires at cluster scope (the barrier also receives arrivals from the peer CTA)
-__device__ __forceinline__ bool wait_cluster(uint64_t* bar, uint32_t parity, uint64_t limit_ns = 2000000000ull) {
-  const uint32_t address = ptx::smem_u32(bar);
-  auto poll = [&] {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done) : "r"(address), "r"(parity) : "memory");
-    return done != 0;
-  };
-  if (poll()) return true;
-  const uint64_t start = ptx::global_timer_ns();
-  for (uint32_t spin = 1;; ++spin) {
-    if (poll()) return true;
-    if ((spin & 255u) == 0 && ptx::global_timer_ns() - start > limit_ns) return false;
-  }
 }
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t* slot, uint32_t columns) {
   asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ptx::smem_u32(slot)), "r"(columns) : "memory");
@@ -133,7 +115,8 @@ gemm_pair_kernel(const __grid_constant__ PairGemmParams p) {
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
   uint64_t* empty_bar = full_bar + kStages;
   uint64_t* sf_ready_bar = empty_bar + kStages;
-  uint64_t* acc_full_bar = sf_ready_bar + kStages;
+  uint64_t* sf_full_bar = sf_ready_bar + kStages;
+  uint64_t* acc_full_bar = sf_full_bar + kStages;
   uint64_t* acc_empty_bar = acc_full_bar + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -146,6 +129,7 @@ gemm_pair_kernel(const __grid_constant__ PairGemmParams p) {
       ptx::mbar_init(full_bar + s, 1);
       ptx::mbar_init(empty_bar + s, 1);
       ptx::mbar_init(sf_ready_bar + s, 2 * kScaleWarps);
+      ptx::mbar_init(sf_full_bar + s, 1);
     }
     ptx::mbar_init(acc_full_bar, 1);
     ptx::mbar_init(acc_empty_bar, 2 * kEpilogueWarps);
@@ -199,13 +183,17 @@ gemm_pair_kernel(const __grid_constant__ PairGemmParams p) {
           if (p.profile) prof[0] += clock64() - t0;
           const int nkb = min(kKBlocks, total_kb - ks * kKBlocks);
           uint8_t* base = smem + stage * kStageBytes;
+          // the scales go first and complete on their own barrier: the loader warps move them into tensor
+          // memory while the operand tiles are still in flight
+          uint64_t* sf_bar = sf_full_bar + stage;
+          ptx::mbar_expect_tx(sf_bar, nkb * 512 + kSfWgtBytes);
+          ptx::bulk_load(base + kTokBytes + kWgtBytes, sf_tokens + size_t(ks) * kKBlocks * 512, nkb * 512, sf_bar);
+          // weight scales of both halves: [row blocks][K/64 atoms] of 8-byte words, box = 4 atoms x 2 row blocks
+          ptx::tma_load_2d(base + kTokBytes + kWgtBytes + kSfTokBytes, &p.map_weight_scales, ks * 256, c_tile * 2, sf_bar);
           uint64_t* bar = full_bar + stage;
-          ptx::mbar_expect_tx(bar, kTokBytes + kWgtBytes + nkb * 512 + kSfWgtBytes);
+          ptx::mbar_expect_tx(bar, kTokBytes + kWgtBytes);
           ptx::tma_load_2d(base, &p.map_tokens, ks * 128, token_row, bar);
           ptx::tma_load_2d(base + kTokBytes, &p.map_weights, ks * 128, weight_row, bar);
-          ptx::bulk_load(base + kTokBytes + kWgtBytes, sf_tokens + size_t(ks) * kKBlocks * 512, nkb * 512, bar);
-          // weight scales of both halves: [row blocks][K/64 atoms] of 8-byte words, box = 4 atoms x 2 row blocks
-          ptx::tma_load_2d(base + kTokBytes + kWgtBytes + kSfTokBytes, &p.map_weight_scales, ks * 256, c_tile * 2, bar);
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
         if (failed) break;
@@ -220,7 +208,7 @@ gemm_pair_kernel(const __grid_constant__ PairGemmParams p) {
       const uint32_t idesc = idesc_pair_nvfp4(256);
       for (int w = pair; w < total_work && !*abort_flag; w += pairs) {
         const long long ta = p.profile ? clock64() : 0;
-        if (!wait_cluster(acc_empty_bar, acc_phase ^ 1)) {
+        if (!ptx::mbar_wait_bounded(acc_empty_bar, acc_phase ^ 1)) {
           report(p.error, 0x21000000u | (blockIdx.x << 8), abort_flag);
           break;
         }
@@ -229,9 +217,10 @@ gemm_pair_kernel(const __grid_constant__ PairGemmParams p) {
         bool failed = false;
         for (int ks = 0; ks < k_stages; ++ks) {
           const long long t0 = p.profile ? clock64() : 0;
-          bool ok = ptx::mbar_wait_bounded(full_bar + stage, phase);
-          const long long t1 = p.profile ? clock64() : 0;
-          ok = ok && wait_cluster(sf_ready_bar + stage, phase);
+          // sf_ready implies that both CTAs' operands have landed (the loader warps arrive after their
+          // CTA's operand barrier), so this is the only wait of the stage
+          const long long t1 = t0;
+          const bool ok = ptx::mbar_wait_bounded(sf_ready_bar + stage, phase);
           const long long t2 = p.profile ? clock64() : 0;
           if (!ok) {
             report(p.error, 0x31000000u | (blockIdx.x << 8) | stage, abort_flag);
@@ -270,7 +259,7 @@ gemm_pair_kernel(const __grid_constant__ PairGemmParams p) {
       bool failed = false;
       for (int ks = 0; ks < k_stages; ++ks) {
         const long long t0 = p.profile ? clock64() : 0;
-        if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(full_bar + stage, phase))) {
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(sf_full_bar + stage, phase))) {
           report(p.error, 0x61000000u | (blockIdx.x << 8) | stage, abort_flag);
           failed = true;
           break;
@@ -302,7 +291,12 @@ gemm_pair_kernel(const __grid_constant__ PairGemmParams p) {
         ptx::tmem_store_wait();
         const long long t2 = p.profile ? clock64() : 0;
         ptx::tc_fence_before_sync();
-        __syncwarp();
+        // the arrival also vouches for this CTA's operand tiles
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(full_bar + stage, phase))) {
+          report(p.error, 0x62000000u | (blockIdx.x << 8) | stage, abort_flag);
+          failed = true;
+          break;
+        }
         if (lane == 0) arrive_cluster(leader_sf_ready + stage * 8);
         if (p.profile) { prof[0] += t2 - t1; prof[1] += clock64() - t2; }
         if (++stage == kStages) { stage = 0; phase ^= 1; }

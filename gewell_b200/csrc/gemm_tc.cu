@@ -396,23 +396,24 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
       bool failed = false;
       for (int ks = ks0; ks < ks1; ++ks) {
         const long long t0 = p.profile ? clock64() : 0;
-        if (!ptx::mbar_wait_bounded(full_bar + stage, phase)) {
-          report(p.error, 0x30000000u | (blockIdx.x << 8) | stage, abort_flag);
-          failed = true;
-          break;
-        }
-        const long long t1 = p.profile ? clock64() : 0;
-        prof_wait += t1 - t0;
-        ptx::tc_fence_after_sync();
         if constexpr (kNvfp4) {
-          // this stage's scales are in its TMEM slot once the four loader warps have arrived
+          // The stage's scales are in its TMEM slot once the four loader warps have arrived; they
+          // arrive after the stage's copies have landed, so this wait covers the operands too.
           if (!ptx::mbar_wait_bounded(sf_ready_bar + stage, phase)) {
             report(p.error, 0x50000000u | (blockIdx.x << 8) | stage, abort_flag);
             failed = true;
             break;
           }
-          ptx::tc_fence_after_sync();
+        } else {
+          if (!ptx::mbar_wait_bounded(full_bar + stage, phase)) {
+            report(p.error, 0x30000000u | (blockIdx.x << 8) | stage, abort_flag);
+            failed = true;
+            break;
+          }
         }
+        const long long t1 = p.profile ? clock64() : 0;
+        prof_wait += t1 - t0;
+        ptx::tc_fence_after_sync();
         if (lane == 0) {
           // Single in-order instruction stream: descriptors are a constant plus
           // stage * (kStageBytes >> 4) in their low word, the loop is unrolled.

@@ -124,6 +124,24 @@ def test_nvfp4_prefill_tiles_that_do_not_fill_whole_waves(gw, rows, k, n):
     assert_reference_tolerance(results[0], exact, f"prefill rows={rows} K={k} N={n}")
 
 
+@pytest.mark.parametrize("k,n", [(192, 256), (1344, 640), (2816, 384)])
+@pytest.mark.parametrize("rows", [256, 257, 385, 512, 1000])
+def test_nvfp4_cta_pair_tile_edges(gw, k, n, rows, monkeypatch):
+    """From 256 rows the projection runs on CTA pairs (256-token x 256-channel tiles).  Row counts
+    that leave the second CTA of a pair empty, partly filled or full; K with a partial last stage
+    and K longer than the stage ring; channel counts with a ragged last tile.  The single-CTA
+    kernel must give the same bits on the same quantised input."""
+    w = onv.pack_weights(to_f32(bf16_normal((n, k), 31 + n % 5, 0.05)), 0.0113)
+    dev = oracle_weight_to_device(w)
+    x = bf16_normal((rows, k), 32 + rows % 11).cuda()
+    y_pair, packed, scales = run_nvfp4(gw, x, dev, n, k)
+    exact = oracle_from_device_quantisation(packed, scales, rows, k, w)
+    assert_reference_tolerance(bits(y_pair), exact, f"pair rows={rows} K={k} N={n}")
+    monkeypatch.setenv("GW_DENSE_NO_PAIR", "1")
+    y_single, _, _ = run_nvfp4(gw, x, dev, n, k)
+    assert np.array_equal(bits(y_pair), bits(y_single))
+
+
 @pytest.mark.parametrize("form", ["direct", "swap"])
 @pytest.mark.parametrize("rows", [5, 64, 128])
 def test_nvfp4_both_operand_roles(gw, form, rows, monkeypatch):
