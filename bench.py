@@ -257,19 +257,35 @@ def run_expert_parallel(args, world: int, rank: int, local_rank: int):
     flops = tokens * TOPK * FLOPS_PER_ASSIGNMENT
     value = flops / (ms * 1e-3) / 1e12
 
+    # end to end with HOST buffers: every step uploads its pinned inputs and downloads its output inside the
+    # timed region; gw.HostStagedMoe overlaps the copies of neighbouring steps with the kernels
     hx, hs = x.cpu().pin_memory(), scores.cpu().pin_memory()
-    hy = torch.empty((local_tokens, H), dtype=torch.bfloat16).pin_memory()
-    dx, ds = torch.empty_like(x), torch.empty_like(scores)
+    hy = [torch.empty((local_tokens, H), dtype=torch.bfloat16).pin_memory() for _ in range(3)]
 
-    def e2e_step():
-        dx.copy_(hx, non_blocking=True)
-        ds.copy_(hs, non_blocking=True)
-        layer.run(dx, ds, expert_scales, local_tokens, out=y)
-        hy.copy_(y, non_blocking=True)
+    def layer_pass(dx, ds, dy, rows, _stream):
+        layer.run(dx, ds, expert_scales, rows, out=dy)
 
-    for _ in range(3):
-        e2e_step()
-    e2e_ms = timed(e2e_step, args.steps)
+    runner = gw.HostStagedMoe(None, None, expert_scales, local_tokens, H, experts=E, depth=3, run=layer_pass)
+    for i in range(3):
+        runner.submit(hx, hs, hy[i % 3], local_tokens)
+    runner.synchronize()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    dist.barrier()
+    torch.cuda.synchronize()
+    begin.record(runner.upload)
+    for i in range(args.steps):
+        runner.submit(hx, hs, hy[i % 3], local_tokens)
+    end.record(runner.download)
+    runner.synchronize()
+    torch.cuda.synchronize()
+    dist.barrier()
+    e2e_t = torch.tensor([begin.elapsed_time(end) / args.steps], device=device)
+    dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(e2e_t.item())
+    if gw.kernel_error() != 0:
+        raise SystemExit("tensor-core kernel reported an error during the host-buffer run")
+    if not torch.equal(hy[(args.steps - 1) % 3], y.cpu()):
+        raise SystemExit("host-buffer run and device-buffer run disagree")
     clocks = sampler.stop(t0, time.time()) if sampler else None
 
     # per-stage device times of this rank and the grouped GEMMs' roofline
@@ -309,7 +325,8 @@ def run_expert_parallel(args, world: int, rank: int, local_rank: int):
                 "config": config,
                 "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                         "h2d_bytes_per_step": world * (hx.numel() + hs.numel()) * 2,
-                        "d2h_bytes_per_step": world * hy.numel() * 2, "ms_per_step": e2e_ms},
+                        "d2h_bytes_per_step": world * hy[0].numel() * 2, "ms_per_step": e2e_ms,
+                        "note": "uploads, kernels and downloads of consecutive steps overlap (gewell_b200.HostStagedMoe)"},
                 # per rank: 3 routing, tables, dispatch, keys, group descriptors, scale re-tiling, 2 GEMMs,
                 # combine (the collectives are NCCL's)
                 "gpu_launches": 11 * args.steps * world, "clocks": clocks,
@@ -399,33 +416,37 @@ def main():
     flops = tokens * TOPK * FLOPS_PER_ASSIGNMENT
     value = flops / (ms * 1e-3) / 1e12
 
-    # end to end through the public call with HOST buffers: pinned inputs are
-    # copied in and the layer output is copied out inside the timed region
+    # end to end through the public host-buffer call (gw.HostStagedMoe): every step uploads its
+    # pinned inputs and downloads the layer output inside the timed region; the runner overlaps
+    # step i+1's upload and step i-1's download with step i's kernels (three streams, ring of 3)
     hx = x.cpu().pin_memory()
     hs = scores.cpu().pin_memory()
-    hy = torch.empty((tokens, H), dtype=torch.bfloat16).pin_memory()
-    dx, ds = torch.empty_like(x), torch.empty_like(scores)
-
-    def e2e_step():
-        dx.copy_(hx, non_blocking=True)
-        ds.copy_(hs, non_blocking=True)
-        ws.run(dx, ds, expert_scales, table, y, tokens)
-        hy.copy_(y, non_blocking=True)
-
-    for _ in range(3):
-        e2e_step()
+    hy = [torch.empty((tokens, H), dtype=torch.bfloat16).pin_memory() for _ in range(3)]
+    runner = gw.HostStagedMoe(ws, table, expert_scales, tokens, H, experts=E, depth=3)
     torch.cuda.synchronize()
-    begin.record(stream)
-    for _ in range(args.steps):
-        e2e_step()
-    end.record(stream)
+
+    for i in range(3):
+        runner.submit(hx, hs, hy[i % 3], tokens)
+    runner.synchronize()
+    before_h2d, before_d2h = runner.h2d_bytes, runner.d2h_bytes
+    begin.record(runner.upload)
+    for i in range(args.steps):
+        runner.submit(hx, hs, hy[i % 3], tokens)
+    end.record(runner.download)
+    runner.synchronize()
     torch.cuda.synchronize()
     t2 = time.time()
     clocks = sampler.stop(t0, t2)
+    if gw.kernel_error() != 0:
+        raise SystemExit("tensor-core kernel reported an error during the host-buffer run")
+    if not torch.equal(hy[(args.steps - 1) % 3], y.cpu()):
+        raise SystemExit("host-buffer run and device-buffer run disagree")
     e2e_ms = begin.elapsed_time(end) / args.steps
     e2e = {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
-           "h2d_bytes_per_step": hx.numel() * 2 + hs.numel() * 2, "d2h_bytes_per_step": hy.numel() * 2,
-           "ms_per_step": e2e_ms}
+           "h2d_bytes_per_step": (runner.h2d_bytes - before_h2d) // args.steps,
+           "d2h_bytes_per_step": (runner.d2h_bytes - before_d2h) // args.steps,
+           "ms_per_step": e2e_ms,
+           "note": "uploads, kernels and downloads of consecutive steps overlap (gewell_b200.HostStagedMoe)"}
 
     # roofline of the dominant kernel (the two grouped tcgen05 GEMMs), timed live
     # with CUDA events recorded on the launching stream between the stages

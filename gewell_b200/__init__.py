@@ -19,6 +19,8 @@ _OPS = (
 def __getattr__(name):
     if name == "lib":
         value = _lib.load()
+    elif name == "HostStagedMoe":
+        from .host_io import HostStagedMoe as value
     elif name in _OPS:
         from . import ops
         value = getattr(ops, name)

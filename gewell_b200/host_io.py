@@ -1,0 +1,110 @@
+"""MoE layer passes whose tokens and results live in pinned HOST memory.
+
+A caller that keeps activations on the host (an engine that runs the
+attention part elsewhere, a test harness, a benchmark) pays a host->device copy
+of the token rows and router logits and a device->host copy of the layer output
+for every pass.  Issued on one stream those three steps run one after another;
+`HostStagedMoe` gives each its own stream and a ring of device buffers, so pass
+i+1's upload and pass i-1's download overlap pass i's kernels (PCIe is full
+duplex, and the copies use the copy engines, not the SMs).
+
+    runner = HostStagedMoe(workspace, table, expert_scales, max_rows, hidden)
+    for batch in batches:
+        runner.submit(batch.x, batch.scores, batch.y, rows)   # returns at once
+    runner.synchronize()                                      # every batch.y is complete
+
+The kernels of consecutive passes still run in order on the compute stream (a
+workspace is one set of scratch buffers), and results are bit-identical to
+`MoeWorkspace.run` on device buffers.
+"""
+from __future__ import annotations
+
+import torch
+
+from .ops import ExpertTable, MoeWorkspace
+
+
+class HostStagedMoe:
+    def __init__(self, workspace: MoeWorkspace, table: ExpertTable, expert_scales: torch.Tensor, max_rows: int,
+                 hidden: int, experts: int = 128, depth: int = 2, device=None, run=None):
+        """`run(x, scores, y, rows, stream)`, when given, replaces `workspace.run` as the layer pass (the
+        expert-parallel layers have their own entry point); it is called with the compute stream current
+        and must issue all of its work on that stream."""
+        if depth < 1:
+            raise ValueError("depth must be at least 1")
+        if not torch.cuda.is_available():
+            raise RuntimeError("HostStagedMoe needs a CUDA device: there is no CPU execution path")
+        self.workspace, self.table, self.expert_scales = workspace, table, expert_scales
+        self.max_rows, self.hidden, self.experts, self.depth = max_rows, hidden, experts, depth
+        self._run = run
+        device = device if device is not None else expert_scales.device
+        self.device = device
+        self.upload, self.compute, self.download = (torch.cuda.Stream(device=device) for _ in range(3))
+        self._x = [torch.empty((max_rows, hidden), dtype=torch.bfloat16, device=device) for _ in range(depth)]
+        self._scores = [torch.empty((max_rows, experts), dtype=torch.bfloat16, device=device) for _ in range(depth)]
+        self._y = [torch.empty((max_rows, hidden), dtype=torch.bfloat16, device=device) for _ in range(depth)]
+        # per slot: the pass that last used it has finished computing / downloading
+        self._computed = [None] * depth
+        self._downloaded = [None] * depth
+        self._submitted = 0
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+
+    def submit(self, host_x: torch.Tensor, host_scores: torch.Tensor, host_y: torch.Tensor, rows: int) -> int:
+        """Queue one layer pass: host_x [rows, hidden] and host_scores [rows, experts] (BF16, pinned) are
+        uploaded, the layer runs, the output lands in host_y [rows, hidden] (BF16, pinned).  Returns the
+        pass's sequence number without waiting; `synchronize()` (or `wait_for`) makes host_y readable."""
+        if rows < 0 or rows > self.max_rows:
+            raise ValueError(f"rows = {rows} outside [0, {self.max_rows}]")
+        for name, t, width in (("host_x", host_x, self.hidden), ("host_scores", host_scores, self.experts),
+                               ("host_y", host_y, self.hidden)):
+            if t.device.type != "cpu" or not t.is_pinned():
+                raise ValueError(f"{name} must be a pinned host tensor")
+            if t.dtype != torch.bfloat16 or t.dim() != 2 or t.shape[1] != width or t.shape[0] < rows \
+                    or not t.is_contiguous():
+                raise ValueError(f"{name} must be contiguous BF16 [>= rows, {width}]")
+        ticket = self._submitted
+        slot = ticket % self.depth
+        x, scores, y = self._x[slot], self._scores[slot], self._y[slot]
+        if rows > 0:
+            with torch.cuda.stream(self.upload):
+                if self._computed[slot] is not None:        # the slot's previous pass no longer reads its inputs
+                    self.upload.wait_event(self._computed[slot])
+                x[:rows].copy_(host_x[:rows], non_blocking=True)
+                scores[:rows].copy_(host_scores[:rows], non_blocking=True)
+                uploaded = torch.cuda.Event()
+                uploaded.record(self.upload)
+            with torch.cuda.stream(self.compute):
+                self.compute.wait_event(uploaded)
+                if self._downloaded[slot] is not None:      # the slot's previous output has left the device
+                    self.compute.wait_event(self._downloaded[slot])
+                if self._run is not None:
+                    self._run(x, scores, y, rows, self.compute)
+                else:
+                    self.workspace.run(x, scores, self.expert_scales, self.table, y, rows, stream=self.compute)
+                computed = torch.cuda.Event()
+                computed.record(self.compute)
+            with torch.cuda.stream(self.download):
+                self.download.wait_event(computed)
+                host_y[:rows].copy_(y[:rows], non_blocking=True)
+                downloaded = torch.cuda.Event()
+                downloaded.record(self.download)
+            self._computed[slot], self._downloaded[slot] = computed, downloaded
+            self.h2d_bytes += rows * (self.hidden + self.experts) * 2
+            self.d2h_bytes += rows * self.hidden * 2
+        self._submitted += 1
+        return ticket
+
+    def wait_for(self, ticket: int) -> None:
+        """Block the host until pass `ticket`'s output is in its host buffer."""
+        if ticket < 0 or ticket >= self._submitted:
+            raise ValueError("no such pass")
+        # the download stream runs in order: the newest download queued on the pass's slot is not
+        # earlier than the pass's own
+        event = self._downloaded[ticket % self.depth]
+        if event is not None:
+            event.synchronize()
+
+    def synchronize(self) -> None:
+        for stream in (self.upload, self.compute, self.download):
+            stream.synchronize()
