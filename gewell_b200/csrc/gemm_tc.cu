@@ -75,19 +75,25 @@ struct WorkItem {
   int c_valid;   // swap form: valid columns (tokens) in this tile
   int halves;    // boxes of the C operand that hold valid rows in this tile
   int mma_n;     // MMA N for this tile
+  int group = -1;   // index of g in the launch's group table (grouped launches)
 };
 
 template <int BLOCK_N, GemmEpilogue EPI>
 __device__ __forceinline__ void decode_work(const GemmParams& p, const int32_t* prefix, int w, WorkItem& item) {
   using C = Config<true, BLOCK_N>;
   if (p.groups != nullptr) {
-    // largest gi with work_begin[gi] <= w; the prefix sums were staged in shared memory
-    int lo = 0, hi = p.num_groups;
-    while (lo + 1 < hi) {
-      const int mid = (lo + hi) / 2;
-      if (prefix[mid] <= w) lo = mid; else hi = mid;
+    // The item decoded into this slot before is usually of the same group: keep its descriptor then
+    // (no search, no global load).  prefix[] holds work_begin of every group plus the total.
+    if (item.group < 0 || w < prefix[item.group] || w >= prefix[item.group + 1]) {
+      // largest gi with work_begin[gi] <= w; the prefix sums were staged in shared memory
+      int lo = 0, hi = p.num_groups;
+      while (lo + 1 < hi) {
+        const int mid = (lo + hi) / 2;
+        if (prefix[mid] <= w) lo = mid; else hi = mid;
+      }
+      item.g = p.groups[lo];
+      item.group = lo;
     }
-    item.g = p.groups[lo];
   } else {
     item.g = p.single;
   }
@@ -113,17 +119,19 @@ __device__ __forceinline__ void decode_work(const GemmParams& p, const int32_t* 
   else item.mma_n = item.halves * C::kHalfRows;
 }
 
-// Walks the work of one CTA.  Normal mode: whole work items blockIdx.x,
-// blockIdx.x + gridDim.x, ...  Split mode (decode shapes): the launch's
+// Walks the work of one CTA.  Normal mode: whole work items in chunks of `chunk`
+// consecutive items (chunk index blockIdx.x, blockIdx.x + gridDim.x, ...).  Split mode (decode shapes): the launch's
 // (item, K-stage) units are cut into gridDim.x equal contiguous ranges, so a CTA
 // may start and end in the middle of an item's K loop; every SM then streams
 // the same number of weight bytes whatever the number of tiles.
 struct SegmentWalk {
   bool split;
-  int w, step, total_work, k_stages;
+  int w, step, total_work, k_stages, chunk, in_chunk;
   long long u, u_begin, u_end, total_units;
-  __device__ SegmentWalk(bool split_, int total_work_, int k_stages_)
-      : split(split_), w(blockIdx.x), step(gridDim.x), total_work(total_work_), k_stages(k_stages_) {
+  __device__ SegmentWalk(bool split_, int total_work_, int k_stages_, int chunk_ = 1)
+      : split(split_), w(blockIdx.x), step(gridDim.x), total_work(total_work_), k_stages(k_stages_),
+        chunk(chunk_ > 1 ? chunk_ : 1), in_chunk(0) {
+    w = blockIdx.x * chunk;
     total_units = (long long)total_work * k_stages;
     u_begin = u = total_units * blockIdx.x / gridDim.x;
     u_end = total_units * (blockIdx.x + 1) / gridDim.x;
@@ -133,7 +141,8 @@ struct SegmentWalk {
     if (!split) {
       if (w >= total_work) return false;
       tile = w; ks0 = 0; ks1 = k_stages; at_range_start = false;
-      w += step;
+      // `chunk` consecutive items, then on to this CTA's next chunk
+      if (++in_chunk == chunk) { in_chunk = 0; w += (step - 1) * chunk + 1; } else { ++w; }
       return true;
     }
     if (u >= u_end) return false;
@@ -257,7 +266,7 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
     uint32_t phase = 0;
     bool waited = !early_weights;        // this warp defers its wait for the previous kernel (see below)
     WorkItem item, next;
-    SegmentWalk walk(split, total_work, k_stages);
+    SegmentWalk walk(split, total_work, k_stages, p.work_chunk);
     int tile, ks0, ks1, next_tile, next_ks0, next_ks1;
     bool at_start, next_at_start;
     bool more = walk.next(next_tile, next_ks0, next_ks1, next_at_start);
@@ -371,7 +380,7 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
     int stage = 0, acc = 0;
     uint32_t phase = 0, acc_phase = 0;
     WorkItem item, next;
-    SegmentWalk walk(split, total_work, k_stages);
+    SegmentWalk walk(split, total_work, k_stages, p.work_chunk);
     int tile, ks0, ks1, next_tile, next_ks0, next_ks1;
     bool at_start, next_at_start;
     bool more = walk.next(next_tile, next_ks0, next_ks1, next_at_start);
@@ -457,7 +466,7 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
       int stage = 0;
       uint32_t phase = 0;
       WorkItem item, next;
-      SegmentWalk walk(split, total_work, k_stages);
+      SegmentWalk walk(split, total_work, k_stages, p.work_chunk);
       int tile, ks0, ks1, next_tile, next_ks0, next_ks1;
       bool at_start, next_at_start;
       bool more = walk.next(next_tile, next_ks0, next_ks1, next_at_start);
@@ -534,7 +543,7 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
     int acc = 0;
     uint32_t acc_phase = 0;
     WorkItem item, next;
-    SegmentWalk walk(split, total_work, k_stages);
+    SegmentWalk walk(split, total_work, k_stages, p.work_chunk);
     int tile, ks0, ks1, next_tile, next_ks0, next_ks1;
     bool at_start, next_at_start;
     bool more = walk.next(next_tile, next_ks0, next_ks1, next_at_start);

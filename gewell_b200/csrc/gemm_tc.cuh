@@ -71,6 +71,7 @@ struct GemmParams {
   // (tile, K stage) units; partial tiles are summed through these buffers.
   float* split_partials;          // [2 * grid][128 * BLOCK_N] FP32, or nullptr (whole tiles per CTA)
   int32_t* split_counters;        // [work items], zero at launch; left zero by the kernel
+  int32_t work_chunk;             // consecutive work items a CTA takes before it strides on (0 or 1: one)
   int32_t early_weights;          // swap form, groups == nullptr: the L operand (weights, weight scales) does not
                                   // depend on the previous kernel in the stream, so its first copies may be
                                   // issued before that kernel has finished (programmatic dependent launch)

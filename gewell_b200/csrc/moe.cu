@@ -250,6 +250,8 @@ gw_status run_experts(gw_moe_workspace* w, const void* input, const int32_t* gat
   first.num_groups = form == kMoeFormFused ? kExperts : 2 * kExperts;
   first.k = kHidden;
   first.c_rows_per_tile = form == kMoeFormFused ? 128 : block_n_first;
+  // two consecutive tiles per CTA (same token tile, same expert) before it strides on: measured best
+  first.work_chunk = env_int("GW_MOE_CHUNK_FIRST", swap ? 1 : 2);
   first.error = device_error_word();
   w->mark(2, s);
   if (form == kMoeFormFused) {
@@ -283,6 +285,7 @@ gw_status run_experts(gw_moe_workspace* w, const void* input, const int32_t* gat
   down.num_groups = kExperts;
   down.k = kInter;
   down.c_rows_per_tile = block_n_down;
+  down.work_chunk = env_int("GW_MOE_CHUNK_DOWN", swap ? 1 : 2);
   down.out = down_out;
   down.ld_out = kHidden;
   down.row_dest = row_home;   // rows go to their homes (possibly on other GPUs) instead of down_out
