@@ -156,7 +156,6 @@ gemm_pair_kernel(const __grid_constant__ PairGemmParams p) {
   constexpr uint32_t kDescHiSw128 = uint32_t(1024 >> 4) | (1u << 14) | (2u << 29);
   auto make_desc = [](uint32_t hi, uint32_t lo) { return (uint64_t(hi) << 32) | lo; };
   const uint32_t smem_base16 = ptx::smem_u32(smem) >> 4;
-  long long prof[5] = {0, 0, 0, 0, 0};
   const long long prof_start = p.profile ? clock64() : 0;
 
   if (warp == 0) {
@@ -164,6 +163,7 @@ gemm_pair_kernel(const __grid_constant__ PairGemmParams p) {
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
+      long long prof_wait = 0;
       for (int w = pair; w < total_work && !*abort_flag; w += pairs) {
         const int c_tile = w % p.c_tiles, l_tile = w / p.c_tiles;
         const int token_row = (l_tile * 2 + int(rank)) * 128;        // this CTA's 128 token rows
@@ -180,7 +180,7 @@ gemm_pair_kernel(const __grid_constant__ PairGemmParams p) {
             failed = true;
             break;
           }
-          if (p.profile) prof[0] += clock64() - t0;
+          if (p.profile) prof_wait += clock64() - t0;
           const int nkb = min(kKBlocks, total_kb - ks * kKBlocks);
           uint8_t* base = smem + stage * kStageBytes;
           // the scales go first and complete on their own barrier: the loader warps move them into tensor
@@ -198,6 +198,7 @@ gemm_pair_kernel(const __grid_constant__ PairGemmParams p) {
         }
         if (failed) break;
       }
+      if (p.profile) p.profile[size_t(blockIdx.x) * 8 + 0] = prof_wait;
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -206,20 +207,20 @@ gemm_pair_kernel(const __grid_constant__ PairGemmParams p) {
       int stage = 0;
       uint32_t phase = 0, acc_phase = 0;
       const uint32_t idesc = idesc_pair_nvfp4(256);
+      long long prof_sf = 0, prof_issue = 0, prof_acc = 0;
       for (int w = pair; w < total_work && !*abort_flag; w += pairs) {
         const long long ta = p.profile ? clock64() : 0;
         if (!ptx::mbar_wait_bounded(acc_empty_bar, acc_phase ^ 1)) {
           report(p.error, 0x21000000u | (blockIdx.x << 8), abort_flag);
           break;
         }
-        if (p.profile) prof[4] += clock64() - ta;
+        if (p.profile) prof_acc += clock64() - ta;
         ptx::tc_fence_after_sync();
         bool failed = false;
         for (int ks = 0; ks < k_stages; ++ks) {
           const long long t0 = p.profile ? clock64() : 0;
           // sf_ready implies that both CTAs' operands have landed (the loader warps arrive after their
           // CTA's operand barrier), so this is the only wait of the stage
-          const long long t1 = t0;
           const bool ok = ptx::mbar_wait_bounded(sf_ready_bar + stage, phase);
           const long long t2 = p.profile ? clock64() : 0;
           if (!ok) {
@@ -227,7 +228,7 @@ gemm_pair_kernel(const __grid_constant__ PairGemmParams p) {
             failed = true;
             break;
           }
-          if (p.profile) { prof[1] += t1 - t0; prof[2] += t2 - t1; }
+          if (p.profile) prof_sf += t2 - t0;
           ptx::tc_fence_after_sync();
           const int nkb = min(kKBlocks, total_kb - ks * kKBlocks);
           const uint32_t base16 = smem_base16 + uint32_t(stage) * uint32_t(kStageBytes >> 4);
@@ -240,14 +241,19 @@ gemm_pair_kernel(const __grid_constant__ PairGemmParams p) {
                              make_desc(kDescHiSw128, base16 + (kTokBytes >> 4) + 2 * kb), idesc, sf_tok + 4 * kb,
                              sf_wgt + 8 * kb, (ks | kb) != 0 ? 1u : 0u);
           commit_pair(empty_bar + stage);
-          if (p.profile) prof[3] += clock64() - t2;
+          if (p.profile) prof_issue += clock64() - t2;
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
         if (failed) break;
         commit_pair(acc_full_bar);
         acc_phase ^= 1;
       }
+      if (p.profile) {
+        long long* row = p.profile + size_t(blockIdx.x) * 8;
+        row[2] = prof_sf; row[3] = prof_issue; row[4] = prof_acc;
+      }
     }
+    if (p.profile && lane == 0) p.profile[size_t(blockIdx.x) * 8 + 6] = clock64() - prof_start;
     __syncwarp();
   } else if (warp < kFirstEpilogueWarp) {
     // ------------------------------------------------------------------ scale loaders
@@ -255,10 +261,10 @@ gemm_pair_kernel(const __grid_constant__ PairGemmParams p) {
     const uint32_t leader_sf_ready = leader_address(sf_ready_bar);
     int stage = 0;
     uint32_t phase = 0;
+    long long prof_copy = 0, prof_arrive = 0;
     for (int w = pair; w < total_work && !*abort_flag; w += pairs) {
       bool failed = false;
       for (int ks = 0; ks < k_stages; ++ks) {
-        const long long t0 = p.profile ? clock64() : 0;
         if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(sf_full_bar + stage, phase))) {
           report(p.error, 0x61000000u | (blockIdx.x << 8) | stage, abort_flag);
           failed = true;
@@ -298,10 +304,15 @@ gemm_pair_kernel(const __grid_constant__ PairGemmParams p) {
           break;
         }
         if (lane == 0) arrive_cluster(leader_sf_ready + stage * 8);
-        if (p.profile) { prof[0] += t2 - t1; prof[1] += clock64() - t2; }
+        if (p.profile) { prof_copy += t2 - t1; prof_arrive += clock64() - t2; }
         if (++stage == kStages) { stage = 0; phase ^= 1; }
       }
       if (failed) break;
+    }
+    if (p.profile && lane == 0 && warp == 2) {
+      long long* row = p.profile + size_t(blockIdx.x) * 8;
+      row[5] = prof_copy;
+      row[7] = prof_arrive;
     }
   } else {
     // ------------------------------------------------------------------ epilogue (own 128 rows x 256 channels)
@@ -373,16 +384,6 @@ gemm_pair_kernel(const __grid_constant__ PairGemmParams p) {
     }
   }
 
-  if (p.profile && lane == 0 && warp == 2) {
-    long long* row = p.profile + size_t(blockIdx.x) * 8;
-    row[5] = prof[0];
-    row[7] = prof[1];
-  }
-  if (p.profile && lane == 0 && warp <= 1) {
-    long long* row = p.profile + size_t(blockIdx.x) * 8;
-    if (warp == 0) row[0] = prof[0];
-    if (warp == 1) { row[1] = prof[1]; row[2] = prof[2]; row[3] = prof[3]; row[4] = prof[4]; row[6] = clock64() - prof_start; }
-  }
   ptx::tc_fence_before_sync();
   __syncthreads();
   cluster_sync_all();                               // the peer no longer reads this CTA's shared or tensor memory

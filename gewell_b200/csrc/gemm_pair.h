@@ -24,8 +24,10 @@ struct PairGemmParams {
   long long* profile;              // optional [grid][8] cycle counters (debug aid)
 };
 
-// Debug aid: later launches write per-CTA cycle counters (producer wait, MMA wait for data, MMA wait
-// for scales, MMA issue, MMA wait for the accumulator, -, total, -) into this device buffer.
+// Debug aid: later launches write per-CTA cycle counters into this device buffer, eight per CTA:
+// [0] producer waiting for an empty stage, [2] MMA lane waiting for the scale-ready barrier, [3] MMA lane
+// issuing (blocked while the tensor pipe is busy), [4] MMA lane waiting for the accumulator, [5] scale
+// loader copying, [6] total, [7] scale loader between its copy and its arrival (operand wait).
 void set_pair_profile_buffer(long long* device_buffer);
 
 cudaError_t launch_gemm_pair(const PairGemmParams& params, int sm_count, cudaStream_t stream);

@@ -239,7 +239,6 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
 
   // shared-memory descriptors: high words are constants, low word = address >> 4
   constexpr uint32_t kDescHiSw128 = uint32_t(1024 >> 4) | (1u << 14) | (2u << 29);   // SBO 1024 B, version 1, SWIZZLE_128B
-  constexpr uint32_t kDescHiSf = uint32_t(128 >> 4) | (1u << 14);                    // SBO 128 B, version 1, no swizzle
   constexpr uint32_t kCOff16 = C::kLBytes >> 4;
   constexpr uint32_t kSflOff16 = (C::kLBytes + C::kCBytes) >> 4;
   constexpr uint32_t kSfcOff16 = (C::kLBytes + C::kCBytes + C::kSflBytes) >> 4;
@@ -399,9 +398,6 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
       ptx::tc_fence_after_sync();
       const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
       const uint32_t idesc = kNvfp4 ? ptx::idesc_nvfp4(item.mma_n) : ptx::idesc_fp8(item.mma_n);
-      const int c_local = item.c_tile * p.c_rows_per_tile;
-      (void)c_local;
-      const int halves = item.halves;
       bool failed = false;
       for (int ks = ks0; ks < ks1; ++ks) {
         const long long t0 = p.profile ? clock64() : 0;
