@@ -23,6 +23,7 @@
 #include "common.cuh"
 #include "gemm_tc.cuh"
 #include "ptx.cuh"
+#include "work_walk.h"
 
 namespace gw {
 namespace {
@@ -118,46 +119,6 @@ __device__ __forceinline__ void decode_work(const GemmParams& p, const int32_t* 
   if constexpr (EPI == GemmEpilogue::swap_store) item.mma_n = (item.c_valid + 15) & ~15;   // kHalves == 1
   else item.mma_n = item.halves * C::kHalfRows;
 }
-
-// Walks the work of one CTA.  Normal mode: whole work items in chunks of `chunk`
-// consecutive items (chunk index blockIdx.x, blockIdx.x + gridDim.x, ...).  Split mode (decode shapes): the launch's
-// (item, K-stage) units are cut into gridDim.x equal contiguous ranges, so a CTA
-// may start and end in the middle of an item's K loop; every SM then streams
-// the same number of weight bytes whatever the number of tiles.
-struct SegmentWalk {
-  bool split;
-  int w, step, total_work, k_stages, chunk, in_chunk;
-  long long u, u_begin, u_end, total_units;
-  __device__ SegmentWalk(bool split_, int total_work_, int k_stages_, int chunk_ = 1)
-      : split(split_), w(blockIdx.x), step(gridDim.x), total_work(total_work_), k_stages(k_stages_),
-        chunk(chunk_ > 1 ? chunk_ : 1), in_chunk(0) {
-    w = blockIdx.x * chunk;
-    total_units = (long long)total_work * k_stages;
-    u_begin = u = total_units * blockIdx.x / gridDim.x;
-    u_end = total_units * (blockIdx.x + 1) / gridDim.x;
-  }
-  // next segment: work item `tile`, K stages [ks0, ks1)
-  __device__ bool next(int& tile, int& ks0, int& ks1, bool& at_range_start) {
-    if (!split) {
-      if (w >= total_work) return false;
-      tile = w; ks0 = 0; ks1 = k_stages; at_range_start = false;
-      // `chunk` consecutive items, then on to this CTA's next chunk
-      if (++in_chunk == chunk) { in_chunk = 0; w += (step - 1) * chunk + 1; } else { ++w; }
-      return true;
-    }
-    if (u >= u_end) return false;
-    tile = int(u / k_stages);
-    ks0 = int(u % k_stages);
-    const long long left = u_end - u;
-    ks1 = left < (long long)(k_stages - ks0) ? ks0 + int(left) : k_stages;
-    at_range_start = u == u_begin;
-    u += ks1 - ks0;
-    return true;
-  }
-  // CTA whose range holds unit x
-  __device__ int cta_of(long long x) const { return int(((x + 1) * step + total_units - 1) / total_units) - 1; }
-  __device__ long long range_begin(int cta) const { return total_units * cta / step; }
-};
 
 __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
@@ -265,7 +226,7 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
     uint32_t phase = 0;
     bool waited = !early_weights;        // this warp defers its wait for the previous kernel (see below)
     WorkItem item, next;
-    SegmentWalk walk(split, total_work, k_stages, p.work_chunk);
+    SegmentWalk walk(int(blockIdx.x), int(gridDim.x), split, total_work, k_stages, p.work_chunk);
     int tile, ks0, ks1, next_tile, next_ks0, next_ks1;
     bool at_start, next_at_start;
     bool more = walk.next(next_tile, next_ks0, next_ks1, next_at_start);
@@ -379,7 +340,7 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
     int stage = 0, acc = 0;
     uint32_t phase = 0, acc_phase = 0;
     WorkItem item, next;
-    SegmentWalk walk(split, total_work, k_stages, p.work_chunk);
+    SegmentWalk walk(int(blockIdx.x), int(gridDim.x), split, total_work, k_stages, p.work_chunk);
     int tile, ks0, ks1, next_tile, next_ks0, next_ks1;
     bool at_start, next_at_start;
     bool more = walk.next(next_tile, next_ks0, next_ks1, next_at_start);
@@ -462,7 +423,7 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
       int stage = 0;
       uint32_t phase = 0;
       WorkItem item, next;
-      SegmentWalk walk(split, total_work, k_stages, p.work_chunk);
+      SegmentWalk walk(int(blockIdx.x), int(gridDim.x), split, total_work, k_stages, p.work_chunk);
       int tile, ks0, ks1, next_tile, next_ks0, next_ks1;
       bool at_start, next_at_start;
       bool more = walk.next(next_tile, next_ks0, next_ks1, next_at_start);
@@ -539,7 +500,7 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
     int acc = 0;
     uint32_t acc_phase = 0;
     WorkItem item, next;
-    SegmentWalk walk(split, total_work, k_stages, p.work_chunk);
+    SegmentWalk walk(int(blockIdx.x), int(gridDim.x), split, total_work, k_stages, p.work_chunk);
     int tile, ks0, ks1, next_tile, next_ks0, next_ks1;
     bool at_start, next_at_start;
     bool more = walk.next(next_tile, next_ks0, next_ks1, next_at_start);

@@ -1,5 +1,6 @@
-"""Compile and run the host-only C++ shim contract test against the built
-library (no GPU needed: every check fails validation before CUDA is touched)."""
+"""Host-only C++ tests: the shim contract against the built library (no GPU needed:
+every check fails validation before CUDA is touched) and the persistent kernels'
+work distribution (plain arithmetic shared by host and device)."""
 import shutil
 import subprocess
 from pathlib import Path
@@ -19,6 +20,16 @@ def test_shim_contract(tmp_path):
                     str(ROOT / "tests" / "cpp" / "shim_contract.cpp"), "-o", str(exe),
                     str(_lib.LIBRARY_PATH), f"-Wl,-rpath,{_lib.LIBRARY_PATH.parent}",
                     "-L/usr/local/cuda/lib64", "-lcudart", "-Wl,-rpath,/usr/local/cuda/lib64"], check=True)
+    done = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert done.returncode == 0, done.stdout + done.stderr
+    assert "PASS" in done.stdout
+
+
+@pytest.mark.skipif(shutil.which("g++") is None, reason="needs g++")
+def test_work_distribution_covers_every_item_once(tmp_path):
+    exe = tmp_path / "work_walk_test"
+    subprocess.run(["g++", "-std=c++17", "-O1", "-I", str(ROOT / "gewell_b200" / "csrc"),
+                    str(ROOT / "tests" / "cpp" / "work_walk_test.cpp"), "-o", str(exe)], check=True)
     done = subprocess.run([str(exe)], capture_output=True, text=True)
     assert done.returncode == 0, done.stdout + done.stderr
     assert "PASS" in done.stdout
