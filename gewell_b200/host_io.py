@@ -16,6 +16,11 @@ duplex, and the copies use the copy engines, not the SMs).
 The kernels of consecutive passes still run in order on the compute stream (a
 workspace is one set of scratch buffers), and results are bit-identical to
 `MoeWorkspace.run` on device buffers.
+
+The runner's three streams are ordered among themselves only: weights, the
+expert table and `expert_scales` must be complete on the device before the
+first `submit` (synchronise the stream that prepared them), and the workspace
+must not be used by other calls while passes are in flight.
 """
 from __future__ import annotations
 
