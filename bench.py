@@ -118,53 +118,56 @@ def build_experts(gw, torch, device, seed=4, expert_ids=None):
     return experts
 
 
-def cpu_baseline_sample(experts, tokens: int, seed: int = 11) -> dict:
-    """The reference's host path for this layer (dequantise the NVFP4 weights,
-    FP32 matmul per expert, ordered BF16 combine) timed on this box's host
-    cores over a bounded sample of the workload."""
+def cpu_host_path(tokens: int, steps: int, warmup: int = 0, seed: int = 11) -> dict:
+    """The reference's host path for this layer on this box's host cores: dequantise the NVFP4
+    expert weights (src/nvfp4_linear.cu:47-55), then per step route, FP32 matmul per expert with
+    BF16 roundings, GeGLU and the ordered BF16 combine over `tokens` tokens.  The reference has no
+    CPU build of this layer, so this is the CPU restatement of its arithmetic (oracle/), run with
+    every host thread NumPy's BLAS takes.  The dequantised weights are kept between steps, as a CPU
+    deployment would; the one-off dequantisation is timed and reported beside the per-step rate.
+    Needs no GPU and does not load the CUDA library."""
     import numpy as np
-    import torch
+    from oracle import codecs as C
     from oracle import moe as omoe
-    from oracle import nvfp4 as onv
-    host = [omoe.ExpertWeights(*[onv.Weight(p.data.cpu().numpy(), p.scales.cpu().numpy(), p.input_scale, p.weight_scale,
-                                            p.data.shape[0], p.data.shape[1] * 2) for p in ex]) for ex in experts]
-    g = torch.Generator().manual_seed(seed)
-    x = torch.randn((tokens, H), generator=g).bfloat16().float().numpy()
-    scores = torch.randn((tokens, E), generator=g).bfloat16().float().numpy()
+    experts = omoe.synthetic_packed_experts(seed=4)
     start = time.perf_counter()
-    omoe.forward(x, scores, np.ones(E, dtype=np.float32), host, mode="w4a16")
-    seconds = time.perf_counter() - start
-    return {"value": tokens * TOPK * FLOPS_PER_ASSIGNMENT / seconds / 1e12, "unit": "TFLOP/s",
-            "cores": os.cpu_count(), "kind": "port",
-            "sample": f"{tokens} tokens of the same layer (dequantise + FP32 matmul per expert, NumPy/BLAS), {seconds:.1f} s"}
+    dense = omoe.dequantize_experts(experts)
+    dequantise_s = time.perf_counter() - start
+    del experts
+    rng = np.random.default_rng(seed)
+    ones = np.ones(E, dtype=np.float32)
+    seconds = []
+    for step in range(warmup + steps):
+        x = C.bf16_round(rng.standard_normal((tokens, H)).astype(np.float32))
+        scores = C.bf16_round(rng.standard_normal((tokens, E)).astype(np.float32))
+        start = time.perf_counter()
+        omoe.forward_dequantized(x, scores, ones, dense)
+        if step >= warmup:
+            seconds.append(time.perf_counter() - start)
+    per_step = statistics.mean(seconds)
+    flops = tokens * TOPK * FLOPS_PER_ASSIGNMENT
+    return {"value": flops / per_step / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
+            "seconds_per_step": per_step, "dequantise_seconds": dequantise_s,
+            "with_dequantise_every_step": flops / (per_step + dequantise_s) / 1e12,
+            "sample": (f"{tokens} tokens per step x {steps} steps of the same layer (route, FP32 matmul per expert on "
+                       f"dequantised weights, GeGLU, ordered combine; NumPy/BLAS): {per_step:.2f} s per step; the "
+                       f"one-off dequantisation of the 384 expert matrices took {dequantise_s:.1f} s and is not in "
+                       f"`value` (`with_dequantise_every_step` includes it)")}
 
 
 def run_reference_arm(args):
-    """CPU arm: the host path of the reference for this layer, all host threads."""
+    """CPU arm: the host path of the reference for this layer, all host threads, no GPU."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    import torch
-    import gewell_b200 as gw
-    device = torch.device("cuda", 0) if torch.cuda.is_available() else None
-    if device is None:
-        print(json.dumps({"impl": "reference", "unavailable": "needs a CUDA device to build the packed expert weights"}))
-        return
-    experts = build_experts(gw, torch, device)
-    tokens = 96
-    values = []
-    for step in range(args.warmup + args.steps):
-        sample = cpu_baseline_sample(experts, tokens, seed=100 + step)
-        if step >= args.warmup:
-            values.append(sample)
-    value = statistics.mean(v["value"] for v in values)
-    seconds = tokens * TOPK * FLOPS_PER_ASSIGNMENT / value / 1e12
+    tokens = 1024
+    result = cpu_host_path(tokens, args.steps, min(args.warmup, 1), seed=100)
+    value = result["value"]
+    config = workload_config(args.gpus) | {"sample_tokens_per_step": tokens}
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": seconds * 1e3, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": workload_config(args.gpus) | {"sample_tokens_per_step": tokens},
-            "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
-                             "sample": f"{tokens} tokens per step, dequantise + FP32 matmul per expert"},
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": result["seconds_per_step"] * 1e3,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": config, "gpu_launches": 0, "cpu_baseline": result,
             "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
 
@@ -177,6 +180,30 @@ def workload_config(n_gpus: int) -> dict:
             "weights": "NVFP4 W4A4 (E2M1 + E4M3 K16 scales + FP32 global)",
             "l2": "inputs larger than L2: 450 MB of expert weights and >400 MB of intermediates are streamed every step",
             "parallelism": "single GPU" if n_gpus == 1 else f"ep{n_gpus}"}
+
+
+def one_gpu_layer_ms(gw, torch, table, expert_scales, tokens: int, zipf: bool, steps: int, warmup: int, seed: int):
+    """Device-timed ms per pass of the whole layer on one GPU (inputs resident)."""
+    device = expert_scales.device
+    ws = gw.MoeWorkspace(tokens)
+    g = torch.Generator(device=device).manual_seed(seed)
+    x = torch.randn((tokens, H), generator=g, device=device).bfloat16()
+    logits = torch.randn((tokens, E), generator=g, device=device)
+    if zipf:
+        logits = logits + zipf_bias().to(device)
+    scores = logits.bfloat16()
+    y = torch.empty((tokens, H), dtype=torch.bfloat16, device=device)
+    stream = torch.cuda.current_stream()
+    for _ in range(warmup):
+        ws.run(x, scores, expert_scales, table, y, tokens)
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    begin.record(stream)
+    for _ in range(steps):
+        ws.run(x, scores, expert_scales, table, y, tokens)
+    end.record(stream)
+    torch.cuda.synchronize()
+    return begin.elapsed_time(end) / steps
 
 
 def run_expert_parallel(args, world: int, rank: int, local_rank: int):
@@ -253,7 +280,9 @@ def run_expert_parallel(args, world: int, rank: int, local_rank: int):
     sampler = ClockSampler(local_rank) if rank == 0 else None
     time.sleep(0.25)
     t0 = time.time()
+    launches_before = gw.launch_count()
     ms = timed(step, args.steps)
+    launches = gw.launch_count() - launches_before          # this rank's kernels inside the timed region
     flops = tokens * TOPK * FLOPS_PER_ASSIGNMENT
     value = flops / (ms * 1e-3) / 1e12
 
@@ -327,9 +356,9 @@ def run_expert_parallel(args, world: int, rank: int, local_rank: int):
                         "h2d_bytes_per_step": world * (hx.numel() + hs.numel()) * 2,
                         "d2h_bytes_per_step": world * hy[0].numel() * 2, "ms_per_step": e2e_ms,
                         "note": "uploads, kernels and downloads of consecutive steps overlap (gewell_b200.HostStagedMoe)"},
-                # per rank: 3 routing, tables, dispatch, keys, group descriptors, scale re-tiling, 2 GEMMs,
-                # combine (the collectives are NCCL's)
-                "gpu_launches": 11 * args.steps * world, "clocks": clocks,
+                # counted by the library at its launch sites on rank 0 (every rank launches the same
+                # sequence; the collectives are NCCL's and not counted)
+                "gpu_launches": launches * world, "clocks": clocks,
                 "roofline": {"kernel": "gemm_tc_kernel<nvfp4> (grouped gate/up + grouped down) on the busiest rank",
                              "bound": "tensor", "achieved": achieved, "peak": fp4_peak, "unit": "TFLOP/s",
                              "frac": achieved / fp4_peak, "traffic": None,
@@ -406,19 +435,22 @@ def main():
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
     t0 = time.time()
+    launches_before = gw.launch_count()
     begin.record(stream)
     for _ in range(args.steps):
         step()
     end.record(stream)
     torch.cuda.synchronize()
+    launches = gw.launch_count() - launches_before          # counted by the library at its launch sites
     t1 = time.time()
     ms = begin.elapsed_time(end) / args.steps
     flops = tokens * TOPK * FLOPS_PER_ASSIGNMENT
     value = flops / (ms * 1e-3) / 1e12
 
-    # end to end through the public host-buffer call (gw.HostStagedMoe): every step uploads its
-    # pinned inputs and downloads the layer output inside the timed region; the runner overlaps
-    # step i+1's upload and step i-1's download with step i's kernels (three streams, ring of 3)
+    # End to end through the C ABI's host-buffer entry point (gw_moe_host_runner_*, wrapped by
+    # gw.HostStagedMoe): every step uploads its pinned inputs and downloads the layer output inside the
+    # timed region; the runner overlaps step i+1's upload and step i-1's download with step i's kernels
+    # (three streams, ring of 3 device buffers).
     hx = x.cpu().pin_memory()
     hs = scores.cpu().pin_memory()
     hy = [torch.empty((tokens, H), dtype=torch.bfloat16).pin_memory() for _ in range(3)]
@@ -435,18 +467,29 @@ def main():
     end.record(runner.download)
     runner.synchronize()
     torch.cuda.synchronize()
-    t2 = time.time()
-    clocks = sampler.stop(t0, t2)
     if gw.kernel_error() != 0:
         raise SystemExit("tensor-core kernel reported an error during the host-buffer run")
     if not torch.equal(hy[(args.steps - 1) % 3], y.cpu()):
         raise SystemExit("host-buffer run and device-buffer run disagree")
     e2e_ms = begin.elapsed_time(end) / args.steps
+    # the same call one pass at a time (submit, wait): the latency a caller sees without pipelining
+    single = gw.HostStagedMoe(ws, table, expert_scales, tokens, H, experts=E, depth=1)
+    single.submit(hx, hs, hy[0], tokens)
+    single.synchronize()
+    latencies = []
+    for _ in range(min(args.steps, 10)):
+        start = time.perf_counter()
+        single.wait_for(single.submit(hx, hs, hy[0], tokens))
+        latencies.append((time.perf_counter() - start) * 1e3)
+    t2 = time.time()
+    clocks = sampler.stop(t0, t2)
     e2e = {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
            "h2d_bytes_per_step": (runner.h2d_bytes - before_h2d) // args.steps,
            "d2h_bytes_per_step": (runner.d2h_bytes - before_d2h) // args.steps,
-           "ms_per_step": e2e_ms,
-           "note": "uploads, kernels and downloads of consecutive steps overlap (gewell_b200.HostStagedMoe)"}
+           "ms_per_step": e2e_ms, "single_pass_ms": statistics.median(latencies),
+           "note": "C-ABI host-buffer runner (gw_moe_host_runner_submit): uploads, kernels and downloads of "
+                   "consecutive steps overlap; single_pass_ms is one submit + wait at a time (host clock)"}
+    del runner, single
 
     # roofline of the dominant kernel (the two grouped tcgen05 GEMMs), timed live
     # with CUDA events recorded on the launching stream between the stages
@@ -474,16 +517,28 @@ def main():
                 "ms_per_launch": {"gate_up": stages["gate_up_gemm"], "down": stages["down_gemm"]},
                 "stage_ms": stages}
 
+    # the same layer at the expert-parallel configuration's size on this one GPU: the like-for-like
+    # denominator of the multi-GPU lines (T = 32768, Zipf(1.2) routing bias)
+    same_as_ep = None
+    if not args.tokens:
+        del ws
+        ep_tokens = workload_config(2)["tokens"]
+        ep_ms = one_gpu_layer_ms(gw, torch, table, expert_scales, ep_tokens, True, max(3, args.steps // 4), 3, seed=1000)
+        same_as_ep = {"workload": "config 5 on one GPU (T = 32768, Zipf(1.2) bias), all 128 experts local",
+                      "tokens": ep_tokens, "ms_per_step": ep_ms,
+                      "value": ep_tokens * TOPK * FLOPS_PER_ASSIGNMENT / (ep_ms * 1e-3) / 1e12, "unit": "TFLOP/s"}
+        if gw.kernel_error() != 0:
+            raise SystemExit("tensor-core kernel reported an error during the config-5 run")
+
     cpu = None
     if not args.no_cpu_baseline:
-        cpu = cpu_baseline_sample(experts, 96)
+        cpu = cpu_host_path(256, 1)
 
     line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "nvfp4 (e2m1 x e2m1, fp32 accumulate)", "data": "synthetic",
-            # launches per step: route, scan, scatter, group descriptors, gather+quantise, 2 GEMMs, combine
-            "config": config, "e2e": e2e, "gpu_launches": 8 * args.steps, "clocks": clocks,
-            "roofline": roofline, "cpu_baseline": cpu}
+            "config": config, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
+            "roofline": roofline, "cpu_baseline": cpu, "config5_on_one_gpu": same_as_ep}
     print(json.dumps(line))
 
 

@@ -2,7 +2,7 @@
 shaped NVFP4, the small NVFP4 linear) and of the MoE layer at decode size, on
 synthetic data of the published shapes.
 
-    python -m gewell_b200.bench_configs [--configs c1,c2,c3,moe64] [--iters 20]
+    python bench_configs.py [--configs c1,c2,c3,moe64] [--iters 20]
 
 Prints one JSON object per configuration.  Weights are rotated through copies
 whose total size exceeds the 126 MB L2 so that every timed pass streams its

@@ -95,12 +95,23 @@ _SIGNATURES = {
     "gw_moe_ep_tables": (c_int, [c_void_p, c_void_p, c_uint32, c_uint32, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_void_p]),
     "gw_moe_ep_run_experts": (c_int, [c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_uint32, c_void_p, c_void_p,
-                                      c_void_p, c_void_p, c_void_p, c_uint32, c_void_p]),
-    "gw_moe_ep_combine": (c_int, [c_void_p, c_uint32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+                                      c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_void_p]),
+    "gw_moe_ep_combine": (c_int, [c_void_p, c_uint32, c_void_p, c_void_p, c_void_p, c_uint32, c_void_p, c_void_p]),
+    "gw_moe_host_runner_create": (c_int, [c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, POINTER(c_void_p)]),
+    "gw_moe_host_runner_destroy": (None, [c_void_p]),
+    "gw_moe_host_runner_submit": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_uint32, POINTER(c_uint64)]),
+    "gw_moe_host_runner_wait": (c_int, [c_void_p, c_uint64]),
+    "gw_moe_host_runner_synchronize": (c_int, [c_void_p]),
+    "gw_moe_host_runner_streams": (c_int, [c_void_p, POINTER(c_void_p), POINTER(c_void_p), POINTER(c_void_p)]),
+    "gw_moe_host_runner_h2d_bytes": (c_uint64, [c_void_p]),
+    "gw_moe_host_runner_d2h_bytes": (c_uint64, [c_void_p]),
     "gw_debug_kernel_error": (c_uint32, []),
+    "gw_debug_launch_count": (c_uint64, []),
     "gw_debug_gemm_profile": (c_int, [c_void_p]),
     "gw_debug_rcp_approx": (c_int, [c_void_p, c_void_p, c_uint64, c_void_p]),
     "gw_debug_geglu_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_uint64, c_void_p]),
+    "gw_debug_moe_quantized_input": (c_int, [c_void_p, POINTER(c_void_p), POINTER(c_void_p), POINTER(c_uint32),
+                                             POINTER(c_uint32)]),
 }
 
 

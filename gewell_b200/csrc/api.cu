@@ -1,5 +1,6 @@
 // C ABI of gewell_b200: argument validation (same contract as the reference
 // classes), plan objects and the element-wise entry points.
+#include <atomic>
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
@@ -26,25 +27,45 @@ gw_status fail(gw_status code, const std::string& message) {
 }
 void clear_error() { g_last_error.clear(); }
 
+namespace {
+std::atomic<unsigned long long> g_launches{0};
+}
+void note_launch(unsigned kernels) { g_launches.fetch_add(kernels, std::memory_order_relaxed); }
+
+// Per-GPU state is keyed by the device ordinal that is current at the call, so one
+// process may drive several GPUs.
+int current_device_slot() {
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0) device = 0;
+  return device % kMaxDeviceSlots;
+}
+
 uint32_t* device_error_word() {
-  static uint32_t* word = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    if (cudaMalloc(&word, sizeof(uint32_t)) == cudaSuccess) cudaMemset(word, 0, sizeof(uint32_t));
-    else word = nullptr;
-  });
-  return word;
+  static uint32_t* words[kMaxDeviceSlots] = {};
+  static std::mutex mutex;
+  const int slot = current_device_slot();
+  std::lock_guard<std::mutex> lock(mutex);
+  if (words[slot] == nullptr) {
+    uint32_t* word = nullptr;
+    if (cudaMalloc(&word, sizeof(uint32_t)) == cudaSuccess && cudaMemset(word, 0, sizeof(uint32_t)) == cudaSuccess)
+      words[slot] = word;
+    else
+      (void)cudaGetLastError();
+  }
+  return words[slot];
 }
 
 int sm_count() {
-  static int count = 0;
-  if (count == 0) {
-    int device = 0;
+  static int counts[kMaxDeviceSlots] = {};
+  const int slot = current_device_slot();
+  if (counts[slot] == 0) {
+    int device = 0, count = 0;
     if (cudaGetDevice(&device) != cudaSuccess ||
         cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0)
       count = 148;
+    counts[slot] = count;
   }
-  return count;
+  return counts[slot];
 }
 
 namespace {
@@ -61,7 +82,7 @@ using namespace gw;
 extern "C" {
 
 const char* gw_last_error(void) { return g_last_error.c_str(); }
-int gw_abi_version(void) { return 1; }
+int gw_abi_version(void) { return 2; }
 
 size_t gw_nvfp4_scale_storage_bytes(size_t rows, size_t input_width) { return scale_storage_bytes(rows, input_width); }
 size_t gw_nvfp4_scale_offset(size_t row, size_t block, size_t input_width) { return scale_offset(row, block, input_width); }
@@ -83,8 +104,12 @@ uint32_t gw_debug_kernel_error(void) {
   if (cudaDeviceSynchronize() != cudaSuccess) return 0xFFFFFFFEu;
   cudaMemcpy(&value, word, sizeof(value), cudaMemcpyDeviceToHost);
   if (value != 0) cudaMemset(word, 0, sizeof(value));
-  return value;
+  // the allocation-free linear reports into a word of its own (it may not use the allocated one)
+  const uint32_t built_in = take_static_scratch_error();
+  return value != 0 ? value : built_in;
 }
+
+uint64_t gw_debug_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 gw_status gw_debug_gemm_profile(void* device_buffer) {
   clear_error();

@@ -11,6 +11,7 @@
 #include <string>
 
 #include "../../include/gewell_b200.h"
+#include "../../include/gewell_b200_test.h"
 
 namespace gw {
 
@@ -33,9 +34,17 @@ inline size_t align_up(size_t value, size_t alignment) {
 
 inline cudaStream_t as_stream(void* stream) { return static_cast<cudaStream_t>(stream); }
 
-// Device-global error word written by bounded waits (0 = no error).
-uint32_t* device_error_word();   // lazily allocated, per process
+// Per-GPU state (keyed by the device that is current at the call).
+constexpr int kMaxDeviceSlots = 64;
+int current_device_slot();
+// Error word written by bounded waits (0 = no error): lazily allocated, one per GPU.
+uint32_t* device_error_word();
 int sm_count();
+// Counts the kernels this library launches (read by gw_debug_launch_count); every launch site calls it.
+void note_launch(unsigned kernels = 1);
+// Error word of the allocation-free linear (static_scratch.cu) on the current GPU, cleared on read;
+// 0 when that entry point has not run on this GPU.
+uint32_t take_static_scratch_error();
 
 constexpr size_t scale_storage_bytes(size_t rows, size_t width) {
   return ((rows + 127) / 128) * ((width + 63) / 64) * 512;
@@ -79,6 +88,7 @@ inline cudaError_t launch_pdl(void (*kernel)(Params...), dim3 grid, dim3 block, 
   attribute.val.programmaticStreamSerializationAllowed = 1;
   config.attrs = &attribute;
   config.numAttrs = 1;
+  note_launch();
   return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
 }
 

@@ -108,8 +108,10 @@ __device__ __forceinline__ uint4 shfl_xor_u4(const uint4& v, int mask) {
                     __shfl_xor_sync(0xffffffffu, v.z, mask), __shfl_xor_sync(0xffffffffu, v.w, mask));
 }
 
+template <bool kProfile>   // cycle counters of the tuning aid live in an instantiation of their own
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ PairGemmParams p) {
+  constexpr bool prof = kProfile;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
@@ -156,7 +158,7 @@ gemm_pair_kernel(const __grid_constant__ PairGemmParams p) {
   constexpr uint32_t kDescHiSw128 = uint32_t(1024 >> 4) | (1u << 14) | (2u << 29);
   auto make_desc = [](uint32_t hi, uint32_t lo) { return (uint64_t(hi) << 32) | lo; };
   const uint32_t smem_base16 = ptx::smem_u32(smem) >> 4;
-  const long long prof_start = p.profile ? clock64() : 0;
+  const long long prof_start = prof ? clock64() : 0;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer (one lane)
@@ -174,13 +176,13 @@ gemm_pair_kernel(const __grid_constant__ PairGemmParams p) {
         const uint8_t* sf_tokens = p.sf_tokens + size_t(token_block) * k_atoms * 512;
         bool failed = false;
         for (int ks = 0; ks < k_stages; ++ks) {
-          const long long t0 = p.profile ? clock64() : 0;
+          const long long t0 = prof ? clock64() : 0;
           if (!ptx::mbar_wait_bounded(empty_bar + stage, phase ^ 1)) {
             report(p.error, 0x11000000u | (blockIdx.x << 8) | stage, abort_flag);
             failed = true;
             break;
           }
-          if (p.profile) prof_wait += clock64() - t0;
+          if (prof) prof_wait += clock64() - t0;
           const int nkb = min(kKBlocks, total_kb - ks * kKBlocks);
           uint8_t* base = smem + stage * kStageBytes;
           // the scales go first and complete on their own barrier: the loader warps move them into tensor
@@ -198,7 +200,7 @@ gemm_pair_kernel(const __grid_constant__ PairGemmParams p) {
         }
         if (failed) break;
       }
-      if (p.profile) p.profile[size_t(blockIdx.x) * 8 + 0] = prof_wait;
+      if (prof) p.profile[size_t(blockIdx.x) * 8 + 0] = prof_wait;
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -209,26 +211,26 @@ gemm_pair_kernel(const __grid_constant__ PairGemmParams p) {
       const uint32_t idesc = idesc_pair_nvfp4(256);
       long long prof_sf = 0, prof_issue = 0, prof_acc = 0;
       for (int w = pair; w < total_work && !*abort_flag; w += pairs) {
-        const long long ta = p.profile ? clock64() : 0;
+        const long long ta = prof ? clock64() : 0;
         if (!ptx::mbar_wait_bounded(acc_empty_bar, acc_phase ^ 1)) {
           report(p.error, 0x21000000u | (blockIdx.x << 8), abort_flag);
           break;
         }
-        if (p.profile) prof_acc += clock64() - ta;
+        if (prof) prof_acc += clock64() - ta;
         ptx::tc_fence_after_sync();
         bool failed = false;
         for (int ks = 0; ks < k_stages; ++ks) {
-          const long long t0 = p.profile ? clock64() : 0;
+          const long long t0 = prof ? clock64() : 0;
           // sf_ready implies that both CTAs' operands have landed (the loader warps arrive after their
           // CTA's operand barrier), so this is the only wait of the stage
           const bool ok = ptx::mbar_wait_bounded(sf_ready_bar + stage, phase);
-          const long long t2 = p.profile ? clock64() : 0;
+          const long long t2 = prof ? clock64() : 0;
           if (!ok) {
             report(p.error, 0x31000000u | (blockIdx.x << 8) | stage, abort_flag);
             failed = true;
             break;
           }
-          if (p.profile) prof_sf += t2 - t0;
+          if (prof) prof_sf += t2 - t0;
           ptx::tc_fence_after_sync();
           const int nkb = min(kKBlocks, total_kb - ks * kKBlocks);
           const uint32_t base16 = smem_base16 + uint32_t(stage) * uint32_t(kStageBytes >> 4);
@@ -241,19 +243,19 @@ gemm_pair_kernel(const __grid_constant__ PairGemmParams p) {
                              make_desc(kDescHiSw128, base16 + (kTokBytes >> 4) + 2 * kb), idesc, sf_tok + 4 * kb,
                              sf_wgt + 8 * kb, (ks | kb) != 0 ? 1u : 0u);
           commit_pair(empty_bar + stage);
-          if (p.profile) prof_issue += clock64() - t2;
+          if (prof) prof_issue += clock64() - t2;
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
         if (failed) break;
         commit_pair(acc_full_bar);
         acc_phase ^= 1;
       }
-      if (p.profile) {
+      if (prof) {
         long long* row = p.profile + size_t(blockIdx.x) * 8;
         row[2] = prof_sf; row[3] = prof_issue; row[4] = prof_acc;
       }
     }
-    if (p.profile && lane == 0) p.profile[size_t(blockIdx.x) * 8 + 6] = clock64() - prof_start;
+    if (prof && lane == 0) p.profile[size_t(blockIdx.x) * 8 + 6] = clock64() - prof_start;
     __syncwarp();
   } else if (warp < kFirstEpilogueWarp) {
     // ------------------------------------------------------------------ scale loaders
@@ -270,7 +272,7 @@ gemm_pair_kernel(const __grid_constant__ PairGemmParams p) {
           failed = true;
           break;
         }
-        const long long t1 = p.profile ? clock64() : 0;
+        const long long t1 = prof ? clock64() : 0;
         const uint32_t src = ptx::smem_u32(smem + stage * kStageBytes + kTokBytes + kWgtBytes) + lane * 16;
         const uint32_t slot = tmem_base + kAccCols + uint32_t(stage) * kSfSlotCols + quad_lane;
         uint32_t r[16];
@@ -295,7 +297,7 @@ gemm_pair_kernel(const __grid_constant__ PairGemmParams p) {
           ptx::tmem_store16(slot + 4 * kKBlocks + 16 * half_pair, r);
         }
         ptx::tmem_store_wait();
-        const long long t2 = p.profile ? clock64() : 0;
+        const long long t2 = prof ? clock64() : 0;
         ptx::tc_fence_before_sync();
         // the arrival also vouches for this CTA's operand tiles
         if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(full_bar + stage, phase))) {
@@ -304,12 +306,12 @@ gemm_pair_kernel(const __grid_constant__ PairGemmParams p) {
           break;
         }
         if (lane == 0) arrive_cluster(leader_sf_ready + stage * 8);
-        if (p.profile) { prof_copy += t2 - t1; prof_arrive += clock64() - t2; }
+        if (prof) { prof_copy += t2 - t1; prof_arrive += clock64() - t2; }
         if (++stage == kStages) { stage = 0; phase ^= 1; }
       }
       if (failed) break;
     }
-    if (p.profile && lane == 0 && warp == 2) {
+    if (prof && lane == 0 && warp == 2) {
       long long* row = p.profile + size_t(blockIdx.x) * 8;
       row[5] = prof_copy;
       row[7] = prof_arrive;
@@ -399,12 +401,14 @@ long long* g_pair_profile = nullptr;
 
 void set_pair_profile_buffer(long long* device_buffer) { g_pair_profile = device_buffer; }
 
-cudaError_t launch_gemm_pair(const PairGemmParams& params_in, int sm_count, cudaStream_t stream) {
-  PairGemmParams params = params_in;
-  params.profile = g_pair_profile;
-  static bool configured = false;
+namespace {
+template <bool kProfile>
+cudaError_t launch_pair_instance(const PairGemmParams& params, int sm_count, cudaStream_t stream) {
+  static bool configured_on[kMaxDeviceSlots] = {};   // the attribute is per GPU
+  bool& configured = configured_on[current_device_slot()];
   if (!configured) {
-    cudaError_t status = cudaFuncSetAttribute(gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaError_t status =
+        cudaFuncSetAttribute(gemm_pair_kernel<kProfile>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (status != cudaSuccess) return status;
     configured = true;
   }
@@ -425,7 +429,16 @@ cudaError_t launch_gemm_pair(const PairGemmParams& params_in, int sm_count, cuda
   attributes[1].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attributes;
   config.numAttrs = 2;
-  return cudaLaunchKernelEx(&config, gemm_pair_kernel, params);
+  note_launch();
+  return cudaLaunchKernelEx(&config, gemm_pair_kernel<kProfile>, params);
+}
+}  // namespace
+
+cudaError_t launch_gemm_pair(const PairGemmParams& params_in, int sm_count, cudaStream_t stream) {
+  PairGemmParams params = params_in;
+  params.profile = g_pair_profile;
+  if (params.profile != nullptr) return launch_pair_instance<true>(params, sm_count, stream);
+  return launch_pair_instance<false>(params, sm_count, stream);
 }
 
 }  // namespace gw

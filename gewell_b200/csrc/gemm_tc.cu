@@ -139,11 +139,14 @@ __device__ __forceinline__ uint4 shfl_xor_u4(const uint4& v, int mask) {
                     __shfl_xor_sync(0xffffffffu, v.z, mask), __shfl_xor_sync(0xffffffffu, v.w, mask));
 }
 
-template <bool kNvfp4, int BLOCK_N, GemmEpilogue EPI>
+// kProfile: the cycle counters of the tuning aid are compiled into an instantiation of their own,
+// so the production kernel carries none of their registers.
+template <bool kNvfp4, int BLOCK_N, GemmEpilogue EPI, bool kProfile>
 // 14 warps are allocated as 16: 128 registers per thread is the most one CTA can have.
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ GemmParams p) {
   using C = Config<kNvfp4, BLOCK_N>;
+  constexpr bool prof = kProfile;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes);
@@ -216,7 +219,7 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
   // optional cycle counters (debug aid): [cta][8] = producer wait, mma wait for data, mma issue,
   // mma wait for accumulator, epilogue wait, epilogue work, role total, items
   long long prof_wait = 0, prof_work = 0, prof_wait2 = 0;
-  const long long prof_start = p.profile ? clock64() : 0;
+  const long long prof_start = prof ? clock64() : 0;
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
     // One thread runs the whole role (no per-stage warp votes or shuffles); the other lanes
@@ -321,12 +324,12 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
         ks_begin = ks0 + ahead;
       }
       for (int ks = ks_begin; ks < ks1; ++ks) {
-        const long long t0 = p.profile ? clock64() : 0;
+        const long long t0 = prof ? clock64() : 0;
         if (!ptx::mbar_wait_bounded(empty_bar + stage, phase ^ 1)) {
           report(p.error, 0x10000000u | (blockIdx.x << 8) | stage, abort_flag);
           break;
         }
-        if (p.profile) prof_wait += clock64() - t0;
+        if (prof) prof_wait += clock64() - t0;
         if (lane == 0) issue(ks, stage, true, true);
         if (++stage == C::kStages) { stage = 0; phase ^= 1; }
       }
@@ -350,18 +353,18 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
       more = walk.next(next_tile, next_ks0, next_ks1, next_at_start);
       if (more) decode_work<BLOCK_N, EPI>(p, prefix, next_tile, next);
       (void)tile; (void)at_start;
-      const long long ta = p.profile ? clock64() : 0;
+      const long long ta = prof ? clock64() : 0;
       if (!ptx::mbar_wait_bounded(acc_empty_bar + acc, acc_phase ^ 1)) {
         report(p.error, 0x20000000u | (blockIdx.x << 8) | acc, abort_flag);
         break;
       }
-      if (p.profile) prof_wait2 += clock64() - ta;
+      if (prof) prof_wait2 += clock64() - ta;
       ptx::tc_fence_after_sync();
       const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
       const uint32_t idesc = kNvfp4 ? ptx::idesc_nvfp4(item.mma_n) : ptx::idesc_fp8(item.mma_n);
       bool failed = false;
       for (int ks = ks0; ks < ks1; ++ks) {
-        const long long t0 = p.profile ? clock64() : 0;
+        const long long t0 = prof ? clock64() : 0;
         if constexpr (kNvfp4) {
           // The stage's scales are in its TMEM slot once the four loader warps have arrived; they
           // arrive after the stage's copies have landed, so this wait covers the operands too.
@@ -377,8 +380,8 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
             break;
           }
         }
-        const long long t1 = p.profile ? clock64() : 0;
-        prof_wait += t1 - t0;
+        const long long t1 = prof ? clock64() : 0;
+        if (prof) prof_wait += t1 - t0;
         ptx::tc_fence_after_sync();
         if (lane == 0) {
           // Single in-order instruction stream: descriptors are a constant plus
@@ -402,7 +405,7 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
           }
           ptx::tc_commit(empty_bar + stage);
         }
-        if (p.profile) prof_work += clock64() - t1;
+        if (prof) prof_work += clock64() - t1;
         if (++stage == C::kStages) { stage = 0; phase ^= 1; }
       }
       if (failed) break;
@@ -510,13 +513,13 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
       more = walk.next(next_tile, next_ks0, next_ks1, next_at_start);
       if (more) decode_work<BLOCK_N, EPI>(p, prefix, next_tile, next);
       (void)tile; (void)at_start;
-      const long long te0 = p.profile ? clock64() : 0;
+      const long long te0 = prof ? clock64() : 0;
       if (!ptx::mbar_wait_warp(acc_full_bar + acc, acc_phase)) {
         report(p.error, 0x40000000u | (blockIdx.x << 8) | acc, abort_flag);
         break;
       }
-      const long long te1 = p.profile ? clock64() : 0;
-      prof_wait += te1 - te0;
+      const long long te1 = prof ? clock64() : 0;
+      if (prof) prof_wait += te1 - te0;
       ptx::tc_fence_after_sync();
       const uint32_t taddr = tmem_base + acc * BLOCK_N + (uint32_t(quad * 32) << 16);
       const int l_index = item.l_tile * kTileL + quad * 32 + lane;   // row of L inside the group
@@ -539,9 +542,11 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
               for (int i = 0; i < 16; ++i)
                 if (c0 + i < item.c_valid) {
                   bf16* token_dst = dst + size_t(c0 + i) * p.ld_out;
-                  if (p.row_dest != nullptr)     // per-row destinations: the token's row may live on another GPU
-                    token_dst = reinterpret_cast<bf16*>(p.row_dest[size_t(item.g.out_row0) + item.c_tile * BLOCK_N + c0 + i]) +
-                                item.g.out_col0 + l_index;
+                  if (p.row_dest != nullptr) {   // per-row destinations: the token's row may live on another GPU
+                    const uint64_t home = p.row_dest[size_t(item.g.out_row0) + item.c_tile * BLOCK_N + c0 + i];
+                    if (home == 0) continue;     // a row without a home (reported when the table was built)
+                    token_dst = reinterpret_cast<bf16*>(home) + item.g.out_col0 + l_index;
+                  }
                   *token_dst = __float2bfloat16_rn(__fmul_rn(__uint_as_float(r[i]), alpha));
                 }
             }
@@ -622,11 +627,11 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
         uint4 unit[kEarlyRelease ? kChunks : 1][4];                  // unit q of a chunk = channels c0 + 8q .. + 7
         auto drain = [&](int c0, uint4* out_units) {
           uint32_t r[32];
-          const long long td0 = p.profile ? clock64() : 0;
+          const long long td0 = prof ? clock64() : 0;
           ptx::tmem_load16(taddr + c0, r);
           ptx::tmem_load16(taddr + c0 + 16, r + 16);
           ptx::tmem_load_wait();
-          if (p.profile) prof_wait2 += clock64() - td0;
+          if (prof) prof_wait2 += clock64() - td0;
           float v[32];
           if (item.g.channel_alpha != nullptr) {
 #pragma unroll
@@ -660,6 +665,7 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             if (i >= rows_left) continue;
+            if (p.row_dest != nullptr && group_dest[i] == 0) continue;   // a row without a home (reported earlier)
             bf16* row_dst = p.row_dest == nullptr
                                 ? dst + size_t(i) * p.ld_out + c0
                                 : reinterpret_cast<bf16*>(group_dest[i]) + item.g.out_col0 + c_base + 8 * (lane & 3) + c0;
@@ -788,11 +794,11 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(acc_empty_bar + acc);
       }
-      if (p.profile) prof_work += clock64() - te1;
+      if (prof) prof_work += clock64() - te1;
       if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1; }
     }
   }
-  if (p.profile && lane == 0 && (warp <= 1 || warp == kFirstEpilogueWarp)) {
+  if (prof && lane == 0 && (warp <= 1 || warp == kFirstEpilogueWarp)) {
     long long* row = p.profile + size_t(blockIdx.x) * 8;
     const long long total = clock64() - prof_start;
     if (warp == 0) { row[0] = prof_wait; }
@@ -811,16 +817,13 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
 long long* g_profile_buffer = nullptr;
 unsigned g_profile_launches = 0;
 
-template <bool kNvfp4, int BLOCK_N, GemmEpilogue EPI>
-cudaError_t launch(const GemmParams& params_in, int grid, cudaStream_t stream) {
-  GemmParams params = params_in;
-  // debug aid: consecutive launches alternate between the two halves of the buffer, so the
-  // two grouped GEMMs of one MoE pass can be told apart
-  params.profile = g_profile_buffer ? g_profile_buffer + size_t(g_profile_launches++ % 2) * 148 * 8 : nullptr;
+template <bool kNvfp4, int BLOCK_N, GemmEpilogue EPI, bool kProfile>
+cudaError_t launch_instance(const GemmParams& params, int grid, cudaStream_t stream) {
   using C = Config<kNvfp4, BLOCK_N>;
-  static bool configured = false;
+  static bool configured_on[kMaxDeviceSlots] = {};   // the attribute is per GPU
+  bool& configured = configured_on[current_device_slot()];
   if (!configured) {
-    cudaError_t status = cudaFuncSetAttribute(gemm_tc_kernel<kNvfp4, BLOCK_N, EPI>,
+    cudaError_t status = cudaFuncSetAttribute(gemm_tc_kernel<kNvfp4, BLOCK_N, EPI, kProfile>,
                                               cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
     if (status != cudaSuccess) return status;
     configured = true;
@@ -835,7 +838,18 @@ cudaError_t launch(const GemmParams& params_in, int grid, cudaStream_t stream) {
   attribute.val.programmaticStreamSerializationAllowed = 1;
   config.attrs = &attribute;
   config.numAttrs = 1;
-  return cudaLaunchKernelEx(&config, gemm_tc_kernel<kNvfp4, BLOCK_N, EPI>, params);
+  note_launch();
+  return cudaLaunchKernelEx(&config, gemm_tc_kernel<kNvfp4, BLOCK_N, EPI, kProfile>, params);
+}
+
+template <bool kNvfp4, int BLOCK_N, GemmEpilogue EPI>
+cudaError_t launch(const GemmParams& params_in, int grid, cudaStream_t stream) {
+  GemmParams params = params_in;
+  // debug aid: consecutive launches alternate between the two halves of the buffer, so the
+  // two grouped GEMMs of one MoE pass can be told apart
+  params.profile = g_profile_buffer ? g_profile_buffer + size_t(g_profile_launches++ % 2) * 148 * 8 : nullptr;
+  if (params.profile != nullptr) return launch_instance<kNvfp4, BLOCK_N, EPI, true>(params, grid, stream);
+  return launch_instance<kNvfp4, BLOCK_N, EPI, false>(params, grid, stream);
 }
 
 }  // namespace

@@ -85,6 +85,7 @@ cudaError_t launch_gemv_w4a16(const void* input, uint32_t rows, const uint8_t* d
   }
 #undef GW_GEMV_CASE
   (void)kMaxRows;
+  note_launch();
   return cudaGetLastError();
 }
 
@@ -175,7 +176,8 @@ cudaError_t launch_gemv_fp8_rows(const void* input, const uint8_t* weights, floa
                                  const float* channel_alpha, uint32_t width, uint32_t out_width, void* output,
                                  int blocks, cudaStream_t stream) {
   const size_t smem = size_t(ROWS) * width * sizeof(__half);
-  static bool configured = false;
+  static bool configured_on[kMaxDeviceSlots] = {};   // the attribute is per GPU
+  bool& configured = configured_on[current_device_slot()];
   if (!configured && smem > 48 * 1024) {
     cudaError_t status = cudaFuncSetAttribute(gemv_fp8_kernel<ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
     if (status != cudaSuccess) return status;
@@ -184,6 +186,7 @@ cudaError_t launch_gemv_fp8_rows(const void* input, const uint8_t* weights, floa
   gemv_fp8_kernel<ROWS><<<blocks, kGemvFp8Warps * 32, smem, stream>>>(
       static_cast<const bf16*>(input), weights, inverse_input_scale, alpha, channel_alpha, width, out_width,
       static_cast<bf16*>(output));
+  note_launch();
   return cudaGetLastError();
 }
 

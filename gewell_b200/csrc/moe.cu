@@ -220,7 +220,7 @@ gw_status run_experts(gw_moe_workspace* w, const void* input, const int32_t* gat
   }
   const int parts = table->shared_gate_up ? 1 : 2;
   MoeGroupPlan plan{offsets, info, w->scales_in.as<uint8_t>(), w->scales_act.as<uint8_t>(), n, w->scale_rows, form,
-                    block_n_first, block_n_down, table->shared_gate_up ? 1 : 0};
+                    block_n_first, block_n_down, table->shared_gate_up ? 1 : 0, device_error_word()};
   w->mark(1, s);
   GW_CUDA_CHECK(launch_moe_prepare_groups(plan, first_groups, down_groups, s), "MoE group descriptors");
   if (records != nullptr) {
@@ -466,7 +466,8 @@ gw_status gw_moe_ep_dispatch(gw_moe_workspace* w, const void* input_bf16, uint32
 gw_status gw_moe_ep_run_experts(gw_moe_workspace* w, const void* records, const int32_t* offsets, uint32_t first_expert,
                                 uint32_t expert_count, uint32_t total_rows, const gw_expert_table* table,
                                 void* down_bf16, const int32_t* segment_start, const int32_t* home_base,
-                                void* const* peer_returned, uint32_t world, void* stream) {
+                                void* const* peer_returned, uint32_t home_capacity_rows, uint32_t world,
+                                void* stream) {
   clear_error();
   if (!w || !table) return fail(GW_INVALID_ARGUMENT, "expert run requires a workspace and an expert table");
   if (!table->shared_gate_up)
@@ -486,7 +487,8 @@ gw_status gw_moe_ep_run_experts(gw_moe_workspace* w, const void* records, const 
                 "MoE keys from offsets");
   if (push)
     GW_CUDA_CHECK(launch_ep_row_home(w->sorted_keys, w->local_offsets, segment_start, home_base, peer_returned,
-                                     first_expert, expert_count, world, total_rows, w->row_home.as<uint64_t>(), s),
+                                     first_expert, expert_count, world, total_rows, home_capacity_rows,
+                                     device_error_word(), w->row_home.as<uint64_t>(), s),
                   "addresses of the rows' homes");
   const gw_status status = run_experts(w, nullptr, nullptr, 1, w->local_offsets, total_rows, table,
                                        push ? w->down.data : down_bf16, s, records,
@@ -496,7 +498,7 @@ gw_status gw_moe_ep_run_experts(gw_moe_workspace* w, const void* records, const 
 }
 
 gw_status gw_moe_ep_combine(gw_moe_workspace* w, uint32_t rows, const int32_t* dest_rank, const int32_t* dest_row0,
-                            void* const* peer_down, void* output_bf16, void* stream) {
+                            void* const* peer_down, uint32_t capacity_rows, void* output_bf16, void* stream) {
   clear_error();
   if (!w) return fail(GW_INVALID_ARGUMENT, "expert-parallel combine requires the workspace that routed the rows");
   if (rows > w->max_rows) return fail(GW_INVALID_ARGUMENT, "MoE rows exceed workspace");
@@ -504,8 +506,20 @@ gw_status gw_moe_ep_combine(gw_moe_workspace* w, uint32_t rows, const int32_t* d
   if (!dest_rank || !dest_row0 || !peer_down || !output_bf16 || reinterpret_cast<uintptr_t>(output_bf16) % 16)
     return fail(GW_INVALID_ARGUMENT, "expert-parallel combine requires the destination tables and a 16-byte aligned output");
   GW_CUDA_CHECK(launch_ep_combine(w->keys, w->inverse, w->weights, w->offsets, dest_rank, dest_row0, peer_down, rows,
-                                  output_bf16, as_stream(stream)),
+                                  capacity_rows, device_error_word(), output_bf16, as_stream(stream)),
                 "expert-parallel combine");
+  return GW_OK;
+}
+
+gw_status gw_debug_moe_quantized_input(const gw_moe_workspace* w, const uint8_t** packed, const uint8_t** scales,
+                                       uint32_t* scale_rows, uint32_t* part_rows) {
+  clear_error();
+  if (!w || !packed || !scales || !scale_rows || !part_rows)
+    return fail(GW_INVALID_ARGUMENT, "quantised-input accessor requires a workspace and four result slots");
+  *packed = w->packed_in.as<uint8_t>();
+  *scales = w->scales_in.as<uint8_t>();
+  *scale_rows = w->scale_rows;
+  *part_rows = w->n;
   return GW_OK;
 }
 

@@ -32,8 +32,8 @@ __device__ __forceinline__ void unpack8(const uint4& raw, float* out) {
 // ---------------------------------------------------------------------------
 // 1. route: FP32 softmax over 128 BF16 logits, eight winners (lower id wins
 //    ties), renormalise, times the per-expert scale, sort the eight by id.
-//    Arithmetic and reduction order follow the reference's select kernel
-//    (models/gemma4/26b_a4b/sm120/moe.cu:104-157) so ids and FP32 weights match
+//    The FP32 operation order is that of the reference's select kernel
+//    (models/gemma4/26b_a4b/sm120/moe.cu:104-157), so ids and FP32 weights match
 //    it bit for bit.  One warp per token, eight tokens per warp.
 // ---------------------------------------------------------------------------
 //    With at most 64 tokens there is one block: it then also does the work of kernels 2
@@ -56,46 +56,61 @@ moe_route_kernel(const bf16* __restrict__ scores, const bf16* __restrict__ exper
     const uint32_t local = warp * tokens_per_warp + t;
     const uint32_t row = chunk * kChunkTokens + local;
     if (row >= rows) break;
-    float elements[4], maximum = -INFINITY;
+    // Softmax over the token's 128 logits; this lane owns experts lane, lane + 32, lane + 64, lane + 96.
+    // The FP32 additions keep the order the reference's weights depend on: the lane's four terms in
+    // ascending expert order first, then the xor butterfly 16, 8, 4, 2, 1 over the lanes.
+    const bf16* token_scores = scores + size_t(row) * kExperts;
+    float prob[4];
+    float peak = -INFINITY;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      elements[i] = __bfloat162float(scores[size_t(row) * kExperts + lane + i * 32]);
-      maximum = fmaxf(maximum, elements[i]);
+    for (int q = 0; q < 4; ++q) {
+      prob[q] = __bfloat162float(token_scores[lane + 32 * q]);
+      peak = fmaxf(peak, prob[q]);
     }
-    for (int offset = 16; offset; offset /= 2)
-      maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, offset));
-    float total = 0;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) { elements[i] = expf(elements[i] - maximum); total += elements[i]; }
-    for (int offset = 16; offset; offset /= 2) total += __shfl_xor_sync(0xffffffffu, total, offset);
+    for (int step = 16; step > 0; step >>= 1) peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, step));
+    float denominator = 0.0F;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) elements[i] = __fdiv_rn(elements[i], total);
+    for (int q = 0; q < 4; ++q) {
+      prob[q] = expf(prob[q] - peak);
+      denominator += prob[q];
+    }
+#pragma unroll
+    for (int step = 16; step > 0; step >>= 1) denominator += __shfl_xor_sync(0xffffffffu, denominator, step);
+    // Eight winners, one 64-bit maximum per round: the probability's bit pattern (probabilities are
+    // not negative, so their patterns order like unsigned integers) in the high word and 128 - id
+    // in the low word, so that the larger probability wins and, among equal ones, the smaller id.
+    // A candidate that has won is replaced by key 0, below every live key.
+    unsigned long long candidate[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      prob[q] = __fdiv_rn(prob[q], denominator);
+      candidate[q] = (static_cast<unsigned long long>(__float_as_uint(prob[q])) << 32) | uint32_t(kExperts - (lane + 32 * q));
+    }
     int ids[kTopK];
     float chosen[kTopK];
-    unsigned used = 0;
 #pragma unroll
-    for (int i = 0; i < kTopK; ++i) {
-      int best = kExperts;
-      float probability = -INFINITY;
+    for (int round = 0; round < kTopK; ++round) {
+      unsigned long long winner = candidate[0];
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
-        if (!(used & (1u << j)) && (best == kExperts || elements[j] > probability)) {
-          best = lane + j * 32;
-          probability = elements[j];
-        }
-      for (int offset = 16; offset; offset /= 2) {
-        const float other = __shfl_xor_sync(0xffffffffu, probability, offset);
-        const int expert = __shfl_xor_sync(0xffffffffu, best, offset);
-        if (other > probability || (other == probability && expert < best)) { best = expert; probability = other; }
+      for (int q = 1; q < 4; ++q) winner = candidate[q] > winner ? candidate[q] : winner;
+#pragma unroll
+      for (int step = 16; step > 0; step >>= 1) {
+        const unsigned long long theirs = __shfl_xor_sync(0xffffffffu, winner, step);
+        winner = theirs > winner ? theirs : winner;
       }
-      ids[i] = best;
-      chosen[i] = probability;
-      if (unsigned(best) % 32 == lane) used |= 1u << (unsigned(best) / 32);
+      const int id = kExperts - int(uint32_t(winner));
+      ids[round] = id;
+      chosen[round] = __uint_as_float(uint32_t(winner >> 32));
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        if (id == int(lane) + 32 * q) candidate[q] = 0;
     }
-    // ((p0+p4)+(p2+p6)) + ((p1+p5)+(p3+p7)), as the reference's stride-4/2/1 fold
-    const float s0 = chosen[0] + chosen[4], s1 = chosen[1] + chosen[5];
-    const float s2 = chosen[2] + chosen[6], s3 = chosen[3] + chosen[7];
-    const float sum = (s0 + s2) + (s1 + s3);
+    // renormalisation: ((p0+p4)+(p2+p6)) + ((p1+p5)+(p3+p7)), the pairwise order of a stride-4/2/1 fold
+    float fold[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) fold[q] = chosen[q] + chosen[q + 4];
+    const float sum = (fold[0] + fold[2]) + (fold[1] + fold[3]);
     int my_id = 0;
     float my_p = 0;
 #pragma unroll
@@ -249,7 +264,17 @@ moe_prepare_groups_kernel(MoeGroupPlan plan, GemmGroup* __restrict__ first_group
   __shared__ int32_t items_first[2 * kExperts], items_down[kExperts];
   const unsigned g = threadIdx.x;            // 0..255: expert = g/2, part = g%2
   const unsigned e = g / 2, part = g % 2;
-  const int32_t first = plan.offsets[e], count = plan.offsets[e + 1] - first;
+  // Offsets that come from other ranks' histograms (expert parallelism) may describe more rows than
+  // the buffers hold: clamp every group to the capacity and report, so that no tile is scheduled
+  // over rows that do not exist.
+  int32_t first = plan.offsets[e], last = plan.offsets[e + 1];
+  const int32_t capacity = int32_t(plan.n);
+  if (first < 0 || last < first || last > capacity) {
+    if (plan.error != nullptr && part == 0) atomicCAS(plan.error, 0u, 0x70000100u | e);
+    first = min(max(first, 0), capacity);
+    last = min(max(last, first), capacity);
+  }
+  const int32_t count = last - first;
   const int32_t token_tiles_swap = (count + plan.block_n_first - 1) / plan.block_n_first;
   const int32_t token_tiles_direct = (count + 127) / 128;
   const int32_t padded_first = (first / 128 + int32_t(e)) * 128;
@@ -684,7 +709,8 @@ __global__ void __launch_bounds__(256)
 ep_row_home_kernel(const int32_t* __restrict__ sorted_keys, const int32_t* __restrict__ offsets,
                    const int32_t* __restrict__ segment_start, const int32_t* __restrict__ home_base,
                    uint8_t* const* __restrict__ peer_returned, uint32_t first_expert, uint32_t per_rank,
-                   uint32_t world, uint32_t n, uint64_t* __restrict__ row_home) {
+                   uint32_t world, uint32_t n, uint32_t home_capacity_rows, uint32_t* __restrict__ error,
+                   uint64_t* __restrict__ row_home) {
   griddep_launch();
   griddep_wait();     // results of earlier kernels in the stream are read from here on
   const uint32_t row = blockIdx.x * 256 + threadIdx.x;
@@ -694,6 +720,11 @@ ep_row_home_kernel(const int32_t* __restrict__ sorted_keys, const int32_t* __res
   for (uint32_t s = 1; s < world; ++s)
     if (uint32_t(segment_start[s * per_rank + slot]) <= row) source = s;     // starts are non-decreasing in s
   const uint32_t home_row = uint32_t(home_base[source * per_rank + slot]) + row - uint32_t(segment_start[source * per_rank + slot]);
+  if (home_row >= home_capacity_rows) {      // inconsistent tables: park the row in this rank's own buffer, report
+    if (error != nullptr) atomicCAS(error, 0u, 0x70000300u | slot);
+    row_home[row] = 0;
+    return;
+  }
   row_home[row] = reinterpret_cast<uint64_t>(peer_returned[source]) + uint64_t(home_row) * (kHidden * 2);
 }
 
@@ -721,7 +752,8 @@ __global__ void __launch_bounds__(128, 8)
 ep_combine_kernel(const int32_t* __restrict__ keys, const int32_t* __restrict__ inverse,
                   const float* __restrict__ weights, const int32_t* __restrict__ offsets,
                   const int32_t* __restrict__ dest_rank, const int32_t* __restrict__ dest_row0,
-                  const uint4* const* __restrict__ peer_down, uint32_t rows, uint4* __restrict__ output) {
+                  const uint4* const* __restrict__ peer_down, uint32_t rows, uint32_t capacity_rows,
+                  uint32_t* __restrict__ error, uint4* __restrict__ output) {
   griddep_launch();
   griddep_wait();     // results of earlier kernels in the stream are read from here on
   constexpr uint32_t kVectors = kHidden / 8;
@@ -735,7 +767,12 @@ ep_combine_kernel(const int32_t* __restrict__ keys, const int32_t* __restrict__ 
     const uint32_t assignment = row * kTopK + j;
     const int32_t e = keys[assignment];
     const size_t remote_row = size_t(dest_row0[e] + inverse[assignment] - offsets[e]);
-    raw[j] = peer_down[dest_rank[e]][remote_row * kVectors + v];
+    if (remote_row >= capacity_rows) {       // outside the owner's buffer: never read there, report
+      if (error != nullptr && v == 0) atomicCAS(error, 0u, 0x70000200u | uint32_t(e));
+      raw[j] = make_uint4(0, 0, 0, 0);
+    } else {
+      raw[j] = peer_down[dest_rank[e]][remote_row * kVectors + v];
+    }
     w[j] = weights[assignment];
   }
   float sum[8];
@@ -864,10 +901,11 @@ cudaError_t launch_ep_tables(const int32_t* counts, const int32_t* physical, uin
 
 cudaError_t launch_ep_row_home(const int32_t* sorted_keys, const int32_t* offsets, const int32_t* segment_start,
                                const int32_t* home_base, void* const* peer_returned, uint32_t first_expert,
-                               uint32_t per_rank, uint32_t world, uint32_t n, uint64_t* row_home, cudaStream_t stream) {
+                               uint32_t per_rank, uint32_t world, uint32_t n, uint32_t home_capacity_rows,
+                               uint32_t* error, uint64_t* row_home, cudaStream_t stream) {
   launch_pdl(ep_row_home_kernel, blocks_for(n), 256, stream, sorted_keys, offsets, segment_start, home_base,
                                                         reinterpret_cast<uint8_t* const*>(peer_returned), first_expert,
-                                                        per_rank, world, n, row_home);
+                                                        per_rank, world, n, home_capacity_rows, error, row_home);
   return cudaGetLastError();
 }
 
@@ -880,10 +918,11 @@ cudaError_t launch_ep_retile_scales(const void* records, const int32_t* sorted_k
 
 cudaError_t launch_ep_combine(const int32_t* keys, const int32_t* inverse, const float* weights,
                               const int32_t* offsets, const int32_t* dest_rank, const int32_t* dest_row0,
-                              void* const* peer_down, uint32_t rows, void* output, cudaStream_t stream) {
+                              void* const* peer_down, uint32_t rows, uint32_t capacity_rows, uint32_t* error,
+                              void* output, cudaStream_t stream) {
   launch_pdl(ep_combine_kernel, unsigned((size_t(rows) * (kHidden / 8) + 127) / 128), 128, stream, 
       keys, inverse, weights, offsets, dest_rank, dest_row0, reinterpret_cast<const uint4* const*>(peer_down), rows,
-      static_cast<uint4*>(output));
+      capacity_rows, error, static_cast<uint4*>(output));
   return cudaGetLastError();
 }
 

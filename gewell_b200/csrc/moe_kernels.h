@@ -32,6 +32,7 @@ struct MoeGroupPlan {
   int block_n_first;               // column tile of the gate/up GEMM
   int block_n_down;                // column tile of the down GEMM
   int shared_gate_up;              // gate and up read one quantised copy of the input
+  uint32_t* error;                 // device error word: offsets beyond n are clamped and reported here
 };
 
 uint32_t moe_chunks(uint32_t rows);
@@ -76,11 +77,13 @@ cudaError_t launch_ep_tables(const int32_t* counts, const int32_t* physical, uin
                              cudaStream_t stream);
 cudaError_t launch_ep_row_home(const int32_t* sorted_keys, const int32_t* offsets, const int32_t* segment_start,
                                const int32_t* home_base, void* const* peer_returned, uint32_t first_expert,
-                               uint32_t per_rank, uint32_t world, uint32_t n, uint64_t* row_home, cudaStream_t stream);
+                               uint32_t per_rank, uint32_t world, uint32_t n, uint32_t home_capacity_rows,
+                               uint32_t* error, uint64_t* row_home, cudaStream_t stream);
 cudaError_t launch_ep_retile_scales(const void* records, const int32_t* sorted_keys, const int32_t* offsets,
                                     uint32_t n, uint8_t* scales, cudaStream_t stream);
 cudaError_t launch_ep_combine(const int32_t* keys, const int32_t* inverse, const float* weights,
                               const int32_t* offsets, const int32_t* dest_rank, const int32_t* dest_row0,
-                              void* const* peer_down, uint32_t rows, void* output, cudaStream_t stream);
+                              void* const* peer_down, uint32_t rows, uint32_t capacity_rows, uint32_t* error,
+                              void* output, cudaStream_t stream);
 
 }  // namespace gw

@@ -302,6 +302,7 @@ cudaError_t launch_nvfp4_dequantize(const uint8_t* data, const uint8_t* scales, 
   const size_t blocks = size_t(rows) * (width / 16);
   nvfp4_dequantize_kernel<<<grid_for(blocks, ~0u), kThreads, 0, stream>>>(
       data, scales, weight_scale, width, blocks, static_cast<uint4*>(output));
+  note_launch();
   return cudaGetLastError();
 }
 
@@ -313,6 +314,7 @@ cudaError_t launch_nvfp4_pack_weights(const void* weights, uint32_t rows, uint32
   nvfp4_pack_weights_kernel<<<grid_for(padded, ~0u), kThreads, 0, stream>>>(
       static_cast<const uint4*>(weights), rows, width, weight_scale, reinterpret_cast<uint2*>(data),
       scales, padded, padded_bpr);
+  note_launch();
   return cudaGetLastError();
 }
 
@@ -329,6 +331,7 @@ cudaError_t launch_nvfp4_quantize(const void* input, uint32_t rows, uint32_t wid
   else
     nvfp4_quantize_kernel<false><<<grid_for(padded, ~0u), kThreads, 0, stream>>>(
         in, rows, width, inverse_global_scale, out, scales, padded, padded_bpr);
+  note_launch();
   return cudaGetLastError();
 }
 
@@ -343,6 +346,7 @@ cudaError_t launch_fp8_quantize(const void* input, uint32_t rows, uint32_t width
   else if (gelu) fp8_quantize_kernel<true, false><<<grid, kThreads, 0, stream>>>(in, groups, width, inverse_scale, out);
   else if (vector) fp8_quantize_kernel<false, true><<<grid, kThreads, 0, stream>>>(in, groups, width, inverse_scale, out);
   else fp8_quantize_kernel<false, false><<<grid, kThreads, 0, stream>>>(in, groups, width, inverse_scale, out);
+  note_launch();
   return cudaGetLastError();
 }
 
@@ -351,17 +355,20 @@ cudaError_t launch_fp8_pack_weights(const void* weights, uint32_t rows, uint32_t
   const size_t groups = size_t(rows) * (width / 8);
   fp8_pack_weights_kernel<<<grid_for(groups, 148 * 32), kThreads, 0, stream>>>(
       static_cast<const uint4*>(weights), groups, width, scale, row_scales, reinterpret_cast<uint2*>(data));
+  note_launch();
   return cudaGetLastError();
 }
 
 cudaError_t launch_rcp_approx(const float* in, float* out, size_t n, cudaStream_t stream) {
   rcp_approx_kernel<<<grid_for(n, ~0u), kThreads, 0, stream>>>(in, out, n);
+  note_launch();
   return cudaGetLastError();
 }
 
 cudaError_t launch_geglu(const void* gate, const void* up, void* out, size_t n, cudaStream_t stream) {
   geglu_kernel<<<grid_for(n, ~0u), kThreads, 0, stream>>>(static_cast<const bf16*>(gate), static_cast<const bf16*>(up),
                                                           static_cast<bf16*>(out), n);
+  note_launch();
   return cudaGetLastError();
 }
 
@@ -370,17 +377,20 @@ cudaError_t launch_absmax(const void* values, uint64_t elements, uint32_t* state
   if (status != cudaSuccess) return status;
   absmax_kernel<<<grid_for(elements, 148 * 16), kThreads, 0, stream>>>(
       static_cast<const bf16*>(values), elements, state);
+  note_launch();
   return cudaGetLastError();
 }
 
 cudaError_t launch_fp8_qdq(void* values, uint64_t elements, float scale, cudaStream_t stream) {
   fp8_qdq_kernel<<<grid_for(elements, 148 * 16), kThreads, 0, stream>>>(static_cast<bf16*>(values), elements, scale);
+  note_launch();
   return cudaGetLastError();
 }
 
 cudaError_t launch_nvfp4_qdq(void* values, uint64_t elements, float global_scale, cudaStream_t stream) {
   nvfp4_qdq_kernel<<<grid_for(elements / 16, 148 * 16), kThreads, 0, stream>>>(
       static_cast<uint4*>(values), elements / 16, global_scale);
+  note_launch();
   return cudaGetLastError();
 }
 

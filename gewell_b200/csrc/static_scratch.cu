@@ -74,6 +74,24 @@ bool aligned(const void* p, size_t a) { return reinterpret_cast<uintptr_t>(p) % 
 
 }  // namespace
 
+// The kernels launched from here record bounded-wait failures in g_static_error_word (they must not
+// touch allocated memory).  gw_debug_kernel_error() collects it through this function; the caller has
+// synchronised the device.
+uint32_t gw::take_static_scratch_error() {
+  int device = -1;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return 0;
+  uint32_t* word = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_slots_mutex);
+    if (!g_slots[device].ready) return 0;      // the entry point never ran on this GPU
+    word = g_slots[device].error;
+  }
+  uint32_t value = 0;
+  if (cudaMemcpy(&value, word, sizeof(value), cudaMemcpyDeviceToHost) != cudaSuccess) return 0xFFFFFFFDu;
+  if (value != 0) cudaMemset(word, 0, sizeof(value));
+  return value;
+}
+
 extern "C" {
 
 size_t gw_nvfp4_linear_static_scratch_limit(void) { return kStaticScratchBytes; }

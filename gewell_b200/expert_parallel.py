@@ -415,7 +415,8 @@ class PeerMemoryExpertParallelMoe:
                                         None if home else self.down.local,
                                         self.segment_start.data_ptr() if home else None,
                                         self.home_base.data_ptr() if home else None,
-                                        self.returned.pointer_table.data_ptr() if home else None, self.world, stream))
+                                        self.returned.pointer_table.data_ptr() if home else None,
+                                        TOPK * self.local_tokens, self.world, stream))
         self._mark("experts")
         if barrier:
             self.results_barrier()
@@ -438,7 +439,7 @@ class PeerMemoryExpertParallelMoe:
                                      out.data_ptr(), stream))
         else:
             check(lib.gw_moe_ep_combine(self.route_ws._ws, rows, self.dest_rank.data_ptr(), self.dest_row0.data_ptr(),
-                                        self.down.pointer_table.data_ptr(), out.data_ptr(), stream))
+                                        self.down.pointer_table.data_ptr(), self.capacity, out.data_ptr(), stream))
         self._mark("combine")
         return out
 

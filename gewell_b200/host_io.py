@@ -6,7 +6,11 @@ of the token rows and router logits and a device->host copy of the layer output
 for every pass.  Issued on one stream those three steps run one after another;
 `HostStagedMoe` gives each its own stream and a ring of device buffers, so pass
 i+1's upload and pass i-1's download overlap pass i's kernels (PCIe is full
-duplex, and the copies use the copy engines, not the SMs).
+duplex, and the copies use the copy engines, not the SMs).  For the single-GPU
+layer this class is a thin wrapper over the library's own runner
+(gw_moe_host_runner_*, csrc/host_staged.cu); with a custom `run` callable (the
+expert-parallel layers, which are driven from Python) the same staging is done
+here with torch streams.
 
     runner = HostStagedMoe(workspace, table, expert_scales, max_rows, hidden)
     for batch in batches:
@@ -24,9 +28,11 @@ must not be used by other calls while passes are in flight.
 """
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
-from .ops import ExpertTable, MoeWorkspace
+from .ops import ExpertTable, MoeWorkspace, _check, _library
 
 
 class HostStagedMoe:
@@ -44,6 +50,20 @@ class HostStagedMoe:
         self._run = run
         device = device if device is not None else expert_scales.device
         self.device = device
+        self._native = None
+        self._submitted = 0
+        if run is None:
+            if hidden != 2816 or experts != 128:
+                raise ValueError("the library's runner is built for hidden 2816 and 128 experts")
+            self._lib = _library()
+            self._native = ctypes.c_void_p()
+            _check(self._lib.gw_moe_host_runner_create(workspace._ws, table.handle, expert_scales.data_ptr(), max_rows,
+                                                       depth, ctypes.byref(self._native)))
+            streams = [ctypes.c_void_p() for _ in range(3)]
+            _check(self._lib.gw_moe_host_runner_streams(self._native, *(ctypes.byref(s) for s in streams)))
+            self.upload, self.compute, self.download = (torch.cuda.ExternalStream(s.value, device=device)
+                                                        for s in streams)
+            return
         self.upload, self.compute, self.download = (torch.cuda.Stream(device=device) for _ in range(3))
         self._x = [torch.empty((max_rows, hidden), dtype=torch.bfloat16, device=device) for _ in range(depth)]
         self._scores = [torch.empty((max_rows, experts), dtype=torch.bfloat16, device=device) for _ in range(depth)]
@@ -51,9 +71,16 @@ class HostStagedMoe:
         # per slot: the pass that last used it has finished computing / downloading
         self._computed = [None] * depth
         self._downloaded = [None] * depth
-        self._submitted = 0
-        self.h2d_bytes = 0
-        self.d2h_bytes = 0
+        self._h2d = 0
+        self._d2h = 0
+
+    @property
+    def h2d_bytes(self) -> int:
+        return int(self._lib.gw_moe_host_runner_h2d_bytes(self._native)) if self._native else self._h2d
+
+    @property
+    def d2h_bytes(self) -> int:
+        return int(self._lib.gw_moe_host_runner_d2h_bytes(self._native)) if self._native else self._d2h
 
     def submit(self, host_x: torch.Tensor, host_scores: torch.Tensor, host_y: torch.Tensor, rows: int) -> int:
         """Queue one layer pass: host_x [rows, hidden] and host_scores [rows, experts] (BF16, pinned) are
@@ -68,6 +95,12 @@ class HostStagedMoe:
             if t.dtype != torch.bfloat16 or t.dim() != 2 or t.shape[1] != width or t.shape[0] < rows \
                     or not t.is_contiguous():
                 raise ValueError(f"{name} must be contiguous BF16 [>= rows, {width}]")
+        if self._native:
+            ticket = ctypes.c_uint64()
+            _check(self._lib.gw_moe_host_runner_submit(self._native, host_x.data_ptr(), host_scores.data_ptr(),
+                                                       host_y.data_ptr(), rows, ctypes.byref(ticket)))
+            self._submitted = ticket.value + 1
+            return int(ticket.value)
         ticket = self._submitted
         slot = ticket % self.depth
         x, scores, y = self._x[slot], self._scores[slot], self._y[slot]
@@ -95,8 +128,8 @@ class HostStagedMoe:
                 downloaded = torch.cuda.Event()
                 downloaded.record(self.download)
             self._computed[slot], self._downloaded[slot] = computed, downloaded
-            self.h2d_bytes += rows * (self.hidden + self.experts) * 2
-            self.d2h_bytes += rows * self.hidden * 2
+            self._h2d += rows * (self.hidden + self.experts) * 2
+            self._d2h += rows * self.hidden * 2
         self._submitted += 1
         return ticket
 
@@ -104,6 +137,9 @@ class HostStagedMoe:
         """Block the host until pass `ticket`'s output is in its host buffer."""
         if ticket < 0 or ticket >= self._submitted:
             raise ValueError("no such pass")
+        if self._native:
+            _check(self._lib.gw_moe_host_runner_wait(self._native, ticket))
+            return
         # the download stream runs in order: the newest download queued on the pass's slot is not
         # earlier than the pass's own
         event = self._downloaded[ticket % self.depth]
@@ -111,5 +147,13 @@ class HostStagedMoe:
             event.synchronize()
 
     def synchronize(self) -> None:
+        if self._native:
+            _check(self._lib.gw_moe_host_runner_synchronize(self._native))
+            return
         for stream in (self.upload, self.compute, self.download):
             stream.synchronize()
+
+    def __del__(self):
+        if getattr(self, "_native", None):
+            self._lib.gw_moe_host_runner_destroy(self._native)
+            self._native = None

@@ -47,6 +47,11 @@ def kernel_error() -> int:
     return int(_library().gw_debug_kernel_error())
 
 
+def launch_count() -> int:
+    """Kernels the CUDA library has launched in this process so far."""
+    return int(_library().gw_debug_launch_count())
+
+
 def rcp_approx(values):
     """rcp.approx.ftz.f32 of a NumPy float32 array, evaluated on the device
     (test aid: lets the CPU oracle use the hardware's reciprocal bits)."""
@@ -388,6 +393,18 @@ class MoeWorkspace:
 
     def down_capture(self):
         return self._view(self._lib.gw_moe_down_capture(self._ws), (8 * self.rows, 2816), torch.bfloat16)
+
+    def quantized_input(self, parts: int = 1):
+        """Test aid: copies of the quantised gate/up input of the last run: packed E2M1
+        [parts, 8*rows, 1408] and the tiled scale storage [parts, scale_rows * 176]."""
+        packed, scales = ctypes.c_void_p(), ctypes.c_void_p()
+        scale_rows, part_rows = ctypes.c_uint32(), ctypes.c_uint32()
+        _check(self._lib.gw_debug_moe_quantized_input(self._ws, ctypes.byref(packed), ctypes.byref(scales),
+                                                      ctypes.byref(scale_rows), ctypes.byref(part_rows)))
+        n = 8 * self.rows
+        whole = self._alias(packed.value, (parts, part_rows.value, 1408), torch.uint8)
+        tiles = self._alias(scales.value, (parts, scale_rows.value * 176), torch.uint8)
+        return whole[:, :n].clone(), tiles.clone()
 
     def bytes(self) -> int:
         return int(self._lib.gw_moe_bytes(self._ws))

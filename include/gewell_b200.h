@@ -246,6 +246,34 @@ gw_status gw_moe_capture(gw_moe_workspace* workspace, int enable);
 gw_status gw_moe_stage_timing(gw_moe_workspace* workspace, int enable);
 gw_status gw_moe_stage_elapsed_ms(gw_moe_workspace* workspace, float* milliseconds);
 
+/* MoE passes over HOST buffers (no counterpart in the reference, whose callers keep activations on
+ * the device): for a caller whose token rows, router logits and layer output live in pinned host
+ * memory.  The runner owns three streams and a ring of `depth` device buffers; submit() queues
+ * upload -> gw_moe_run -> download and returns at once, so the copies of neighbouring passes
+ * overlap the kernels.  Results equal gw_moe_run on device buffers bit for bit.
+ *   - create/destroy allocate and free device memory (set-up time, not capturable);
+ *   - the workspace, the expert table, the weights and `expert_scales_bf16` (device, 128 BF16)
+ *     must be complete on the device before the first submit, and the workspace must not be used
+ *     by other calls while passes are in flight;
+ *   - host_x [rows, 2816], host_scores [rows, 128], host_y [rows, 2816] are BF16 in pinned host
+ *     memory (pageable memory works but serialises the copies); host_y is readable after wait()
+ *     on the pass's ticket or after synchronize();
+ *   - NVFP4 experts with FP4 activations (the mode gw_moe_run is built for). */
+typedef struct gw_moe_host_runner gw_moe_host_runner;
+gw_status gw_moe_host_runner_create(gw_moe_workspace* workspace, const gw_expert_table* table,
+                                    const void* expert_scales_bf16, uint32_t max_rows, uint32_t depth,
+                                    gw_moe_host_runner** runner);
+void gw_moe_host_runner_destroy(gw_moe_host_runner* runner);
+gw_status gw_moe_host_runner_submit(gw_moe_host_runner* runner, const void* host_x, const void* host_scores,
+                                    void* host_y, uint32_t rows, uint64_t* ticket);
+gw_status gw_moe_host_runner_wait(gw_moe_host_runner* runner, uint64_t ticket);
+gw_status gw_moe_host_runner_synchronize(gw_moe_host_runner* runner);
+/* The runner's streams (cudaStream_t as void*), e.g. to record timing events around a batch of passes. */
+gw_status gw_moe_host_runner_streams(gw_moe_host_runner* runner, void** upload, void** compute, void** download);
+/* Bytes copied so far in each direction. */
+uint64_t gw_moe_host_runner_h2d_bytes(const gw_moe_host_runner* runner);
+uint64_t gw_moe_host_runner_d2h_bytes(const gw_moe_host_runner* runner);
+
 /* Expert-parallel building blocks (no counterpart in the reference, which is
  * single GPU).  A rank that owns experts [first, first+count) runs the expert
  * MLP over rows that are already sorted by expert: `offsets` (device, int32,
@@ -317,43 +345,33 @@ gw_status gw_moe_ep_run_experts(gw_moe_workspace* workspace, const void* records
                                 uint32_t first_expert, uint32_t expert_count, uint32_t total_rows,
                                 const gw_expert_table* table, void* down_bf16,
                                 const int32_t* segment_start, const int32_t* home_base,
-                                void* const* peer_returned, uint32_t world, void* stream);
+                                void* const* peer_returned, uint32_t home_capacity_rows, uint32_t world,
+                                void* stream);
 /* With peer_returned != NULL (one [8 * tokens, 2816] BF16 gw_ipc_alloc buffer per
  * rank, pointers in device memory) the down GEMM's epilogue stores every result row
  * straight into its source rank's buffer, at the row's position in that rank's
  * expert-sorted order, so the transfer home overlaps the GEMM; down_bf16 is then
- * unused and the source folds its rows with gw_moe_combine after a barrier.
+ * unused and the source folds its rows with gw_moe_combine after a barrier;
+ * home_capacity_rows is the row count of each of those buffers (a row whose home
+ * would lie outside is not stored and is reported through the kernel error word).
  * With peer_returned == NULL the rows stay in down_bf16 and gw_moe_ep_combine pulls
- * them. */
+ * them.
+ * Offsets that describe more than total_rows rows are clamped to total_rows and
+ * reported through the kernel error word: nothing is read or written beyond the
+ * declared capacity. */
 
 /* Ordered BF16 fold (moe.cu:446-456) of each token's eight result rows, read
- * from their owners: row dest_row0[e] + position of peer_down[dest_rank[e]]. */
+ * from their owners: row dest_row0[e] + position of peer_down[dest_rank[e]].
+ * capacity_rows is the row count of every owner's buffer; a row that would lie
+ * outside is not read (it counts as zero) and is reported through the kernel
+ * error word. */
 gw_status gw_moe_ep_combine(gw_moe_workspace* workspace, uint32_t rows, const int32_t* dest_rank,
-                            const int32_t* dest_row0, void* const* peer_down, void* output_bf16,
-                            void* stream);
+                            const int32_t* dest_row0, void* const* peer_down, uint32_t capacity_rows,
+                            void* output_bf16, void* stream);
 
 /* Last kernel-reported error word of this process's device (0 = none); set by
  * bounded waits inside the tensor-core kernels.  Synchronises the device. */
 uint32_t gw_debug_kernel_error(void);
-
-/* Tuning aid: when `device_buffer` (2 x 148 x 8 int64 on the device; consecutive launches alternate between the halves) is not NULL,
- * every later tensor-core GEMM launch writes per-CTA cycle counters into it
- * (producer wait, MMA wait for data, MMA issue, MMA wait for the accumulator,
- * epilogue wait, epilogue work, total, time the direct-store epilogue spends in
- * tensor-memory loads); NULL switches it off again. */
-gw_status gw_debug_gemm_profile(void* device_buffer);
-
-/* Test aid: output[i] = rcp.approx.ftz.f32(input[i]) evaluated on the device.
- * The activation recipe (src/nvfp4_linear.cu:92-114) is defined in terms of
- * this instruction, whose last bit a CPU cannot predict; the parity tests feed
- * the hardware's values into the CPU oracle so that the comparison is exact. */
-gw_status gw_debug_rcp_approx(const float* input, float* output, uint64_t count, void* stream);
-
-/* Test aid: element-wise GeGLU with both BF16 roundings
- * (src/bf16_activation.cuh:10-16) on the device, so that the CPU oracle can use
- * the device's tanhf bits where a one-ulp difference would flip an FP4 code. */
-gw_status gw_debug_geglu_bf16(const void* gate_bf16, const void* up_bf16, void* output_bf16, uint64_t count,
-                              void* stream);
 
 #ifdef __cplusplus
 }

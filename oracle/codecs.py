@@ -22,6 +22,7 @@ from __future__ import annotations
 import numpy as np
 
 E2M1_LEVELS = np.array([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0], dtype=np.float32)
+E2M1_SIGNED = np.concatenate([E2M1_LEVELS, -E2M1_LEVELS]).astype(np.float32)     # code 8 decodes to -0.0
 
 
 def _e4m3_table() -> np.ndarray:
@@ -102,8 +103,7 @@ def e4m3_round(values) -> np.ndarray:
 
 def e2m1_decode(codes) -> np.ndarray:
     codes = np.asarray(codes, dtype=np.uint8)
-    magnitude = E2M1_LEVELS[codes & 7]
-    return np.where(codes & 8, -magnitude, magnitude).astype(np.float32)
+    return np.take(E2M1_SIGNED, codes & 15)
 
 
 def e2m1_encode(values) -> np.ndarray:

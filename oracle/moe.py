@@ -144,3 +144,63 @@ def combine(down: np.ndarray, inverse: np.ndarray, weights: np.ndarray) -> np.nd
         product = C.bf16_round((rows * weights[:, j:j + 1]).astype(np.float32))
         total = C.bf16_round((total + product).astype(np.float32))
     return C.bf16_bits(total)
+
+
+# ----------------------------------------------------------------------------
+# The W4A16 host path with the dequantised weights kept: what a CPU deployment of
+# the reference's host path does (dequantise at load, FP32 matmul per step).  Used
+# by the benchmark's CPU arm; same arithmetic as forward(mode="w4a16").
+# ----------------------------------------------------------------------------
+
+def dequantize_experts(experts: list[ExpertWeights]) -> list[tuple[np.ndarray, np.ndarray, np.ndarray]]:
+    """BF16-rounded FP32 matrices (gate [704,2816], up [704,2816], down [2816,704]) of every
+    expert: src/nvfp4_linear.cu:47-55 applied to each projection, padding rows dropped."""
+    dense = []
+    for w in experts:
+        dense.append((C.bf16_to_f32(nvfp4.dequantize(w.gate))[:INTERMEDIATE],
+                      C.bf16_to_f32(nvfp4.dequantize(w.up))[:INTERMEDIATE],
+                      C.bf16_to_f32(nvfp4.dequantize(w.down))[:HIDDEN]))
+    return dense
+
+
+def forward_dequantized(x_bf16: np.ndarray, scores_bf16: np.ndarray, expert_scales_bf16: np.ndarray,
+                        dense: list[tuple[np.ndarray, np.ndarray, np.ndarray]]) -> np.ndarray:
+    """forward(mode="w4a16") over weights already dequantised by dequantize_experts."""
+    x = np.asarray(x_bf16, dtype=np.float32)
+    tokens = x.shape[0]
+    ids, weights = route(scores_bf16, expert_scales_bf16)
+    order, offsets = permutation(ids)
+    n = TOP_K * tokens
+    down = np.zeros((n, HIDDEN), dtype=np.float32)
+    for e in range(EXPERTS):
+        lo, hi = int(offsets[e]), int(offsets[e + 1])
+        if lo == hi:
+            continue
+        rows = x[order[lo:hi] // TOP_K]
+        gate, up, down_w = dense[e]
+        g = C.bf16_round(rows @ gate.T)
+        u = C.bf16_round(rows @ up.T)
+        a = C.gelu_tanh_multiply_bf16(g, u)
+        down[lo:hi] = C.bf16_round(a @ down_w.T)
+    inverse = np.empty(n, dtype=np.int64)
+    inverse[order] = np.arange(n)
+    return combine(down, inverse, weights)
+
+
+def synthetic_packed_experts(seed: int = 4) -> list[ExpertWeights]:
+    """128 experts of valid NVFP4 bytes drawn directly (uniform E2M1 codes, block scale codes in
+    [2^-1, 2^2), one global scale that gives the weights a spread near 0.02), for timing the host
+    path without running a packer over 760 M weights first.  Rows 704..767 of gate and up are the
+    zero padding the artifact carries."""
+    rng = np.random.default_rng(seed)
+    experts = []
+    for _ in range(EXPERTS):
+        parts = []
+        for rows, physical, width in ((INTERMEDIATE, 768, HIDDEN), (INTERMEDIATE, 768, HIDDEN), (HIDDEN, HIDDEN, INTERMEDIATE)):
+            data = np.zeros((physical, width // 2), dtype=np.uint8)
+            data[:rows] = rng.integers(0, 256, (rows, width // 2), dtype=np.uint8)
+            linear = np.zeros((physical, width // nvfp4.BLOCK), dtype=np.uint8)
+            linear[:rows] = rng.integers(0x30, 0x48, (rows, width // nvfp4.BLOCK), dtype=np.uint8)
+            parts.append(nvfp4.Weight(data, nvfp4.tile_scales(linear, width), 6.0 / 2688, 0.02 / 3.0, physical, width))
+        experts.append(ExpertWeights(*parts))
+    return experts

@@ -1,6 +1,7 @@
 """The C-ABI library loads on a machine without a GPU and exports every
-symbol that include/gewell_b200.h declares; layout helpers agree with the
-oracle.  No compute call is made here."""
+symbol that include/gewell_b200.h (the drop-in surface) and
+include/gewell_b200_test.h (test and tuning aids) declare; layout helpers agree
+with the oracle.  No compute call is made here."""
 import re
 from pathlib import Path
 
@@ -11,8 +12,8 @@ from oracle import nvfp4 as onv
 ROOT = Path(__file__).resolve().parents[1]
 
 
-def declared_symbols():
-    header = (ROOT / "include" / "gewell_b200.h").read_text()
+def declared_symbols(header_name="gewell_b200.h"):
+    header = (ROOT / "include" / header_name).read_text()
     return sorted(set(re.findall(r"\b(gw_[a-z0-9_]+)\s*\(", header)))
 
 
@@ -20,11 +21,14 @@ def test_library_exports_every_declared_symbol():
     from gewell_b200 import _lib
     lib = _lib.load()
     names = declared_symbols()
-    assert len(names) >= 40
-    for name in names:
-        assert hasattr(lib, name), f"{name} is declared in the header but not exported"
-    assert set(names) == set(_lib.exported_symbols())
-    assert lib.gw_abi_version() == 1
+    aids = declared_symbols("gewell_b200_test.h")
+    assert len(names) >= 40 and len(aids) >= 3
+    assert not any(name.startswith("gw_debug_") and name != "gw_debug_kernel_error" for name in names), \
+        "test aids belong in gewell_b200_test.h"
+    for name in names + aids:
+        assert hasattr(lib, name), f"{name} is declared in a header but not exported"
+    assert set(names) | set(aids) == set(_lib.exported_symbols())
+    assert lib.gw_abi_version() == 2
 
 
 def test_layout_helpers_match_oracle():

@@ -1,7 +1,7 @@
 """GPU tests of the expert-parallel building blocks through the C ABI:
 gw_moe_run_sorted against the captured intermediates of the whole layer (one
-GPU), and the two-rank NCCL layer against the single-GPU layer (needs two GPUs;
-skipped otherwise)."""
+GPU), and the 2-, 4- and 8-rank layer against the single-GPU layer (each needs
+that many GPUs; skipped otherwise)."""
 from __future__ import annotations
 
 import os
@@ -167,21 +167,32 @@ def test_record_path_on_one_rank_equals_layer(layer, tokens, send_home):
     down_table = torch.tensor([down.data_ptr()], dtype=torch.int64, device="cuda")
     check(lib.gw_moe_ep_dispatch(route_ws._ws, x.data_ptr(), tokens, inverse_scales.data_ptr(), dest_rank.data_ptr(),
                                  row0.data_ptr(), record_table.data_ptr(), capacity, stream))
+    if tokens <= 64:
+        # the travelling records byte for byte: 1408 bytes of E2M1 and the 176 scale bytes in K order,
+        # the row quantised with its expert's input scale (same recipe as moe.cu:254-304)
+        from oracle import nvfp4 as onv
+        torch.cuda.synchronize()
+        host_records = records[:8 * tokens * 1584].reshape(8 * tokens, 1584).cpu().numpy()
+        route_ws.rows = tokens
+        order = route_ws.sorted_assignments().cpu().numpy()
+        q = onv.quantize_activations(x.float().cpu().numpy()[order // 8], 6.0 / 2688, rcp_fn=gw.rcp_approx)
+        assert np.array_equal(host_records[:, :1408], q.packed[:8 * tokens])
+        assert np.array_equal(host_records[:, 1408:], q.scales_linear)
     out = torch.empty((tokens, H), dtype=torch.bfloat16, device="cuda")
     if send_home:
         returned = torch.full((8 * tokens, H), float("nan"), dtype=torch.bfloat16, device="cuda")
         returned_table = torch.tensor([returned.data_ptr()], dtype=torch.int64, device="cuda")
         check(lib.gw_moe_ep_run_experts(expert_ws._ws, records.data_ptr(), local_offsets.data_ptr(), 0, E, capacity,
                                         table.handle, None, segment_start.data_ptr(), home_base.data_ptr(),
-                                        returned_table.data_ptr(), 1, stream))
+                                        returned_table.data_ptr(), 8 * tokens, 1, stream))
         _, _, inverse, weights = route_ws.routing_state(tokens)
         check(lib.gw_moe_combine(returned.data_ptr(), inverse.data_ptr(), weights.data_ptr(), tokens, H, out.data_ptr(),
                                  stream))
     else:
         check(lib.gw_moe_ep_run_experts(expert_ws._ws, records.data_ptr(), local_offsets.data_ptr(), 0, E, capacity,
-                                        table.handle, down.data_ptr(), None, None, None, 1, stream))
+                                        table.handle, down.data_ptr(), None, None, None, 0, 1, stream))
         check(lib.gw_moe_ep_combine(route_ws._ws, tokens, dest_rank.data_ptr(), row0.data_ptr(), down_table.data_ptr(),
-                                    out.data_ptr(), stream))
+                                    capacity, out.data_ptr(), stream))
     torch.cuda.synchronize()
     assert gw.kernel_error() == 0
     assert np.array_equal(local_offsets.cpu().numpy(), offsets.cpu().numpy())
@@ -190,6 +201,48 @@ def test_record_path_on_one_rank_equals_layer(layer, tokens, send_home):
     check(lib.gw_moe_ep_dispatch(route_ws._ws, x.data_ptr(), tokens, inverse_scales.data_ptr(), dest_rank.data_ptr(),
                                  row0.data_ptr(), record_table.data_ptr(), 8, stream))
     assert gw.kernel_error() >> 28 == 7
+
+
+def test_undersized_receive_capacity_is_reported_not_overrun(layer):
+    """The group boundaries of a rank come from the other ranks' histograms.  If they describe more
+    rows than the receive buffers were sized for, the grouped GEMMs must stop at the declared
+    capacity and the combine must not read beyond it: guard rows behind the declared capacity stay
+    untouched and the kernel error word reports the overflow."""
+    gw, _, table = layer
+    lib, check = gw.lib, gw.ops._check
+    stream = torch.cuda.current_stream().cuda_stream
+    tokens, declared = 48, 128            # 384 routed rows, buffers declared as 128 rows
+    x, scores, scales = (t.cuda() for t in _inputs(tokens, 61, False))
+    route_ws, expert_ws = gw.MoeWorkspace(tokens), gw.MoeWorkspace(tokens)
+    route_ws.dispatch(scores, scales, tokens)
+    offsets, _, _, _ = route_ws.routing_state(tokens)
+    counts = (offsets[1:] - offsets[:-1]).contiguous()
+    physical = torch.arange(E, dtype=torch.int32, device="cuda")
+    dest_rank = torch.zeros(E, dtype=torch.int32, device="cuda")
+    row0 = torch.zeros(E, dtype=torch.int32, device="cuda")
+    local_offsets = torch.zeros(E + 1, dtype=torch.int32, device="cuda")
+    check(lib.gw_moe_ep_tables(counts.data_ptr(), physical.data_ptr(), 0, 1, row0.data_ptr(), local_offsets.data_ptr(),
+                               None, None, stream))
+    backing = 8 * tokens                  # real allocation: large enough that a missing clamp shows in the guards
+    records = torch.zeros((backing * 1584,), dtype=torch.uint8, device="cuda")
+    down = torch.full((backing, H), -9.0, dtype=torch.bfloat16, device="cuda")
+    inverse_scales = (torch.ones(E) / torch.full((E,), 6.0 / 2688)).cuda()
+    record_table = torch.tensor([records.data_ptr()], dtype=torch.int64, device="cuda")
+    down_table = torch.tensor([down.data_ptr()], dtype=torch.int64, device="cuda")
+    check(lib.gw_moe_ep_dispatch(route_ws._ws, x.data_ptr(), tokens, inverse_scales.data_ptr(), dest_rank.data_ptr(),
+                                 row0.data_ptr(), record_table.data_ptr(), declared, stream))
+    assert gw.kernel_error() >> 28 == 7
+    assert torch.all(records[declared * 1584:] == 0), "dispatch wrote beyond the declared capacity"
+    check(lib.gw_moe_ep_run_experts(expert_ws._ws, records.data_ptr(), local_offsets.data_ptr(), 0, E, declared,
+                                    table.handle, down.data_ptr(), None, None, None, 0, 1, stream))
+    assert gw.kernel_error() >> 28 == 7
+    assert torch.all(down[declared:] == -9.0), "the grouped GEMMs wrote beyond the declared capacity"
+    assert torch.isfinite(down[:declared].float()).all()
+    out = torch.empty((tokens, H), dtype=torch.bfloat16, device="cuda")
+    check(lib.gw_moe_ep_combine(route_ws._ws, tokens, dest_rank.data_ptr(), row0.data_ptr(), down_table.data_ptr(),
+                                declared, out.data_ptr(), stream))
+    assert gw.kernel_error() >> 28 == 7
+    assert torch.isfinite(out.float()).all()
 
 
 def _free_port() -> int:
@@ -239,15 +292,19 @@ def _worker(rank: int, world: int, port: int, placement_name: str, exchange: str
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("placement_name,exchange", [("contiguous", "nccl"), ("balanced", "nccl"),
-                                                     ("contiguous", "peer"), ("balanced", "peer"),
-                                                     ("balanced", "peer_pull")])
-def test_two_ranks_equal_single_gpu(layer, tmp_path, placement_name, exchange):
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
+@pytest.mark.parametrize("world,placement_name,exchange", [
+    (2, "contiguous", "nccl"), (2, "balanced", "nccl"), (2, "contiguous", "peer"), (2, "balanced", "peer"),
+    (2, "balanced", "peer_pull"),
+    (4, "balanced", "peer_pull"), (4, "contiguous", "nccl"), (4, "interleaved", "peer"),
+    (8, "balanced", "peer_pull"), (8, "interleaved", "nccl"), (8, "contiguous", "peer")])
+def test_ranks_equal_single_gpu(layer, tmp_path, world, placement_name, exchange):
+    """The expert-parallel layer over 2, 4 or 8 ranks (one process per GPU) returns the bits of the
+    single-GPU layer, for every exchange implementation and placement."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
     gw, _, table = layer
-    tokens, world = 1536, 2
+    tokens = 1536
     mp.spawn(_worker, args=(world, _free_port(), placement_name, exchange, tokens, str(tmp_path)), nprocs=world,
              join=True)
     x, scores, scales = (t.cuda() for t in _inputs(tokens, 50, True))
@@ -260,4 +317,4 @@ def test_two_ranks_equal_single_gpu(layer, tmp_path, placement_name, exchange):
     mismatch = float(np.mean(got != expected))
     # the same kernels see the same rows; only the grouped-GEMM plan may differ with
     # the per-rank row count, and both plans accumulate the same products in FP32
-    assert mismatch == 0.0, f"{mismatch:.2e} of the outputs differ between 2 ranks and 1 GPU"
+    assert mismatch == 0.0, f"{mismatch:.2e} of the outputs differ between {world} ranks and 1 GPU"

@@ -244,3 +244,80 @@ def test_moe_unsupported_modes(gw, experts):
     with pytest.raises(gw.GewellUnsupported):
         ws.run(x, s, one, table, x.clone(), 4, has_bf16=True)
     ws.run(x, s, one, table, x.clone(), 0)          # rows == 0 is a no-op
+
+
+_sampled_oracle_cache = {}
+
+
+def _zipf_bias():
+    ranks = torch.arange(1, E + 1, dtype=torch.float32)
+    p = ranks.pow(-1.2)
+    return (p / p.sum()).log()
+
+
+@pytest.mark.parametrize("rows,form,skew", [(8192, None, False), (8192, "direct", False), (32768, None, True)])
+def test_moe_layer_sampled_tokens_vs_oracle(gw, experts_shared, moe_form, rows, form, skew):
+    """The published layer sizes (8192 tokens on one GPU; 32768 tokens with the Zipf(1.2) routing
+    bias, the expert-parallel configuration's whole batch) against the faithful W4A4 oracle.  The
+    layer is row independent (tests/gemma4_26b_moe_quantized.cu:57-253 checks it per row too), so
+    the oracle evaluates a sample of tokens -- first, last and random ones -- with the routing it
+    computes itself, and those rows of the full-size run must match."""
+    table, host = experts_shared
+    moe_form(form)
+    x = bf16_normal((rows, H), 300 + rows % 97)
+    scores = make_scores(rows, "normal", 12)
+    if skew:
+        scores = (scores.float() + _zipf_bias()).bfloat16()
+    ws = gw.MoeWorkspace(rows)
+    y = torch.empty((rows, H), dtype=torch.bfloat16, device="cuda")
+    ws.run(x.cuda(), scores.cuda(), torch.ones(E, dtype=torch.bfloat16, device="cuda"), table, y, rows)
+    torch.cuda.synchronize()
+    assert gw.kernel_error() == 0
+    rng = np.random.default_rng(rows)
+    sample = np.unique(np.concatenate([[0, 1, 63, 64, rows - 1], rng.integers(0, rows, 19)]))
+    key = (rows, skew)
+    if key not in _sampled_oracle_cache:
+        capture = {}
+        expected = omoe.forward(to_f32(x[sample]), to_f32(scores[sample]), np.ones(E, dtype=np.float32), host,
+                                capture=capture, rcp_fn=gw.rcp_approx, gelu_fn=gw.geglu_bf16)
+        _sampled_oracle_cache[key] = (expected, capture["ids"])
+    expected, ids = _sampled_oracle_cache[key]
+    assert np.array_equal(ws.selected_experts().cpu().numpy()[sample], ids)
+    m = assert_gemm_close(bits(y[torch.from_numpy(sample).cuda()]), expected, f"MoE rows={rows} form={form} sampled tokens")
+    print(f"rows={rows} form={form}: {len(sample)} sampled tokens rel_fro {m['rel_fro']:.2e} "
+          f"max_abs/max {m['max_abs'] / m['max_ref']:.2e}")
+
+
+@pytest.mark.parametrize("rows", [100, 700])
+def test_moe_quantised_input_bytes_exact(gw, experts, rows):
+    """The gather + FP4 quantisation step (moe.cu:183-186,254-304) byte for byte: every sorted row is
+    its token quantised with the destination expert's input scale, gate and up separately when their
+    scales differ; scale bytes sit in the expert's 128-row aligned region in the tiled layout.  Both
+    quantisers are covered: one thread per block (small batches) and one warp per token (from 512
+    tokens on)."""
+    table, host = experts
+    x = bf16_normal((rows, H), 55)
+    scores = make_scores(rows, "normal", 3)
+    ws = gw.MoeWorkspace(rows)
+    y = torch.empty((rows, H), dtype=torch.bfloat16, device="cuda")
+    ws.run(x.cuda(), scores.cuda(), torch.ones(E, dtype=torch.bfloat16, device="cuda"), table, y, rows)
+    torch.cuda.synchronize()
+    assert gw.kernel_error() == 0
+    packed, tiles = ws.quantized_input(parts=2)
+    packed, tiles = packed.cpu().numpy(), tiles.cpu().numpy()
+    order, offsets = ws.sorted_assignments().cpu().numpy(), ws.offsets().cpu().numpy()
+    xf = to_f32(x)
+    checked = 0
+    for e in range(E):
+        lo, hi = int(offsets[e]), int(offsets[e + 1])
+        if lo == hi:
+            continue
+        tokens = order[lo:hi] // 8
+        region = (lo // 128 + e) * 128 * (H // 16)
+        for part, weight in enumerate((host[e].gate, host[e].up)):
+            q = onv.quantize_activations(xf[tokens], weight.input_scale, rcp_fn=gw.rcp_approx)
+            assert np.array_equal(packed[part, lo:hi], q.packed[:hi - lo]), f"expert {e} part {part}: packed bytes"
+            got = onv.untile_scales(tiles[part, region:region + onv.scale_storage_bytes(hi - lo, H)], hi - lo, H)
+            assert np.array_equal(got, q.scales_linear), f"expert {e} part {part}: scale bytes"
+            checked += hi - lo
+    assert checked == 2 * 8 * rows
