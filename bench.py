@@ -359,7 +359,7 @@ def run_expert_parallel(args, world: int, rank: int, local_rank: int):
                 # counted by the library at its launch sites on rank 0 (every rank launches the same
                 # sequence; the collectives are NCCL's and not counted)
                 "gpu_launches": launches * world, "clocks": clocks,
-                "roofline": {"kernel": "gemm_tc_kernel<nvfp4> (grouped gate/up + grouped down) on the busiest rank",
+                "roofline": {"kernel": "pair_moe_gate_up_kernel + pair_moe_down_kernel (grouped NVFP4 GEMMs on CTA pairs) on the busiest rank",
                              "bound": "tensor", "achieved": achieved, "peak": fp4_peak, "unit": "TFLOP/s",
                              "frac": achieved / fp4_peak, "traffic": None,
                              "peak_note": f"4 x the {peaks['source']} dense BF16 burst figure per GPU",
@@ -505,7 +505,7 @@ def main():
     peaks = measured_peaks()
     fp4_peak = 4.0 * peaks["bf16_tflops"]
     achieved = flops / (gemm_ms * 1e-3) / 1e12
-    roofline = {"kernel": "gemm_tc_kernel<nvfp4> (grouped gate/up + grouped down)", "bound": "tensor",
+    roofline = {"kernel": "pair_moe_gate_up_kernel + pair_moe_down_kernel (grouped NVFP4 GEMMs on CTA pairs)", "bound": "tensor",
                 "achieved": achieved, "peak": fp4_peak, "unit": "TFLOP/s", "frac": achieved / fp4_peak,
                 # dram__bytes_read.sum + dram__bytes_write.sum of the two launches at this size, from the one-pass
                 # ncu capture summarised in profiles/bench_moe_T8192_launch_list.md (gate/up 441.3 MB, down 486.1 MB)

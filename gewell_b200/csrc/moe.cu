@@ -10,6 +10,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "gemm_pair_moe.h"
 #include "gemm_tc.cuh"
 #include "moe_kernels.h"
 
@@ -38,13 +39,53 @@ struct DeviceBuffer {
 }  // namespace
 
 struct gw_expert_table {
-  DeviceBuffer maps;    // CUtensorMap[128*3]: gate, up, down of every expert (box 128 rows)
+  DeviceBuffer maps;    // CUtensorMap[128*4]: gate, up, down of every expert (128-row boxes), down again (64-row boxes)
   DeviceBuffer info;    // MoeExpertInfo[128]
   bool shared_gate_up = false;   // every expert quantises gate and up inputs with one scale
 };
 
+// Tuning overrides, read from the environment once, when a workspace is created:
+//   GW_MOE_FORM          swap / direct / fused: plan of the grouped GEMMs (default: by batch size)
+//   GW_MOE_NO_PAIR       1: never use the CTA-pair kernels (single-CTA kernels for every batch size)
+//   GW_MOE_BLOCK_N, GW_MOE_BLOCK_N_DOWN, GW_MOE_CHUNK_FIRST, GW_MOE_CHUNK_DOWN: tile / schedule of the
+//                        single-CTA kernels
+struct MoeTuning {
+  char form = 0;
+  bool no_pair = false;
+  int block_n = 0, block_n_down = 0, chunk_first = 0, chunk_down = 0;
+  static int number(const char* name) {
+    const char* value = std::getenv(name);
+    return value ? std::atoi(value) : 0;
+  }
+  void read() {
+    const char* forced = std::getenv("GW_MOE_FORM");
+    form = forced ? forced[0] : 0;
+    no_pair = number("GW_MOE_NO_PAIR") != 0;
+    block_n = number("GW_MOE_BLOCK_N");
+    block_n_down = number("GW_MOE_BLOCK_N_DOWN");
+    chunk_first = number("GW_MOE_CHUNK_FIRST");
+    chunk_down = number("GW_MOE_CHUNK_DOWN");
+  }
+};
+
+// An activation tensor map, re-encoded only when what it describes changes.
+struct CachedMap {
+  CUtensorMap map{};
+  const void* base = nullptr;
+  uint64_t rows = 0, pitch = 0;
+  uint32_t box = 0;
+  bool get(const void* b, uint64_t row_bytes, uint64_t r, uint32_t box_rows, uint64_t pitch_bytes, std::string* error) {
+    if (b == base && r == rows && box_rows == box && pitch_bytes == pitch) return true;
+    if (!encode_tensor_map_2d(&map, b, row_bytes, r, box_rows, error, pitch_bytes)) return false;
+    base = b; rows = r; box = box_rows; pitch = pitch_bytes;
+    return true;
+  }
+};
+
 struct gw_moe_workspace {
   uint32_t max_rows = 0, n = 0, scale_rows = 0, chunks = 0;
+  MoeTuning tuning;
+  CachedMap first_map, down_map;
   DeviceBuffer metadata, bitmaps, groups, packed_in, scales_in, gate_up, activated, packed_act, scales_act, down;
   DeviceBuffer row_home;   // expert parallelism: address of every produced row's home in its source rank
   int32_t *keys = nullptr, *sorted_keys = nullptr, *sorted_assignments = nullptr, *inverse = nullptr;
@@ -63,7 +104,7 @@ gw_status gw_moe_expert_table_create(const gw_expert_weights* experts, uint32_t 
   clear_error();
   if (!experts || !table || count != kExperts)
     return fail(GW_INVALID_ARGUMENT, "expert table requires 128 host-resident entries");
-  std::vector<CUtensorMap> maps(kExperts * 3);
+  std::vector<CUtensorMap> maps(kExperts * kMoeMapsPerExpert);
   std::vector<MoeExpertInfo> info(kExperts);
   bool shared = true;
   std::string error;
@@ -86,7 +127,9 @@ gw_status gw_moe_expert_table_create(const gw_expert_weights* experts, uint32_t 
           !finite_positive(p.nvfp4_weight_scale) || !std::isfinite(1.0F / p.nvfp4_input_scale) ||
           !finite_positive(p.nvfp4_input_scale * p.nvfp4_weight_scale))
         return fail(GW_INVALID_ARGUMENT, "invalid 26B expert projection binding (expert " + std::to_string(e) + ")");
-      if (!encode_tensor_map_2d(&maps[e * 3 + i], p.nvfp4_data, p.input / 2, p.physical_output, 128, &error))
+      if (!encode_tensor_map_2d(&maps[e * kMoeMapsPerExpert + i], p.nvfp4_data, p.input / 2, p.physical_output, 128, &error) ||
+          (i == 2 && !encode_tensor_map_2d(&maps[e * kMoeMapsPerExpert + 3], p.nvfp4_data, p.input / 2, p.physical_output, 64,
+                                           &error)))
         return fail(GW_CUDA_ERROR, "expert weight descriptor: " + error);
       info[e].scales[i] = p.nvfp4_scales;
       info[e].alpha[i] = p.nvfp4_input_scale * p.nvfp4_weight_scale;   // == __fmul_rn on the device
@@ -122,7 +165,10 @@ gw_status gw_moe_create(uint32_t max_rows, gw_moe_workspace** workspace) {
   w->max_rows = max_rows;
   w->n = 8 * max_rows;
   const size_t n = w->n;
-  w->scale_rows = uint32_t(((n + 127) / 128 + 128) * 128);
+  // per-expert 128-row aligned regions (at most 128 blocks of padding) plus two blocks that the
+  // pair kernels may read past an expert's last block (never used in a result)
+  w->scale_rows = uint32_t(((n + 127) / 128 + 128 + 2) * 128);
+  w->tuning.read();
   w->chunks = moe_chunks(max_rows);
   const size_t metadata_ints = 5 * n + 2 * 132 + size_t(w->chunks) * kExperts;
   cudaError_t status = w->metadata.allocate((metadata_ints + n) * sizeof(int32_t));
@@ -177,11 +223,6 @@ gw_status gw_moe_dispatch(gw_moe_workspace* w, const void* scores_bf16, const vo
 
 namespace {
 
-int env_int(const char* name, int fallback) {
-  const char* value = std::getenv(name);
-  return value ? std::atoi(value) : fallback;
-}
-
 // Expert MLP over rows sorted by expert: quantise -> gate/up GEMM -> GeGLU +
 // quantise -> down GEMM.  `gather_index` != nullptr reads input rows through
 // the permutation (input row = index / gather_divisor); otherwise input row i
@@ -201,28 +242,31 @@ gw_status run_experts(gw_moe_workspace* w, const void* input, const int32_t* gat
   const auto* info = table->info.as<MoeExpertInfo>();
   auto* first_groups = w->groups.as<GemmGroup>();
   auto* down_groups = first_groups + 2 * kExperts + 1;
+  const MoeTuning& tune = w->tuning;
   int form = n <= 8 * 512 ? kMoeFormSwap : (table->shared_gate_up ? kMoeFormFused : kMoeFormDirect);
-  if (const char* forced = std::getenv("GW_MOE_FORM")) {   // tuning override: swap / direct / fused
-    if (forced[0] == 's') form = kMoeFormSwap;
-    if (forced[0] == 'd') form = kMoeFormDirect;
-    if (forced[0] == 'f' && table->shared_gate_up) form = kMoeFormFused;
-  }
+  if (tune.form == 's') form = kMoeFormSwap;
+  if (tune.form == 'd') form = kMoeFormDirect;
+  if (tune.form == 'f' && table->shared_gate_up) form = kMoeFormFused;
+  // Large batches run on CTA pairs: the gate/up GEMM when one quantised copy of a row serves both
+  // projections (the fused plan), the down GEMM whenever tokens sit on the lanes.
+  const bool pair_first = form == kMoeFormFused && !tune.no_pair;
+  const bool pair_down = form != kMoeFormSwap && !tune.no_pair;
   int block_n_first, block_n_down;
   if (form == kMoeFormSwap) {
     block_n_first = n <= 8 * 64 ? 32 : (n <= 8 * 256 ? 64 : 128);
-    block_n_first = block_n_down = env_int("GW_MOE_BLOCK_N", block_n_first);
-    if (block_n_first != 32 && block_n_first != 64 && block_n_first != 128) block_n_first = block_n_down = 128;
+    if (tune.block_n == 32 || tune.block_n == 64 || tune.block_n == 128) block_n_first = tune.block_n;
+    block_n_down = block_n_first;
   } else {
-    block_n_first = form == kMoeFormFused ? 256 : env_int("GW_MOE_BLOCK_N", 128);
-    block_n_down = env_int("GW_MOE_BLOCK_N_DOWN", 128);
-    if (block_n_first != 128 && block_n_first != 256) block_n_first = 128;
-    if (block_n_down != 128 && block_n_down != 256) block_n_down = 128;
+    block_n_first = form == kMoeFormFused ? 256 : (tune.block_n == 256 ? 256 : 128);
+    block_n_down = tune.block_n_down == 256 ? 256 : 128;
   }
   const int parts = table->shared_gate_up ? 1 : 2;
-  MoeGroupPlan plan{offsets, info, w->scales_in.as<uint8_t>(), w->scales_act.as<uint8_t>(), n, w->scale_rows, form,
-                    block_n_first, block_n_down, table->shared_gate_up ? 1 : 0, device_error_word()};
   w->mark(1, s);
-  GW_CUDA_CHECK(launch_moe_prepare_groups(plan, first_groups, down_groups, s), "MoE group descriptors");
+  if (!(pair_first && pair_down)) {
+    MoeGroupPlan plan{offsets, info, w->scales_in.as<uint8_t>(), w->scales_act.as<uint8_t>(), n, w->scale_rows, form,
+                      block_n_first, block_n_down, table->shared_gate_up ? 1 : 0, device_error_word()};
+    GW_CUDA_CHECK(launch_moe_prepare_groups(plan, first_groups, down_groups, s), "MoE group descriptors");
+  }
   if (records != nullptr) {
     GW_CUDA_CHECK(launch_ep_retile_scales(records, w->sorted_keys, offsets, n, w->scales_in.as<uint8_t>(), s),
                   "MoE scale re-tiling of received rows");
@@ -239,61 +283,91 @@ gw_status run_experts(gw_moe_workspace* w, const void* input, const int32_t* gat
   }
   std::string error;
   const bool swap = form == kMoeFormSwap;
-  GemmParams first{};
-  CUtensorMap token_map;
-  if (!encode_tensor_map_2d(&token_map, records ? records : w->packed_in.data, kHidden / 2, size_t(parts) * n,
-                            swap ? block_n_first : 128, &error, records ? kEpRecordBytes : 0))
+  if (!w->first_map.get(records ? records : w->packed_in.data, kHidden / 2, size_t(parts) * n,
+                        swap ? block_n_first : 128, records ? kEpRecordBytes : kHidden / 2, &error))
     return fail(GW_CUDA_ERROR, "MoE activation descriptor: " + error);
-  (swap ? first.map_c : first.map_l) = token_map;
-  first.map_table = table->maps.as<CUtensorMap>();
-  first.groups = first_groups;
-  first.num_groups = form == kMoeFormFused ? kExperts : 2 * kExperts;
-  first.k = kHidden;
-  first.c_rows_per_tile = form == kMoeFormFused ? 128 : block_n_first;
-  // two consecutive tiles per CTA (same token tile, same expert) before it strides on: measured best
-  first.work_chunk = env_int("GW_MOE_CHUNK_FIRST", swap ? 1 : 2);
-  first.error = device_error_word();
+  if (!w->down_map.get(w->packed_act.data, kInter / 2, n, swap ? block_n_down : 128, kInter / 2, &error))
+    return fail(GW_CUDA_ERROR, "MoE activation descriptor: " + error);
   w->mark(2, s);
-  if (form == kMoeFormFused) {
-    first.out = w->packed_act.data;
-    first.ld_out = kInter / 2;
-    first.out_scales = w->scales_act.as<uint8_t>();
-    first.out_width = kInter;
+  if (pair_first) {
+    PairMoeParams first{};
+    first.map_tokens = w->first_map.map;
+    first.map_table = table->maps.as<CUtensorMap>();
+    first.experts = info;
+    first.offsets = offsets;
+    first.sf_tokens = w->scales_in.as<uint8_t>();
+    first.capacity = n;
+    first.packed_out = w->packed_act.as<uint8_t>();
+    first.scales_out = w->scales_act.as<uint8_t>();
     first.capture_gate_up = w->capture ? w->gate_up.data : nullptr;
     first.capture_activated = w->capture ? w->activated.data : nullptr;
-    GW_CUDA_CHECK(launch_gemm_tc(GemmKind::nvfp4, GemmEpilogue::geglu_quant, 256, first, sm_count(), s),
-                  "MoE grouped gate/up GEMM with fused GeGLU + quantise");
+    first.error = device_error_word();
+    GW_CUDA_CHECK(launch_pair_moe_gate_up(first, sm_count(), s), "MoE grouped gate/up GEMM on CTA pairs");
     w->mark(3, s);
   } else {
-    first.out = w->gate_up.data;
-    first.ld_out = 2 * kInter;
-    GW_CUDA_CHECK(launch_gemm_tc(GemmKind::nvfp4, swap ? GemmEpilogue::swap_store : GemmEpilogue::direct_store,
-                                 block_n_first, first, sm_count(), s),
-                  "MoE grouped gate/up GEMM");
-    w->mark(3, s);
-    GW_CUDA_CHECK(launch_moe_activate_quantize(w->gate_up.data, w->sorted_keys, offsets, info, n, w->scale_rows,
-                                               w->packed_act.as<uint8_t>(), w->scales_act.as<uint8_t>(),
-                                               w->activated.data, s),
-                  "MoE GeGLU + quantise");
+    GemmParams first{};
+    (swap ? first.map_c : first.map_l) = w->first_map.map;
+    first.map_table = table->maps.as<CUtensorMap>();
+    first.groups = first_groups;
+    first.num_groups = form == kMoeFormFused ? kExperts : 2 * kExperts;
+    first.k = kHidden;
+    first.c_rows_per_tile = form == kMoeFormFused ? 128 : block_n_first;
+    // two consecutive tiles per CTA (same token tile, same expert) before it strides on: measured best
+    first.work_chunk = tune.chunk_first > 0 ? tune.chunk_first : (swap ? 1 : 2);
+    first.error = device_error_word();
+    if (form == kMoeFormFused) {
+      first.out = w->packed_act.data;
+      first.ld_out = kInter / 2;
+      first.out_scales = w->scales_act.as<uint8_t>();
+      first.out_width = kInter;
+      first.capture_gate_up = w->capture ? w->gate_up.data : nullptr;
+      first.capture_activated = w->capture ? w->activated.data : nullptr;
+      GW_CUDA_CHECK(launch_gemm_tc(GemmKind::nvfp4, GemmEpilogue::geglu_quant, 256, first, sm_count(), s),
+                    "MoE grouped gate/up GEMM with fused GeGLU + quantise");
+      w->mark(3, s);
+    } else {
+      first.out = w->gate_up.data;
+      first.ld_out = 2 * kInter;
+      GW_CUDA_CHECK(launch_gemm_tc(GemmKind::nvfp4, swap ? GemmEpilogue::swap_store : GemmEpilogue::direct_store,
+                                   block_n_first, first, sm_count(), s),
+                    "MoE grouped gate/up GEMM");
+      w->mark(3, s);
+      GW_CUDA_CHECK(launch_moe_activate_quantize(w->gate_up.data, w->sorted_keys, offsets, info, n, w->scale_rows,
+                                                 w->packed_act.as<uint8_t>(), w->scales_act.as<uint8_t>(),
+                                                 w->activated.data, s),
+                    "MoE GeGLU + quantise");
+    }
   }
-  GemmParams down{};
-  if (!encode_tensor_map_2d(&token_map, w->packed_act.data, kInter / 2, n, swap ? block_n_down : 128, &error))
-    return fail(GW_CUDA_ERROR, "MoE activation descriptor: " + error);
-  (swap ? down.map_c : down.map_l) = token_map;
-  down.map_table = table->maps.as<CUtensorMap>();
-  down.groups = down_groups;
-  down.num_groups = kExperts;
-  down.k = kInter;
-  down.c_rows_per_tile = block_n_down;
-  down.work_chunk = env_int("GW_MOE_CHUNK_DOWN", swap ? 1 : 2);
-  down.out = down_out;
-  down.ld_out = kHidden;
-  down.row_dest = row_home;   // rows go to their homes (possibly on other GPUs) instead of down_out
-  down.error = device_error_word();
   w->mark(4, s);
-  GW_CUDA_CHECK(launch_gemm_tc(GemmKind::nvfp4, swap ? GemmEpilogue::swap_store : GemmEpilogue::direct_store,
-                               block_n_down, down, sm_count(), s),
-                "MoE grouped down GEMM");
+  if (pair_down) {
+    PairMoeParams down{};
+    down.map_tokens = w->down_map.map;
+    down.map_table = table->maps.as<CUtensorMap>();
+    down.experts = info;
+    down.offsets = offsets;
+    down.sf_tokens = w->scales_act.as<uint8_t>();
+    down.capacity = n;
+    down.out = down_out;
+    down.row_dest = row_home;   // rows go to their homes (possibly on other GPUs) instead of down_out
+    down.error = device_error_word();
+    GW_CUDA_CHECK(launch_pair_moe_down(down, sm_count(), s), "MoE grouped down GEMM on CTA pairs");
+  } else {
+    GemmParams down{};
+    (swap ? down.map_c : down.map_l) = w->down_map.map;
+    down.map_table = table->maps.as<CUtensorMap>();
+    down.groups = down_groups;
+    down.num_groups = kExperts;
+    down.k = kInter;
+    down.c_rows_per_tile = block_n_down;
+    down.work_chunk = tune.chunk_down > 0 ? tune.chunk_down : (swap ? 1 : 2);
+    down.out = down_out;
+    down.ld_out = kHidden;
+    down.row_dest = row_home;   // rows go to their homes (possibly on other GPUs) instead of down_out
+    down.error = device_error_word();
+    GW_CUDA_CHECK(launch_gemm_tc(GemmKind::nvfp4, swap ? GemmEpilogue::swap_store : GemmEpilogue::direct_store,
+                                 block_n_down, down, sm_count(), s),
+                  "MoE grouped down GEMM");
+  }
   w->mark(5, s);
   return GW_OK;
 }

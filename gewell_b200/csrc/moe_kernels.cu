@@ -18,6 +18,7 @@ constexpr int kExperts = 128;
 constexpr int kTopK = 8;
 constexpr int kHidden = 2816;
 constexpr int kInter = 704;
+constexpr int kMapsPerExpert = 4;   // tensor maps per expert in the table: gate, up, down, down with 64-row boxes
 constexpr int kChunkTokens = 64;   // tokens per routing block (two 32-bit bitmap words per expert)
 
 __device__ __forceinline__ void unpack8(const uint4& raw, float* out) {
@@ -293,8 +294,8 @@ moe_prepare_groups_kernel(MoeGroupPlan plan, GemmGroup* __restrict__ first_group
       grp.l_tiles = token_tiles_direct;
       grp.sf_c[0] = info.scales[0];
       grp.sf_c[1] = info.scales[1];
-      grp.map_c[0] = int32_t(e) * 3;
-      grp.map_c[1] = int32_t(e) * 3 + 1;
+      grp.map_c[0] = int32_t(e) * kMapsPerExpert;
+      grp.map_c[1] = int32_t(e) * kMapsPerExpert + 1;
       grp.c_row0 = 0;
       grp.c_rows = kInter;
       grp.c_tiles = (kInter + 127) / 128;
@@ -315,7 +316,7 @@ moe_prepare_groups_kernel(MoeGroupPlan plan, GemmGroup* __restrict__ first_group
       grp.l_rows = count;
       grp.l_tiles = token_tiles_direct;
       grp.sf_c[0] = grp.sf_c[1] = info.scales[proj];
-      grp.map_c[0] = grp.map_c[1] = int32_t(e) * 3 + proj;
+      grp.map_c[0] = grp.map_c[1] = int32_t(e) * kMapsPerExpert + proj;
       grp.c_row0 = 0;
       grp.c_rows = kInter;
       grp.c_tiles = (kInter + plan.block_n_first - 1) / plan.block_n_first;
@@ -328,7 +329,7 @@ moe_prepare_groups_kernel(MoeGroupPlan plan, GemmGroup* __restrict__ first_group
     } else {
       const int proj = part;
       grp.sf_l = info.scales[proj];
-      grp.map_l = int32_t(e) * 3 + proj;
+      grp.map_l = int32_t(e) * kMapsPerExpert + proj;
       grp.l_row0 = 0;
       grp.l_rows = kInter;
       grp.l_tiles = (kInter + 127) / 128;
@@ -349,7 +350,7 @@ moe_prepare_groups_kernel(MoeGroupPlan plan, GemmGroup* __restrict__ first_group
     GemmGroup grp{};
     if (plan.form == kMoeFormSwap) {
       grp.sf_l = info.scales[2];
-      grp.map_l = int32_t(e) * 3 + 2;
+      grp.map_l = int32_t(e) * kMapsPerExpert + 2;
       grp.l_row0 = 0;
       grp.l_rows = kHidden;
       grp.l_tiles = kHidden / 128;
@@ -366,7 +367,7 @@ moe_prepare_groups_kernel(MoeGroupPlan plan, GemmGroup* __restrict__ first_group
       grp.l_rows = count;
       grp.l_tiles = token_tiles_direct;
       grp.sf_c[0] = grp.sf_c[1] = info.scales[2];
-      grp.map_c[0] = grp.map_c[1] = int32_t(e) * 3 + 2;
+      grp.map_c[0] = grp.map_c[1] = int32_t(e) * kMapsPerExpert + 2;
       grp.c_row0 = 0;
       grp.c_rows = kHidden;
       grp.c_tiles = kHidden / plan.block_n_down;

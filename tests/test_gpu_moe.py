@@ -71,14 +71,20 @@ def experts_shared(gw, experts):
 
 @pytest.fixture
 def moe_form():
-    """Sets / clears the tuning override that selects the grouped-GEMM plan."""
+    """Sets / clears the tuning overrides that select the grouped-GEMM plan (read when a workspace is
+    created): "swap", "direct" or "fused", optionally followed by "-single" to keep the CTA-pair
+    kernels out (the fused and direct plans then run on the single-CTA kernel)."""
     def choose(name):
-        if name is None:
-            os.environ.pop("GW_MOE_FORM", None)
-        else:
-            os.environ["GW_MOE_FORM"] = name
+        os.environ.pop("GW_MOE_FORM", None)
+        os.environ.pop("GW_MOE_NO_PAIR", None)
+        if name is not None:
+            form, _, variant = name.partition("-")
+            os.environ["GW_MOE_FORM"] = form
+            if variant == "single":
+                os.environ["GW_MOE_NO_PAIR"] = "1"
     yield choose
     os.environ.pop("GW_MOE_FORM", None)
+    os.environ.pop("GW_MOE_NO_PAIR", None)
 
 
 def make_scores(rows, mode, seed=0):
@@ -146,12 +152,19 @@ def test_combine_kernel_exact(gw):
     (40, "hot", None), (64, "hot", None), (200, "hot", None),
     (7, "normal", "direct"), (129, "uneven", "direct"), (300, "normal", "direct"),
     (1, "hot", "fused"), (33, "normal", "fused"), (129, "uneven", "fused"), (300, "normal", "fused"),
+    # 200 hot tokens: eight experts with 200 rows each (a pair tile whose second CTA is partly filled);
+    # 4096 uneven: experts with thousands of rows next to empty ones
+    (200, "hot", "fused"), (600, "uneven", "fused"),
+    (7, "normal", "direct-single"), (300, "normal", "direct-single"),
+    (1, "hot", "fused-single"), (129, "uneven", "fused-single"), (300, "normal", "fused-single"),
 ])
 def test_moe_layer_vs_oracle(gw, experts, experts_shared, moe_form, rows, mode, form):
     """Whole layer against the faithful W4A4 oracle, for each grouped-GEMM plan:
     swap (small batches), direct (tokens on the lane operand) and fused (GeGLU +
-    quantisation in the gate/up epilogue; needs one input scale for gate and up)."""
-    table, host = experts_shared if form == "fused" else experts
+    quantisation in the gate/up epilogue; needs one input scale for gate and up).
+    Fused and direct run their GEMMs on CTA pairs (gate/up only when fused; down in
+    both) unless "-single" keeps them on the single-CTA kernel."""
+    table, host = experts_shared if form is not None and form.startswith("fused") else experts
     moe_form(form)
     x = bf16_normal((rows, H), 200 + rows)
     scores = make_scores(rows, mode, rows)
@@ -199,13 +212,14 @@ def test_moe_fused_without_capture_matches_captured_run(gw, experts_shared, moe_
     assert torch.equal(outs[0], outs[1])
 
 
-@pytest.mark.parametrize("rows,form", [(2048, None), (2048, "fused"), (8192, "fused"), (8192, "direct")])
+@pytest.mark.parametrize("rows,form", [(2048, None), (2048, "fused"), (8192, "fused"), (8192, "direct"),
+                                       (2048, "fused-single"), (8192, "direct-single")])
 def test_moe_layer_combine_consistency(gw, experts, experts_shared, moe_form, rows, form):
     """Size-independent properties at sizes where the full oracle is slow: the
     layer output is exactly the ordered BF16 fold of its own down capture
     (moe.cu:446-456), offsets are the histogram of the selected ids, and the
     plans agree with each other to GEMM tolerance."""
-    table, _ = experts_shared if form == "fused" else experts
+    table, _ = experts_shared if form is not None and form.startswith("fused") else experts
     moe_form(form)
     x = bf16_normal((rows, H), 77)
     scores = make_scores(rows, "normal", 5)
@@ -255,7 +269,8 @@ def _zipf_bias():
     return (p / p.sum()).log()
 
 
-@pytest.mark.parametrize("rows,form,skew", [(8192, None, False), (8192, "direct", False), (32768, None, True)])
+@pytest.mark.parametrize("rows,form,skew", [(8192, None, False), (8192, "direct", False), (8192, "fused-single", False),
+                                            (32768, None, True)])
 def test_moe_layer_sampled_tokens_vs_oracle(gw, experts_shared, moe_form, rows, form, skew):
     """The published layer sizes (8192 tokens on one GPU; 32768 tokens with the Zipf(1.2) routing
     bias, the expert-parallel configuration's whole batch) against the faithful W4A4 oracle.  The
