@@ -12,6 +12,7 @@
 #include "common.cuh"
 #include "dense.h"
 #include "gemm_pair.h"
+#include "gemm_pair_moe.h"
 #include "gemm_tc.cuh"
 #include "kernels.h"
 
@@ -115,6 +116,7 @@ gw_status gw_debug_gemm_profile(void* device_buffer) {
   clear_error();
   set_gemm_profile_buffer(static_cast<long long*>(device_buffer));
   set_pair_profile_buffer(static_cast<long long*>(device_buffer));
+  set_pair_moe_profile_buffer(static_cast<long long*>(device_buffer));
   return GW_OK;
 }
 

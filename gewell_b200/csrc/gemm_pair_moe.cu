@@ -37,8 +37,7 @@ using namespace pair;
 constexpr int kExperts = 128;
 constexpr int kHidden = 2816;
 constexpr int kInter = 704;
-constexpr int kScaleWarps = 4, kEpilogueWarps = 8, kFirstEpilogueWarp = 2 + kScaleWarps;
-constexpr int kThreads = 32 * (2 + kScaleWarps + kEpilogueWarps);
+constexpr int kScaleWarps = 4, kFirstEpilogueWarp = 2 + kScaleWarps;
 constexpr uint32_t kDescHiSw128 = uint32_t(1024 >> 4) | (1u << 14) | (2u << 29);   // SBO 1024 B, version 1, SWIZZLE_128B
 
 __device__ __forceinline__ uint64_t make_desc(uint32_t lo16) { return (uint64_t(kDescHiSw128) << 32) | lo16; }
@@ -132,11 +131,26 @@ constexpr int kTmemCols = 512;
 static_assert(kAccCols + kStages * kSfSlotCols <= kTmemCols, "tensor memory over-subscribed");
 constexpr int kBarriers = 4 * kStages + 2;
 constexpr int kSmemBytes = kStages * kStageBytes + kBarriers * 8 + 16 + int(sizeof(WorkTable)) + 1024;
+// GeGLU (tanhf) and the FP4 quantisation cost about as many issue slots per tile as the tile's MMAs
+// take cycles; with two epilogue warps per scheduler their dependency chains set the pace of the
+// whole kernel, so there are four per scheduler: sixteen warps, each with 32 channels of 32 rows.
+constexpr int kEpilogueWarps = 16;
+constexpr int kThreads = 32 * (2 + kScaleWarps + kEpilogueWarps);     // 704: at most 88 registers per thread
+// A pair takes kChunk consecutive units (same token tile and expert, neighbouring channel tiles: the
+// expert's descriptors stay hot and the token tile is re-read from L2) before it strides on.
+constexpr int kChunk = 2;
+__device__ __forceinline__ int first_unit(int pair_index) { return pair_index * kChunk; }
+__device__ __forceinline__ int next_unit(int w, int pairs) {
+  return (w + 1) % kChunk != 0 ? w + 1 : w + 1 + (pairs - 1) * kChunk;
+}
 }  // namespace gu
 
-__global__ void __launch_bounds__(kThreads, 1)
+template <bool kProfile>   // cycle counters of the tuning aid live in an instantiation of their own
+__global__ void __launch_bounds__(gu::kThreads, 1)
 pair_moe_gate_up_kernel(const __grid_constant__ PairMoeParams p) {
   using namespace gu;
+  constexpr bool prof = kProfile;
+  const long long prof_start = prof ? clock64() : 0;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
@@ -190,7 +204,8 @@ pair_moe_gate_up_kernel(const __grid_constant__ PairMoeParams p) {
       const uint8_t* sf_gate = nullptr;
       const uint8_t* sf_up = nullptr;
       int info_of = -1;
-      for (int w = pair_index; w < total && !*abort_flag; w += pairs) {
+      long long prof_wait = 0;
+      for (int w = first_unit(pair_index); w < total && !*abort_flag; w = next_unit(w, pairs)) {
         decode_unit(table, w, kCTiles, u);
         if (info_of != u.e) {
           sf_gate = p.experts[u.e].scales[0];
@@ -198,7 +213,17 @@ pair_moe_gate_up_kernel(const __grid_constant__ PairMoeParams p) {
           info_of = u.e;
         }
         const int block = 2 * u.tile + int(rank);                 // this CTA's 128-row block of the expert
+        const bool have_rows = block * 128 < u.count;
         const int token_row = u.first + block * 128;
+        {
+          // the weight descriptor of the unit after this one is fetched while this one streams
+          const int next = next_unit(w, pairs);
+          if (next < total) {
+            Unit v = u;
+            decode_unit(table, next, kCTiles, v);
+            if (v.e != u.e) ptx::prefetch_tensormap(p.map_table + v.e * kMoeMapsPerExpert + int(rank));
+          }
+        }
         const uint8_t* sf_tokens = p.sf_tokens + (size_t(u.first / 128 + u.e) + block) * size_t(kKAtoms) * 512;
         const CUtensorMap* map_weights = p.map_table + u.e * kMoeMapsPerExpert + int(rank);   // gate or up
         const int weight_row = u.part * 128;
@@ -206,28 +231,38 @@ pair_moe_gate_up_kernel(const __grid_constant__ PairMoeParams p) {
         const uint8_t* sfw1 = sf_up + size_t(u.part) * kKAtoms * 512;
         bool failed = false;
         for (int ks = 0; ks < kKStages; ++ks) {
+          const long long t0 = prof ? clock64() : 0;
           if (!ptx::mbar_wait_bounded(empty_bar + stage, phase ^ 1)) {
             report(p.error, 0x12000000u | (blockIdx.x << 8) | stage, abort_flag);
             failed = true;
             break;
           }
+          if (prof) prof_wait += clock64() - t0;
           uint8_t* base = smem + stage * kStageBytes;
           // the scales go first and complete on their own barrier: the loader warps move them into tensor
           // memory while the operand tiles are still in flight
           uint64_t* sf_bar = sf_full_bar + stage;
-          ptx::mbar_expect_tx(sf_bar, kSfTokBytes + kSfWgtBytes);
-          ptx::bulk_load(base + kTokBytes + kWgtBytes, sf_tokens + size_t(ks) * kSfTokBytes, kSfTokBytes, sf_bar);
+          uint64_t* bar = full_bar + stage;
+          if (have_rows) {
+            ptx::mbar_expect_tx(sf_bar, kSfTokBytes + kSfWgtBytes);
+            ptx::bulk_load(base + kTokBytes + kWgtBytes, sf_tokens + size_t(ks) * kSfTokBytes, kSfTokBytes, sf_bar);
+          } else {
+            // This CTA's block lies past the expert's last row: its lanes are masked in the epilogue, so
+            // whatever the stage still holds serves as their operand and scales; only the shared column
+            // operand is fetched.
+            ptx::mbar_expect_tx(sf_bar, kSfWgtBytes);
+          }
           ptx::bulk_load(base + kTokBytes + kWgtBytes + kSfTokBytes, sfw0 + size_t(ks) * kSfTokBytes, kSfTokBytes, sf_bar);
           ptx::bulk_load(base + kTokBytes + kWgtBytes + 2 * kSfTokBytes, sfw1 + size_t(ks) * kSfTokBytes, kSfTokBytes,
                          sf_bar);
-          uint64_t* bar = full_bar + stage;
-          ptx::mbar_expect_tx(bar, kTokBytes + kWgtBytes);
-          ptx::tma_load_2d(base, &p.map_tokens, ks * 128, token_row, bar);
+          ptx::mbar_expect_tx(bar, (have_rows ? kTokBytes : 0) + kWgtBytes);
+          if (have_rows) ptx::tma_load_2d(base, &p.map_tokens, ks * 128, token_row, bar);
           ptx::tma_load_2d(base + kTokBytes, map_weights, ks * 128, weight_row, bar);
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
         if (failed) break;
       }
+      if (prof) p.profile[size_t(blockIdx.x) * 8 + 0] = prof_wait;
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -236,21 +271,27 @@ pair_moe_gate_up_kernel(const __grid_constant__ PairMoeParams p) {
       int stage = 0;
       uint32_t phase = 0, acc_phase = 0;
       const uint32_t idesc = idesc_pair_nvfp4(256);
-      for (int w = pair_index; w < total && !*abort_flag; w += pairs) {
+      long long prof_ready = 0, prof_issue = 0, prof_acc = 0;
+      for (int w = first_unit(pair_index); w < total && !*abort_flag; w = next_unit(w, pairs)) {
+        const long long ta = prof ? clock64() : 0;
         if (!ptx::mbar_wait_bounded(acc_empty_bar, acc_phase ^ 1)) {
           report(p.error, 0x22000000u | (blockIdx.x << 8), abort_flag);
           break;
         }
+        if (prof) prof_acc += clock64() - ta;
         ptx::tc_fence_after_sync();
         bool failed = false;
         for (int ks = 0; ks < kKStages; ++ks) {
           // sf_ready implies that both CTAs' operands have landed (the loader warps arrive after their
           // CTA's operand barrier), so this is the only wait of the stage
+          const long long t0 = prof ? clock64() : 0;
           if (!ptx::mbar_wait_bounded(sf_ready_bar + stage, phase)) {
             report(p.error, 0x32000000u | (blockIdx.x << 8) | stage, abort_flag);
             failed = true;
             break;
           }
+          const long long t1 = prof ? clock64() : 0;
+          if (prof) prof_ready += t1 - t0;
           ptx::tc_fence_after_sync();
           const uint32_t base16 = smem_base16 + uint32_t(stage) * uint32_t(kStageBytes >> 4);
           const uint32_t sf_tok = tmem_base + kAccCols + uint32_t(stage) * kSfSlotCols;
@@ -260,11 +301,16 @@ pair_moe_gate_up_kernel(const __grid_constant__ PairMoeParams p) {
             mma_pair_nvfp4(tmem_base, make_desc(base16 + 2 * kb), make_desc(base16 + (kTokBytes >> 4) + 2 * kb), idesc,
                            sf_tok + 4 * kb, sf_wgt + 8 * kb, (ks | kb) != 0 ? 1u : 0u);
           commit_pair(empty_bar + stage);
+          if (prof) prof_issue += clock64() - t1;
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
         if (failed) break;
         commit_pair(acc_full_bar);
         acc_phase ^= 1;
+      }
+      if (prof) {
+        long long* row = p.profile + size_t(blockIdx.x) * 8;
+        row[1] = prof_ready; row[2] = prof_issue; row[3] = prof_acc; row[6] = clock64() - prof_start;
       }
     }
     __syncwarp();
@@ -274,7 +320,7 @@ pair_moe_gate_up_kernel(const __grid_constant__ PairMoeParams p) {
     const uint32_t leader_sf_ready = leader_address(sf_ready_bar);
     int stage = 0;
     uint32_t phase = 0;
-    for (int w = pair_index; w < total && !*abort_flag; w += pairs) {
+    for (int w = first_unit(pair_index); w < total && !*abort_flag; w = next_unit(w, pairs)) {
       bool failed = false;
       for (int ks = 0; ks < kKStages; ++ks) {
         if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(sf_full_bar + stage, phase))) {
@@ -321,21 +367,22 @@ pair_moe_gate_up_kernel(const __grid_constant__ PairMoeParams p) {
   } else {
     // ------------------------------------------------------------------ epilogue: GeGLU + FP4 quantise
     // Columns [0,128) of the accumulator are the gate channels of this tile, [128,256) the up channels
-    // of the same 128 output channels; this warp owns 64 of them (four K16 blocks of the down input) for
+    // of the same 128 output channels; this warp owns 32 of them (two K16 blocks of the down input) for
     // the 32 token rows of its lane quadrant.  The accumulator has no second stage (tensor memory is
     // full), so the warp first drains its share into registers -- scaled and rounded to BF16, which is
     // what GeGLU consumes anyway, two values per register -- and hands the accumulator back at once;
     // the transcendental math and the stores then overlap the next tile's MMAs.
     const int quad = warp % 4;
-    const int col_half = (warp - kFirstEpilogueWarp) / 4;
+    const int quarter = (warp - kFirstEpilogueWarp) / 4;
     const uint32_t leader_acc_empty = leader_address(acc_empty_bar);
     uint32_t acc_phase = 0;
     Unit u{-1, 0, 0, 0, 0};
     float alpha_gate = 0.0F, alpha_up = 0.0F, inverse_scale = 0.0F;
     int info_of = -1;
+    long long prof_wait = 0, prof_work = 0;
     bf16* cap_gu = static_cast<bf16*>(p.capture_gate_up);
     bf16* cap_act = static_cast<bf16*>(p.capture_activated);
-    for (int w = pair_index; w < total && !*abort_flag; w += pairs) {
+    for (int w = first_unit(pair_index); w < total && !*abort_flag; w = next_unit(w, pairs)) {
       decode_unit(table, w, kCTiles, u);
       if (info_of != u.e) {
         alpha_gate = p.experts[u.e].alpha[0];
@@ -343,24 +390,27 @@ pair_moe_gate_up_kernel(const __grid_constant__ PairMoeParams p) {
         inverse_scale = p.experts[u.e].inverse_input_scale[2];
         info_of = u.e;
       }
+      const long long t0 = prof ? clock64() : 0;
       if (!ptx::mbar_wait_warp(acc_full_bar, acc_phase)) {
         report(p.error, 0x42000000u | (blockIdx.x << 8), abort_flag);
         break;
       }
+      const long long t1 = prof ? clock64() : 0;
+      if (prof) prof_wait += t1 - t0;
       acc_phase ^= 1;
       ptx::tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16);
       const int l_index = (2 * u.tile + int(rank)) * 128 + quad * 32 + lane;     // row inside the expert's group
       const bool l_ok = l_index < u.count;
-      const int channel0 = u.part * 128 + col_half * 64;                          // first channel of this warp
+      const int channel0 = u.part * 128 + quarter * 32;                           // first channel of this warp
       const bool active = channel0 < kInter;                                      // warp uniform
-      uint32_t gate_words[32], up_words[32];                                      // BF16 pairs
+      uint32_t gate_words[16], up_words[16];                                      // BF16 pairs
       if (active) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < 2; ++j) {
           uint32_t g[16], v[16];
-          ptx::tmem_load16(taddr + col_half * 64 + 16 * j, g);
-          ptx::tmem_load16(taddr + 128 + col_half * 64 + 16 * j, v);
+          ptx::tmem_load16(taddr + quarter * 32 + 16 * j, g);
+          ptx::tmem_load16(taddr + 128 + quarter * 32 + 16 * j, v);
           ptx::tmem_load_wait();
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
@@ -376,10 +426,10 @@ pair_moe_gate_up_kernel(const __grid_constant__ PairMoeParams p) {
       if (lane == 0) arrive_cluster(leader_acc_empty);               // the next tile's MMAs may start
       if (active) {
         const size_t row = size_t(u.first) + l_index;
-        uint32_t packed_words[8];
-        uint32_t scale_word = 0;
+        uint32_t packed_words[4];
+        uint32_t scale_pair = 0;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < 2; ++j) {
           float act[16];
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
@@ -393,7 +443,7 @@ pair_moe_gate_up_kernel(const __grid_constant__ PairMoeParams p) {
           const uint8_t code = float_to_e4m3(inverse_scale * (amax * rcp_approx_ftz(6.0F)));
           const float block_scale = e4m3_to_float(code);
           const float factor = block_scale == 0.0F ? 0.0F : rcp_approx_ftz(block_scale * rcp_approx_ftz(inverse_scale));
-          scale_word |= uint32_t(code) << (8 * j);
+          scale_pair |= uint32_t(code) << (8 * j);
           uint32_t lo = 0, hi = 0;
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
@@ -418,13 +468,20 @@ pair_moe_gate_up_kernel(const __grid_constant__ PairMoeParams p) {
           }
         }
         if (l_ok) {
-          uint4* dst = reinterpret_cast<uint4*>(p.packed_out + row * size_t(kInter / 2) + channel0 / 2);
-          dst[0] = make_uint4(packed_words[0], packed_words[1], packed_words[2], packed_words[3]);
-          dst[1] = make_uint4(packed_words[4], packed_words[5], packed_words[6], packed_words[7]);
+          *reinterpret_cast<uint4*>(p.packed_out + row * size_t(kInter / 2) + channel0 / 2) =
+              make_uint4(packed_words[0], packed_words[1], packed_words[2], packed_words[3]);
           const size_t region = size_t(u.first / 128 + u.e) * 128 * (kInter / 16);
-          *reinterpret_cast<uint32_t*>(p.scales_out + region + scale_offset(l_index, channel0 / 16, kInter)) = scale_word;
+          // two neighbouring K16 blocks (an even and the following odd one): two adjacent bytes of the tile
+          *reinterpret_cast<uint16_t*>(p.scales_out + region + scale_offset(l_index, channel0 / 16, kInter)) =
+              uint16_t(scale_pair);
         }
       }
+      if (prof) prof_work += clock64() - t1;
+    }
+    if (prof && lane == 0 && warp == kFirstEpilogueWarp) {
+      long long* row = p.profile + size_t(blockIdx.x) * 8;
+      row[4] = prof_wait;
+      row[5] = prof_work;
     }
   }
 
@@ -472,11 +529,18 @@ static_assert(kSfBCol + kBStages * kSfSlotCols <= kTmemCols, "tensor memory over
 constexpr int kBarriers = 3 * 2 + 4 * kBStages + 2 * 2;
 constexpr int kSmemBytes = 2 * kABufBytes + kBStages * kBStageBytes + kBarriers * 8 + 16 + int(sizeof(WorkTable)) + 1024;
 static_assert(kSmemBytes <= 227 * 1024, "shared memory over-subscribed");
+// The epilogue of a tile (drain, scale, transpose, store 32 KB) has to fit into the ~900 cycles of the
+// next tile's MMAs; with two warps per scheduler it took ~1500.  Sixteen warps, 32 channels of 32 rows each.
+constexpr int kEpilogueWarps = 16;
+constexpr int kThreads = 32 * (2 + kScaleWarps + kEpilogueWarps);
 }  // namespace dn
 
-__global__ void __launch_bounds__(kThreads, 1)
+template <bool kProfile>
+__global__ void __launch_bounds__(dn::kThreads, 1)
 pair_moe_down_kernel(const __grid_constant__ PairMoeParams p) {
   using namespace dn;
+  constexpr bool prof = kProfile;
+  const long long prof_start = prof ? clock64() : 0;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* a_buf = smem;                                       // [2][kABufBytes]
@@ -558,6 +622,7 @@ pair_moe_down_kernel(const __grid_constant__ PairMoeParams p) {
       Unit u{-1, 0, 0, 0, 0};
       const uint8_t* sf_weights = nullptr;
       int info_of = -1;
+      long long prof_wait = 0;
       bool failed = pair_index < total ? !request_rows(pair_index, 0) : false;
       for (int w = pair_index; w < total && !failed && !*abort_flag; w += pairs, ++number) {
         decode_unit(table, w, kChunks, u);
@@ -568,11 +633,13 @@ pair_moe_down_kernel(const __grid_constant__ PairMoeParams p) {
         const CUtensorMap* map_weights = p.map_table + u.e * kMoeMapsPerExpert + 3;   // down weights, 64-row boxes
         for (int t = 0; t < kTilesPerUnit; ++t) {
           const int c_tile = u.part * kTilesPerUnit + t;
+          const long long t0 = prof ? clock64() : 0;
           if (!ptx::mbar_wait_bounded(b_empty_bar + stage, phase ^ 1)) {
             report(p.error, 0x14000000u | (blockIdx.x << 8) | stage, abort_flag);
             failed = true;
             break;
           }
+          if (prof) prof_wait += clock64() - t0;
           uint8_t* base = b_ring + stage * kBStageBytes;
           uint64_t* sf_bar = b_sf_full_bar + stage;
           ptx::mbar_expect_tx(sf_bar, kSfBytes);
@@ -591,6 +658,7 @@ pair_moe_down_kernel(const __grid_constant__ PairMoeParams p) {
           }
         }
       }
+      if (prof) p.profile[size_t(blockIdx.x) * 8 + 0] = prof_wait;
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -601,26 +669,33 @@ pair_moe_down_kernel(const __grid_constant__ PairMoeParams p) {
       const uint32_t idesc = idesc_pair_nvfp4(kTileCols);
       const uint32_t a_base16 = ptx::smem_u32(a_buf) >> 4, b_base16 = ptx::smem_u32(b_ring) >> 4;
       bool failed = false;
+      long long prof_rows = 0, prof_ready = 0, prof_issue = 0, prof_acc = 0;
       for (int w = pair_index; w < total && !failed && !*abort_flag; w += pairs, ++number) {
         const int buffer = number & 1;
+        const long long tr = prof ? clock64() : 0;
         if (!ptx::mbar_wait_bounded(a_ready_bar + buffer, uint32_t(number >> 1) & 1u)) {
           report(p.error, 0x23000000u | (blockIdx.x << 8) | buffer, abort_flag);
           break;
         }
+        if (prof) prof_rows += clock64() - tr;
         const uint32_t a16 = a_base16 + uint32_t(buffer) * uint32_t(kABufBytes >> 4);
         const uint32_t sfa = tmem_base + kSfACol + uint32_t(buffer) * kSfSlotCols;
         for (int t = 0; t < kTilesPerUnit; ++t, ++tiles) {
           const int acc = tiles & 1;
+          const long long ta = prof ? clock64() : 0;
           if (!ptx::mbar_wait_bounded(acc_empty_bar + acc, (uint32_t(tiles >> 1) & 1u) ^ 1u)) {
             report(p.error, 0x24000000u | (blockIdx.x << 8) | acc, abort_flag);
             failed = true;
             break;
           }
+          const long long tb = prof ? clock64() : 0;
           if (!ptx::mbar_wait_bounded(b_ready_bar + stage, phase)) {
             report(p.error, 0x33000000u | (blockIdx.x << 8) | stage, abort_flag);
             failed = true;
             break;
           }
+          const long long tc = prof ? clock64() : 0;
+          if (prof) { prof_acc += tb - ta; prof_ready += tc - tb; }
           ptx::tc_fence_after_sync();
           const uint32_t b16 = b_base16 + uint32_t(stage) * uint32_t(kBStageBytes >> 4);
           const uint32_t sfb = tmem_base + kSfBCol + uint32_t(stage) * kSfSlotCols;
@@ -632,9 +707,14 @@ pair_moe_down_kernel(const __grid_constant__ PairMoeParams p) {
                            sfb + 4 * kb, kb != 0 ? 1u : 0u);
           commit_pair(b_empty_bar + stage);
           commit_pair(acc_full_bar + acc);
+          if (prof) prof_issue += clock64() - tc;
           if (++stage == kBStages) { stage = 0; phase ^= 1; }
         }
         commit_pair(a_empty_bar + buffer);
+      }
+      if (prof) {
+        long long* row = p.profile + size_t(blockIdx.x) * 8;
+        row[1] = prof_ready; row[2] = prof_issue; row[3] = prof_acc; row[6] = clock64() - prof_start; row[7] = prof_rows;
       }
     }
     __syncwarp();
@@ -695,7 +775,7 @@ pair_moe_down_kernel(const __grid_constant__ PairMoeParams p) {
     // 16-byte units inside every group of four lanes then lets four neighbouring lanes write 64
     // contiguous bytes of one row.
     const int quad = warp % 4;
-    const int col_half = (warp - kFirstEpilogueWarp) / 4;            // 64 of the tile's 128 channels
+    const int quarter = (warp - kFirstEpilogueWarp) / 4;             // 32 of the tile's 128 channels
     const uint32_t leader_acc_empty = leader_address(acc_empty_bar);
     int tiles = 0;
     Unit u{-1, 0, 0, 0, 0};
@@ -703,6 +783,7 @@ pair_moe_down_kernel(const __grid_constant__ PairMoeParams p) {
     int info_of = -1;
     bf16* out = static_cast<bf16*>(p.out);
     bool failed = false;
+    long long prof_wait = 0, prof_work = 0;
     for (int w = pair_index; w < total && !failed && !*abort_flag; w += pairs) {
       decode_unit(table, w, kChunks, u);
       if (info_of != u.e) {
@@ -721,24 +802,26 @@ pair_moe_down_kernel(const __grid_constant__ PairMoeParams p) {
       }
       for (int t = 0; t < kTilesPerUnit; ++t, ++tiles) {
         const int acc = tiles & 1;
+        const long long t0 = prof ? clock64() : 0;
         if (!ptx::mbar_wait_warp(acc_full_bar + acc, uint32_t(tiles >> 1) & 1u)) {
           report(p.error, 0x43000000u | (blockIdx.x << 8) | acc, abort_flag);
           failed = true;
           break;
         }
+        const long long t1 = prof ? clock64() : 0;
+        if (prof) prof_wait += t1 - t0;
         ptx::tc_fence_after_sync();
         const uint32_t taddr = tmem_base + uint32_t(acc) * kTileCols + (uint32_t(quad * 32) << 16);
-        const int c_base = (u.part * kTilesPerUnit + t) * kTileCols + col_half * 64;
-        uint4 unit[2][4];
-#pragma unroll
-        for (int ch = 0; ch < 2; ++ch) {
+        const int c_base = (u.part * kTilesPerUnit + t) * kTileCols + quarter * 32;
+        uint4 unit[4];
+        {
           uint32_t r[32];
-          ptx::tmem_load16(taddr + col_half * 64 + 32 * ch, r);
-          ptx::tmem_load16(taddr + col_half * 64 + 32 * ch + 16, r + 16);
+          ptx::tmem_load16(taddr + quarter * 32, r);
+          ptx::tmem_load16(taddr + quarter * 32 + 16, r + 16);
           ptx::tmem_load_wait();
 #pragma unroll
           for (int q = 0; q < 4; ++q)
-            unit[ch][q] = make_uint4(
+            unit[q] = make_uint4(
                 pack_bf16x2(__fmul_rn(__uint_as_float(r[8 * q]), alpha), __fmul_rn(__uint_as_float(r[8 * q + 1]), alpha)),
                 pack_bf16x2(__fmul_rn(__uint_as_float(r[8 * q + 2]), alpha), __fmul_rn(__uint_as_float(r[8 * q + 3]), alpha)),
                 pack_bf16x2(__fmul_rn(__uint_as_float(r[8 * q + 4]), alpha), __fmul_rn(__uint_as_float(r[8 * q + 5]), alpha)),
@@ -747,24 +830,27 @@ pair_moe_down_kernel(const __grid_constant__ PairMoeParams p) {
         ptx::tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) arrive_cluster(leader_acc_empty + acc * 8);   // this accumulator stage may be overwritten
+        transpose_units(unit, lane);
+        const int c = c_base + 8 * (lane & 3);
 #pragma unroll
-        for (int ch = 0; ch < 2; ++ch) {
-          transpose_units(unit[ch], lane);
-          const int c = c_base + 32 * ch + 8 * (lane & 3);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            if (i >= rows_left) continue;
-            bf16* dst;
-            if (p.row_dest != nullptr) {
-              if (group_dest[i] == 0) continue;       // a row without a home (reported when the table was built)
-              dst = reinterpret_cast<bf16*>(group_dest[i]) + c;
-            } else {
-              dst = out + (sorted_row0 + i) * size_t(kHidden) + c;
-            }
-            *reinterpret_cast<uint4*>(dst) = unit[ch][i];
+        for (int i = 0; i < 4; ++i) {
+          if (i >= rows_left) continue;
+          bf16* dst;
+          if (p.row_dest != nullptr) {
+            if (group_dest[i] == 0) continue;         // a row without a home (reported when the table was built)
+            dst = reinterpret_cast<bf16*>(group_dest[i]) + c;
+          } else {
+            dst = out + (sorted_row0 + i) * size_t(kHidden) + c;
           }
+          *reinterpret_cast<uint4*>(dst) = unit[i];
         }
+        if (prof) prof_work += clock64() - t1;
       }
+    }
+    if (prof && lane == 0 && warp == kFirstEpilogueWarp) {
+      long long* row = p.profile + size_t(blockIdx.x) * 8;
+      row[4] = prof_wait;
+      row[5] = prof_work;
     }
   }
 
@@ -777,9 +863,11 @@ pair_moe_down_kernel(const __grid_constant__ PairMoeParams p) {
   }
 }
 
+long long* g_pair_moe_profile = nullptr;
+
 template <typename Kernel>
-cudaError_t launch_pair_kernel(Kernel kernel, int smem_bytes, const PairMoeParams& params, int sm_count, bool* configured,
-                               cudaStream_t stream) {
+cudaError_t launch_pair_kernel(Kernel kernel, int threads, int smem_bytes, const PairMoeParams& params, int sm_count,
+                               bool* configured, cudaStream_t stream) {
   if (!*configured) {
     cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
     if (status != cudaSuccess) return status;
@@ -787,7 +875,7 @@ cudaError_t launch_pair_kernel(Kernel kernel, int smem_bytes, const PairMoeParam
   }
   cudaLaunchConfig_t config{};
   config.gridDim = dim3(2 * (sm_count / 2));
-  config.blockDim = dim3(kThreads);
+  config.blockDim = dim3(threads);
   config.dynamicSmemBytes = smem_bytes;
   config.stream = stream;
   cudaLaunchAttribute attributes[2]{};
@@ -805,16 +893,30 @@ cudaError_t launch_pair_kernel(Kernel kernel, int smem_bytes, const PairMoeParam
 
 }  // namespace
 
-cudaError_t launch_pair_moe_gate_up(const PairMoeParams& params, int sm_count, cudaStream_t stream) {
-  static bool configured_on[kMaxDeviceSlots] = {};   // the attribute is per GPU
-  return launch_pair_kernel(pair_moe_gate_up_kernel, gu::kSmemBytes, params, sm_count,
-                            &configured_on[current_device_slot()], stream);
+void set_pair_moe_profile_buffer(long long* device_buffer) { g_pair_moe_profile = device_buffer; }
+
+cudaError_t launch_pair_moe_gate_up(const PairMoeParams& params_in, int sm_count, cudaStream_t stream) {
+  static bool configured_on[2][kMaxDeviceSlots] = {};   // the attribute is per GPU (and per instantiation)
+  PairMoeParams params = params_in;
+  params.profile = g_pair_moe_profile;                   // gate/up: first half of the buffer
+  const int slot = current_device_slot();
+  if (params.profile != nullptr)
+    return launch_pair_kernel(pair_moe_gate_up_kernel<true>, gu::kThreads, gu::kSmemBytes, params, sm_count,
+                              &configured_on[1][slot], stream);
+  return launch_pair_kernel(pair_moe_gate_up_kernel<false>, gu::kThreads, gu::kSmemBytes, params, sm_count,
+                            &configured_on[0][slot], stream);
 }
 
-cudaError_t launch_pair_moe_down(const PairMoeParams& params, int sm_count, cudaStream_t stream) {
-  static bool configured_on[kMaxDeviceSlots] = {};
-  return launch_pair_kernel(pair_moe_down_kernel, dn::kSmemBytes, params, sm_count,
-                            &configured_on[current_device_slot()], stream);
+cudaError_t launch_pair_moe_down(const PairMoeParams& params_in, int sm_count, cudaStream_t stream) {
+  static bool configured_on[2][kMaxDeviceSlots] = {};
+  PairMoeParams params = params_in;
+  params.profile = g_pair_moe_profile ? g_pair_moe_profile + 148 * 8 : nullptr;   // down: second half
+  const int slot = current_device_slot();
+  if (params.profile != nullptr)
+    return launch_pair_kernel(pair_moe_down_kernel<true>, dn::kThreads, dn::kSmemBytes, params, sm_count,
+                              &configured_on[1][slot], stream);
+  return launch_pair_kernel(pair_moe_down_kernel<false>, dn::kThreads, dn::kSmemBytes, params, sm_count,
+                            &configured_on[0][slot], stream);
 }
 
 }  // namespace gw

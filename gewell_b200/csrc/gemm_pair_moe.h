@@ -38,7 +38,15 @@ struct PairMoeParams {
   void* out;
   const uint64_t* row_dest;        // optional: byte address of the home of every sorted row (0 = none)
   uint32_t* error;                 // device error word (0 = fine)
+  long long* profile;              // optional [grid][8] cycle counters (tuning aid), normally nullptr
 };
+
+// Tuning aid: later launches write per-CTA cycle counters into this device buffer ([2][148][8] int64: the
+// gate/up kernel into the first half, the down kernel into the second): [0] producer waiting for a free
+// stage, [1] MMA lane waiting for a stage's data, [2] MMA lane issuing, [3] MMA lane waiting for the
+// accumulator, [4] an epilogue warp waiting for the accumulator, [5] that warp working, [6] total,
+// [7] down: MMA lane waiting for a unit's resident rows.  nullptr switches it off.
+void set_pair_moe_profile_buffer(long long* device_buffer);
 
 cudaError_t launch_pair_moe_gate_up(const PairMoeParams& params, int sm_count, cudaStream_t stream);
 cudaError_t launch_pair_moe_down(const PairMoeParams& params, int sm_count, cudaStream_t stream);

@@ -470,8 +470,8 @@ moe_quantize_kernel(const uint4* __restrict__ input, const int32_t* __restrict__
 }
 
 // ---------------------------------------------------------------------------
-// 5b. The same quantisation, token-major: one warp reads a token's row once
-//     (a lane keeps six K16 blocks as packed BF16 and their maxima) and writes
+// 5b. The same quantisation, token-major: two warps read a token's row once
+//     (a lane keeps three K16 blocks as packed BF16 and their maxima) and write
 //     the token's eight quantised copies, one per chosen expert, each with that
 //     expert's input scale, at the copy's sorted position.  Arithmetic per
 //     value is that of kernel 5, so the bytes are identical; the input is read
@@ -484,18 +484,23 @@ moe_quantize_tokens_kernel(const uint4* __restrict__ input, const int32_t* __res
                            uint2* __restrict__ packed, uint8_t* __restrict__ scales) {
   griddep_launch();
   griddep_wait();     // results of earlier kernels in the stream are read from here on
+  // Two warps per token, each with one half of the row (88 K16 blocks, three per lane): half the
+  // registers of a whole row per warp, so twice as many warps are resident to cover the loads.
   constexpr uint32_t kBlocks = kHidden / 16;            // 176
-  constexpr int kPerLane = (kBlocks + 31) / 32;         // 6
-  const uint32_t token = (blockIdx.x * 256 + threadIdx.x) / 32, lane = threadIdx.x % 32;
+  constexpr uint32_t kHalfBlocks = kBlocks / 2;         // 88
+  constexpr int kPerLane = (kHalfBlocks + 31) / 32;     // 3
+  const uint32_t warp_index = (blockIdx.x * 256 + threadIdx.x) / 32, lane = threadIdx.x % 32;
+  const uint32_t token = warp_index / 2, half = warp_index % 2;
   if (token >= tokens) return;
   const uint32_t n = tokens * kTopK;
   uint32_t raw[kPerLane][8];
   float amax[kPerLane];
 #pragma unroll
   for (int i = 0; i < kPerLane; ++i) {
-    const uint32_t kb = lane + 32 * i;
+    const uint32_t local = lane + 32 * i;
+    const uint32_t kb = half * kHalfBlocks + local;
     amax[i] = 0.0F;
-    if (kb < kBlocks) {
+    if (local < kHalfBlocks) {
       const uint4 a = input[2 * (size_t(token) * kBlocks + kb)], b = input[2 * (size_t(token) * kBlocks + kb) + 1];
       raw[i][0] = a.x; raw[i][1] = a.y; raw[i][2] = a.z; raw[i][3] = a.w;
       raw[i][4] = b.x; raw[i][5] = b.y; raw[i][6] = b.z; raw[i][7] = b.w;
@@ -516,8 +521,9 @@ moe_quantize_tokens_kernel(const uint4* __restrict__ input, const int32_t* __res
       const size_t region = (size_t(part) * scale_rows + size_t(first / 128 + e) * 128) * kBlocks;
 #pragma unroll
       for (int i = 0; i < kPerLane; ++i) {
-        const uint32_t kb = lane + 32 * i;
-        if (kb >= kBlocks) continue;
+        const uint32_t local = lane + 32 * i;
+        const uint32_t kb = half * kHalfBlocks + local;
+        if (local >= kHalfBlocks) continue;
         const uint8_t scale_code = float_to_e4m3(inverse_scale * (amax[i] * rcp_approx_ftz(6.0F)));
         const float block_scale = e4m3_to_float(scale_code);
         const float factor =
@@ -574,6 +580,54 @@ moe_combine_kernel(const uint4* __restrict__ down, const int32_t* __restrict__ i
   for (int i = 0; i < 4; ++i)
     words[i] = (__float_as_uint(sum[2 * i]) >> 16) | (__float_as_uint(sum[2 * i + 1]) & 0xFFFF0000u);
   output[index] = make_uint4(words[0], words[1], words[2], words[3]);
+}
+
+// The same fold for the layer's own width (2816 = 352 vectors), one block per token: the eight row
+// numbers and weights are fetched once per block, and the arithmetic is packed -- the product of two
+// channels is rounded to BF16 by one cvt.rn.bf16x2.f32, and the BF16 add of the running sum is a
+// single bfloat162 add.  That add rounds the exact sum once; the reference rounds FP32(a + b) to BF16,
+// which is the same value: the exact sum of two BF16 numbers either fits FP32's 24 bits or its smaller
+// term lies far below half a BF16 ulp of the larger one.
+__global__ void __launch_bounds__(kHidden / 8)
+moe_combine_token_kernel(const uint4* __restrict__ down, const int32_t* __restrict__ inverse,
+                         const float* __restrict__ weights, uint32_t rows, uint4* __restrict__ output) {
+  griddep_launch();
+  griddep_wait();     // results of earlier kernels in the stream are read from here on
+  constexpr uint32_t kVectors = kHidden / 8;
+  __shared__ int32_t slot_row[kTopK];
+  __shared__ float slot_weight[kTopK];
+  const uint32_t token = blockIdx.x;
+  if (threadIdx.x < kTopK) {
+    slot_row[threadIdx.x] = inverse[size_t(token) * kTopK + threadIdx.x];
+    slot_weight[threadIdx.x] = weights[size_t(token) * kTopK + threadIdx.x];
+  }
+  __syncthreads();
+  const uint32_t v = threadIdx.x;
+  uint4 raw[kTopK];
+#pragma unroll
+  for (int j = 0; j < kTopK; ++j)          // all eight gathered loads are in flight before the fold starts
+    raw[j] = __ldcs(down + size_t(slot_row[j]) * kVectors + v);
+  __nv_bfloat162 sum[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) sum[i] = __floats2bfloat162_rn(0.0F, 0.0F);
+#pragma unroll
+  for (int j = 0; j < kTopK; ++j) {
+    const float w = slot_weight[j];
+    const uint32_t words[4] = {raw[j].x, raw[j].y, raw[j].z, raw[j].w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __nv_bfloat162 product = __floats2bfloat162_rn(__fmul_rn(__uint_as_float(words[i] << 16), w),
+                                                           __fmul_rn(__uint_as_float(words[i] & 0xFFFF0000u), w));
+      sum[i] = __hadd2(sum[i], product);
+    }
+  }
+  uint4 result;
+  result.x = *reinterpret_cast<const uint32_t*>(&sum[0]);
+  result.y = *reinterpret_cast<const uint32_t*>(&sum[1]);
+  result.z = *reinterpret_cast<const uint32_t*>(&sum[2]);
+  result.w = *reinterpret_cast<const uint32_t*>(&sum[3]);
+  __stcs(output + size_t(token) * kVectors + v, result);
+  (void)rows;
 }
 
 __global__ void __launch_bounds__(256)
@@ -852,7 +906,7 @@ cudaError_t launch_moe_quantize_tokens(const void* input, const int32_t* keys, c
                                        const int32_t* offsets, const MoeExpertInfo* experts, uint32_t tokens,
                                        uint32_t scale_rows, int parts, uint8_t* packed, uint8_t* scales,
                                        cudaStream_t stream) {
-  launch_pdl(moe_quantize_tokens_kernel, blocks_for(size_t(tokens) * 32), 256, stream, 
+  launch_pdl(moe_quantize_tokens_kernel, blocks_for(size_t(tokens) * 64), 256, stream, 
       static_cast<const uint4*>(input), keys, inverse, offsets, experts, tokens, scale_rows, parts,
       reinterpret_cast<uint2*>(packed), scales);
   return cudaGetLastError();
@@ -870,6 +924,11 @@ cudaError_t launch_moe_activate_quantize(const void* gate_up, const int32_t* sor
 
 cudaError_t launch_moe_combine(const void* down, const int32_t* inverse, const float* weights, uint32_t rows,
                                uint32_t width, void* output, cudaStream_t stream) {
+  if (width == kHidden) {
+    launch_pdl(moe_combine_token_kernel, rows, kHidden / 8, stream, static_cast<const uint4*>(down), inverse, weights, rows,
+               static_cast<uint4*>(output));
+    return cudaGetLastError();
+  }
   launch_pdl(moe_combine_kernel, blocks_for(size_t(rows) * (width / 8)), 256, stream, 
       static_cast<const uint4*>(down), inverse, weights, rows, width, static_cast<uint4*>(output));
   return cudaGetLastError();

@@ -133,10 +133,15 @@ def test_dispatch_zero_rows_and_capacity(gw):
         gw.MoeWorkspace(0)
 
 
-def test_combine_kernel_exact(gw):
+@pytest.mark.parametrize("width", [H, 704])
+def test_combine_kernel_exact(gw, width):
+    """Ordered BF16 fold, bit for bit: the layer's own width runs the block-per-token kernel with
+    packed BF16 adds, any other width the generic kernel."""
+    H = width
     rows = 37
     rng = np.random.default_rng(0)
     down = bf16_normal((rows * 8, H), 7)
+    down[5, :8] = torch.tensor([0.0, -0.0, 1e-30, -1e-30, 3.0e38, -3.0e38, 1.0, -1.0], dtype=torch.bfloat16)
     weights = rng.random((rows, 8)).astype(np.float32)
     inverse = rng.permutation(rows * 8).astype(np.int32)
     out = gw.moe_combine(down.cuda(), torch.from_numpy(inverse).cuda(), torch.from_numpy(weights).cuda(), rows)
