@@ -13,6 +13,8 @@ GW_OK, GW_INVALID_ARGUMENT, GW_CUDA_ERROR, GW_KERNEL_ERROR, GW_UNSUPPORTED = ran
 TRANSFORM_IDENTITY, TRANSFORM_GELU_TANH_MULTIPLY = 0, 1
 QDQ_BF16, QDQ_FP8, QDQ_NVFP4 = 0, 1, 2
 STORAGE_BF16, STORAGE_NVFP4_W4A4, STORAGE_FP8_W8A8, STORAGE_ABSENT = 0, 1, 2, 3
+POLICY_ALWAYS, POLICY_PREFILL = 0, 1
+PHASE_PREFILL, PHASE_DECODE = 0, 1
 
 
 class Projection(ctypes.Structure):
@@ -59,11 +61,24 @@ _SIGNATURES = {
     "gw_fp8_plan_run": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_float, c_void_p, c_void_p, c_void_p,
                                 c_size_t, c_void_p, c_int]),
     "gw_fp8_plan_destroy": (None, [c_void_p]),
+    "gw_bf16_plan_create": (c_int, [c_uint32, c_uint32, c_uint32, POINTER(c_void_p)]),
+    "gw_bf16_plan_scratch_bytes": (c_size_t, [c_void_p]),
+    "gw_bf16_plan_run": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "gw_bf16_plan_destroy": (None, [c_void_p]),
+    "gw_nvfp4_fp4_activations": (c_int, [c_int, c_int]),
+    "gw_bind_projection": (c_int, [c_uint32, c_uint32, c_uint32, c_void_p, c_void_p, c_size_t, POINTER(Projection)]),
+    "gw_projection_workspace_create": (c_int, [POINTER(Projection), c_uint32, c_uint32, c_int, c_void_p, POINTER(c_void_p)]),
+    "gw_projection_workspace_prepare": (c_int, [c_void_p, c_uint32, c_int]),
+    "gw_projection_workspace_run": (c_int, [c_void_p, POINTER(Projection), c_void_p, c_void_p]),
+    "gw_projection_workspace_bytes": (c_size_t, [c_void_p]),
+    "gw_projection_workspace_destroy": (None, [c_void_p]),
     "gw_absmax_bf16": (c_int, [c_void_p, c_uint64, c_void_p, c_void_p]),
     "gw_weight_qdq_apply": (c_int, [c_int, c_void_p, c_uint64, c_void_p, c_void_p]),
     "gw_moe_expert_table_create": (c_int, [POINTER(ExpertWeights), c_uint32, POINTER(c_void_p)]),
     "gw_moe_expert_table_destroy": (None, [c_void_p]),
     "gw_moe_create": (c_int, [c_uint32, POINTER(c_void_p)]),
+    "gw_moe_create_ex": (c_int, [c_uint32, c_uint32, POINTER(c_void_p)]),
+    "gw_moe_expert_table_enable_w4a16": (c_int, [c_void_p, c_void_p]),
     "gw_moe_destroy": (None, [c_void_p]),
     "gw_moe_dispatch": (c_int, [c_void_p, c_void_p, c_void_p, c_uint32, c_void_p]),
     "gw_moe_run": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_uint32, c_int, c_int,

@@ -226,10 +226,17 @@ gw_status gw_nvfp4_plan_create(uint32_t rows, uint32_t input_width, uint32_t out
   // by the plan and room for FP32 partial tiles in the scratch.  Without a usable device
   // (or memory for the counters) the plan falls back to whole tiles per CTA.
   p->total_bytes = p->split_offset;
-  if (p->descriptors.allocate_split_counters(rows, output_width) == cudaSuccess && p->descriptors.split_counters)
-    p->total_bytes += align_up(dense_split_bytes(rows, output_width), 256);
-  else
+  const cudaError_t counters = p->descriptors.allocate_split_counters(rows, output_width);
+  if (counters != cudaSuccess) {
     (void)cudaGetLastError();
+    // Without any device the plan is only a shape record (it cannot run); every other failure is an error,
+    // not a silent fall-back to whole tiles per CTA, which would be a performance cliff.
+    if (counters != cudaErrorNoDevice && counters != cudaErrorInsufficientDriver) {
+      delete p;
+      return fail(GW_CUDA_ERROR, std::string("plan: tile counters of the K split: ") + cudaGetErrorString(counters));
+    }
+  }
+  if (p->descriptors.split_counters) p->total_bytes += align_up(dense_split_bytes(rows, output_width), 256);
   *plan = p;
   return GW_OK;
 }
@@ -317,10 +324,17 @@ gw_status gw_fp8_plan_create(uint32_t rows, uint32_t input_width, uint32_t outpu
   // by the plan and room for FP32 partial tiles in the scratch.  Without a usable device
   // (or memory for the counters) the plan falls back to whole tiles per CTA.
   p->total_bytes = p->split_offset;
-  if (p->descriptors.allocate_split_counters(rows, output_width) == cudaSuccess && p->descriptors.split_counters)
-    p->total_bytes += align_up(dense_split_bytes(rows, output_width), 256);
-  else
+  const cudaError_t counters = p->descriptors.allocate_split_counters(rows, output_width);
+  if (counters != cudaSuccess) {
     (void)cudaGetLastError();
+    // Without any device the plan is only a shape record (it cannot run); every other failure is an error,
+    // not a silent fall-back to whole tiles per CTA, which would be a performance cliff.
+    if (counters != cudaErrorNoDevice && counters != cudaErrorInsufficientDriver) {
+      delete p;
+      return fail(GW_CUDA_ERROR, std::string("plan: tile counters of the K split: ") + cudaGetErrorString(counters));
+    }
+  }
+  if (p->descriptors.split_counters) p->total_bytes += align_up(dense_split_bytes(rows, output_width), 256);
   *plan = p;
   return GW_OK;
 }
@@ -367,6 +381,59 @@ gw_status gw_fp8_plan_run(gw_fp8_plan* plan, const void* input_bf16, const uint8
                        device_error_word()};
   if (plan->total_bytes != plan->split_offset) problem.split_workspace = packed + plan->split_offset;
   return launch_dense(problem, &plan->descriptors, s);
+}
+
+// --------------------------------------------------------------------------- BF16
+
+struct gw_bf16_plan {
+  uint32_t rows, input_width, output_width;
+  size_t total_bytes;
+  DenseDescriptors descriptors;
+};
+
+gw_status gw_bf16_plan_create(uint32_t rows, uint32_t input_width, uint32_t output_width, gw_bf16_plan** plan) {
+  clear_error();
+  const uint32_t int_max = uint32_t(std::numeric_limits<int>::max());
+  if (!plan || rows == 0 || rows > int_max - 127 || input_width == 0 || input_width % 8 || input_width > int_max / 2 ||
+      output_width == 0 || output_width % 8 || output_width > int_max)
+    return fail(GW_INVALID_ARGUMENT, "BF16 plan requires positive rows and K and N divisible by 8");
+  auto* p = new (std::nothrow) gw_bf16_plan();
+  if (!p) return fail(GW_CUDA_ERROR, "out of host memory");
+  p->rows = rows;
+  p->input_width = input_width;
+  p->output_width = output_width;
+  // Decode shapes split the K loop evenly over the SMs (FP32 partial tiles in the scratch).
+  p->total_bytes = 0;
+  const cudaError_t status = p->descriptors.allocate_split_counters(rows, output_width);
+  if (status == cudaSuccess && p->descriptors.split_counters) {
+    p->total_bytes = align_up(dense_split_bytes(rows, output_width), 256);
+  } else if (status != cudaSuccess) {
+    (void)cudaGetLastError();
+    if (status != cudaErrorNoDevice && status != cudaErrorInsufficientDriver) {
+      delete p;
+      return fail(GW_CUDA_ERROR, std::string("BF16 plan: tile counters of the K split: ") + cudaGetErrorString(status));
+    }
+  }
+  *plan = p;
+  return GW_OK;
+}
+
+size_t gw_bf16_plan_scratch_bytes(const gw_bf16_plan* plan) { return plan ? plan->total_bytes : 0; }
+void gw_bf16_plan_destroy(gw_bf16_plan* plan) { delete plan; }
+
+gw_status gw_bf16_plan_run(gw_bf16_plan* plan, const void* input_bf16, const void* weight_bf16, void* output_bf16,
+                           void* scratch, size_t scratch_capacity, void* stream) {
+  clear_error();
+  if (!plan) return fail(GW_INVALID_ARGUMENT, "BF16 run requires a plan");
+  // scratch == NULL is allowed: decode-shaped plans then keep whole tiles per CTA instead of the K split
+  if (!input_bf16 || !weight_bf16 || !output_bf16 || !aligned(input_bf16, 16) || !aligned(weight_bf16, 16) ||
+      !aligned(output_bf16, 16) || (scratch && plan->total_bytes != 0 && (!aligned(scratch, 256) ||
+                                                                           scratch_capacity < plan->total_bytes)))
+    return fail(GW_INVALID_ARGUMENT, "BF16 run requires 16-byte aligned device buffers and aligned sufficient scratch");
+  DenseProblem problem{GemmKind::bf16, plan->rows, plan->input_width, plan->output_width, weight_bf16, nullptr,
+                       input_bf16, nullptr, 1.0F, nullptr, output_bf16, device_error_word()};
+  if (plan->total_bytes != 0 && scratch) problem.split_workspace = scratch;
+  return launch_dense(problem, &plan->descriptors, as_stream(stream));
 }
 
 // --------------------------------------------------------------------------- weight QDQ

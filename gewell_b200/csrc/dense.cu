@@ -53,7 +53,7 @@ gw_status launch_dense(const DenseProblem& q, DenseDescriptors* cache, cudaStrea
   const bool swap = dense_uses_swap_form(q.rows);
   const int block_n = dense_block_n(q.rows);
   const bool fp4 = q.kind == GemmKind::nvfp4;
-  const uint64_t row_bytes = fp4 ? q.k / 2 : q.k;
+  const uint64_t row_bytes = fp4 ? q.k / 2 : (q.kind == GemmKind::bf16 ? uint64_t(2) * q.k : q.k);
   std::string error;
   const bool single_box = !swap && block_n == 256;   // both column halves come from the one weight matrix
   if (cache->weight != q.weight) {
@@ -146,7 +146,7 @@ gw_status launch_dense(const DenseProblem& q, DenseDescriptors* cache, cudaStrea
   }
   GW_CUDA_CHECK(launch_gemm_tc(q.kind, swap ? GemmEpilogue::swap_store : GemmEpilogue::direct_store, block_n, params,
                                grid, stream),
-                fp4 ? "NVFP4 tensor-core GEMM" : "FP8 tensor-core GEMM");
+                fp4 ? "NVFP4 tensor-core GEMM" : (q.kind == GemmKind::bf16 ? "BF16 tensor-core GEMM" : "FP8 tensor-core GEMM"));
   return GW_OK;
 }
 

@@ -25,9 +25,9 @@ struct DenseDescriptors {          // re-encoded only when a pointer changes
 struct DenseProblem {
   GemmKind kind;
   uint32_t rows, k, n;
-  const void* weight;              // [n, k] E4M3 or [n, k/2] packed E2M1
+  const void* weight;              // [n, k] E4M3, [n, k/2] packed E2M1 or [n, k] BF16
   const uint8_t* weight_scales;    // NVFP4 only
-  const void* activations;         // quantised [rows, k(/2)]
+  const void* activations;         // quantised [rows, k(/2)], or the BF16 input itself for the BF16 kind
   const uint8_t* activation_scales;
   float alpha;
   const float* channel_alpha;

@@ -19,9 +19,6 @@
 
 namespace gw {
 
-// tensor maps per expert in the table: gate, up, down (128-row boxes), down (64-row boxes)
-constexpr int kMoeMapsPerExpert = 4;
-
 struct PairMoeParams {
   CUtensorMap map_tokens;          // quantised token rows [capacity, K/2] (row pitch may exceed K/2), box 128 rows
   const CUtensorMap* map_table;    // kMoeMapsPerExpert maps per expert, in global memory (host written)

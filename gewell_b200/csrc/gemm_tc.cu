@@ -141,10 +141,11 @@ __device__ __forceinline__ uint4 shfl_xor_u4(const uint4& v, int mask) {
 
 // kProfile: the cycle counters of the tuning aid are compiled into an instantiation of their own,
 // so the production kernel carries none of their registers.
-template <bool kNvfp4, int BLOCK_N, GemmEpilogue EPI, bool kProfile>
+template <GemmKind KIND, int BLOCK_N, GemmEpilogue EPI, bool kProfile>
 // 14 warps are allocated as 16: 128 registers per thread is the most one CTA can have.
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ GemmParams p) {
+  constexpr bool kNvfp4 = KIND == GemmKind::nvfp4;
   using C = Config<kNvfp4, BLOCK_N>;
   constexpr bool prof = kProfile;
   extern __shared__ uint8_t smem_raw[];
@@ -195,7 +196,8 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
   }
 
   const int total_work = p.groups != nullptr ? prefix[p.num_groups] : p.total_work;
-  const int k_bytes = kNvfp4 ? p.k / 2 : p.k;
+  // bytes of K per row: two E2M1 values, one E4M3 value or half a BF16 value per byte
+  const int k_bytes = kNvfp4 ? p.k / 2 : (KIND == GemmKind::bf16 ? 2 * p.k : p.k);
   const int total_kb = (k_bytes + 31) / 32;                 // MMA K-blocks (32 bytes of K each)
   const int k_stages = (total_kb + kKBlocksPerStage - 1) / kKBlocksPerStage;
   const int k_atoms = p.k / 64;                             // scale atoms per 128-row block (NVFP4)
@@ -361,7 +363,8 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
       if (prof) prof_wait2 += clock64() - ta;
       ptx::tc_fence_after_sync();
       const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
-      const uint32_t idesc = kNvfp4 ? ptx::idesc_nvfp4(item.mma_n) : ptx::idesc_fp8(item.mma_n);
+      const uint32_t idesc = kNvfp4 ? ptx::idesc_nvfp4(item.mma_n)
+                             : (KIND == GemmKind::bf16 ? ptx::idesc_bf16(item.mma_n) : ptx::idesc_fp8(item.mma_n));
       bool failed = false;
       for (int ks = ks0; ks < ks1; ++ks) {
         const long long t0 = prof ? clock64() : 0;
@@ -398,6 +401,9 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
                 ptx::tc_mma_nvfp4(d_tmem, make_desc(kDescHiSw128, base16 + 2 * kb),
                                   make_desc(kDescHiSw128, base16 + kCOff16 + 2 * kb), idesc, sfl_t + 4 * kb,
                                   sfc_t + kb * C::kSfcColsPerKb, kb == 0 ? first : 1u);
+              else if constexpr (KIND == GemmKind::bf16)
+                ptx::tc_mma_bf16(d_tmem, make_desc(kDescHiSw128, base16 + 2 * kb),
+                                 make_desc(kDescHiSw128, base16 + kCOff16 + 2 * kb), idesc, kb == 0 ? first : 1u);
               else
                 ptx::tc_mma_fp8(d_tmem, make_desc(kDescHiSw128, base16 + 2 * kb),
                                 make_desc(kDescHiSw128, base16 + kCOff16 + 2 * kb), idesc, kb == 0 ? first : 1u);
@@ -817,13 +823,13 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
 long long* g_profile_buffer = nullptr;
 unsigned g_profile_launches = 0;
 
-template <bool kNvfp4, int BLOCK_N, GemmEpilogue EPI, bool kProfile>
+template <GemmKind KIND, int BLOCK_N, GemmEpilogue EPI, bool kProfile>
 cudaError_t launch_instance(const GemmParams& params, int grid, cudaStream_t stream) {
-  using C = Config<kNvfp4, BLOCK_N>;
+  using C = Config<KIND == GemmKind::nvfp4, BLOCK_N>;
   static bool configured_on[kMaxDeviceSlots] = {};   // the attribute is per GPU
   bool& configured = configured_on[current_device_slot()];
   if (!configured) {
-    cudaError_t status = cudaFuncSetAttribute(gemm_tc_kernel<kNvfp4, BLOCK_N, EPI, kProfile>,
+    cudaError_t status = cudaFuncSetAttribute(gemm_tc_kernel<KIND, BLOCK_N, EPI, kProfile>,
                                               cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
     if (status != cudaSuccess) return status;
     configured = true;
@@ -839,17 +845,17 @@ cudaError_t launch_instance(const GemmParams& params, int grid, cudaStream_t str
   config.attrs = &attribute;
   config.numAttrs = 1;
   note_launch();
-  return cudaLaunchKernelEx(&config, gemm_tc_kernel<kNvfp4, BLOCK_N, EPI, kProfile>, params);
+  return cudaLaunchKernelEx(&config, gemm_tc_kernel<KIND, BLOCK_N, EPI, kProfile>, params);
 }
 
-template <bool kNvfp4, int BLOCK_N, GemmEpilogue EPI>
+template <GemmKind KIND, int BLOCK_N, GemmEpilogue EPI>
 cudaError_t launch(const GemmParams& params_in, int grid, cudaStream_t stream) {
   GemmParams params = params_in;
   // debug aid: consecutive launches alternate between the two halves of the buffer, so the
   // two grouped GEMMs of one MoE pass can be told apart
   params.profile = g_profile_buffer ? g_profile_buffer + size_t(g_profile_launches++ % 2) * 148 * 8 : nullptr;
-  if (params.profile != nullptr) return launch_instance<kNvfp4, BLOCK_N, EPI, true>(params, grid, stream);
-  return launch_instance<kNvfp4, BLOCK_N, EPI, false>(params, grid, stream);
+  if (params.profile != nullptr) return launch_instance<KIND, BLOCK_N, EPI, true>(params, grid, stream);
+  return launch_instance<KIND, BLOCK_N, EPI, false>(params, grid, stream);
 }
 
 }  // namespace
@@ -859,30 +865,37 @@ void set_gemm_profile_buffer(long long* device_buffer) {
   g_profile_launches = 0;
 }
 
-cudaError_t launch_gemm_tc(GemmKind kind, GemmEpilogue epilogue, int block_n, const GemmParams& params, int grid,
-                           cudaStream_t stream) {
-  const bool fp4 = kind == GemmKind::nvfp4;
+namespace {
+template <GemmKind KIND>
+cudaError_t launch_kind(GemmEpilogue epilogue, int block_n, const GemmParams& params, int grid, cudaStream_t stream) {
   if (epilogue == GemmEpilogue::swap_store) {
     switch (block_n) {
-      case 32: return fp4 ? launch<true, 32, GemmEpilogue::swap_store>(params, grid, stream)
-                          : launch<false, 32, GemmEpilogue::swap_store>(params, grid, stream);
-      case 64: return fp4 ? launch<true, 64, GemmEpilogue::swap_store>(params, grid, stream)
-                          : launch<false, 64, GemmEpilogue::swap_store>(params, grid, stream);
-      case 128: return fp4 ? launch<true, 128, GemmEpilogue::swap_store>(params, grid, stream)
-                           : launch<false, 128, GemmEpilogue::swap_store>(params, grid, stream);
+      case 32: return launch<KIND, 32, GemmEpilogue::swap_store>(params, grid, stream);
+      case 64: return launch<KIND, 64, GemmEpilogue::swap_store>(params, grid, stream);
+      case 128: return launch<KIND, 128, GemmEpilogue::swap_store>(params, grid, stream);
       default: return cudaErrorInvalidValue;
     }
   }
   if (epilogue == GemmEpilogue::direct_store) {
     switch (block_n) {
-      case 128: return fp4 ? launch<true, 128, GemmEpilogue::direct_store>(params, grid, stream)
-                           : launch<false, 128, GemmEpilogue::direct_store>(params, grid, stream);
-      case 256: return fp4 ? launch<true, 256, GemmEpilogue::direct_store>(params, grid, stream)
-                           : launch<false, 256, GemmEpilogue::direct_store>(params, grid, stream);
+      case 128: return launch<KIND, 128, GemmEpilogue::direct_store>(params, grid, stream);
+      case 256: return launch<KIND, 256, GemmEpilogue::direct_store>(params, grid, stream);
       default: return cudaErrorInvalidValue;
     }
   }
-  if (fp4 && block_n == 256) return launch<true, 256, GemmEpilogue::geglu_quant>(params, grid, stream);
+  if constexpr (KIND == GemmKind::nvfp4)
+    if (block_n == 256) return launch<GemmKind::nvfp4, 256, GemmEpilogue::geglu_quant>(params, grid, stream);
+  return cudaErrorInvalidValue;
+}
+}  // namespace
+
+cudaError_t launch_gemm_tc(GemmKind kind, GemmEpilogue epilogue, int block_n, const GemmParams& params, int grid,
+                           cudaStream_t stream) {
+  switch (kind) {
+    case GemmKind::nvfp4: return launch_kind<GemmKind::nvfp4>(epilogue, block_n, params, grid, stream);
+    case GemmKind::fp8: return launch_kind<GemmKind::fp8>(epilogue, block_n, params, grid, stream);
+    case GemmKind::bf16: return launch_kind<GemmKind::bf16>(epilogue, block_n, params, grid, stream);
+  }
   return cudaErrorInvalidValue;
 }
 

@@ -79,7 +79,9 @@ struct GemmParams {
   long long* profile;             // optional [grid][8] cycle counters (debug aid), normally nullptr
 };
 
-enum class GemmKind { nvfp4, fp8 };
+// nvfp4: E2M1 with E4M3 K16 block scales (kind::mxf4nvf4); fp8: E4M3 (kind::f8f6f4); bf16: BF16 (kind::f16).
+// All accumulate in FP32 in tensor memory.
+enum class GemmKind { nvfp4, fp8, bf16 };
 enum class GemmEpilogue { swap_store, direct_store, geglu_quant };
 
 // swap_store: block_n in {32, 64, 128}; direct_store: {128, 256}; geglu_quant: 256 (NVFP4).

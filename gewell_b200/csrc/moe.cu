@@ -39,9 +39,16 @@ struct DeviceBuffer {
 }  // namespace
 
 struct gw_expert_table {
-  DeviceBuffer maps;    // CUtensorMap[128*4]: gate, up, down of every expert (128-row boxes), down again (64-row boxes)
+  DeviceBuffer maps;    // CUtensorMap[128 * kMoeMapsPerExpert] (see moe_kernels.h)
   DeviceBuffer info;    // MoeExpertInfo[128]
+  DeviceBuffer bf16_copies;      // W4A16: BF16 copies of every NVFP4 matrix (gw_moe_expert_table_enable_w4a16)
+  std::vector<CUtensorMap> host_maps;
+  std::vector<MoeExpertInfo> host_info;
+  std::vector<gw_expert_weights> bound;   // the bindings as given
   bool shared_gate_up = false;   // every expert quantises gate and up inputs with one scale
+  bool all_nvfp4 = false;        // every present projection is NVFP4
+  bool any_nvfp4 = false, any_bf16 = false, any_fp8 = false;
+  bool w4a16 = false;            // BF16 copies exist
 };
 
 // Tuning overrides, read from the environment once, when a workspace is created:
@@ -88,6 +95,9 @@ struct gw_moe_workspace {
   CachedMap first_map, down_map;
   DeviceBuffer metadata, bitmaps, groups, packed_in, scales_in, gate_up, activated, packed_act, scales_act, down;
   DeviceBuffer row_home;   // expert parallelism: address of every produced row's home in its source rank
+  DeviceBuffer fp8_in, fp8_act;   // FP8 experts (GW_MOE_FP8_EXPERTS): E4M3 gate / up inputs [2][n, 2816], down input [n, 704]
+  DeviceBuffer kind_groups;       // group descriptors of the BF16 and FP8 launches of a mixed table
+  CachedMap bf16_first_map, bf16_down_map, fp8_first_map, fp8_down_map;
   int32_t *keys = nullptr, *sorted_keys = nullptr, *sorted_assignments = nullptr, *inverse = nullptr;
   int32_t *offsets = nullptr, *chunk_counts = nullptr, *local_offsets = nullptr;
   float* weights = nullptr;
@@ -106,40 +116,77 @@ gw_status gw_moe_expert_table_create(const gw_expert_weights* experts, uint32_t 
     return fail(GW_INVALID_ARGUMENT, "expert table requires 128 host-resident entries");
   std::vector<CUtensorMap> maps(kExperts * kMoeMapsPerExpert);
   std::vector<MoeExpertInfo> info(kExperts);
-  bool shared = true;
+  bool shared = true, all_nvfp4 = true, any_nvfp4 = false, any_bf16 = false, any_fp8 = false;
   std::string error;
+  const auto address = [](const void* p) { return reinterpret_cast<uintptr_t>(p); };
   for (uint32_t e = 0; e < kExperts; ++e) {
     const gw_projection* proj[3] = {&experts[e].gate, &experts[e].up, &experts[e].down};
+    info[e] = MoeExpertInfo{};
+    for (int i = 0; i < 3; ++i) info[e].storage[i] = GW_STORAGE_ABSENT;
     if (proj[0]->storage == GW_STORAGE_ABSENT && proj[1]->storage == GW_STORAGE_ABSENT &&
-        proj[2]->storage == GW_STORAGE_ABSENT) {
-      info[e] = MoeExpertInfo{};   // lives on another rank: no rows may be routed to it here
-      continue;
-    }
+        proj[2]->storage == GW_STORAGE_ABSENT)
+      continue;     // lives on another rank: no rows may be routed to it here
+    const std::string who = " (expert " + std::to_string(e) + ")";
     for (int i = 0; i < 3; ++i) {
       const gw_projection& p = *proj[i];
       const uint32_t want_in = i < 2 ? kHidden : kInter, want_out = i < 2 ? kInter : kHidden;
-      if (p.storage != GW_STORAGE_NVFP4_W4A4)
-        return fail(GW_UNSUPPORTED, "only NVFP4 (W4A4) experts are built; expert " + std::to_string(e) +
-                                        " uses another storage type");
-      if (p.input != want_in || p.output != want_out || p.physical_output != (want_out + 127) / 128 * 128 ||
-          !p.nvfp4_data || !p.nvfp4_scales || reinterpret_cast<uintptr_t>(p.nvfp4_data) % 16 ||
-          reinterpret_cast<uintptr_t>(p.nvfp4_scales) % 16 || !finite_positive(p.nvfp4_input_scale) ||
-          !finite_positive(p.nvfp4_weight_scale) || !std::isfinite(1.0F / p.nvfp4_input_scale) ||
-          !finite_positive(p.nvfp4_input_scale * p.nvfp4_weight_scale))
-        return fail(GW_INVALID_ARGUMENT, "invalid 26B expert projection binding (expert " + std::to_string(e) + ")");
-      if (!encode_tensor_map_2d(&maps[e * kMoeMapsPerExpert + i], p.nvfp4_data, p.input / 2, p.physical_output, 128, &error) ||
-          (i == 2 && !encode_tensor_map_2d(&maps[e * kMoeMapsPerExpert + 3], p.nvfp4_data, p.input / 2, p.physical_output, 64,
-                                           &error)))
-        return fail(GW_CUDA_ERROR, "expert weight descriptor: " + error);
-      info[e].scales[i] = p.nvfp4_scales;
-      info[e].alpha[i] = p.nvfp4_input_scale * p.nvfp4_weight_scale;   // == __fmul_rn on the device
-      info[e].inverse_input_scale[i] = 1.0F / p.nvfp4_input_scale;
+      CUtensorMap* slot = &maps[e * kMoeMapsPerExpert];
+      if (p.input != want_in || p.output != want_out)
+        return fail(GW_INVALID_ARGUMENT, "invalid 26B expert projection shape" + who);
+      info[e].storage[i] = int32_t(p.storage);
+      info[e].alpha[i] = 1.0F;
+      info[e].inverse_input_scale[i] = 1.0F;
+      if (p.storage == GW_STORAGE_NVFP4_W4A4) {
+        if (p.physical_output != (want_out + 127) / 128 * 128 || !p.nvfp4_data || !p.nvfp4_scales ||
+            address(p.nvfp4_data) % 16 || address(p.nvfp4_scales) % 16 || !finite_positive(p.nvfp4_input_scale) ||
+            !finite_positive(p.nvfp4_weight_scale) || !std::isfinite(1.0F / p.nvfp4_input_scale) ||
+            !finite_positive(p.nvfp4_input_scale * p.nvfp4_weight_scale))
+          return fail(GW_INVALID_ARGUMENT, "invalid 26B expert projection binding" + who);
+        if (!encode_tensor_map_2d(slot + i, p.nvfp4_data, p.input / 2, p.physical_output, 128, &error) ||
+            (i == 2 && !encode_tensor_map_2d(slot + 3, p.nvfp4_data, p.input / 2, p.physical_output, 64, &error)))
+          return fail(GW_CUDA_ERROR, "expert weight descriptor: " + error);
+        info[e].scales[i] = p.nvfp4_scales;
+        info[e].alpha[i] = p.nvfp4_input_scale * p.nvfp4_weight_scale;   // == __fmul_rn on the device
+        info[e].inverse_input_scale[i] = 1.0F / p.nvfp4_input_scale;
+        any_nvfp4 = true;
+      } else if (p.storage == GW_STORAGE_BF16) {
+        if (!p.bf16 || address(p.bf16) % 16 || p.physical_output != p.output)
+          return fail(GW_INVALID_ARGUMENT, "invalid 26B BF16 expert projection binding" + who);
+        if (!encode_tensor_map_2d(slot + 4 + i, p.bf16, size_t(p.input) * 2, p.output, 128, &error))
+          return fail(GW_CUDA_ERROR, "expert weight descriptor: " + error);
+        any_bf16 = true;
+        all_nvfp4 = false;
+      } else if (p.storage == GW_STORAGE_FP8_W8A8) {
+        if (!p.fp8_data || address(p.fp8_data) % 16 || p.physical_output != p.output ||
+            !finite_positive(p.fp8_input_scale) || !finite_positive(p.fp8_weight_scale) ||
+            !std::isfinite(1.0F / p.fp8_input_scale) || !finite_positive(p.fp8_input_scale * p.fp8_weight_scale) ||
+            address(p.fp8_channel_scales) % 16)
+          return fail(GW_INVALID_ARGUMENT, "invalid 26B FP8 expert projection binding" + who);
+        if (!encode_tensor_map_2d(slot + 4 + i, p.fp8_data, p.input, p.output, 128, &error))
+          return fail(GW_CUDA_ERROR, "expert weight descriptor: " + error);
+        info[e].alpha[i] = p.fp8_input_scale * p.fp8_weight_scale;
+        info[e].inverse_input_scale[i] = 1.0F / p.fp8_input_scale;
+        info[e].channel_alpha[i] = p.fp8_channel_scales;
+        any_fp8 = true;
+        all_nvfp4 = false;
+      } else {
+        return fail(GW_INVALID_ARGUMENT, "invalid 26B expert projection storage" + who);
+      }
     }
-    if (experts[e].gate.nvfp4_input_scale != experts[e].up.nvfp4_input_scale) shared = false;
+    if (experts[e].gate.storage != GW_STORAGE_NVFP4_W4A4 || experts[e].up.storage != GW_STORAGE_NVFP4_W4A4 ||
+        experts[e].gate.nvfp4_input_scale != experts[e].up.nvfp4_input_scale)
+      shared = false;
   }
   auto* t = new (std::nothrow) gw_expert_table();
   if (!t) return fail(GW_CUDA_ERROR, "out of host memory");
-  t->shared_gate_up = shared;
+  t->shared_gate_up = shared && all_nvfp4;
+  t->all_nvfp4 = all_nvfp4;
+  t->any_nvfp4 = any_nvfp4;
+  t->any_bf16 = any_bf16;
+  t->any_fp8 = any_fp8;
+  t->host_maps = maps;
+  t->host_info = info;
+  t->bound.assign(experts, experts + kExperts);
   cudaError_t status = t->maps.allocate(maps.size() * sizeof(CUtensorMap));
   if (status == cudaSuccess) status = t->info.allocate(info.size() * sizeof(MoeExpertInfo));
   if (status == cudaSuccess)
@@ -154,10 +201,53 @@ gw_status gw_moe_expert_table_create(const gw_expert_weights* experts, uint32_t 
   return GW_OK;
 }
 
+gw_status gw_moe_expert_table_enable_w4a16(gw_expert_table* t, void* stream) {
+  clear_error();
+  if (!t) return fail(GW_INVALID_ARGUMENT, "W4A16 preparation requires an expert table");
+  if (t->w4a16 || !t->any_nvfp4) return GW_OK;
+  // one BF16 copy per NVFP4 matrix, padding rows included (they decode to zero)
+  size_t bytes = 0;
+  for (const auto& e : t->bound)
+    for (const gw_projection* p : {&e.gate, &e.up, &e.down})
+      if (p->storage == GW_STORAGE_NVFP4_W4A4) bytes += align_up(size_t(p->physical_output) * p->input * sizeof(bf16), 256);
+  GW_CUDA_CHECK(t->bf16_copies.allocate(bytes), "BF16 copies of the NVFP4 expert weights");
+  cudaStream_t s = as_stream(stream);
+  std::string error;
+  size_t cursor = 0;
+  for (uint32_t e = 0; e < kExperts; ++e) {
+    const gw_projection* proj[3] = {&t->bound[e].gate, &t->bound[e].up, &t->bound[e].down};
+    for (int i = 0; i < 3; ++i) {
+      const gw_projection& p = *proj[i];
+      if (p.storage != GW_STORAGE_NVFP4_W4A4) continue;
+      auto* copy = t->bf16_copies.as<uint8_t>() + cursor;
+      cursor += align_up(size_t(p.physical_output) * p.input * sizeof(bf16), 256);
+      const gw_status status = gw_nvfp4_dequantize(p.nvfp4_data, p.nvfp4_scales, p.nvfp4_weight_scale, p.input,
+                                                   p.physical_output, copy, s);
+      if (status != GW_OK) return status;
+      if (!encode_tensor_map_2d(&t->host_maps[e * kMoeMapsPerExpert + 4 + i], copy, size_t(p.input) * 2, p.physical_output,
+                                128, &error))
+        return fail(GW_CUDA_ERROR, "expert weight descriptor: " + error);
+    }
+    t->host_info[e].bf16_copy = 1;
+  }
+  GW_CUDA_CHECK(cudaMemcpyAsync(t->maps.data, t->host_maps.data(), t->host_maps.size() * sizeof(CUtensorMap),
+                                cudaMemcpyHostToDevice, s), "expert table upload");
+  GW_CUDA_CHECK(cudaMemcpyAsync(t->info.data, t->host_info.data(), t->host_info.size() * sizeof(MoeExpertInfo),
+                                cudaMemcpyHostToDevice, s), "expert table upload");
+  GW_CUDA_CHECK(cudaStreamSynchronize(s), "W4A16 preparation");
+  t->w4a16 = true;
+  return GW_OK;
+}
+
 void gw_moe_expert_table_destroy(gw_expert_table* table) { delete table; }
 
 gw_status gw_moe_create(uint32_t max_rows, gw_moe_workspace** workspace) {
+  return gw_moe_create_ex(max_rows, 0, workspace);
+}
+
+gw_status gw_moe_create_ex(uint32_t max_rows, uint32_t flags, gw_moe_workspace** workspace) {
   clear_error();
+  if (flags & ~uint32_t(GW_MOE_FP8_EXPERTS)) return fail(GW_INVALID_ARGUMENT, "unknown MoE workspace flag");
   if (!workspace || max_rows == 0 || max_rows > kMaxRows)
     return fail(GW_INVALID_ARGUMENT, "MoE capacity must be in 1..65536");
   auto* w = new (std::nothrow) gw_moe_workspace();
@@ -182,6 +272,11 @@ gw_status gw_moe_create(uint32_t max_rows, gw_moe_workspace** workspace) {
   if (status == cudaSuccess) status = w->scales_act.allocate(size_t(w->scale_rows) * (kInter / 16));
   if (status == cudaSuccess) status = w->down.allocate(n * kHidden * sizeof(bf16));
   if (status == cudaSuccess) status = w->row_home.allocate(n * sizeof(uint64_t));
+  if (status == cudaSuccess) status = w->kind_groups.allocate(2 * (2 * kExperts + 1 + kExperts + 1) * sizeof(GemmGroup));
+  if (status == cudaSuccess && (flags & GW_MOE_FP8_EXPERTS)) {
+    status = w->fp8_in.allocate(2 * n * kHidden);
+    if (status == cudaSuccess) status = w->fp8_act.allocate(n * kInter);
+  }
   // Scale regions contain rows no kernel writes (tile padding); start from zero so
   // that they never hold NaN patterns.
   if (status == cudaSuccess) status = cudaMemset(w->scales_in.data, 0, w->scales_in.bytes);
@@ -239,6 +334,8 @@ namespace {
 gw_status run_experts(gw_moe_workspace* w, const void* input, const int32_t* gather_index, uint32_t gather_divisor,
                       const int32_t* offsets, uint32_t n, const gw_expert_table* table, void* down_out, cudaStream_t s,
                       const void* records = nullptr, const uint64_t* row_home = nullptr) {
+  if (!table->all_nvfp4)
+    return fail(GW_UNSUPPORTED, "this entry point runs NVFP4 (W4A4) expert tables only; mixed tables run through gw_moe_run");
   const auto* info = table->info.as<MoeExpertInfo>();
   auto* first_groups = w->groups.as<GemmGroup>();
   auto* down_groups = first_groups + 2 * kExperts + 1;
@@ -264,7 +361,7 @@ gw_status run_experts(gw_moe_workspace* w, const void* input, const int32_t* gat
   w->mark(1, s);
   if (!(pair_first && pair_down)) {
     MoeGroupPlan plan{offsets, info, w->scales_in.as<uint8_t>(), w->scales_act.as<uint8_t>(), n, w->scale_rows, form,
-                      block_n_first, block_n_down, table->shared_gate_up ? 1 : 0, device_error_word()};
+                      block_n_first, block_n_down, table->shared_gate_up ? 1 : 0, device_error_word(), kMoeKindNvfp4, 1};
     GW_CUDA_CHECK(launch_moe_prepare_groups(plan, first_groups, down_groups, s), "MoE group descriptors");
   }
   if (records != nullptr) {
@@ -372,6 +469,117 @@ gw_status run_experts(gw_moe_workspace* w, const void* input, const int32_t* gat
   return GW_OK;
 }
 
+// Expert MLP of one whole layer pass for tables with BF16 / FP8 projections, or NVFP4 weights used with
+// BF16 activations (W4A16, through their BF16 copies) -- the storage mixes of MoeWorkspace::run
+// (moe.cu:489-534), where each kernel of the reference skips the projections that are not of its kind.
+// Every kind that is present runs its own grouped gate/up and down GEMM over the projections that run as
+// that kind (the others get no work items); all of them write the shared BF16 gate_up and down buffers.
+// GeGLU runs unfused, as in the reference.
+gw_status run_experts_general(gw_moe_workspace* w, const void* input, uint32_t n, const gw_expert_table* table,
+                              bool run_nvfp4, bool run_bf16, bool run_fp8, int fp4, cudaStream_t s) {
+  const auto* info = table->info.as<MoeExpertInfo>();
+  const int32_t* offsets = w->offsets;
+  const MoeTuning& tune = w->tuning;
+  int form = n <= 8 * 512 ? kMoeFormSwap : kMoeFormDirect;
+  if (tune.form == 's') form = kMoeFormSwap;
+  if (tune.form == 'd' || tune.form == 'f') form = kMoeFormDirect;
+  const bool swap = form == kMoeFormSwap;
+  int block_n = 128;
+  if (swap) {
+    block_n = n <= 8 * 64 ? 32 : (n <= 8 * 256 ? 64 : 128);
+    if (tune.block_n == 32 || tune.block_n == 64 || tune.block_n == 128) block_n = tune.block_n;
+  }
+  const GemmEpilogue epilogue = swap ? GemmEpilogue::swap_store : GemmEpilogue::direct_store;
+  const uint32_t token_box = swap ? uint32_t(block_n) : 128;
+  void* expanded = w->down.data;     // the gathered BF16 rows are dead once gate/up has run: share the down buffer
+  std::string error;
+  w->mark(1, s);
+  // ---- inputs of the gate/up GEMMs, per kind
+  if (run_bf16)
+    GW_CUDA_CHECK(launch_gather_rows(input, w->sorted_assignments, 8, n, kHidden, expanded, s), "MoE gather");
+  if (run_nvfp4)
+    GW_CUDA_CHECK(launch_moe_quantize_input(input, w->sorted_assignments, 8, w->sorted_keys, offsets, info, n, w->scale_rows,
+                                            2, w->packed_in.as<uint8_t>(), w->scales_in.as<uint8_t>(), s),
+                  "MoE gather + quantise");
+  if (run_fp8)
+    GW_CUDA_CHECK(launch_moe_quantize_fp8(input, w->sorted_assignments, 8, w->sorted_keys, offsets, info, n, kHidden, 0, 2,
+                                          w->fp8_in.as<uint8_t>(), s),
+                  "MoE gather + FP8 quantise");
+  struct KindRun {
+    bool enabled;
+    int kind;
+    GemmKind gemm;
+    GemmGroup* groups;
+    CachedMap* first_map;
+    CachedMap* down_map;
+    const void* first_rows;
+    uint64_t first_row_bytes, first_row_count;
+    const void* down_rows;
+    uint64_t down_row_bytes;
+  };
+  auto* extra = w->kind_groups.as<GemmGroup>();
+  constexpr size_t kGroupSet = 2 * kExperts + 1 + kExperts + 1;
+  KindRun runs[3] = {
+      {run_nvfp4, kMoeKindNvfp4, GemmKind::nvfp4, w->groups.as<GemmGroup>(), &w->first_map, &w->down_map,
+       w->packed_in.data, kHidden / 2, uint64_t(2) * n, w->packed_act.data, kInter / 2},
+      {run_bf16, kMoeKindBf16, GemmKind::bf16, extra, &w->bf16_first_map, &w->bf16_down_map, expanded, kHidden * 2,
+       uint64_t(n), w->activated.data, kInter * 2},
+      {run_fp8, kMoeKindFp8, GemmKind::fp8, extra + kGroupSet, &w->fp8_first_map, &w->fp8_down_map, w->fp8_in.data, kHidden,
+       uint64_t(2) * n, w->fp8_act.data, kInter}};
+  w->mark(2, s);
+  for (KindRun& run : runs) {
+    if (!run.enabled) continue;
+    MoeGroupPlan plan{offsets, info, w->scales_in.as<uint8_t>(), w->scales_act.as<uint8_t>(), n, w->scale_rows, form,
+                      block_n, block_n, 0, device_error_word(), run.kind, fp4};
+    GW_CUDA_CHECK(launch_moe_prepare_groups(plan, run.groups, run.groups + 2 * kExperts + 1, s), "MoE group descriptors");
+    if (!run.first_map->get(run.first_rows, run.first_row_bytes, run.first_row_count, token_box, run.first_row_bytes, &error) ||
+        !run.down_map->get(run.down_rows, run.down_row_bytes, n, token_box, run.down_row_bytes, &error))
+      return fail(GW_CUDA_ERROR, "MoE activation descriptor: " + error);
+    GemmParams first{};
+    (swap ? first.map_c : first.map_l) = run.first_map->map;
+    first.map_table = table->maps.as<CUtensorMap>();
+    first.groups = run.groups;
+    first.num_groups = 2 * kExperts;
+    first.k = kHidden;
+    first.c_rows_per_tile = block_n;
+    first.work_chunk = swap ? 1 : 2;
+    first.out = w->gate_up.data;
+    first.ld_out = 2 * kInter;
+    first.error = device_error_word();
+    GW_CUDA_CHECK(launch_gemm_tc(run.gemm, epilogue, block_n, first, sm_count(), s), "MoE grouped gate/up GEMM");
+  }
+  w->mark(3, s);
+  // ---- GeGLU and the inputs of the down GEMMs
+  if (run_nvfp4)
+    GW_CUDA_CHECK(launch_moe_activate_quantize(w->gate_up.data, w->sorted_keys, offsets, info, n, w->scale_rows,
+                                               w->packed_act.as<uint8_t>(), w->scales_act.as<uint8_t>(), w->activated.data, s),
+                  "MoE GeGLU + quantise");
+  else
+    GW_CUDA_CHECK(launch_moe_activate(w->gate_up.data, offsets, n, w->activated.data, s), "MoE GeGLU");
+  if (run_fp8)
+    GW_CUDA_CHECK(launch_moe_quantize_fp8(w->activated.data, nullptr, 1, w->sorted_keys, offsets, info, n, kInter, 2, 1,
+                                          w->fp8_act.as<uint8_t>(), s),
+                  "MoE FP8 quantise of the down input");
+  w->mark(4, s);
+  for (KindRun& run : runs) {
+    if (!run.enabled) continue;
+    GemmParams down{};
+    (swap ? down.map_c : down.map_l) = run.down_map->map;
+    down.map_table = table->maps.as<CUtensorMap>();
+    down.groups = run.groups + 2 * kExperts + 1;
+    down.num_groups = kExperts;
+    down.k = kInter;
+    down.c_rows_per_tile = block_n;
+    down.work_chunk = swap ? 1 : 2;
+    down.out = w->down.data;
+    down.ld_out = kHidden;
+    down.error = device_error_word();
+    GW_CUDA_CHECK(launch_gemm_tc(run.gemm, epilogue, block_n, down, sm_count(), s), "MoE grouped down GEMM");
+  }
+  w->mark(5, s);
+  return GW_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -386,13 +594,31 @@ gw_status gw_moe_run(gw_moe_workspace* w, const void* input_bf16, const void* sc
   if (!input_bf16 || !scores_bf16 || !expert_scales_bf16 || !table || !output_bf16 ||
       reinterpret_cast<uintptr_t>(input_bf16) % 16 || reinterpret_cast<uintptr_t>(output_bf16) % 16)
     return fail(GW_INVALID_ARGUMENT, "MoE run requires 16-byte aligned input/output, scores, expert scales and a bound expert table");
-  if (has_bf16 || has_fp8 || !has_nvfp4 || !fp4)
-    return fail(GW_UNSUPPORTED, "only NVFP4 experts with FP4 activations (W4A4) are built");
+  // The storage flags say which kinds of expert weights the caller's table holds (the reference launches
+  // one set of kernels per flag); fp4 == 0 runs NVFP4 weights with BF16 activations (W4A16).
+  const bool fast = table->all_nvfp4 && has_nvfp4 && fp4;
+  const bool run_nvfp4 = has_nvfp4 && fp4 && table->any_nvfp4;
+  const bool w4a16 = has_nvfp4 && !fp4 && table->any_nvfp4;
+  const bool run_bf16 = (has_bf16 && table->any_bf16) || w4a16;
+  const bool run_fp8 = has_fp8 && table->any_fp8;
+  if (!fast) {
+    if (!run_nvfp4 && !run_bf16 && !run_fp8)
+      return fail(GW_INVALID_ARGUMENT, "MoE run: the storage flags select none of the table's expert weights");
+    if (w4a16 && !table->w4a16)
+      return fail(GW_UNSUPPORTED,
+                  "NVFP4 experts with BF16 activations (W4A16) need their BF16 copies: call "
+                  "gw_moe_expert_table_enable_w4a16 once, at set-up");
+    if (run_fp8 && !w->fp8_in.data)
+      return fail(GW_UNSUPPORTED, "FP8 experts need a workspace created with GW_MOE_FP8_EXPERTS (gw_moe_create_ex)");
+  }
   cudaStream_t s = as_stream(stream);
   w->mark(0, s);
   gw_status status = gw_moe_dispatch(w, scores_bf16, expert_scales_bf16, rows, stream);
   if (status != GW_OK) return status;
-  status = run_experts(w, input_bf16, w->sorted_assignments, 8, w->offsets, 8 * rows, table, w->down.data, s);
+  if (fast)
+    status = run_experts(w, input_bf16, w->sorted_assignments, 8, w->offsets, 8 * rows, table, w->down.data, s);
+  else
+    status = run_experts_general(w, input_bf16, 8 * rows, table, run_nvfp4, run_bf16, run_fp8, fp4, s);
   if (status != GW_OK) return status;
   GW_CUDA_CHECK(launch_moe_combine(w->down.data, w->inverse, w->weights, rows, kHidden, output_bf16, s), "MoE combine");
   w->mark(6, s);

@@ -18,7 +18,7 @@ constexpr int kExperts = 128;
 constexpr int kTopK = 8;
 constexpr int kHidden = 2816;
 constexpr int kInter = 704;
-constexpr int kMapsPerExpert = 4;   // tensor maps per expert in the table: gate, up, down, down with 64-row boxes
+constexpr int kMapsPerExpert = kMoeMapsPerExpert;
 constexpr int kChunkTokens = 64;   // tokens per routing block (two 32-bit bitmap words per expert)
 
 __device__ __forceinline__ void unpack8(const uint4& raw, float* out) {
@@ -275,27 +275,36 @@ moe_prepare_groups_kernel(MoeGroupPlan plan, GemmGroup* __restrict__ first_group
     first = min(max(first, 0), capacity);
     last = min(max(last, first), capacity);
   }
+  const MoeExpertInfo info = plan.experts[e];
+  // A projection gets work in this launch only if it runs as the launch's kind.
+  const bool nv = plan.kind == kMoeKindNvfp4;
+  auto runs_here = [&](int proj) { return moe_effective_kind(info.storage[proj], plan.fp4) == plan.kind; };
+  const int map_base = int32_t(e) * kMapsPerExpert + (nv ? 0 : 4);
+  // BF16 operands carry no scales (the info's alpha belongs to the NVFP4 form of a W4A16 projection)
+  auto alpha_of = [&](int proj) { return plan.kind == kMoeKindBf16 ? 1.0F : info.alpha[proj]; };
   const int32_t count = last - first;
   const int32_t token_tiles_swap = (count + plan.block_n_first - 1) / plan.block_n_first;
   const int32_t token_tiles_direct = (count + 127) / 128;
   const int32_t padded_first = (first / 128 + int32_t(e)) * 128;
-  const MoeExpertInfo info = plan.experts[e];
-  const int src_part = plan.shared_gate_up ? 0 : int(part);
-  const uint8_t* in_scales = plan.scales_in + (size_t(src_part) * plan.scale_rows + padded_first) * (kHidden / 16);
-  const uint8_t* act_scales = plan.scales_act + size_t(padded_first) * (kInter / 16);
+  // which copy of the quantised input a gate/up projection reads: NVFP4 keeps one copy when gate and up
+  // share their input scale, FP8 always keeps two, BF16 rows are not quantised at all
+  const int src_part = nv ? (plan.shared_gate_up ? 0 : int(part)) : (plan.kind == kMoeKindFp8 ? int(part) : 0);
+  const uint8_t* in_scales = nv ? plan.scales_in + (size_t(src_part) * plan.scale_rows + padded_first) * (kHidden / 16) : nullptr;
+  const uint8_t* act_scales = nv ? plan.scales_act + size_t(padded_first) * (kInter / 16) : nullptr;
   {
     GemmGroup grp{};
     if (plan.form == kMoeFormFused) {
-      // one group per expert (threads with part == 1 write nothing)
+      // one group per expert (threads with part == 1 write nothing); NVFP4 only
+      const bool active = runs_here(0) && runs_here(1);
       grp.sf_l = in_scales;
       grp.map_l = -1;
       grp.l_row0 = first;
       grp.l_rows = count;
-      grp.l_tiles = token_tiles_direct;
+      grp.l_tiles = active ? token_tiles_direct : 0;
       grp.sf_c[0] = info.scales[0];
       grp.sf_c[1] = info.scales[1];
-      grp.map_c[0] = int32_t(e) * kMapsPerExpert;
-      grp.map_c[1] = int32_t(e) * kMapsPerExpert + 1;
+      grp.map_c[0] = map_base;
+      grp.map_c[1] = map_base + 1;
       grp.c_row0 = 0;
       grp.c_rows = kInter;
       grp.c_tiles = (kInter + 127) / 128;
@@ -314,14 +323,15 @@ moe_prepare_groups_kernel(MoeGroupPlan plan, GemmGroup* __restrict__ first_group
       grp.map_l = -1;
       grp.l_row0 = src_part * int32_t(plan.n) + first;
       grp.l_rows = count;
-      grp.l_tiles = token_tiles_direct;
+      grp.l_tiles = runs_here(proj) ? token_tiles_direct : 0;
       grp.sf_c[0] = grp.sf_c[1] = info.scales[proj];
-      grp.map_c[0] = grp.map_c[1] = int32_t(e) * kMapsPerExpert + proj;
+      grp.map_c[0] = grp.map_c[1] = map_base + proj;
       grp.c_row0 = 0;
       grp.c_rows = kInter;
       grp.c_tiles = (kInter + plan.block_n_first - 1) / plan.block_n_first;
       grp.c_half_stride = plan.block_n_first > 128 ? 128 : 0;
-      grp.alpha[0] = grp.alpha[1] = info.alpha[proj];
+      grp.alpha[0] = grp.alpha[1] = alpha_of(proj);
+      grp.channel_alpha = nv ? nullptr : info.channel_alpha[proj];
       grp.out_row0 = first;
       grp.out_col0 = proj * kInter;
       items_first[g] = grp.l_tiles * grp.c_tiles;
@@ -329,17 +339,18 @@ moe_prepare_groups_kernel(MoeGroupPlan plan, GemmGroup* __restrict__ first_group
     } else {
       const int proj = part;
       grp.sf_l = info.scales[proj];
-      grp.map_l = int32_t(e) * kMapsPerExpert + proj;
+      grp.map_l = map_base + proj;
       grp.l_row0 = 0;
       grp.l_rows = kInter;
-      grp.l_tiles = (kInter + 127) / 128;
+      grp.l_tiles = runs_here(proj) ? (kInter + 127) / 128 : 0;
       grp.sf_c[0] = grp.sf_c[1] = in_scales;
       grp.map_c[0] = grp.map_c[1] = -1;
       grp.c_row0 = src_part * int32_t(plan.n) + first;
       grp.c_rows = count;
       grp.c_tiles = token_tiles_swap;
       grp.c_half_stride = 0;
-      grp.alpha[0] = grp.alpha[1] = info.alpha[proj];
+      grp.alpha[0] = grp.alpha[1] = alpha_of(proj);
+      grp.channel_alpha = nv ? nullptr : info.channel_alpha[proj];
       grp.out_row0 = first;
       grp.out_col0 = proj * kInter;
       items_first[g] = grp.l_tiles * grp.c_tiles;
@@ -348,12 +359,13 @@ moe_prepare_groups_kernel(MoeGroupPlan plan, GemmGroup* __restrict__ first_group
   }
   if (part == 0) {
     GemmGroup grp{};
+    const bool active = runs_here(2);
     if (plan.form == kMoeFormSwap) {
       grp.sf_l = info.scales[2];
-      grp.map_l = int32_t(e) * kMapsPerExpert + 2;
+      grp.map_l = map_base + 2;
       grp.l_row0 = 0;
       grp.l_rows = kHidden;
-      grp.l_tiles = kHidden / 128;
+      grp.l_tiles = active ? kHidden / 128 : 0;
       grp.sf_c[0] = grp.sf_c[1] = act_scales;
       grp.map_c[0] = grp.map_c[1] = -1;
       grp.c_row0 = first;
@@ -365,15 +377,16 @@ moe_prepare_groups_kernel(MoeGroupPlan plan, GemmGroup* __restrict__ first_group
       grp.map_l = -1;
       grp.l_row0 = first;
       grp.l_rows = count;
-      grp.l_tiles = token_tiles_direct;
+      grp.l_tiles = active ? token_tiles_direct : 0;
       grp.sf_c[0] = grp.sf_c[1] = info.scales[2];
-      grp.map_c[0] = grp.map_c[1] = int32_t(e) * kMapsPerExpert + 2;
+      grp.map_c[0] = grp.map_c[1] = map_base + 2;
       grp.c_row0 = 0;
       grp.c_rows = kHidden;
       grp.c_tiles = kHidden / plan.block_n_down;
       grp.c_half_stride = plan.block_n_down > 128 ? 128 : 0;
     }
-    grp.alpha[0] = grp.alpha[1] = info.alpha[2];
+    grp.alpha[0] = grp.alpha[1] = alpha_of(2);
+    grp.channel_alpha = nv ? nullptr : info.channel_alpha[2];
     grp.out_row0 = first;
     grp.out_col0 = 0;
     items_down[e] = grp.l_tiles * grp.c_tiles;
@@ -538,6 +551,58 @@ moe_quantize_tokens_kernel(const uint4* __restrict__ input, const int32_t* __res
       }
     }
   }
+}
+
+// ---------------------------------------------------------------------------
+// 5c. FP8 expert inputs (the role of pack_fp8 inside the reference's grouped_fp8,
+//     moe.cu:187-251, which quantises in registers): e4m3_satfinite(x * 1/input_scale)
+//     with the input scale of the row's expert and projection; eight values per thread.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+moe_quantize_fp8_kernel(const uint4* __restrict__ input, const int32_t* __restrict__ gather_index,
+                        uint32_t gather_divisor, const int32_t* __restrict__ sorted_keys,
+                        const int32_t* __restrict__ offsets, const MoeExpertInfo* __restrict__ experts, uint32_t n,
+                        uint32_t vectors, int first_projection, uint2* __restrict__ packed) {
+  griddep_launch();
+  griddep_wait();     // results of earlier kernels in the stream are read from here on
+  const size_t index = size_t(blockIdx.x) * 256 + threadIdx.x;
+  const uint32_t part = blockIdx.y;
+  if (index >= size_t(n) * vectors) return;
+  const uint32_t row = index / vectors, v = index % vectors;
+  if (row >= uint32_t(offsets[kExperts])) return;       // n may be an upper bound
+  const int32_t e = sorted_keys[row];
+  const float inverse_scale = experts[e].inverse_input_scale[first_projection + part];
+  const size_t source_row = gather_index ? size_t(uint32_t(gather_index[row]) / gather_divisor) : row;
+  float x[8];
+  unpack8(input[source_row * vectors + v], x);
+  uint32_t words[2] = {0, 0};
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    words[i / 4] |= uint32_t(float_to_e4m3(__fmul_rn(x[i], inverse_scale))) << (8 * (i % 4));
+  packed[(size_t(part) * n + row) * vectors + v] = make_uint2(words[0], words[1]);
+}
+
+// GeGLU alone (moe.cu:439-445) for expert tables without FP4 activations.
+__global__ void __launch_bounds__(256)
+moe_activate_kernel(const uint4* __restrict__ gate_up, const int32_t* __restrict__ offsets, uint32_t n,
+                    uint4* __restrict__ activated) {
+  griddep_launch();
+  griddep_wait();     // results of earlier kernels in the stream are read from here on
+  constexpr uint32_t kVectors = kInter / 8;
+  const size_t index = size_t(blockIdx.x) * 256 + threadIdx.x;
+  if (index >= size_t(n) * kVectors) return;
+  const uint32_t row = index / kVectors, v = index % kVectors;
+  if (row >= uint32_t(offsets[kExperts])) return;
+  float g[8], u[8];
+  unpack8(gate_up[size_t(row) * (2 * kVectors) + v], g);
+  unpack8(gate_up[size_t(row) * (2 * kVectors) + kVectors + v], u);
+  uint32_t words[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float a = gelu_tanh_multiply_bf16(g[2 * i], u[2 * i]), b = gelu_tanh_multiply_bf16(g[2 * i + 1], u[2 * i + 1]);
+    words[i] = (__float_as_uint(a) >> 16) | (__float_as_uint(b) & 0xFFFF0000u);
+  }
+  activated[index] = make_uint4(words[0], words[1], words[2], words[3]);
 }
 
 // ---------------------------------------------------------------------------
@@ -919,6 +984,24 @@ cudaError_t launch_moe_activate_quantize(const void* gate_up, const int32_t* sor
   launch_pdl(moe_quantize_kernel<kInter, true>, grid, 256, stream, 
       static_cast<const uint4*>(gate_up), nullptr, sorted_keys, offsets, experts, n, scale_rows, 2, 1,
       reinterpret_cast<uint2*>(packed), scales, static_cast<uint4*>(activated));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_moe_quantize_fp8(const void* input, const int32_t* gather_index, uint32_t gather_divisor,
+                                    const int32_t* sorted_keys, const int32_t* offsets, const MoeExpertInfo* experts,
+                                    uint32_t n, uint32_t width, int first_projection, int parts, uint8_t* packed,
+                                    cudaStream_t stream) {
+  const dim3 grid(blocks_for(size_t(n) * (width / 8)), parts);
+  launch_pdl(moe_quantize_fp8_kernel, grid, 256, stream, static_cast<const uint4*>(input), gather_index,
+             gather_divisor ? gather_divisor : 1, sorted_keys, offsets, experts, n, width / 8, first_projection,
+             reinterpret_cast<uint2*>(packed));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_moe_activate(const void* gate_up, const int32_t* offsets, uint32_t n, void* activated,
+                                cudaStream_t stream) {
+  launch_pdl(moe_activate_kernel, blocks_for(size_t(n) * (kInter / 8)), 256, stream, static_cast<const uint4*>(gate_up),
+             offsets, n, static_cast<uint4*>(activated));
   return cudaGetLastError();
 }
 

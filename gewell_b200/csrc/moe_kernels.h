@@ -5,18 +5,38 @@
 #include <cuda_runtime.h>
 #include <cstdint>
 
+#include "../../include/gewell_b200.h"
 #include "gemm_tc.cuh"
 
 namespace gw {
 
+// Tensor maps per expert in the table: [0..2] gate, up, down as NVFP4 (128-row boxes), [3] down as NVFP4
+// with 64-row boxes, [4..6] gate, up, down in their 8/16-bit form: the FP8 matrix, the BF16 matrix, or
+// the BF16 copy of an NVFP4 matrix (W4A16).
+constexpr int kMoeMapsPerExpert = 7;
+
+// How a projection's GEMM runs: which tcgen05 kind, which operand preparation.
+enum { kMoeKindNvfp4 = 0, kMoeKindBf16 = 1, kMoeKindFp8 = 2, kMoeKindNone = 3 };
+
 // Static per-expert data the device kernels need; built once when the expert
 // table is bound.  Index 0 gate, 1 up, 2 down.
 struct MoeExpertInfo {
-  const uint8_t* scales[3];        // tiled E4M3 weight scales
-  float alpha[3];                  // fmul_rn(input_scale, weight_scale)
-  float inverse_input_scale[3];    // 1 / input_scale (IEEE division)
-  int32_t pad_;
+  const uint8_t* scales[3];        // NVFP4: tiled E4M3 weight scales
+  const float* channel_alpha[3];   // FP8: optional per-output-channel multipliers (input * weight scale)
+  float alpha[3];                  // fmul_rn(input_scale, weight_scale); 1 for BF16
+  float inverse_input_scale[3];    // 1 / input_scale (IEEE division); 1 for BF16
+  int32_t storage[3];              // GW_STORAGE_* of the projection (GW_STORAGE_ABSENT: lives on another rank)
+  int32_t bf16_copy;               // NVFP4 projections also have BF16 copies behind maps [4..6]
 };
+
+// The kind a projection runs as: NVFP4 weights take FP4 activations (W4A4) or, with fp4 == 0, their
+// BF16 copies take BF16 activations (W4A16); BF16 and FP8 weights run as what they are.
+__host__ __device__ inline int moe_effective_kind(int storage, int fp4) {
+  if (storage == GW_STORAGE_NVFP4_W4A4) return fp4 ? kMoeKindNvfp4 : kMoeKindBf16;
+  if (storage == GW_STORAGE_BF16) return kMoeKindBf16;
+  if (storage == GW_STORAGE_FP8_W8A8) return kMoeKindFp8;
+  return kMoeKindNone;
+}
 
 enum { kMoeFormSwap = 0, kMoeFormDirect = 1, kMoeFormFused = 2 };
 
@@ -33,6 +53,8 @@ struct MoeGroupPlan {
   int block_n_down;                // column tile of the down GEMM
   int shared_gate_up;              // gate and up read one quantised copy of the input
   uint32_t* error;                 // device error word: offsets beyond n are clamped and reported here
+  int kind;                        // kMoeKind*: only projections that run as this kind get work
+  int fp4;                         // NVFP4 weights run with FP4 activations (else as BF16 copies)
 };
 
 uint32_t moe_chunks(uint32_t rows);
@@ -60,6 +82,15 @@ cudaError_t launch_moe_quantize_tokens(const void* input, const int32_t* keys, c
 cudaError_t launch_moe_activate_quantize(const void* gate_up, const int32_t* sorted_keys, const int32_t* offsets,
                                          const MoeExpertInfo* experts, uint32_t n, uint32_t scale_rows, uint8_t* packed,
                                          uint8_t* scales, void* activated, cudaStream_t stream);
+// FP8 expert inputs: row r (sorted) of part p is e4m3_sat(x * 1 / input_scale of expert(r)'s projection
+// first_projection + p); source rows through gather_index / gather_divisor like the NVFP4 quantiser.
+cudaError_t launch_moe_quantize_fp8(const void* input, const int32_t* gather_index, uint32_t gather_divisor,
+                                    const int32_t* sorted_keys, const int32_t* offsets, const MoeExpertInfo* experts,
+                                    uint32_t n, uint32_t width, int first_projection, int parts, uint8_t* packed,
+                                    cudaStream_t stream);
+// GeGLU alone: gate_up BF16 [n, 1408] -> activated BF16 [n, 704] (moe.cu:439-445).
+cudaError_t launch_moe_activate(const void* gate_up, const int32_t* offsets, uint32_t n, void* activated,
+                                cudaStream_t stream);
 cudaError_t launch_moe_combine(const void* down, const int32_t* inverse, const float* weights, uint32_t rows,
                                uint32_t width, void* output, cudaStream_t stream);
 cudaError_t launch_gather_rows(const void* input, const int32_t* index, uint32_t divisor, uint32_t rows,

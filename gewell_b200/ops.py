@@ -247,6 +247,70 @@ class Fp8Plan:
             self._plan = None
 
 
+# --------------------------------------------------------------------------- BF16
+
+class Bf16Plan:
+    """BF16 linear layer Y = X . W^T (the reference's BF16 LinearPlan / cublasGemmEx path)."""
+
+    def __init__(self, rows: int, input_width: int, output_width: int):
+        self._lib = _library()
+        self._plan = ctypes.c_void_p()
+        _check(self._lib.gw_bf16_plan_create(rows, input_width, output_width, ctypes.byref(self._plan)))
+        self.rows, self.input_width, self.output_width = rows, input_width, output_width
+
+    def scratch_bytes(self) -> int:
+        return int(self._lib.gw_bf16_plan_scratch_bytes(self._plan))
+
+    def run(self, x, weight, y, scratch=None, stream=None):
+        capacity = scratch.numel() * scratch.element_size() if scratch is not None else 0
+        _check(self._lib.gw_bf16_plan_run(self._plan, _ptr(x), _ptr(weight), _ptr(y), _ptr(scratch), capacity,
+                                          _stream(stream)))
+        return y
+
+    def __del__(self):
+        if getattr(self, "_plan", None):
+            self._lib.gw_bf16_plan_destroy(self._plan)
+            self._plan = None
+
+
+# --------------------------------------------------------------------------- 26B projections
+
+def bind_projection(storage: int, rows: int, columns: int, host_payload: bytes, device_payload: torch.Tensor):
+    """sm120::bind_projection: describe one artifact entry (payload = weights [, tiled scales], two FP32
+    globals at the end) as a Projection.  `device_payload` holds the same bytes on the device."""
+    projection = _lib.Projection()
+    buffer = (ctypes.c_uint8 * len(host_payload)).from_buffer_copy(host_payload)
+    _check(_library().gw_bind_projection(storage, rows, columns, buffer, device_payload.data_ptr(), len(host_payload),
+                                         ctypes.byref(projection)))
+    return projection
+
+
+class ProjectionWorkspace:
+    """sm120::ProjectionWorkspace(projections, max_rows, policy, stream): prepare(rows, phase), run(...)."""
+
+    def __init__(self, projections, max_rows: int, policy: int, stream=None):
+        self._lib = _library()
+        self._ws = ctypes.c_void_p()
+        array = (_lib.Projection * len(projections))(*projections)
+        _check(self._lib.gw_projection_workspace_create(array, len(projections), max_rows, policy, _stream(stream),
+                                                        ctypes.byref(self._ws)))
+
+    def prepare(self, rows: int, phase: int):
+        _check(self._lib.gw_projection_workspace_prepare(self._ws, rows, phase))
+
+    def run(self, projection, x, y):
+        _check(self._lib.gw_projection_workspace_run(self._ws, ctypes.byref(projection), _ptr(x), _ptr(y)))
+        return y
+
+    def bytes(self) -> int:
+        return int(self._lib.gw_projection_workspace_bytes(self._ws))
+
+    def __del__(self):
+        if getattr(self, "_ws", None):
+            self._lib.gw_projection_workspace_destroy(self._ws)
+            self._ws = None
+
+
 # --------------------------------------------------------------------------- weight QDQ
 
 def weight_qdq_apply(kind: int, values: torch.Tensor, stream=None) -> torch.Tensor:
@@ -258,15 +322,25 @@ def weight_qdq_apply(kind: int, values: torch.Tensor, stream=None) -> torch.Tens
 
 # --------------------------------------------------------------------------- MoE
 
-def make_projection(weight: Nvfp4Weight, input_width: int, output_width: int) -> _lib.Projection:
-    """sm120::Projection for an NVFP4 expert matrix whose rows are already
-    padded to a multiple of 128 (bind_projection, projection.cu:31-50)."""
+def make_projection(weight, input_width: int, output_width: int) -> _lib.Projection:
+    """sm120::Projection (bind_projection, projection.cu:31-50) for an expert matrix: an Nvfp4Weight
+    whose rows are already padded to a multiple of 128, an Fp8Weight, or a BF16 tensor [N, K]."""
     p = _lib.Projection()
-    p.storage = _lib.STORAGE_NVFP4_W4A4
     p.input, p.output = input_width, output_width
-    p.physical_output = (output_width + 127) // 128 * 128
-    p.nvfp4_data, p.nvfp4_scales = weight.data.data_ptr(), weight.scales.data_ptr()
-    p.nvfp4_input_scale, p.nvfp4_weight_scale = weight.input_scale, weight.weight_scale
+    p.physical_output = output_width
+    if isinstance(weight, Nvfp4Weight):
+        p.storage = _lib.STORAGE_NVFP4_W4A4
+        p.physical_output = (output_width + 127) // 128 * 128
+        p.nvfp4_data, p.nvfp4_scales = weight.data.data_ptr(), weight.scales.data_ptr()
+        p.nvfp4_input_scale, p.nvfp4_weight_scale = weight.input_scale, weight.weight_scale
+    elif isinstance(weight, Fp8Weight):
+        p.storage = _lib.STORAGE_FP8_W8A8
+        p.fp8_data = weight.data.data_ptr()
+        p.fp8_input_scale, p.fp8_weight_scale = weight.input_scale, weight.weight_scale
+        p.fp8_channel_scales = _ptr(weight.channel_scales) or None
+    else:
+        p.storage = _lib.STORAGE_BF16
+        p.bf16 = weight.data_ptr()
     return p
 
 
@@ -281,9 +355,10 @@ class _RawDeviceBytes:
 class ExpertTable:
     """The 128-entry ExpertWeights table, bound once (keeps the tensors alive)."""
 
-    def __init__(self, experts: list[tuple[Nvfp4Weight, Nvfp4Weight, Nvfp4Weight] | None]):
-        """`experts[i] is None` marks an expert whose weights live on another
-        rank (expert parallelism); no row may be routed to it on this rank."""
+    def __init__(self, experts: list[tuple | None]):
+        """experts[i] = (gate, up, down), each an Nvfp4Weight, an Fp8Weight or a BF16 tensor [N, K];
+        `experts[i] is None` marks an expert whose weights live on another rank (expert parallelism):
+        no row may be routed to it on this rank."""
         self._lib = _library()
         self._keep = experts
         array = (_lib.ExpertWeights * len(experts))()
@@ -302,6 +377,10 @@ class ExpertTable:
     def handle(self):
         return self._table
 
+    def enable_w4a16(self, stream=None):
+        """Make the BF16 copies that NVFP4 experts need to run with BF16 activations (set-up time)."""
+        _check(self._lib.gw_moe_expert_table_enable_w4a16(self._table, _stream(stream)))
+
     def __del__(self):
         if getattr(self, "_table", None):
             self._lib.gw_moe_expert_table_destroy(self._table)
@@ -311,12 +390,12 @@ class ExpertTable:
 class MoeWorkspace:
     """sm120::MoeWorkspace(max_rows): run, dispatch and the capture accessors."""
 
-    def __init__(self, max_rows: int, device=None):
+    def __init__(self, max_rows: int, device=None, fp8_experts: bool = False):
         self._lib = _library()
         self._ws = ctypes.c_void_p()
         self.max_rows = max_rows
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
-        _check(self._lib.gw_moe_create(max_rows, ctypes.byref(self._ws)))
+        _check(self._lib.gw_moe_create_ex(max_rows, 1 if fp8_experts else 0, ctypes.byref(self._ws)))
         self.rows = 0
 
     def dispatch(self, scores, expert_scales, rows: int, stream=None):

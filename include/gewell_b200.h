@@ -144,6 +144,23 @@ gw_status gw_fp8_plan_run(gw_fp8_plan* plan, const void* input_bf16, const uint8
 void gw_fp8_plan_destroy(gw_fp8_plan* plan);
 
 /* ------------------------------------------------------------------------- */
+/* BF16                                                                       */
+/* ------------------------------------------------------------------------- */
+
+/* BF16 linear layer Y[rows,N] = bf16(X . W^T), FP32 accumulation on tcgen05 kind::f16: the role of
+ * the reference's BF16 LinearPlan (models/gemma4/31b/sm120/resources.cuh:118) and of the
+ * cublasGemmEx call of its W4A16 / BF16 projection path (models/gemma4/26b_a4b/sm120/projection.cu:
+ * 130-139).  K and N divisible by 8; X [rows,K], W [N,K], Y [rows,N] row-major BF16, 16-byte aligned.
+ * scratch: gw_bf16_plan_scratch_bytes() bytes, 256-byte aligned (FP32 partial tiles of the K split
+ * that decode-shaped plans use), or NULL to run without the split. */
+typedef struct gw_bf16_plan gw_bf16_plan;
+gw_status gw_bf16_plan_create(uint32_t rows, uint32_t input_width, uint32_t output_width, gw_bf16_plan** plan);
+size_t gw_bf16_plan_scratch_bytes(const gw_bf16_plan* plan);
+gw_status gw_bf16_plan_run(gw_bf16_plan* plan, const void* input_bf16, const void* weight_bf16, void* output_bf16,
+                           void* scratch, size_t scratch_capacity, void* stream);
+void gw_bf16_plan_destroy(gw_bf16_plan* plan);
+
+/* ------------------------------------------------------------------------- */
 /* Weight QDQ -- src/weight_qdq.cu:105-189,222-258 (detail::apply_tensor)     */
 /* ------------------------------------------------------------------------- */
 enum { GW_QDQ_BF16 = 0, GW_QDQ_FP8 = 1, GW_QDQ_NVFP4 = 2 };
@@ -185,6 +202,39 @@ typedef struct gw_expert_weights {
   gw_projection gate, up, down;
 } gw_expert_weights;
 
+/* nvfp4::ActivationPolicy / nvfp4::Phase / fp4_activations (include/gewell/nvfp4_policy.h:7-12):
+ * policy "prefill" keeps decode activations in BF16 (NVFP4 weights are then used as W4A16). */
+enum { GW_POLICY_ALWAYS = 0, GW_POLICY_PREFILL = 1 };
+enum { GW_PHASE_PREFILL = 0, GW_PHASE_DECODE = 1 };
+int gw_nvfp4_fp4_activations(int policy, int phase);
+
+/* bind_projection (projection.cu:31-50): describe one artifact entry as a projection.  The entry is
+ * `rows` x `columns` (output x input) in `storage`; its payload starts at host_payload /
+ * device_payload (the same bytes on both sides) and is entry_bytes long:
+ *   BF16   [rows, columns] BF16
+ *   FP8    [rows, columns] E4M3, then <f32 weight_scale><f32 input_scale>
+ *   NVFP4  [rows padded to 128, columns/2] packed E2M1 (padding rows zero), tiled E4M3 scales for the
+ *          padded rows (padding zero), then <f32 weight_scale><f32 input_scale>
+ * with the two globals in the entry's last eight bytes (little endian).  Host-only; no device access. */
+gw_status gw_bind_projection(uint32_t storage, uint32_t rows, uint32_t columns, const uint8_t* host_payload,
+                             const void* device_payload, size_t entry_bytes, gw_projection* projection);
+
+/* ProjectionWorkspace (projection.cuh:19-41, projection.cu:52-145): shared scratch and plans for
+ * sequential projections on ONE stream, bound at construction.  create() sizes the scratch for
+ * max_rows and the given bindings and allocates it; prepare(rows, phase) builds the plans for a row
+ * count before the layer loop (it allocates small per-plan state: not capturable); run() allocates
+ * nothing and picks the path by storage, policy and phase (W8A8, W4A4, or BF16 GEMM on BF16 weights /
+ * on the NVFP4 weight dequantised to BF16), then strips NVFP4 output padding.  The reference's
+ * cublasHandle_t argument of run has no counterpart (no library GEMM). */
+typedef struct gw_projection_workspace gw_projection_workspace;
+gw_status gw_projection_workspace_create(const gw_projection* projections, uint32_t count, uint32_t max_rows,
+                                         int policy, void* stream, gw_projection_workspace** workspace);
+gw_status gw_projection_workspace_prepare(gw_projection_workspace* workspace, uint32_t rows, int phase);
+gw_status gw_projection_workspace_run(gw_projection_workspace* workspace, const gw_projection* projection,
+                                      const void* input_bf16, void* output_bf16);
+size_t gw_projection_workspace_bytes(const gw_projection_workspace* workspace);
+void gw_projection_workspace_destroy(gw_projection_workspace* workspace);
+
 /* The reference keeps the 128-entry ExpertWeights table in device memory and
  * reads it from its kernels (batched_executor.cu:62-88).  Here the table is
  * bound once from the host copy: the call validates it, builds the TMA
@@ -194,11 +244,23 @@ typedef struct gw_expert_table gw_expert_table;
 gw_status gw_moe_expert_table_create(const gw_expert_weights* experts, uint32_t count,
                                      gw_expert_table** table);
 void gw_moe_expert_table_destroy(gw_expert_table* table);
+/* Every projection may have its own storage type (BF16, FP8 W8A8, NVFP4), as in the reference.
+ * NVFP4 experts used with BF16 activations (fp4 == 0 in gw_moe_run: the reference's grouped_linear,
+ * moe.cu:96-103,353-395, which decodes weight tiles to BF16 in shared memory) run here on BF16 copies
+ * of their weights, made once by this call (allocates 2 bytes per weight and dequantises on `stream`,
+ * then synchronises it): set-up time, not capturable.  Without it gw_moe_run(fp4 == 0) returns
+ * GW_UNSUPPORTED for NVFP4 experts. */
+gw_status gw_moe_expert_table_enable_w4a16(gw_expert_table* table, void* stream);
 
 /* sm120::MoeWorkspace (moe.cuh:20-48, moe.cu:462-545).  max_rows in 1..65536
  * (the reference stops at 4096).  All buffers are allocated here, once. */
 typedef struct gw_moe_workspace gw_moe_workspace;
 gw_status gw_moe_create(uint32_t max_rows, gw_moe_workspace** workspace);
+/* The same with options.  GW_MOE_FP8_EXPERTS: also allocate the E4M3 staging of FP8 experts' inputs
+ * (24 KB per routed token), which the reference's grouped_fp8 (moe.cu:187-251) quantises in registers
+ * instead; without it gw_moe_run(has_fp8) returns GW_UNSUPPORTED for tables with FP8 experts. */
+enum { GW_MOE_FP8_EXPERTS = 1 };
+gw_status gw_moe_create_ex(uint32_t max_rows, uint32_t flags, gw_moe_workspace** workspace);
 void gw_moe_destroy(gw_moe_workspace* workspace);
 
 /* MoeWorkspace::dispatch (moe.cu:477-488): routing, stable sort by expert,
@@ -206,9 +268,12 @@ void gw_moe_destroy(gw_moe_workspace* workspace);
 gw_status gw_moe_dispatch(gw_moe_workspace* workspace, const void* scores_bf16,
                           const void* expert_scales_bf16, uint32_t rows, void* stream);
 
-/* MoeWorkspace::run (moe.cu:489-534).  fp4 != 0 selects W4A4 (NVFP4
- * activations); only NVFP4 experts with fp4 != 0 are built here, other
- * combinations return GW_UNSUPPORTED. */
+/* MoeWorkspace::run (moe.cu:489-534).  has_bf16 / has_fp8 / has_nvfp4 say which kinds of expert
+ * weights the table holds (a kind whose flag is 0 is not computed, as in the reference); fp4 != 0 runs
+ * NVFP4 experts with FP4 activations (W4A4), fp4 == 0 with BF16 activations (W4A16, see
+ * gw_moe_expert_table_enable_w4a16).  A table of NVFP4 experts only with fp4 != 0 takes the fused
+ * large-batch path; every other combination runs one grouped gate/up and down GEMM per kind present
+ * (tcgen05 kind::mxf4nvf4 / kind::f16 / kind::f8f6f4) with GeGLU unfused. */
 gw_status gw_moe_run(gw_moe_workspace* workspace, const void* input_bf16, const void* scores_bf16,
                      const void* expert_scales_bf16, const gw_expert_table* table, void* output_bf16,
                      uint32_t rows, int has_bf16, int has_fp8, int has_nvfp4, int fp4, void* stream);

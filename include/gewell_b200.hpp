@@ -77,11 +77,26 @@ constexpr std::size_t scale_offset(std::size_t row, std::size_t block, std::size
          block % 4;
 }
 
+enum class ActivationPolicy : std::uint8_t { always = GW_POLICY_ALWAYS, prefill = GW_POLICY_PREFILL };
+enum class Phase : std::uint8_t { prefill = GW_PHASE_PREFILL, decode = GW_PHASE_DECODE };
+// include/gewell/nvfp4_policy.h:9-16
+constexpr bool fp4_activations(ActivationPolicy policy, Phase phase) {
+  return policy == ActivationPolicy::always || phase == Phase::prefill;
+}
+constexpr const char* activation_policy_name(ActivationPolicy policy) {
+  return policy == ActivationPolicy::prefill ? "prefill" : "always";
+}
+
 class Plan {
  public:
-  // The reference constructor also takes a cublasLtHandle_t; no library GEMM
-  // is used here, so the parameter is gone.
   Plan(std::uint32_t rows, std::uint32_t input_width, std::uint32_t output_width) {
+    detail::check(gw_nvfp4_plan_create(rows, input_width, output_width, &plan_));
+  }
+  // The reference constructor takes a cublasLtHandle_t first.  No library GEMM is used here, so the
+  // handle is ignored; call sites compile unchanged (any pointer converts), and a null handle is still
+  // rejected as the reference rejects it.
+  Plan(const void* handle, std::uint32_t rows, std::uint32_t input_width, std::uint32_t output_width) {
+    if (handle == nullptr) throw std::invalid_argument("NVFP4 plan requires a handle");
     detail::check(gw_nvfp4_plan_create(rows, input_width, output_width, &plan_));
   }
   ~Plan() { gw_nvfp4_plan_destroy(plan_); }
@@ -207,6 +222,12 @@ class Plan {
   Plan(std::uint32_t rows, std::uint32_t input_width, std::uint32_t output_width, bool channel_scales = false) {
     detail::check(gw_fp8_plan_create(rows, input_width, output_width, channel_scales ? 1 : 0, &plan_));
   }
+  // reference signature with its (ignored, but non-null) cublasLtHandle_t first
+  Plan(const void* handle, std::uint32_t rows, std::uint32_t input_width, std::uint32_t output_width,
+       bool channel_scales = false) {
+    if (handle == nullptr) throw std::invalid_argument("FP8 plan requires a handle");
+    detail::check(gw_fp8_plan_create(rows, input_width, output_width, channel_scales ? 1 : 0, &plan_));
+  }
   ~Plan() { gw_fp8_plan_destroy(plan_); }
   Plan(Plan&& other) noexcept : plan_(other.plan_) { other.plan_ = nullptr; }
   Plan& operator=(Plan&& other) noexcept {
@@ -247,10 +268,66 @@ using ProjectionPlans = detail::PlanCache<Plan, Weight, InputTransform>;
 
 }  // namespace fp8
 
+namespace bf16 {
+// The reference's BF16 LinearPlan (models/gemma4/31b/sm120/resources.cuh:118-190): Y = X . W^T.
+class LinearPlan {
+ public:
+  LinearPlan(std::uint32_t rows, std::uint32_t input_width, std::uint32_t output_width) {
+    detail::check(gw_bf16_plan_create(rows, input_width, output_width, &plan_));
+  }
+  ~LinearPlan() { gw_bf16_plan_destroy(plan_); }
+  LinearPlan(const LinearPlan&) = delete;
+  LinearPlan& operator=(const LinearPlan&) = delete;
+  std::size_t scratch_bytes() const { return gw_bf16_plan_scratch_bytes(plan_); }
+  // scratch may be null (decode-shaped plans then run without the K split)
+  void run(const __nv_bfloat16* input, const __nv_bfloat16* weight, __nv_bfloat16* output, void* scratch = nullptr,
+           std::size_t scratch_capacity = 0, cudaStream_t stream = nullptr) {
+    detail::check(gw_bf16_plan_run(plan_, input, weight, output, scratch, scratch_capacity, stream));
+  }
+
+ private:
+  gw_bf16_plan* plan_{};
+};
+}  // namespace bf16
+
 namespace sm120 {
 
 using Projection = gw_projection;
 using ExpertWeights = gw_expert_weights;
+
+// bind_projection (projection.cu:31-50).  `storage` is a GW_STORAGE_* tag; rows x columns is the logical
+// (output x input) shape of the entry whose payload starts at host_payload / device_payload.
+inline Projection bind_projection(std::uint32_t storage, std::uint32_t rows, std::uint32_t columns,
+                                  const std::uint8_t* host_payload, const void* device_payload,
+                                  std::size_t entry_bytes) {
+  Projection projection{};
+  detail::check(gw_bind_projection(storage, rows, columns, host_payload, device_payload, entry_bytes, &projection));
+  return projection;
+}
+
+// ProjectionWorkspace (projection.cuh:19-41).  run() keeps the reference's handle parameter (ignored).
+class ProjectionWorkspace {
+ public:
+  ProjectionWorkspace(const std::vector<Projection>& projections, unsigned max_rows, nvfp4::ActivationPolicy policy,
+                      cudaStream_t stream) {
+    detail::check(gw_projection_workspace_create(projections.data(), static_cast<std::uint32_t>(projections.size()),
+                                                 max_rows, static_cast<int>(policy), stream, &workspace_));
+  }
+  ~ProjectionWorkspace() { gw_projection_workspace_destroy(workspace_); }
+  ProjectionWorkspace(const ProjectionWorkspace&) = delete;
+  ProjectionWorkspace& operator=(const ProjectionWorkspace&) = delete;
+  void prepare(unsigned rows, nvfp4::Phase phase) {
+    detail::check(gw_projection_workspace_prepare(workspace_, rows, static_cast<int>(phase)));
+  }
+  void run(const void* /*cublas handle, unused*/, const Projection& projection, const __nv_bfloat16* input,
+           __nv_bfloat16* output) {
+    detail::check(gw_projection_workspace_run(workspace_, &projection, input, output));
+  }
+  std::size_t bytes() const { return gw_projection_workspace_bytes(workspace_); }
+
+ private:
+  gw_projection_workspace* workspace_{};
+};
 
 // Host-bound expert table (see gw_moe_expert_table_create).
 class ExpertTable {

@@ -23,6 +23,7 @@ from dataclasses import dataclass
 import numpy as np
 
 from . import codecs as C
+from . import fp8
 from . import nvfp4
 
 EXPERTS = 128
@@ -33,11 +34,13 @@ INTERMEDIATE = 704
 
 @dataclass
 class ExpertWeights:
-    """Mirror of sm120::ExpertWeights{gate, up, down} (moe.cuh:11-13); each
-    member is an oracle nvfp4.Weight whose rows may be padded to 128."""
-    gate: nvfp4.Weight
-    up: nvfp4.Weight
-    down: nvfp4.Weight
+    """Mirror of sm120::ExpertWeights{gate, up, down} (moe.cuh:11-13).  Each
+    member carries its own storage, as in the reference: an oracle nvfp4.Weight
+    (rows may be padded to 128), an fp8.Weight, or a BF16-valued FP32 matrix
+    [N, K] for BF16 storage."""
+    gate: object
+    up: object
+    down: object
 
 
 def softmax_device_order(scores: np.ndarray) -> np.ndarray:
@@ -85,8 +88,14 @@ def permutation(ids: np.ndarray):
     return order, offsets
 
 
-def _project(x: np.ndarray, weight: nvfp4.Weight, logical: int, mode: str, accumulate: str, rcp_fn=None) -> np.ndarray:
-    """One expert projection; BF16-valued FP32 result [rows, logical]."""
+def _project(x: np.ndarray, weight, logical: int, mode: str, accumulate: str, rcp_fn=None) -> np.ndarray:
+    """One expert projection; BF16-valued FP32 result [rows, logical].  BF16 weights: FP32 matmul,
+    BF16 out (moe.cu:21-63,396-438); FP8 weights: the W8A8 oracle of the FP8 linear layer with the
+    projection's own scales (moe.cu:187-251); NVFP4 weights by `mode`."""
+    if isinstance(weight, np.ndarray):
+        return C.bf16_round(np.asarray(x, dtype=np.float32) @ weight[:logical].T)
+    if isinstance(weight, fp8.Weight):
+        return C.bf16_to_f32(fp8.linear_w8a8(x, weight))[:, :logical]
     if mode == "w4a16":
         return C.bf16_to_f32(nvfp4.linear_w4a16(x, weight, logical))
     q = nvfp4.quantize_activations(x, weight.input_scale, rcp_fn=rcp_fn)

@@ -252,17 +252,122 @@ def test_moe_layer_combine_consistency(gw, experts, experts_shared, moe_form, ro
         assert_gemm_close(bits(y), bits(y2), f"{form} plan vs swap plan at rows={rows}")
 
 
-def test_moe_unsupported_modes(gw, experts):
+def test_moe_mode_validation(gw, experts):
     table, _ = experts
     ws = gw.MoeWorkspace(4)
     x = torch.zeros((4, H), dtype=torch.bfloat16, device="cuda")
     s = torch.zeros((4, E), dtype=torch.bfloat16, device="cuda")
     one = torch.ones(E, dtype=torch.bfloat16, device="cuda")
-    with pytest.raises(gw.GewellUnsupported):
-        ws.run(x, s, one, table, x.clone(), 4, fp4=False)
-    with pytest.raises(gw.GewellUnsupported):
-        ws.run(x, s, one, table, x.clone(), 4, has_bf16=True)
-    ws.run(x, s, one, table, x.clone(), 0)          # rows == 0 is a no-op
+    with pytest.raises(gw.GewellUnsupported, match="enable_w4a16"):
+        ws.run(x, s, one, table, x.clone(), 4, fp4=False)          # W4A16 needs the BF16 copies first
+    with pytest.raises(gw.GewellInvalidArgument):
+        ws.run(x, s, one, table, x.clone(), 4, has_nvfp4=False)    # nothing selected
+    ws.run(x, s, one, table, x.clone(), 4, has_bf16=True)          # extra flags are hints only
+    ws.run(x, s, one, table, x.clone(), 0)                         # rows == 0 is a no-op
+    torch.cuda.synchronize()
+    assert gw.kernel_error() == 0
+
+
+@pytest.fixture(scope="module")
+def experts_w4a16(gw, experts):
+    """The NVFP4 experts with their BF16 copies made (a table of its own: the copies cost 1.6 GB)."""
+    table, host = experts
+    w4a16 = gw.ExpertTable(table._keep)
+    w4a16.enable_w4a16()
+    return w4a16, host
+
+
+@pytest.mark.parametrize("rows,mode", [(1, "hot"), (7, "normal"), (33, "normal"), (129, "uneven"), (600, "uneven")])
+def test_moe_w4a16_experts_vs_host_path(gw, experts_w4a16, rows, mode):
+    """NVFP4 experts with BF16 activations (fp4 = 0; the reference's grouped_linear, moe.cu:96-103,353-395):
+    against the W4A16 host path -- dequantise the weights to BF16, FP32 matmul -- at the path's tolerance."""
+    table, host = experts_w4a16
+    x = bf16_normal((rows, H), 400 + rows)
+    scores = make_scores(rows, mode, rows)
+    ws = gw.MoeWorkspace(max(rows, 64))
+    y = torch.full((rows * H + 64,), -3.0, dtype=torch.bfloat16, device="cuda")
+    ws.run(x.cuda(), scores.cuda(), torch.ones(E, dtype=torch.bfloat16, device="cuda"), table, y, rows, fp4=False)
+    torch.cuda.synchronize()
+    assert gw.kernel_error() == 0
+    assert torch.all(y[rows * H:] == -3.0)
+    capture = {}
+    expected = omoe.forward(to_f32(x), to_f32(scores), np.ones(E, dtype=np.float32), host, mode="w4a16", capture=capture)
+    assert np.array_equal(ws.selected_experts().cpu().numpy(), capture["ids"])
+    assert_gemm_close(bits(ws.gate_up_capture()), C.bf16_bits(capture["gate_up"]), "W4A16 gate/up capture")
+    assert_gemm_close(bits(ws.down_capture()), C.bf16_bits(capture["down"]), "W4A16 down capture")
+    m = assert_gemm_close(bits(y[:rows * H].reshape(rows, H)), expected, f"W4A16 MoE rows={rows} {mode}")
+    print(f"W4A16 rows={rows} {mode}: rel_fro {m['rel_fro']:.2e} max_abs/max {m['max_abs'] / m['max_ref']:.2e}")
+    # the same table still runs with FP4 activations
+    y4 = torch.empty((rows, H), dtype=torch.bfloat16, device="cuda")
+    ws.run(x.cuda(), scores.cuda(), torch.ones(E, dtype=torch.bfloat16, device="cuda"), table, y4, rows, fp4=True)
+    torch.cuda.synchronize()
+    assert gw.kernel_error() == 0 and torch.isfinite(y4.float()).all()
+
+
+@pytest.fixture(scope="module")
+def experts_mixed(gw):
+    """Every (expert, projection) with its own storage type, cycling BF16 / FP8 / NVFP4 as (expert + role) % 3
+    (the fourth storage recipe of tests/gemma4_26b_moe_quantized.cu:104-118), all from the same N(0, 0.02)
+    matrices; FP8 with per-tensor weight scale amax/448."""
+    from oracle import fp8 as ofp8
+    device, host = [], []
+    for e in range(E):
+        g = torch.Generator().manual_seed(9 * 1000 + e)
+        shapes = [(I, H), (I, H), (H, I)]
+        dev_row, host_row = [], []
+        for role, (n, k) in enumerate(shapes):
+            m = (torch.randn((n, k), generator=g) * 0.02).bfloat16()
+            kind = (e + role) % 3
+            input_scale = [0.004, 0.0045, 0.0007][role] * (1 + 0.1 * (e % 3))
+            if kind == 0:
+                dev_row.append(m.cuda())
+                host_row.append(to_f32(m))
+            elif kind == 1:
+                hw = ofp8.pack_weights(to_f32(m), input_scale)
+                dev_row.append(gw.Fp8Weight(torch.from_numpy(hw.data.copy()).cuda(), hw.input_scale, hw.weight_scale))
+                host_row.append(hw)
+            else:
+                packed = pack_padded(gw, m.cuda(), input_scale, (n + 127) // 128 * 128)
+                dev_row.append(packed)
+                host_row.append(onv.Weight(packed.data.cpu().numpy(), packed.scales.cpu().numpy(), packed.input_scale,
+                                           packed.weight_scale, packed.data.shape[0], k))
+        device.append(tuple(dev_row))
+        host.append(omoe.ExpertWeights(*host_row))
+    return gw.ExpertTable(device), host
+
+
+@pytest.mark.parametrize("rows,mode,fp4", [(1, "hot", True), (17, "distributed", True), (129, "uneven", True),
+                                           (300, "normal", True), (700, "normal", True), (33, "normal", False),
+                                           (600, "uneven", False)])
+def test_moe_mixed_storage_vs_oracle(gw, experts_mixed, rows, mode, fp4):
+    """BF16, FP8 and NVFP4 projections side by side in one table (tests/gemma4_26b_moe_quantized.cu:57-253
+    runs six such recipes): each projection against the oracle of its own storage type -- FP32 matmul for
+    BF16, the W8A8 oracle for FP8, W4A4 or (fp4 = 0) W4A16 for NVFP4."""
+    table, host = experts_mixed
+    if not fp4:
+        table.enable_w4a16()
+    x = bf16_normal((rows, H), 500 + rows)
+    scores = make_scores(rows, mode, rows)
+    ws = gw.MoeWorkspace(max(rows, 64), fp8_experts=True)
+    y = torch.full((rows * H + 64,), -3.0, dtype=torch.bfloat16, device="cuda")
+    ws.run(x.cuda(), scores.cuda(), torch.ones(E, dtype=torch.bfloat16, device="cuda"), table, y, rows,
+           has_bf16=True, has_fp8=True, has_nvfp4=True, fp4=fp4)
+    torch.cuda.synchronize()
+    assert gw.kernel_error() == 0
+    assert torch.all(y[rows * H:] == -3.0)
+    capture = {}
+    expected = omoe.forward(to_f32(x), to_f32(scores), np.ones(E, dtype=np.float32), host,
+                            mode="w4a4" if fp4 else "w4a16", capture=capture, rcp_fn=gw.rcp_approx, gelu_fn=gw.geglu_bf16)
+    assert np.array_equal(ws.selected_experts().cpu().numpy(), capture["ids"])
+    assert_gemm_close(bits(ws.gate_up_capture()), C.bf16_bits(capture["gate_up"]), "mixed gate/up capture")
+    assert_gemm_close(bits(ws.activated_capture()), C.bf16_bits(capture["activated"]), "mixed activated capture")
+    assert_gemm_close(bits(ws.down_capture()), C.bf16_bits(capture["down"]), "mixed down capture")
+    m = assert_gemm_close(bits(y[:rows * H].reshape(rows, H)), expected, f"mixed MoE rows={rows} {mode} fp4={fp4}")
+    print(f"mixed rows={rows} {mode} fp4={fp4}: rel_fro {m['rel_fro']:.2e}")
+    # a workspace without the FP8 staging refuses FP8 experts instead of computing garbage
+    with pytest.raises(gw.GewellUnsupported, match="GW_MOE_FP8_EXPERTS"):
+        gw.MoeWorkspace(4).run(x.cuda(), scores.cuda(), torch.ones(E, dtype=torch.bfloat16, device="cuda"), table, y, 1,
+                               has_bf16=True, has_fp8=True, has_nvfp4=True, fp4=True)
 
 
 _sampled_oracle_cache = {}
