@@ -54,11 +54,12 @@ struct gw_expert_table {
 // Tuning overrides, read from the environment once, when a workspace is created:
 //   GW_MOE_FORM          swap / direct / fused: plan of the grouped GEMMs (default: by batch size)
 //   GW_MOE_NO_PAIR       1: never use the CTA-pair kernels (single-CTA kernels for every batch size)
+//   GW_MOE_ROUTE_THREE_LAUNCHES  1: route, scan and scatter as three launches instead of one with a grid barrier
 //   GW_MOE_BLOCK_N, GW_MOE_BLOCK_N_DOWN, GW_MOE_CHUNK_FIRST, GW_MOE_CHUNK_DOWN: tile / schedule of the
 //                        single-CTA kernels
 struct MoeTuning {
   char form = 0;
-  bool no_pair = false;
+  bool no_pair = false, route_three_launches = false;
   int block_n = 0, block_n_down = 0, chunk_first = 0, chunk_down = 0;
   static int number(const char* name) {
     const char* value = std::getenv(name);
@@ -68,6 +69,7 @@ struct MoeTuning {
     const char* forced = std::getenv("GW_MOE_FORM");
     form = forced ? forced[0] : 0;
     no_pair = number("GW_MOE_NO_PAIR") != 0;
+    route_three_launches = number("GW_MOE_ROUTE_THREE_LAUNCHES") != 0;
     block_n = number("GW_MOE_BLOCK_N");
     block_n_down = number("GW_MOE_BLOCK_N_DOWN");
     chunk_first = number("GW_MOE_CHUNK_FIRST");
@@ -94,6 +96,7 @@ struct gw_moe_workspace {
   MoeTuning tuning;
   CachedMap first_map, down_map;
   DeviceBuffer metadata, bitmaps, groups, packed_in, scales_in, gate_up, activated, packed_act, scales_act, down;
+  DeviceBuffer route_barrier;   // counter and generation of the routing kernel's grid-wide barrier
   DeviceBuffer row_home;   // expert parallelism: address of every produced row's home in its source rank
   DeviceBuffer fp8_in, fp8_act;   // FP8 experts (GW_MOE_FP8_EXPERTS): E4M3 gate / up inputs [2][n, 2816], down input [n, 704]
   DeviceBuffer kind_groups;       // group descriptors of the BF16 and FP8 launches of a mixed table
@@ -272,6 +275,8 @@ gw_status gw_moe_create_ex(uint32_t max_rows, uint32_t flags, gw_moe_workspace**
   if (status == cudaSuccess) status = w->scales_act.allocate(size_t(w->scale_rows) * (kInter / 16));
   if (status == cudaSuccess) status = w->down.allocate(n * kHidden * sizeof(bf16));
   if (status == cudaSuccess) status = w->row_home.allocate(n * sizeof(uint64_t));
+  if (status == cudaSuccess) status = w->route_barrier.allocate(2 * sizeof(uint32_t));
+  if (status == cudaSuccess) status = cudaMemset(w->route_barrier.data, 0, 2 * sizeof(uint32_t));
   if (status == cudaSuccess) status = w->kind_groups.allocate(2 * (2 * kExperts + 1 + kExperts + 1) * sizeof(GemmGroup));
   if (status == cudaSuccess && (flags & GW_MOE_FP8_EXPERTS)) {
     status = w->fp8_in.allocate(2 * n * kHidden);
@@ -309,7 +314,8 @@ gw_status gw_moe_dispatch(gw_moe_workspace* w, const void* scores_bf16, const vo
   if (!scores_bf16 || !expert_scales_bf16) return fail(GW_INVALID_ARGUMENT, "MoE dispatch requires scores and expert scales");
   GW_CUDA_CHECK(launch_moe_dispatch(scores_bf16, expert_scales_bf16, rows, w->keys, w->weights, w->bitmaps.as<uint32_t>(),
                                     w->chunk_counts, w->offsets, w->sorted_assignments, w->sorted_keys, w->inverse,
-                                    as_stream(stream)),
+                                    w->route_barrier.as<uint32_t>(), device_error_word(), sm_count(),
+                                    !w->tuning.route_three_launches, as_stream(stream)),
                 "MoE dispatch");
   return GW_OK;
 }

@@ -21,12 +21,94 @@ constexpr int kInter = 704;
 constexpr int kMapsPerExpert = kMoeMapsPerExpert;
 constexpr int kChunkTokens = 64;   // tokens per routing block (two 32-bit bitmap words per expert)
 
+__device__ __forceinline__ uint64_t ptx_global_timer() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
 __device__ __forceinline__ void unpack8(const uint4& raw, float* out) {
   const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     out[2 * i] = __uint_as_float(w[i] << 16);
     out[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+
+// One token (one warp): FP32 softmax over its 128 logits, eight winners, renormalised weights, and the
+// winners' bits in the chunk's bitmaps.  The FP32 operation order is that of the reference's select
+// kernel (models/gemma4/26b_a4b/sm120/moe.cu:104-157), so ids and FP32 weights match it bit for bit.
+__device__ __forceinline__ void route_token(const bf16* __restrict__ scores, const bf16* __restrict__ expert_scales,
+                                            uint32_t row, uint32_t local, unsigned lane, int32_t* __restrict__ keys,
+                                            float* __restrict__ weights, uint32_t (*bitmap)[2]) {
+  // Softmax over the token's 128 logits; this lane owns experts lane, lane + 32, lane + 64, lane + 96.
+  // The FP32 additions keep the order the reference's weights depend on: the lane's four terms in
+  // ascending expert order first, then the xor butterfly 16, 8, 4, 2, 1 over the lanes.
+  const bf16* token_scores = scores + size_t(row) * kExperts;
+  float prob[4];
+  float peak = -INFINITY;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    prob[q] = __bfloat162float(token_scores[lane + 32 * q]);
+    peak = fmaxf(peak, prob[q]);
+  }
+#pragma unroll
+  for (int step = 16; step > 0; step >>= 1) peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, step));
+  float denominator = 0.0F;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    prob[q] = expf(prob[q] - peak);
+    denominator += prob[q];
+  }
+#pragma unroll
+  for (int step = 16; step > 0; step >>= 1) denominator += __shfl_xor_sync(0xffffffffu, denominator, step);
+  // Eight winners, one 64-bit maximum per round: the probability's bit pattern (probabilities are
+  // not negative, so their patterns order like unsigned integers) in the high word and 128 - id
+  // in the low word, so that the larger probability wins and, among equal ones, the smaller id.
+  // A candidate that has won is replaced by key 0, below every live key.
+  unsigned long long candidate[4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    prob[q] = __fdiv_rn(prob[q], denominator);
+    candidate[q] = (static_cast<unsigned long long>(__float_as_uint(prob[q])) << 32) | uint32_t(kExperts - (lane + 32 * q));
+  }
+  int ids[kTopK];
+  float chosen[kTopK];
+#pragma unroll
+  for (int round = 0; round < kTopK; ++round) {
+    unsigned long long winner = candidate[0];
+#pragma unroll
+    for (int q = 1; q < 4; ++q) winner = candidate[q] > winner ? candidate[q] : winner;
+#pragma unroll
+    for (int step = 16; step > 0; step >>= 1) {
+      const unsigned long long theirs = __shfl_xor_sync(0xffffffffu, winner, step);
+      winner = theirs > winner ? theirs : winner;
+    }
+    const int id = kExperts - int(uint32_t(winner));
+    ids[round] = id;
+    chosen[round] = __uint_as_float(uint32_t(winner >> 32));
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      if (id == int(lane) + 32 * q) candidate[q] = 0;
+  }
+  // renormalisation: ((p0+p4)+(p2+p6)) + ((p1+p5)+(p3+p7)), the pairwise order of a stride-4/2/1 fold
+  float fold[4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) fold[q] = chosen[q] + chosen[q + 4];
+  const float sum = (fold[0] + fold[2]) + (fold[1] + fold[3]);
+  int my_id = 0;
+  float my_p = 0;
+#pragma unroll
+  for (int i = 0; i < kTopK; ++i) if (lane == unsigned(i)) { my_id = ids[i]; my_p = chosen[i]; }
+  if (lane < kTopK) {
+    int rank = 0;
+#pragma unroll
+    for (int i = 0; i < kTopK; ++i) rank += ids[i] < my_id;
+    const float weight = __fmul_rn(__fdiv_rn(my_p, sum), __bfloat162float(expert_scales[my_id]));
+    keys[size_t(row) * kTopK + rank] = my_id;
+    weights[size_t(row) * kTopK + rank] = weight;
+    atomicOr(&bitmap[my_id][local / 32], 1u << (local % 32));
   }
 }
 
@@ -37,6 +119,7 @@ __device__ __forceinline__ void unpack8(const uint4& raw, float* out) {
 //    (models/gemma4/26b_a4b/sm120/moe.cu:104-157), so ids and FP32 weights match
 //    it bit for bit.  One warp per token, eight tokens per warp.
 // ---------------------------------------------------------------------------
+//    (route_token below; used by the single-block kernel and by the grid-wide kernel)
 //    With at most 64 tokens there is one block: it then also does the work of kernels 2
 //    and 3 (`offsets` != nullptr), which saves two dependent launches on the decode path.
 __global__ void __launch_bounds__(1024)
@@ -57,74 +140,7 @@ moe_route_kernel(const bf16* __restrict__ scores, const bf16* __restrict__ exper
     const uint32_t local = warp * tokens_per_warp + t;
     const uint32_t row = chunk * kChunkTokens + local;
     if (row >= rows) break;
-    // Softmax over the token's 128 logits; this lane owns experts lane, lane + 32, lane + 64, lane + 96.
-    // The FP32 additions keep the order the reference's weights depend on: the lane's four terms in
-    // ascending expert order first, then the xor butterfly 16, 8, 4, 2, 1 over the lanes.
-    const bf16* token_scores = scores + size_t(row) * kExperts;
-    float prob[4];
-    float peak = -INFINITY;
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      prob[q] = __bfloat162float(token_scores[lane + 32 * q]);
-      peak = fmaxf(peak, prob[q]);
-    }
-#pragma unroll
-    for (int step = 16; step > 0; step >>= 1) peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, step));
-    float denominator = 0.0F;
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      prob[q] = expf(prob[q] - peak);
-      denominator += prob[q];
-    }
-#pragma unroll
-    for (int step = 16; step > 0; step >>= 1) denominator += __shfl_xor_sync(0xffffffffu, denominator, step);
-    // Eight winners, one 64-bit maximum per round: the probability's bit pattern (probabilities are
-    // not negative, so their patterns order like unsigned integers) in the high word and 128 - id
-    // in the low word, so that the larger probability wins and, among equal ones, the smaller id.
-    // A candidate that has won is replaced by key 0, below every live key.
-    unsigned long long candidate[4];
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      prob[q] = __fdiv_rn(prob[q], denominator);
-      candidate[q] = (static_cast<unsigned long long>(__float_as_uint(prob[q])) << 32) | uint32_t(kExperts - (lane + 32 * q));
-    }
-    int ids[kTopK];
-    float chosen[kTopK];
-#pragma unroll
-    for (int round = 0; round < kTopK; ++round) {
-      unsigned long long winner = candidate[0];
-#pragma unroll
-      for (int q = 1; q < 4; ++q) winner = candidate[q] > winner ? candidate[q] : winner;
-#pragma unroll
-      for (int step = 16; step > 0; step >>= 1) {
-        const unsigned long long theirs = __shfl_xor_sync(0xffffffffu, winner, step);
-        winner = theirs > winner ? theirs : winner;
-      }
-      const int id = kExperts - int(uint32_t(winner));
-      ids[round] = id;
-      chosen[round] = __uint_as_float(uint32_t(winner >> 32));
-#pragma unroll
-      for (int q = 0; q < 4; ++q)
-        if (id == int(lane) + 32 * q) candidate[q] = 0;
-    }
-    // renormalisation: ((p0+p4)+(p2+p6)) + ((p1+p5)+(p3+p7)), the pairwise order of a stride-4/2/1 fold
-    float fold[4];
-#pragma unroll
-    for (int q = 0; q < 4; ++q) fold[q] = chosen[q] + chosen[q + 4];
-    const float sum = (fold[0] + fold[2]) + (fold[1] + fold[3]);
-    int my_id = 0;
-    float my_p = 0;
-#pragma unroll
-    for (int i = 0; i < kTopK; ++i) if (lane == unsigned(i)) { my_id = ids[i]; my_p = chosen[i]; }
-    if (lane < kTopK) {
-      int rank = 0;
-#pragma unroll
-      for (int i = 0; i < kTopK; ++i) rank += ids[i] < my_id;
-      const float weight = __fmul_rn(__fdiv_rn(my_p, sum), __bfloat162float(expert_scales[my_id]));
-      keys[size_t(row) * kTopK + rank] = my_id;
-      weights[size_t(row) * kTopK + rank] = weight;
-      atomicOr(&bitmap[my_id][local / 32], 1u << (local % 32));
-    }
+    route_token(scores, expert_scales, row, local, lane, keys, weights, bitmap);
   }
   __syncthreads();
   if (threadIdx.x < kExperts) {
@@ -158,6 +174,157 @@ moe_route_kernel(const bf16* __restrict__ scores, const bf16* __restrict__ exper
     sorted_assignments[position] = int32_t(assignment);
     sorted_keys[position] = e;
     inverse[assignment] = position;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// 1b. route + scan + scatter in ONE launch for more than 64 tokens.  At most
+//     kRouteGridBlocksPerSm blocks per SM, each walking chunks b, b + grid, ...:
+//       phase 1  route the block's chunks (bitmaps and per-chunk counts to global memory)
+//       barrier  every block has published its counts
+//       phase 2  every block walks all chunk counts once: the running sums at its own chunks are
+//                their bases, the totals give the expert offsets (block 0 stores them)
+//       phase 3  scatter the block's chunks
+//     The barrier is a counter plus a generation word in the workspace (the last block to arrive
+//     resets the counter and bumps the generation, so replays need no host-side reset).  All blocks
+//     are resident together -- the grid is sized below what the GPU holds at once -- and the wait is
+//     bounded: on a timeout the block reports through the error word and returns.
+// ---------------------------------------------------------------------------
+constexpr int kRouteGridBlocksPerSm = 1;
+constexpr int kRouteGridThreads = 1024;
+constexpr int kRouteOwnChunks = 16;     // chunks per block the launch sizes the grid for (65536 tokens / 64 / 148 < 8)
+constexpr int kRouteParts = kRouteGridThreads / kExperts;   // phase 2: eight threads share an expert's chunk list
+
+__device__ __forceinline__ bool route_grid_barrier(uint32_t* state, uint32_t blocks, uint32_t* error) {
+  __shared__ int passed;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();                                        // this block's counts are visible before it arrives
+    const uint32_t generation = atomicAdd(state + 1, 0u);
+    int ok = 1;
+    if (atomicAdd(state, 1u) == blocks - 1) {
+      atomicExch(state, 0u);                                // ready for the next launch
+      __threadfence();
+      atomicAdd(state + 1, 1u);
+    } else {
+      const uint64_t start = ptx_global_timer();
+      for (uint32_t spin = 1; atomicAdd(state + 1, 0u) == generation; ++spin) {
+        if ((spin & 63u) == 0 && ptx_global_timer() - start > 2000000000ull) { ok = 0; break; }
+        __nanosleep(32);
+      }
+    }
+    __threadfence();
+    if (!ok && error != nullptr) atomicCAS(error, 0u, 0x80000000u | blockIdx.x);
+    passed = ok;
+  }
+  __syncthreads();
+  return passed != 0;
+}
+
+__global__ void __launch_bounds__(kRouteGridThreads)
+moe_route_grid_kernel(const bf16* __restrict__ scores, const bf16* __restrict__ expert_scales, uint32_t rows,
+                      uint32_t chunks, int32_t* __restrict__ keys, float* __restrict__ weights,
+                      uint32_t* __restrict__ bitmaps, int32_t* __restrict__ chunk_counts, int32_t* __restrict__ offsets,
+                      int32_t* __restrict__ sorted_assignments, int32_t* __restrict__ sorted_keys,
+                      int32_t* __restrict__ inverse, uint32_t* __restrict__ barrier_state, uint32_t* __restrict__ error) {
+  griddep_launch();
+  griddep_wait();     // results of earlier kernels in the stream are read from here on
+  __shared__ uint32_t bitmap[kExperts][2];
+  __shared__ int32_t own_base[kRouteOwnChunks][kExperts];
+  __shared__ int32_t part_sum[kRouteParts][kExperts];
+  __shared__ int32_t expert_offset[kExperts];
+  __shared__ int32_t warp_totals[4];
+  const unsigned lane = threadIdx.x % 32, warp = threadIdx.x / 32;
+  constexpr int kTokensPerWarp = kChunkTokens / (kRouteGridThreads / 32);     // 2
+  // ---- phase 1: 32 warps, two tokens each, per chunk
+  for (uint32_t chunk = blockIdx.x; chunk < chunks; chunk += gridDim.x) {
+    if (threadIdx.x < kExperts) { bitmap[threadIdx.x][0] = 0; bitmap[threadIdx.x][1] = 0; }
+    __syncthreads();
+#pragma unroll
+    for (int t = 0; t < kTokensPerWarp; ++t) {
+      const uint32_t local = warp * kTokensPerWarp + t;
+      const uint32_t row = chunk * kChunkTokens + local;
+      if (row < rows) route_token(scores, expert_scales, row, local, lane, keys, weights, bitmap);
+    }
+    __syncthreads();
+    if (threadIdx.x < kExperts) {
+      const uint32_t w0 = bitmap[threadIdx.x][0], w1 = bitmap[threadIdx.x][1];
+      bitmaps[(size_t(chunk) * kExperts + threadIdx.x) * 2] = w0;
+      bitmaps[(size_t(chunk) * kExperts + threadIdx.x) * 2 + 1] = w1;
+      chunk_counts[size_t(chunk) * kExperts + threadIdx.x] = __popc(w0) + __popc(w1);
+    }
+    __syncthreads();
+  }
+  if (!route_grid_barrier(barrier_state, gridDim.x, error)) return;
+  // ---- phase 2: expert e's counts summed over the chunks in order; eight threads share the list (contiguous
+  // ranges of chunks), their partial sums are combined in order afterwards
+  {
+    const unsigned e = threadIdx.x % kExperts, part = threadIdx.x / kExperts;
+    const uint32_t per_part = (chunks + kRouteParts - 1) / kRouteParts;
+    const uint32_t c_begin = min(part * per_part, chunks), c_end = min(c_begin + per_part, chunks);
+    int32_t running = 0;
+#pragma unroll 8
+    for (uint32_t c = c_begin; c < c_end; ++c) running += __ldcg(chunk_counts + size_t(c) * kExperts + e);
+    part_sum[part][e] = running;
+    __syncthreads();
+    // bases of this block's own chunks: sum of the parts before the chunk's part plus the counts inside it
+    if (part == 0) {
+      int32_t before[kRouteParts];
+      int32_t total = 0;
+#pragma unroll
+      for (int q = 0; q < kRouteParts; ++q) { before[q] = total; total += part_sum[q][e]; }
+      uint32_t own = 0;
+      for (uint32_t chunk = blockIdx.x; chunk < chunks; chunk += gridDim.x, ++own) {
+        const uint32_t q = chunk / per_part;
+        int32_t base = before[q];
+        for (uint32_t c = q * per_part; c < chunk; ++c) base += __ldcg(chunk_counts + size_t(c) * kExperts + e);
+        own_base[own][e] = base;
+      }
+      // exclusive scan of the totals over the 128 experts (threads 0..127 are four whole warps)
+      int32_t scan = total;
+#pragma unroll
+      for (int step = 1; step < 32; step *= 2) {
+        const int32_t other = __shfl_up_sync(0xffffffffu, scan, step);
+        if (lane >= unsigned(step)) scan += other;
+      }
+      if (lane == 31) warp_totals[warp] = scan;
+      expert_offset[e] = scan - total;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < kExperts) {
+    int32_t base = 0;
+    for (unsigned w = 0; w < warp; ++w) base += warp_totals[w];
+    expert_offset[threadIdx.x] += base;
+    if (blockIdx.x == 0) {
+      offsets[threadIdx.x] = expert_offset[threadIdx.x];
+      if (threadIdx.x == kExperts - 1) offsets[kExperts] = base + warp_totals[3];
+    }
+  }
+  __syncthreads();
+  // ---- phase 3
+  uint32_t own = 0;
+  for (uint32_t chunk = blockIdx.x; chunk < chunks; chunk += gridDim.x, ++own) {
+    if (threadIdx.x < kExperts) {
+      bitmap[threadIdx.x][0] = __ldcg(bitmaps + (size_t(chunk) * kExperts + threadIdx.x) * 2);
+      bitmap[threadIdx.x][1] = __ldcg(bitmaps + (size_t(chunk) * kExperts + threadIdx.x) * 2 + 1);
+    }
+    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < kChunkTokens * kTopK; i += kRouteGridThreads) {
+      const uint32_t local = i / kTopK;
+      const uint32_t row = chunk * kChunkTokens + local;
+      if (row >= rows) continue;
+      const uint32_t assignment = row * kTopK + i % kTopK;
+      const int32_t e = keys[assignment];
+      const uint32_t w0 = bitmap[e][0], w1 = bitmap[e][1];
+      const int rank = local < 32 ? __popc(w0 & ((1u << local) - 1u))
+                                  : __popc(w0) + __popc(w1 & ((1u << (local - 32)) - 1u));
+      const int32_t position = expert_offset[e] + own_base[own][e] + rank;
+      sorted_assignments[position] = int32_t(assignment);
+      sorted_keys[position] = e;
+      inverse[assignment] = position;
+    }
+    __syncthreads();
   }
 }
 
@@ -924,12 +1091,20 @@ uint32_t moe_chunks(uint32_t rows) { return (rows + kChunkTokens - 1) / kChunkTo
 cudaError_t launch_moe_dispatch(const void* scores, const void* expert_scales, uint32_t rows, int32_t* keys,
                                 float* weights, uint32_t* bitmaps, int32_t* chunk_counts, int32_t* offsets,
                                 int32_t* sorted_assignments, int32_t* sorted_keys, int32_t* inverse,
+                                uint32_t* barrier_state, uint32_t* error, int sm_count, bool one_launch,
                                 cudaStream_t stream) {
   const uint32_t chunks = moe_chunks(rows);
   if (chunks == 1) {     // decode sizes: one block (32 warps, two tokens each) routes, scans and scatters
     launch_pdl(moe_route_kernel, chunks, 1024, stream, static_cast<const bf16*>(scores),
                static_cast<const bf16*>(expert_scales), rows, keys, weights, bitmaps, chunk_counts, offsets,
                sorted_assignments, sorted_keys, inverse);
+    return cudaGetLastError();
+  }
+  const uint32_t resident = uint32_t(sm_count) * kRouteGridBlocksPerSm;
+  if (one_launch && barrier_state != nullptr && chunks <= resident * kRouteOwnChunks) {
+    launch_pdl(moe_route_grid_kernel, chunks < resident ? chunks : resident, kRouteGridThreads, stream,
+               static_cast<const bf16*>(scores), static_cast<const bf16*>(expert_scales), rows, chunks, keys, weights,
+               bitmaps, chunk_counts, offsets, sorted_assignments, sorted_keys, inverse, barrier_state, error);
     return cudaGetLastError();
   }
   launch_pdl(moe_route_kernel, chunks, 256, stream, static_cast<const bf16*>(scores),

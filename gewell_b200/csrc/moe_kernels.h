@@ -62,7 +62,10 @@ uint32_t moe_chunks(uint32_t rows);
 cudaError_t launch_moe_dispatch(const void* scores, const void* expert_scales, uint32_t rows, int32_t* keys,
                                 float* weights, uint32_t* bitmaps, int32_t* chunk_counts, int32_t* offsets,
                                 int32_t* sorted_assignments, int32_t* sorted_keys, int32_t* inverse,
+                                uint32_t* barrier_state, uint32_t* error, int sm_count, bool one_launch,
                                 cudaStream_t stream);
+// barrier_state: two zero-initialised uint32 in device memory owned by the workspace (counter, generation)
+// for the grid-wide barrier of the one-launch form; one_launch == false keeps the three-launch form.
 cudaError_t launch_moe_keys_from_offsets(const int32_t* offsets, uint32_t first_expert, uint32_t expert_count,
                                          uint32_t rows, int32_t* sorted_keys, int32_t* full_offsets,
                                          cudaStream_t stream);

@@ -100,12 +100,19 @@ def make_scores(rows, mode, seed=0):
     return scores
 
 
-@pytest.mark.parametrize("rows,mode", [(1, "hot"), (17, "distributed"), (129, "uneven"), (257, "distributed"),
-                                       (17, "ties"), (4096, "hot"), (4096, "distributed"), (1000, "normal"),
-                                       (8192, "normal")])
-def test_dispatch_exact(gw, rows, mode):
+@pytest.mark.parametrize("rows,mode,launches", [
+    (1, "hot", 1), (17, "distributed", 1), (65, "normal", 1), (129, "uneven", 1), (257, "distributed", 1), (17, "ties", 1),
+    (4096, "hot", 1), (4096, "distributed", 1), (1000, "normal", 1), (8192, "normal", 1),
+    # more chunks than resident blocks: several chunks per block of the one-launch kernel
+    (40000, "normal", 1), (65536, "uneven", 1),
+    (1000, "normal", 3), (8192, "normal", 3)])
+def test_dispatch_exact(gw, rows, mode, launches, monkeypatch):
     """Selected ids, stable permutation and offsets are bit-exact; the FP32
-    routing weights agree to a few ulps (host exp vs device expf)."""
+    routing weights agree to a few ulps (host exp vs device expf).  From 65 tokens on
+    routing, scan and scatter are one launch with a grid-wide barrier (or, on request,
+    three launches)."""
+    if launches == 3:
+        monkeypatch.setenv("GW_MOE_ROUTE_THREE_LAUNCHES", "1")
     scores = make_scores(rows, mode)
     scales = C.bf16_round(1.0 + 0.1 * np.sin(np.arange(E, dtype=np.float32)))
     ws = gw.MoeWorkspace(rows)
