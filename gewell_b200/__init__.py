@@ -12,7 +12,7 @@ _OPS = (
     "fp8_pack_weights", "fp8_quantize_activations", "gather_rows", "moe_combine", "nvfp4_dequantize",
     "nvfp4_gemv_w4a16", "nvfp4_pack_weights", "nvfp4_quantize_activations", "nvfp4_scale_offset",
     "nvfp4_scale_storage_bytes", "weight_qdq_apply", "kernel_error", "TRANSFORM_IDENTITY",
-    "TRANSFORM_GELU_TANH_MULTIPLY", "rcp_approx", "geglu_bf16", "nvfp4_linear_static_scratch", "launch_count", "Bf16Plan", "bind_projection", "ProjectionWorkspace",
+    "TRANSFORM_GELU_TANH_MULTIPLY", "rcp_approx", "geglu_bf16", "nvfp4_linear_static_scratch", "launch_count", "Bf16Plan", "bind_projection", "ProjectionWorkspace", "MlpChain", "make_projection",
 )
 
 

@@ -67,11 +67,21 @@ _SIGNATURES = {
     "gw_bf16_plan_destroy": (None, [c_void_p]),
     "gw_nvfp4_fp4_activations": (c_int, [c_int, c_int]),
     "gw_bind_projection": (c_int, [c_uint32, c_uint32, c_uint32, c_void_p, c_void_p, c_size_t, POINTER(Projection)]),
+    "gw_projection_entry_bytes": (c_size_t, [c_uint32, c_uint32, c_uint32]),
+    "gw_validate_projection_entry": (c_int, [c_uint32, c_uint32, c_uint32, c_void_p, c_size_t]),
     "gw_projection_workspace_create": (c_int, [POINTER(Projection), c_uint32, c_uint32, c_int, c_void_p, POINTER(c_void_p)]),
     "gw_projection_workspace_prepare": (c_int, [c_void_p, c_uint32, c_int]),
     "gw_projection_workspace_run": (c_int, [c_void_p, POINTER(Projection), c_void_p, c_void_p]),
     "gw_projection_workspace_bytes": (c_size_t, [c_void_p]),
     "gw_projection_workspace_destroy": (None, [c_void_p]),
+    "gw_gelu_tanh_multiply_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_uint64, c_void_p]),
+    "gw_gelu_tanh_multiply_interleaved_bf16": (c_int, [c_void_p, c_void_p, c_uint32, c_uint32, c_void_p]),
+    "gw_mlp_chain_create": (c_int, [c_uint32, c_uint32, c_uint32, c_int, POINTER(c_void_p)]),
+    "gw_mlp_chain_prepare": (c_int, [c_void_p, c_uint32]),
+    "gw_mlp_chain_run": (c_int, [c_void_p, POINTER(Projection), POINTER(Projection), POINTER(Projection), c_void_p,
+                                 c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
+    "gw_mlp_chain_bytes": (c_size_t, [c_void_p]),
+    "gw_mlp_chain_destroy": (None, [c_void_p]),
     "gw_absmax_bf16": (c_int, [c_void_p, c_uint64, c_void_p, c_void_p]),
     "gw_weight_qdq_apply": (c_int, [c_int, c_void_p, c_uint64, c_void_p, c_void_p]),
     "gw_moe_expert_table_create": (c_int, [POINTER(ExpertWeights), c_uint32, POINTER(c_void_p)]),

@@ -20,6 +20,8 @@ cudaError_t launch_fp8_pack_weights(const void* weights, uint32_t rows, uint32_t
                                     const float* row_scales, uint8_t* data, cudaStream_t stream);
 cudaError_t launch_rcp_approx(const float* in, float* out, size_t n, cudaStream_t stream);
 cudaError_t launch_geglu(const void* gate, const void* up, void* out, size_t n, cudaStream_t stream);
+// [rows, gate | up] (2 * width columns) -> [rows, width]
+cudaError_t launch_geglu_interleaved(const void* gate_up, void* out, uint32_t rows, uint32_t width, cudaStream_t stream);
 cudaError_t launch_absmax(const void* values, uint64_t elements, uint32_t* state, cudaStream_t stream);
 cudaError_t launch_fp8_qdq(void* values, uint64_t elements, float scale, cudaStream_t stream);
 cudaError_t launch_nvfp4_qdq(void* values, uint64_t elements, float global_scale, cudaStream_t stream);

@@ -123,6 +123,60 @@ gw_status gw_bind_projection(uint32_t storage, uint32_t rows, uint32_t columns, 
   return GW_OK;
 }
 
+size_t gw_projection_entry_bytes(uint32_t storage, uint32_t rows, uint32_t columns) {
+  // tensor_bytes (models/gemma4/26b_a4b/artifact.cc:64-71)
+  if (storage == GW_STORAGE_BF16) return size_t(rows) * columns * 2;
+  if (storage == GW_STORAGE_FP8_W8A8) return size_t(rows) * columns + 8;
+  if (storage != GW_STORAGE_NVFP4_W4A4) return 0;
+  const size_t padded_rows = (size_t(rows) + 127) / 128 * 128;
+  const size_t scale_columns = (size_t(columns) / 16 + 3) / 4 * 4;
+  return padded_rows * columns / 2 + padded_rows * scale_columns + 8;
+}
+
+gw_status gw_validate_projection_entry(uint32_t storage, uint32_t rows, uint32_t columns, const uint8_t* host_payload,
+                                       size_t entry_bytes) {
+  clear_error();
+  if (!host_payload || rows == 0 || columns == 0) return fail(GW_INVALID_ARGUMENT, "invalid 26B projection entry");
+  const size_t expected = gw_projection_entry_bytes(storage, rows, columns);
+  if (expected == 0) return fail(GW_INVALID_ARGUMENT, "invalid 26B storage type");
+  if (entry_bytes != expected) return fail(GW_INVALID_ARGUMENT, "26B entry size does not match its shape and storage type");
+  if (storage == GW_STORAGE_BF16) return GW_OK;
+  // validate_globals (artifact.cc:72-80)
+  float weight, input;
+  std::memcpy(&weight, host_payload + entry_bytes - 8, 4);
+  std::memcpy(&input, host_payload + entry_bytes - 4, 4);
+  if (!(std::isfinite(weight) && weight > 0 && std::isfinite(input) && input > 0 && std::isfinite(1.0F / input) &&
+        std::isfinite(weight * input) && weight * input > 0))
+    return fail(GW_INVALID_ARGUMENT, "invalid 26B global scales");
+  // validate_quantized_payload (artifact.cc:81-104)
+  if (storage == GW_STORAGE_FP8_W8A8) {
+    const size_t elements = size_t(rows) * columns;
+    for (size_t i = 0; i < elements; ++i)
+      if ((host_payload[i] & 0x7F) == 0x7F) return fail(GW_INVALID_ARGUMENT, "nonfinite 26B FP8 payload");
+    return GW_OK;
+  }
+  if (columns % 16) return fail(GW_INVALID_ARGUMENT, "NVFP4 entry needs a column count divisible by 16");
+  const size_t padded_rows = (size_t(rows) + 127) / 128 * 128;
+  const size_t logical_bytes = size_t(rows) * columns / 2, packed_bytes = padded_rows * columns / 2;
+  for (size_t i = logical_bytes; i < packed_bytes; ++i)
+    if (host_payload[i] != 0) return fail(GW_INVALID_ARGUMENT, "nonzero 26B NVFP4 weight padding");
+  const size_t blocks = columns / 16, scale_columns = (blocks + 3) / 4 * 4;
+  const uint8_t* scales = host_payload + packed_bytes;
+  // every 128-row tile stores its scales as [K tile][row % 32][row / 32][block % 4]
+  for (size_t row = 0; row < padded_rows; ++row)
+    for (size_t column = 0; column < scale_columns; ++column) {
+      const size_t local = row % 128;
+      const size_t offset = (row / 128) * 128 * scale_columns + (((column / 4) * 32 + local % 32) * 4 + local / 32) * 4 + column % 4;
+      const uint8_t value = scales[offset];
+      if (row >= rows || column >= blocks) {
+        if (value != 0) return fail(GW_INVALID_ARGUMENT, "nonzero 26B NVFP4 scale padding");
+      } else if (value >= 0x7F) {
+        return fail(GW_INVALID_ARGUMENT, "invalid 26B NVFP4 block scale");
+      }
+    }
+  return GW_OK;
+}
+
 gw_status gw_projection_workspace_create(const gw_projection* projections, uint32_t count, uint32_t max_rows,
                                          int policy, void* stream, gw_projection_workspace** workspace) {
   clear_error();

@@ -288,6 +288,24 @@ __global__ void geglu_kernel(const bf16* __restrict__ gate, const bf16* __restri
   if (i < n) out[i] = __float2bfloat16_rn(gelu_tanh_multiply_bf16(__bfloat162float(gate[i]), __bfloat162float(up[i])));
 }
 
+// [rows, gate | up] -> [rows, width]: eight channels per thread, 16-byte loads and stores
+__global__ void geglu_interleaved_kernel(const uint4* __restrict__ gate_up, uint4* __restrict__ out, size_t vectors,
+                                         uint32_t row_vectors) {
+  const size_t i = size_t(blockIdx.x) * kThreads + threadIdx.x;
+  if (i >= vectors) return;
+  const size_t row = i / row_vectors, v = i % row_vectors;
+  const uint4 g = gate_up[row * 2 * row_vectors + v], u = gate_up[row * 2 * row_vectors + row_vectors + v];
+  const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+  uint32_t words[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float a = gelu_tanh_multiply_bf16(__uint_as_float(gw[k] << 16), __uint_as_float(uw[k] << 16));
+    const float b = gelu_tanh_multiply_bf16(__uint_as_float(gw[k] & 0xFFFF0000u), __uint_as_float(uw[k] & 0xFFFF0000u));
+    words[k] = (__float_as_uint(a) >> 16) | (__float_as_uint(b) & 0xFFFF0000u);
+  }
+  out[i] = make_uint4(words[0], words[1], words[2], words[3]);
+}
+
 unsigned grid_for(size_t items, size_t cap = 1u << 20) {
   size_t blocks = (items + kThreads - 1) / kThreads;
   if (blocks < 1) blocks = 1;
@@ -368,6 +386,14 @@ cudaError_t launch_rcp_approx(const float* in, float* out, size_t n, cudaStream_
 cudaError_t launch_geglu(const void* gate, const void* up, void* out, size_t n, cudaStream_t stream) {
   geglu_kernel<<<grid_for(n, ~0u), kThreads, 0, stream>>>(static_cast<const bf16*>(gate), static_cast<const bf16*>(up),
                                                           static_cast<bf16*>(out), n);
+  note_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_geglu_interleaved(const void* gate_up, void* out, uint32_t rows, uint32_t width, cudaStream_t stream) {
+  const size_t vectors = size_t(rows) * (width / 8);
+  geglu_interleaved_kernel<<<grid_for(vectors, ~0u), kThreads, 0, stream>>>(static_cast<const uint4*>(gate_up),
+                                                                            static_cast<uint4*>(out), vectors, width / 8);
   note_launch();
   return cudaGetLastError();
 }

@@ -311,6 +311,38 @@ class ProjectionWorkspace:
             self._ws = None
 
 
+class MlpChain:
+    """31B Executor::project_mlp: gate + up projection -> GeGLU -> down projection of one layer from its
+    three bound projections (make_projection), choosing joined / fused forms where the layout allows."""
+
+    def __init__(self, hidden: int, mlp: int, max_rows: int, policy: int):
+        self._lib = _library()
+        self._chain = ctypes.c_void_p()
+        self.hidden, self.mlp = hidden, mlp
+        _check(self._lib.gw_mlp_chain_create(hidden, mlp, max_rows, policy, ctypes.byref(self._chain)))
+
+    def prepare(self, rows: int):
+        _check(self._lib.gw_mlp_chain_prepare(self._chain, rows))
+        self.rows = rows
+
+    def run(self, gate, up, down, x, phase: int, stream=None):
+        rows = self.rows
+        gate_up = torch.empty((rows, 2 * self.mlp), dtype=torch.bfloat16, device=x.device)
+        product = torch.empty((rows, self.mlp), dtype=torch.bfloat16, device=x.device)
+        y = torch.empty((rows, self.hidden), dtype=torch.bfloat16, device=x.device)
+        _check(self._lib.gw_mlp_chain_run(self._chain, ctypes.byref(gate), ctypes.byref(up), ctypes.byref(down), _ptr(x),
+                                          _ptr(gate_up), _ptr(product), _ptr(y), phase, _stream(stream)))
+        return y
+
+    def bytes(self) -> int:
+        return int(self._lib.gw_mlp_chain_bytes(self._chain))
+
+    def __del__(self):
+        if getattr(self, "_chain", None):
+            self._lib.gw_mlp_chain_destroy(self._chain)
+            self._chain = None
+
+
 # --------------------------------------------------------------------------- weight QDQ
 
 def weight_qdq_apply(kind: int, values: torch.Tensor, stream=None) -> torch.Tensor:

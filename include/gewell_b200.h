@@ -219,6 +219,16 @@ int gw_nvfp4_fp4_activations(int policy, int phase);
 gw_status gw_bind_projection(uint32_t storage, uint32_t rows, uint32_t columns, const uint8_t* host_payload,
                              const void* device_payload, size_t entry_bytes, gw_projection* projection);
 
+/* Size and content checks of one artifact entry before it is bound, as the reference's artifact reader
+ * applies them to every projection (models/gemma4/26b_a4b/artifact.cc:64-104): the entry's byte count
+ * for its shape and storage, finite positive global scales with a finite reciprocal and product, no
+ * NaN codes in FP8 payloads, zero padding rows and zero padding scales in NVFP4 payloads, block scale
+ * codes below 0x7f.  Host-only.  (The file container around the entries -- header, entry table,
+ * SHA-256 digests -- is not read here.) */
+size_t gw_projection_entry_bytes(uint32_t storage, uint32_t rows, uint32_t columns);
+gw_status gw_validate_projection_entry(uint32_t storage, uint32_t rows, uint32_t columns, const uint8_t* host_payload,
+                                       size_t entry_bytes);
+
 /* ProjectionWorkspace (projection.cuh:19-41, projection.cu:52-145): shared scratch and plans for
  * sequential projections on ONE stream, bound at construction.  create() sizes the scratch for
  * max_rows and the given bindings and allocates it; prepare(rows, phase) builds the plans for a row
@@ -234,6 +244,41 @@ gw_status gw_projection_workspace_run(gw_projection_workspace* workspace, const 
                                       const void* input_bf16, void* output_bf16);
 size_t gw_projection_workspace_bytes(const gw_projection_workspace* workspace);
 void gw_projection_workspace_destroy(gw_projection_workspace* workspace);
+
+/* ------------------------------------------------------------------------- */
+/* Dense MLP chain of the 31B model                                           */
+/* ------------------------------------------------------------------------- */
+
+/* GeGLU with both BF16 roundings (src/bf16_activation.cuh:10-16) as stand-alone kernels: on separate
+ * gate / up arrays, and on a joined [rows, gate | up] tensor (primitives::gelu_tanh_multiply and
+ * gelu_tanh_multiply_interleaved of the 31B executor). */
+gw_status gw_gelu_tanh_multiply_bf16(const void* gate_bf16, const void* up_bf16, void* output_bf16, uint64_t count,
+                                     void* stream);
+gw_status gw_gelu_tanh_multiply_interleaved_bf16(const void* gate_up_bf16, void* output_bf16, uint32_t rows,
+                                                 uint32_t width, void* stream);
+
+/* Executor::project_mlp with projection_linear (models/gemma4/31b/sm120/executor.cuh:1187-1215,
+ * 1248-1291): gate + up projection -> GeGLU -> down projection of one layer, from the layer's three
+ * bound weights (gw_projection: BF16, FP8 or NVFP4 each; physical_output == output).  Gate and up run
+ * as ONE GEMM when they are stored back to back (NVFP4: contiguous rows and scale tiles with equal
+ * globals, 31b/sm120/nvfp4_projections.h:21-33; FP8: adjacent with per-channel scales,
+ * fp8_projections.h:20-50; BF16: adjacent); GeGLU is fused into the down projection's activation
+ * quantiser whenever that one runs quantised on the joined tensor.  policy / phase as in
+ * nvfp4_policy.h: with policy "prefill" decode keeps BF16 activations (NVFP4 weights are dequantised
+ * into the chain's scratch, W4A16).
+ *   create    allocates the shared scratch for max_rows (set-up time)
+ *   prepare   builds the plans for a row count, outside the layer loop
+ *   run       gate_up_bf16: [rows, 2 * mlp] scratch of the caller ([rows, gate | up] when joined, gate
+ *             rows then up rows otherwise), product_bf16: [rows, mlp] scratch (used by the unfused
+ *             GeGLU), output_bf16: [rows, hidden]; allocates nothing */
+typedef struct gw_mlp_chain gw_mlp_chain;
+gw_status gw_mlp_chain_create(uint32_t hidden, uint32_t mlp, uint32_t max_rows, int policy, gw_mlp_chain** chain);
+gw_status gw_mlp_chain_prepare(gw_mlp_chain* chain, uint32_t rows);
+gw_status gw_mlp_chain_run(gw_mlp_chain* chain, const gw_projection* gate, const gw_projection* up,
+                           const gw_projection* down, const void* input_bf16, void* gate_up_bf16, void* product_bf16,
+                           void* output_bf16, int phase, void* stream);
+size_t gw_mlp_chain_bytes(const gw_mlp_chain* chain);
+void gw_mlp_chain_destroy(gw_mlp_chain* chain);
 
 /* The reference keeps the 128-entry ExpertWeights table in device memory and
  * reads it from its kernels (batched_executor.cu:62-88).  Here the table is
