@@ -30,6 +30,18 @@ class Projection(ctypes.Structure):
     ]
 
 
+class FfnBlockWeights(ctypes.Structure):
+    """gw_ffn_block_weights: one 26B layer's feed-forward weights (device pointers)."""
+    _fields_ = [
+        ("pre_feedforward_norm", c_void_p), ("router_scale", c_void_p), ("pre_feedforward_norm_2", c_void_p),
+        ("post_feedforward_norm_1", c_void_p), ("post_feedforward_norm_2", c_void_p),
+        ("post_feedforward_norm", c_void_p), ("layer_scalar", c_void_p),
+        ("gate", Projection), ("up", Projection), ("down", Projection),
+        ("router_proj", c_void_p), ("router_per_expert_scale", c_void_p), ("experts", c_void_p),
+        ("has_bf16", c_int), ("has_fp8", c_int), ("has_nvfp4", c_int),
+    ]
+
+
 class ExpertWeights(ctypes.Structure):
     """gw_expert_weights (mirrors sm120::ExpertWeights, moe.cuh:11-13)."""
     _fields_ = [("gate", Projection), ("up", Projection), ("down", Projection)]
@@ -67,6 +79,20 @@ _SIGNATURES = {
     "gw_bf16_plan_destroy": (None, [c_void_p]),
     "gw_nvfp4_fp4_activations": (c_int, [c_int, c_int]),
     "gw_bind_projection": (c_int, [c_uint32, c_uint32, c_uint32, c_void_p, c_void_p, c_size_t, POINTER(Projection)]),
+    "gw_rms_norm_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_void_p]),
+    "gw_rms_norm_feedforward_bf16": (c_int, [c_void_p] * 7 + [c_uint32, c_uint32, c_void_p]),
+    "gw_add_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_uint64, c_void_p]),
+    "gw_scale_bf16": (c_int, [c_void_p, c_void_p, c_uint64, c_void_p]),
+    "gw_ffn_tail_bf16": (c_int, [c_void_p] * 7 + [c_uint32, c_uint32, c_void_p]),
+    "gw_ffn_block_create": (c_int, [c_void_p, c_uint32, c_uint32, c_int, c_uint32, c_void_p, POINTER(c_void_p)]),
+    "gw_ffn_block_prepare": (c_int, [c_void_p, c_uint32, c_int]),
+    "gw_ffn_block_run": (c_int, [c_void_p, c_void_p, c_void_p]),
+    "gw_ffn_block_bytes": (c_size_t, [c_void_p]),
+    "gw_ffn_block_destroy": (None, [c_void_p]),
+    "gw_ffn_block_buffer": (c_void_p, [c_void_p, c_int]),
+    "gw_ffn_block_moe": (c_void_p, [c_void_p]),
+    "gw_debug_rsqrt": (c_int, [c_void_p, c_void_p, c_uint32]),
+    "gw_rms_norm_reduction_lanes": (c_uint32, [c_uint32, c_uint32]),
     "gw_projection_entry_bytes": (c_size_t, [c_uint32, c_uint32, c_uint32]),
     "gw_validate_projection_entry": (c_int, [c_uint32, c_uint32, c_uint32, c_void_p, c_size_t]),
     "gw_projection_workspace_create": (c_int, [POINTER(Projection), c_uint32, c_uint32, c_int, c_void_p, POINTER(c_void_p)]),

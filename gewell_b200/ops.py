@@ -540,6 +540,115 @@ class MoeWorkspace:
             self._ws = None
 
 
+# --------------------------------------------------------------------------- 26B feed-forward block
+
+def rsqrt_device(values):
+    """rsqrtf evaluated on the device for a NumPy float32 array (test aid of the RMS norms)."""
+    import numpy as np
+    flat = np.ascontiguousarray(values, dtype=np.float32).ravel()
+    out = np.empty_like(flat)
+    _check(_library().gw_debug_rsqrt(flat.ctypes.data, out.ctypes.data, flat.size))
+    return out.reshape(np.shape(values))
+
+
+def rms_norm(x: torch.Tensor, weight=None, y=None, stream=None):
+    """bf16_math::normalize over the rows of x [rows, width]."""
+    y = torch.empty_like(x) if y is None else y
+    _check(_library().gw_rms_norm_bf16(_ptr(x), _ptr(weight), _ptr(y), x.shape[0], x.shape[1], _stream(stream)))
+    return y
+
+
+def rms_norm_feedforward(x, shared_weight, router_weight, expert_weight, stream=None):
+    """bf16_math::normalize_feedforward: (shared, router, expert) inputs from one RMS of x."""
+    shared, router, expert = torch.empty_like(x), torch.empty_like(x), torch.empty_like(x)
+    _check(_library().gw_rms_norm_feedforward_bf16(_ptr(x), _ptr(shared_weight), _ptr(router_weight), _ptr(expert_weight),
+                                                   _ptr(shared), _ptr(router), _ptr(expert), x.shape[0], x.shape[1],
+                                                   _stream(stream)))
+    return shared, router, expert
+
+
+def add_bf16(a, b, y=None, stream=None):
+    y = torch.empty_like(a) if y is None else y
+    _check(_library().gw_add_bf16(_ptr(a), _ptr(b), _ptr(y), a.numel(), _stream(stream)))
+    return y
+
+
+def scale_bf16(x, scalar, stream=None):
+    """x *= scalar[0] in place (row_scale of the 26B executor)."""
+    _check(_library().gw_scale_bf16(_ptr(x), _ptr(scalar), x.numel(), _stream(stream)))
+    return x
+
+
+def ffn_tail(shared_mlp, routed, norm_shared, norm_routed, norm_sum, layer_scalar, hidden, stream=None):
+    """Post norms, adds and the layer scalar of the block in one launch; updates hidden in place."""
+    _check(_library().gw_ffn_tail_bf16(_ptr(shared_mlp), _ptr(routed), _ptr(norm_shared), _ptr(norm_routed), _ptr(norm_sum),
+                                       _ptr(layer_scalar), _ptr(hidden), hidden.shape[0], hidden.shape[1], _stream(stream)))
+    return hidden
+
+
+class FfnBlock:
+    """The feed-forward block of 26B layers (shared MLP + router + MoE + norms and residuals).
+
+    layers: list of dicts with the BF16 tensors pre_feedforward_norm, router_scale, pre_feedforward_norm_2,
+    post_feedforward_norm_1, post_feedforward_norm_2, post_feedforward_norm, layer_scalar, router_proj,
+    router_per_expert_scale, the shared-MLP weights gate / up / down (Nvfp4Weight, Fp8Weight or BF16 tensor)
+    and `experts` (an ExpertTable), plus optional has_bf16 / has_fp8 / has_nvfp4 flags."""
+
+    BUFFERS = {"normalized": (0, 2816), "router_input": (1, 2816), "expert_input": (2, 2816), "shared_mlp": (3, 2816),
+               "router_logits": (4, 128), "routed": (5, 2816)}
+
+    def __init__(self, layers, max_rows: int, policy: int, fp8_experts: bool = False, stream=None):
+        self._lib = _library()
+        self._keep = layers
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        self._weights = (_lib.FfnBlockWeights * len(layers))()
+        for w, layer in zip(self._weights, layers):
+            for name in ("pre_feedforward_norm", "router_scale", "pre_feedforward_norm_2", "post_feedforward_norm_1",
+                         "post_feedforward_norm_2", "post_feedforward_norm", "layer_scalar", "router_proj",
+                         "router_per_expert_scale"):
+                setattr(w, name, _ptr(layer[name]))
+            w.gate = make_projection(layer["gate"], 2816, 2112)
+            w.up = make_projection(layer["up"], 2816, 2112)
+            w.down = make_projection(layer["down"], 2112, 2816)
+            w.experts = layer["experts"].handle
+            w.has_bf16 = int(layer.get("has_bf16", False))
+            w.has_fp8 = int(layer.get("has_fp8", False))
+            w.has_nvfp4 = int(layer.get("has_nvfp4", True))
+        self._block = ctypes.c_void_p()
+        _check(self._lib.gw_ffn_block_create(self._weights, len(layers), max_rows, policy, 1 if fp8_experts else 0,
+                                             _stream(stream), ctypes.byref(self._block)))
+        self.rows = 0
+
+    def prepare(self, rows: int, phase: int):
+        _check(self._lib.gw_ffn_block_prepare(self._block, rows, phase))
+        self.rows = rows
+
+    def run(self, layer: int, hidden: torch.Tensor):
+        """Applies layer `layer`'s block to hidden [rows, 2816] in place."""
+        _check(self._lib.gw_ffn_block_run(self._block, ctypes.byref(self._weights[layer]), _ptr(hidden)))
+        return hidden
+
+    def buffer(self, name: str) -> torch.Tensor:
+        """Copy of an intermediate of the last run."""
+        which, width = self.BUFFERS[name]
+        pointer = self._lib.gw_ffn_block_buffer(self._block, which)
+        raw = torch.as_tensor(_RawDeviceBytes(pointer, self.rows * width * 2), device=self.device)
+        return raw.view(torch.bfloat16).reshape(self.rows, width).clone()
+
+    def selected_experts(self) -> torch.Tensor:
+        pointer = self._lib.gw_moe_selected_experts(self._lib.gw_ffn_block_moe(self._block))
+        raw = torch.as_tensor(_RawDeviceBytes(pointer, self.rows * 8 * 4), device=self.device)
+        return raw.view(torch.int32).reshape(self.rows, 8).clone()
+
+    def bytes(self) -> int:
+        return int(self._lib.gw_ffn_block_bytes(self._block))
+
+    def __del__(self):
+        if getattr(self, "_block", None):
+            self._lib.gw_ffn_block_destroy(self._block)
+            self._block = None
+
+
 def gather_rows(x, index, divisor: int, rows: int, stream=None):
     out = torch.empty((rows, x.shape[1]), dtype=torch.bfloat16, device=x.device)
     _check(_library().gw_gather_rows_bf16(_ptr(x), _ptr(index), divisor, rows, x.shape[1], _ptr(out), _stream(stream)))

@@ -356,6 +356,68 @@ gw_status gw_moe_capture(gw_moe_workspace* workspace, int enable);
 gw_status gw_moe_stage_timing(gw_moe_workspace* workspace, int enable);
 gw_status gw_moe_stage_elapsed_ms(gw_moe_workspace* workspace, float* milliseconds);
 
+/* ------------------------------------------------------------------------- */
+/* Feed-forward block of a 26B-A4B layer around the MoE                       */
+/* ------------------------------------------------------------------------- */
+
+/* bf16_math::normalize (bf16_math.cuh:96-98): y[r, c] = bf16(x[r, c] * rsqrt(mean(x[r]^2) + 1e-6) *
+ * weight[c]) for `rows` rows of `width` BF16 values (weight NULL: no weight).  The FP32 mean is
+ * accumulated in the reference's fixed order, which depends on rows and width (four accumulators per
+ * logical lane, lanes folded in a halving tree, normalize_to :86-95), without fused multiply-add.
+ * width divisible by 8, at most 16384; x 16-byte aligned. */
+gw_status gw_rms_norm_bf16(const void* input_bf16, const void* weight_bf16, void* output_bf16, uint32_t rows,
+                           uint32_t width, void* stream);
+/* bf16_math::normalize_feedforward (bf16_math.cuh:25-37,99-104): one RMS of the hidden state, three
+ * outputs -- shared = bf16(n * shared_weight), expert = bf16(n * expert_weight), and the router input
+ * bf16(bf16(bf16(n) * router_weight) / sqrt(width)) with its three separate roundings. */
+gw_status gw_rms_norm_feedforward_bf16(const void* input_bf16, const void* shared_weight, const void* router_weight,
+                                       const void* expert_weight, void* shared_bf16, void* router_bf16,
+                                       void* expert_bf16, uint32_t rows, uint32_t width, void* stream);
+/* bf16_math::add (bf16_math.cuh:109-112) and row_scale (batched_executor.cu:30-33). */
+gw_status gw_add_bf16(const void* a_bf16, const void* b_bf16, void* output_bf16, uint64_t count, void* stream);
+gw_status gw_scale_bf16(void* values_bf16, const void* scalar_bf16, uint64_t count, void* stream);
+/* The end of the block in one launch (seven in the reference, batched_executor.cu:260,278-285):
+ *   shared = norm(shared_mlp, norm_shared_weight); branch = norm(routed, norm_routed_weight);
+ *   shared = bf16(shared + branch); branch = norm(shared, norm_sum_weight);
+ *   hidden = bf16(hidden + branch); hidden = bf16(hidden * layer_scalar[0]).
+ * Bit-identical to the seven calls above composed. */
+gw_status gw_ffn_tail_bf16(const void* shared_mlp_bf16, const void* routed_bf16, const void* norm_shared_weight,
+                           const void* norm_routed_weight, const void* norm_sum_weight, const void* layer_scalar_bf16,
+                           void* hidden_bf16, uint32_t rows, uint32_t width, void* stream);
+
+/* One layer's feed-forward weights: TensorRole pre_feedforward_norm, router_scale,
+ * pre_feedforward_norm_2, post_feedforward_norm_1/_2, post_feedforward_norm, layer_scalar, gate_proj /
+ * up_proj / down_proj (shared MLP, 2816 -> 2112 -> 2816), router_proj, router_per_expert_scale and
+ * the expert table (include/gewell/models/gemma4/26b_a4b/model.h:38-45,88-105).  Norm weights BF16 [2816],
+ * layer_scalar BF16 [1], router_proj BF16 [128, 2816], router_per_expert_scale BF16 [128]: device. */
+typedef struct gw_ffn_block_weights {
+  const void *pre_feedforward_norm, *router_scale, *pre_feedforward_norm_2;
+  const void *post_feedforward_norm_1, *post_feedforward_norm_2, *post_feedforward_norm, *layer_scalar;
+  gw_projection gate, up, down;
+  const void* router_proj;
+  const void* router_per_expert_scale;
+  const gw_expert_table* experts;
+  int has_bf16, has_fp8, has_nvfp4;
+} gw_ffn_block_weights;
+
+/* The block's state for up to max_rows rows: projection workspace over the `count` layers' shared-MLP
+ * and router projections, MoE workspace (moe_flags as gw_moe_create_ex) and the intermediate buffers.
+ * prepare(rows, phase) builds the plans outside the layer loop; run() applies one layer's block to
+ * hidden [rows, 2816] in place on the stream given at creation and allocates nothing
+ * (batched_executor.cu:250-286). */
+typedef struct gw_ffn_block gw_ffn_block;
+gw_status gw_ffn_block_create(const gw_ffn_block_weights* layers, uint32_t count, uint32_t max_rows, int policy,
+                              uint32_t moe_flags, void* stream, gw_ffn_block** block);
+gw_status gw_ffn_block_prepare(gw_ffn_block* block, uint32_t rows, int phase);
+gw_status gw_ffn_block_run(gw_ffn_block* block, const gw_ffn_block_weights* weights, void* hidden_bf16);
+size_t gw_ffn_block_bytes(const gw_ffn_block* block);
+void gw_ffn_block_destroy(gw_ffn_block* block);
+/* Intermediates of the last run (the tensors the reference's capture sink names), device pointers. */
+enum { GW_FFN_NORMALIZED = 0, GW_FFN_ROUTER_INPUT = 1, GW_FFN_EXPERT_INPUT = 2, GW_FFN_SHARED_MLP = 3,
+       GW_FFN_ROUTER_LOGITS = 4, GW_FFN_ROUTED = 5 };
+const void* gw_ffn_block_buffer(const gw_ffn_block* block, int which);
+gw_moe_workspace* gw_ffn_block_moe(gw_ffn_block* block);
+
 /* MoE passes over HOST buffers (no counterpart in the reference, whose callers keep activations on
  * the device): for a caller whose token rows, router logits and layer output live in pinned host
  * memory.  The runner owns three streams and a ring of `depth` device buffers; submit() queues

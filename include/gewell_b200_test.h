@@ -45,6 +45,12 @@ uint64_t gw_debug_launch_count(void);
 gw_status gw_debug_moe_quantized_input(const gw_moe_workspace* workspace, const uint8_t** packed,
                                        const uint8_t** scales, uint32_t* scale_rows, uint32_t* part_rows);
 
+/* Test aids of the RMS norms: rsqrtf evaluated on the device for `count` host values (the norm is
+ * defined in terms of this approximate instruction), and the number of logical lanes the row
+ * reduction uses for a launch of `rows` rows of `width` values. */
+gw_status gw_debug_rsqrt(const float* host_input, float* host_output, uint32_t count);
+uint32_t gw_rms_norm_reduction_lanes(uint32_t rows, uint32_t width);
+
 #ifdef __cplusplus
 }
 #endif
