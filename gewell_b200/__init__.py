@@ -13,7 +13,7 @@ _OPS = (
     "nvfp4_gemv_w4a16", "nvfp4_pack_weights", "nvfp4_quantize_activations", "nvfp4_scale_offset",
     "nvfp4_scale_storage_bytes", "weight_qdq_apply", "kernel_error", "TRANSFORM_IDENTITY",
     "TRANSFORM_GELU_TANH_MULTIPLY", "rcp_approx", "geglu_bf16", "nvfp4_linear_static_scratch", "launch_count", "Bf16Plan", "bind_projection", "ProjectionWorkspace", "MlpChain", "make_projection",
-    "rsqrt_device", "rms_norm", "rms_norm_feedforward", "add_bf16", "scale_bf16", "ffn_tail", "FfnBlock",
+    "rsqrt_device", "rms_norm", "rms_norm_feedforward", "add_bf16", "scale_bf16", "ffn_tail", "FfnBlock", "QkvProjector", "join_nvfp4_pair", "join_fp8_group",
 )
 
 

@@ -79,6 +79,13 @@ _SIGNATURES = {
     "gw_bf16_plan_destroy": (None, [c_void_p]),
     "gw_nvfp4_fp4_activations": (c_int, [c_int, c_int]),
     "gw_bind_projection": (c_int, [c_uint32, c_uint32, c_uint32, c_void_p, c_void_p, c_size_t, POINTER(Projection)]),
+    "gw_qkv_projector_create": (c_int, [c_uint32, c_uint32, c_uint32, c_uint32, c_int, POINTER(c_void_p)]),
+    "gw_qkv_projector_prepare": (c_int, [c_void_p, c_uint32]),
+    "gw_qkv_projector_run": (c_int, [c_void_p] * 8 + [c_int, c_void_p, POINTER(c_int)]),
+    "gw_qkv_projector_bytes": (c_size_t, [c_void_p]),
+    "gw_qkv_projector_destroy": (None, [c_void_p]),
+    "gw_join_nvfp4_pair": (c_int, [c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, POINTER(c_int)]),
+    "gw_join_fp8_group": (c_int, [c_void_p, c_uint32, c_void_p, c_void_p, c_size_t, c_void_p, POINTER(c_int)]),
     "gw_rms_norm_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_void_p]),
     "gw_rms_norm_feedforward_bf16": (c_int, [c_void_p] * 7 + [c_uint32, c_uint32, c_void_p]),
     "gw_add_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_uint64, c_void_p]),

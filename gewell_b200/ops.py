@@ -343,6 +343,65 @@ class MlpChain:
             self._chain = None
 
 
+class QkvProjector:
+    """31B Executor::project_qkv without its norms: Q, K (and V) of one layer from their bound projections,
+    as one joined GEMM where the weights lie back to back."""
+
+    def __init__(self, hidden: int, q_width: int, kv_width: int, max_rows: int, policy: int):
+        self._lib = _library()
+        self._projector = ctypes.c_void_p()
+        self.hidden, self.q, self.kv = hidden, q_width, kv_width
+        _check(self._lib.gw_qkv_projector_create(hidden, q_width, kv_width, max_rows, policy, ctypes.byref(self._projector)))
+        self.rows = 0
+
+    def prepare(self, rows: int):
+        _check(self._lib.gw_qkv_projector_prepare(self._projector, rows))
+        self.rows = rows
+
+    def run(self, query, key, value, x, phase: int, stream=None):
+        """Returns (q, k, v) views ([rows, width] each; v None when `value` is None) and whether one joined GEMM ran."""
+        rows, n = self.rows, self.q + self.kv * (2 if value is not None else 1)
+        out = torch.empty((rows * n,), dtype=torch.bfloat16, device=x.device)
+        q, k = out[:rows * self.q], out[rows * self.q:rows * (self.q + self.kv)]
+        v = out[rows * (self.q + self.kv):] if value is not None else None
+        joined = ctypes.c_int(0)
+        _check(self._lib.gw_qkv_projector_run(self._projector, ctypes.byref(query), ctypes.byref(key),
+                                              ctypes.byref(value) if value is not None else None, _ptr(x), _ptr(q), _ptr(k),
+                                              _ptr(v), phase, _stream(stream), ctypes.byref(joined)))
+        if joined.value:
+            both = out.view(rows, n)
+            return both[:, :self.q], both[:, self.q:self.q + self.kv], (both[:, self.q + self.kv:] if value is not None else None), True
+        return q.view(rows, self.q), k.view(rows, self.kv), (v.view(rows, self.kv) if v is not None else None), False
+
+    def bytes(self) -> int:
+        return int(self._lib.gw_qkv_projector_bytes(self._projector))
+
+    def __del__(self):
+        if getattr(self, "_projector", None):
+            self._lib.gw_qkv_projector_destroy(self._projector)
+            self._projector = None
+
+
+def join_nvfp4_pair(first, second, stream=None) -> bool:
+    """In-place join of two bound NVFP4 projections (gw_join_nvfp4_pair); updates their pointers."""
+    packed = first.physical_output * first.input // 2
+    temp = torch.empty(2 * (packed + nvfp4_scale_storage_bytes(first.physical_output, first.input)), dtype=torch.uint8, device="cuda")
+    joined = ctypes.c_int(0)
+    _check(_library().gw_join_nvfp4_pair(ctypes.byref(first), ctypes.byref(second), _ptr(temp), temp.numel(), _stream(stream),
+                                         ctypes.byref(joined)))
+    torch.cuda.synchronize()
+    return bool(joined.value)
+
+
+def join_fp8_group(group, channel_scales: torch.Tensor, stream=None) -> bool:
+    """In-place join of bound FP8 projections (gw_join_fp8_group); `group` is a ctypes array of Projection."""
+    temp = torch.empty(sum(p.output * p.input for p in group), dtype=torch.uint8, device="cuda")
+    joined = ctypes.c_int(0)
+    _check(_library().gw_join_fp8_group(group, len(group), _ptr(channel_scales), _ptr(temp), temp.numel(), _stream(stream),
+                                        ctypes.byref(joined)))
+    return bool(joined.value)
+
+
 # --------------------------------------------------------------------------- weight QDQ
 
 def weight_qdq_apply(kind: int, values: torch.Tensor, stream=None) -> torch.Tensor:

@@ -280,6 +280,39 @@ gw_status gw_mlp_chain_run(gw_mlp_chain* chain, const gw_projection* gate, const
 size_t gw_mlp_chain_bytes(const gw_mlp_chain* chain);
 void gw_mlp_chain_destroy(gw_mlp_chain* chain);
 
+/* Executor::project_qkv without its norms (models/gemma4/31b/sm120/executor.cuh:1218-1247): the
+ * attention input projections of one layer.  One joined GEMM when Q, K (and V) are adjacent BF16
+ * matrices (fusion::qkv_weight, projection_fusion.h:23-33) or adjacent FP8 matrices with adjacent
+ * per-channel scales and one input scale (fp8::qkv_weight, fp8_projections.h:26-35): *joined = 1 and
+ * q_bf16 receives [rows, Q | K | V]; otherwise *joined = 0 and every projection writes its own output
+ * (FP8 -> NVFP4 with FP4 activations -> BF16 GEMM, as projection_linear :1187-1215).  `value` NULL for
+ * layers whose values are their keys (global attention).  Widths divisible by 128. */
+typedef struct gw_qkv_projector gw_qkv_projector;
+gw_status gw_qkv_projector_create(uint32_t hidden, uint32_t q_width, uint32_t kv_width, uint32_t max_rows, int policy,
+                                  gw_qkv_projector** projector);
+gw_status gw_qkv_projector_prepare(gw_qkv_projector* projector, uint32_t rows);
+gw_status gw_qkv_projector_run(gw_qkv_projector* projector, const gw_projection* query, const gw_projection* key,
+                               const gw_projection* value, const void* input_bf16, void* q_bf16, void* k_bf16,
+                               void* v_bf16, int phase, void* stream, int* joined);
+size_t gw_qkv_projector_bytes(const gw_qkv_projector* projector);
+void gw_qkv_projector_destroy(gw_qkv_projector* projector);
+
+/* The joins the 31B loader makes in place after uploading a layer (Weights, weights.cuh:146-223), so
+ * that the joined forms above apply.  Both rewrite device memory on `stream` and update the
+ * projections' pointers; *joined = 0 and nothing changes when the group does not qualify.
+ *   gw_join_nvfp4_pair: two NVFP4 matrices of one shape with equal input and weight scales, the
+ *     second payload somewhere behind the first in one region -> [first rows | second rows | first
+ *     scale tiles | second scale tiles] from the first matrix's address on.  temp: 2 * (packed +
+ *     scale) bytes of device memory.
+ *   gw_join_fp8_group: FP8 matrices with one input scale and one K, in ascending address order ->
+ *     their rows packed back to back from the first matrix's address on, channel_scales (device,
+ *     one float per output channel of the group) filled with input_scale * weight_scale of each
+ *     channel's own matrix.  temp: the group's weight bytes.  Synchronises the stream. */
+gw_status gw_join_nvfp4_pair(gw_projection* first, gw_projection* second, void* temp, size_t temp_bytes, void* stream,
+                             int* joined);
+gw_status gw_join_fp8_group(gw_projection* group, uint32_t count, float* channel_scales, void* temp, size_t temp_bytes,
+                            void* stream, int* joined);
+
 /* The reference keeps the 128-entry ExpertWeights table in device memory and
  * reads it from its kernels (batched_executor.cu:62-88).  Here the table is
  * bound once from the host copy: the call validates it, builds the TMA

@@ -138,3 +138,120 @@ def test_mlp_chain_validation(gw):
     with pytest.raises(gw.GewellInvalidArgument):      # run before prepare
         chain.rows = 4
         chain.run(p, p, gw.make_projection(bf16_normal((H, M), 2).cuda(), M, H), bf16_normal((4, H), 3).cuda(), 0)
+
+
+# ------------------------------------------------------------------------------------------------
+# Attention input projections (Executor::project_qkv, executor.cuh:1218-1247) and the loader's joins
+# (weights.cuh:146-223)
+
+Q, KV = 256, 128
+
+
+@pytest.mark.parametrize("rows", [3, 150])
+@pytest.mark.parametrize("with_value", [True, False])
+@pytest.mark.parametrize("adjacent", [True, False])
+def test_qkv_bf16(gw, rows, with_value, adjacent):
+    from gewell_b200 import _lib
+    x = bf16_normal((rows, H), 11)
+    w = bf16_normal((Q + 2 * KV, H), 12, 0.05).cuda()
+    parts = [w[:Q], w[Q:Q + KV], w[Q + KV:]]
+    if not adjacent:                                 # the same matrices with 128 bytes between them
+        spaced = torch.zeros((Q + 2 * KV) * H + 3 * 64, dtype=torch.bfloat16, device="cuda")
+        starts = [0, Q * H + 64, (Q + KV) * H + 128]
+        parts = [spaced[s0:s0 + p.numel()].view(p.shape).copy_(p) for s0, p in zip(starts, parts)]
+    projector = gw.QkvProjector(H, Q, KV, 256, _lib.POLICY_ALWAYS)
+    projector.prepare(rows)
+    bound = [gw.make_projection(p, H, p.shape[0]) for p in parts]
+    q, k, v, joined = projector.run(bound[0], bound[1], bound[2] if with_value else None, x.cuda(), _lib.PHASE_DECODE)
+    torch.cuda.synchronize()
+    assert gw.kernel_error() == 0 and joined == adjacent
+    for name, got, weight in (("q", q, parts[0]), ("k", k, parts[1]), ("v", v, parts[2])):
+        if got is None:
+            assert name == "v" and not with_value
+            continue
+        expected = C.bf16_bits(to_f32(x) @ to_f32(weight).T)
+        assert_gemm_close(bits(got.contiguous()), expected, f"BF16 {name} rows={rows} adjacent={adjacent}")
+
+
+def test_fp8_group_join_then_joined_qkv(gw):
+    """Three FP8 matrices with their own weight scales and 8-byte trailers between them, as an artifact holds
+    them: separate projections before the join, one channel-scaled GEMM after it, same results."""
+    from gewell_b200 import _lib
+    rows = 40
+    x = bf16_normal((rows, H), 13)
+    xs = float(np.abs(to_f32(x)).max() / 448)
+    shapes = [Q, KV, KV]
+    host = [ofp8.pack_weights(to_f32(bf16_normal((n, H), 20 + i, 0.05)), xs) for i, n in enumerate(shapes)]
+    region = torch.zeros(sum(n * H + 256 for n in shapes), dtype=torch.uint8, device="cuda")
+    group = (_lib.Projection * 3)()
+    offset = 0
+    for p, h, n in zip(group, host, shapes):
+        region[offset:offset + n * H] = torch.from_numpy(h.data.copy()).cuda().reshape(-1)
+        p.storage, p.input, p.output, p.physical_output = _lib.STORAGE_FP8_W8A8, H, n, n
+        p.fp8_data = region.data_ptr() + offset
+        p.fp8_input_scale, p.fp8_weight_scale = h.input_scale, h.weight_scale
+        offset += n * H + 256                       # trailer and alignment padding
+    projector = gw.QkvProjector(H, Q, KV, 64, _lib.POLICY_ALWAYS)
+    projector.prepare(rows)
+    before = projector.run(group[0], group[1], group[2], x.cuda(), _lib.PHASE_PREFILL)
+    assert before[3] is False
+    before = [t.clone() for t in before[:3]]
+    channel = torch.zeros(sum(shapes), dtype=torch.float32, device="cuda")
+    assert gw.join_fp8_group(group, channel)
+    assert group[1].fp8_data == group[0].fp8_data + Q * H and group[2].fp8_data == group[1].fp8_data + KV * H
+    expected_scales = np.concatenate([np.full(n, np.float32(h.input_scale) * np.float32(h.weight_scale), dtype=np.float32)
+                                      for h, n in zip(host, shapes)])
+    assert np.array_equal(channel.cpu().numpy(), expected_scales)
+    q, k, v, joined = projector.run(group[0], group[1], group[2], x.cuda(), _lib.PHASE_PREFILL)
+    torch.cuda.synchronize()
+    assert joined and gw.kernel_error() == 0
+    for got, old, h in zip((q, k, v), before, host):
+        expected = ofp8.linear_w8a8(to_f32(x), h)
+        assert_gemm_close(bits(got.contiguous()), expected, "FP8 joined QKV")
+        assert_gemm_close(bits(got.contiguous()), bits(old), "FP8 joined vs separate")
+    # different input scales: the group is left apart
+    group[1].fp8_input_scale = xs * 2
+    assert not gw.join_fp8_group(group, channel)
+
+
+def test_nvfp4_pair_join_in_place(gw):
+    """Gate and up payloads apart in one region (rows, scale tiles, trailer each) -> joined in place; the chain
+    then runs the joined GEMM and gives the bits of a layer packed jointly from the start."""
+    from gewell_b200 import _lib
+    rows = 70
+    x = bf16_normal((rows, H), 14)
+    gate, up, down, both = nvfp4_layer(gw, True, float(np.abs(to_f32(x)).max()))
+    packed, scales = M * H // 2, gw.nvfp4_scale_storage_bytes(M, H)
+    stride = packed + scales + 256
+    region = torch.zeros(2 * stride, dtype=torch.uint8, device="cuda")
+    bound = []
+    for i, w in enumerate((gate, up)):
+        region[i * stride:i * stride + packed] = w.data.reshape(-1)
+        region[i * stride + packed:i * stride + packed + scales] = w.scales.reshape(-1)
+        p = gw.make_projection(w, H, M)
+        p.physical_output = M
+        p.nvfp4_data = region.data_ptr() + i * stride
+        p.nvfp4_scales = region.data_ptr() + i * stride + packed
+        bound.append(p)
+    p_down = gw.make_projection(down, M, H)
+    p_down.physical_output = H
+    chain = gw.MlpChain(H, M, 128, _lib.POLICY_ALWAYS)
+    chain.prepare(rows)
+    apart = chain.run(bound[0], bound[1], p_down, x.cuda(), _lib.PHASE_PREFILL).clone()
+    assert gw.join_nvfp4_pair(bound[0], bound[1])
+    assert bound[1].nvfp4_data == bound[0].nvfp4_data + packed
+    assert bound[0].nvfp4_scales == bound[0].nvfp4_data + 2 * packed and bound[1].nvfp4_scales == bound[0].nvfp4_scales + scales
+    assert torch.equal(region[:2 * packed].view(2 * M, H // 2), both.data)
+    assert torch.equal(region[2 * packed:2 * (packed + scales)], both.scales.reshape(-1))
+    together = chain.run(bound[0], bound[1], p_down, x.cuda(), _lib.PHASE_PREFILL)
+    reference_bound = [gw.make_projection(w, H, M) for w in (gate, up)]
+    for p in reference_bound:
+        p.physical_output = M
+    expected = chain.run(reference_bound[0], reference_bound[1], p_down, x.cuda(), _lib.PHASE_PREFILL)
+    torch.cuda.synchronize()
+    assert gw.kernel_error() == 0
+    assert torch.equal(together, expected)
+    assert_gemm_close(bits(together), bits(apart), "joined vs apart")
+    # different weight scales: left apart
+    bound[1].nvfp4_weight_scale *= 2
+    assert not gw.join_nvfp4_pair(bound[0], bound[1])
