@@ -508,9 +508,11 @@ def main():
     roofline = {"kernel": "pair_moe_gate_up_kernel + pair_moe_down_kernel (grouped NVFP4 GEMMs on CTA pairs)", "bound": "tensor",
                 "achieved": achieved, "peak": fp4_peak, "unit": "TFLOP/s", "frac": achieved / fp4_peak,
                 # dram__bytes_read.sum + dram__bytes_write.sum of the two launches at this size, from the one-pass
-                # ncu capture summarised in profiles/bench_moe_T8192_launch_list.md (gate/up 441.3 MB, down 486.1 MB)
-                "traffic": 927.4e6 if tokens == 8192 else None, "traffic_unit": "bytes per layer pass (both launches)",
-                "algorithmic_bytes": 979.0e6 if tokens == 8192 else None,
+                # ncu capture summarised in profiles/bench_moe_T8192_launch_list.md (gate/up 442.6 MB, down 483.5 MB)
+                "traffic": 926.1e6 if tokens == 8192 else None, "traffic_unit": "bytes per layer pass (both launches)",
+                # weights and their scales of the 128 experts once, quantised rows in and out, BF16 rows out
+                "algorithmic_bytes": float(128 * (1408 * (1408 + 176) + 2816 * (352 + 44))
+                                           + tokens * TOPK * ((1408 + 176) + 2 * (352 + 44) + 5632)),
                 "peak_note": f"4 x the {peaks['source']} dense BF16 burst figure ({peaks['bf16_tflops']} TFLOP/s); "
                              "no FP4 GEMM peak was measured on this pool (nominal dense FP4: 9000 TFLOP/s)",
                 "frac_of_nominal_fp4": achieved / 9000.0,
