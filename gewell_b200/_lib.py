@@ -30,6 +30,18 @@ class Projection(ctypes.Structure):
     ]
 
 
+class ArtifactTensorSpec(ctypes.Structure):
+    """gw_artifact_tensor_spec: one tensor of a model's artifact inventory."""
+    _fields_ = [("layer", c_int32), ("role", c_uint32), ("rank", c_uint32), ("rows", c_uint32), ("columns", c_uint32),
+                ("projection", c_uint32)]
+
+
+class ArtifactEntry(ctypes.Structure):
+    """gw_artifact_entry: where a tensor lies in the mapped file."""
+    _fields_ = [("offset", c_uint64), ("bytes", c_uint64), ("storage", c_uint32), ("sha256", ctypes.c_uint8 * 32),
+                ("data", c_void_p)]
+
+
 class FfnBlockWeights(ctypes.Structure):
     """gw_ffn_block_weights: one 26B layer's feed-forward weights (device pointers)."""
     _fields_ = [
@@ -100,6 +112,13 @@ _SIGNATURES = {
     "gw_ffn_block_moe": (c_void_p, [c_void_p]),
     "gw_debug_rsqrt": (c_int, [c_void_p, c_void_p, c_uint32]),
     "gw_rms_norm_reduction_lanes": (c_uint32, [c_uint32, c_uint32]),
+    "gw_artifact_open": (c_int, [c_char_p, c_void_p, c_uint32, POINTER(c_void_p)]),
+    "gw_artifact_count": (c_uint32, [c_void_p]),
+    "gw_artifact_is_mixed": (c_int, [c_void_p]),
+    "gw_artifact_file_bytes": (c_uint64, [c_void_p]),
+    "gw_artifact_entry_at": (c_int, [c_void_p, c_uint32, c_void_p]),
+    "gw_artifact_verify_full": (c_int, [c_void_p]),
+    "gw_artifact_close": (None, [c_void_p]),
     "gw_projection_entry_bytes": (c_size_t, [c_uint32, c_uint32, c_uint32]),
     "gw_validate_projection_entry": (c_int, [c_uint32, c_uint32, c_uint32, c_void_p, c_size_t]),
     "gw_projection_workspace_create": (c_int, [POINTER(Projection), c_uint32, c_uint32, c_int, c_void_p, POINTER(c_void_p)]),

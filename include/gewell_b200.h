@@ -229,6 +229,38 @@ size_t gw_projection_entry_bytes(uint32_t storage, uint32_t rows, uint32_t colum
 gw_status gw_validate_projection_entry(uint32_t storage, uint32_t rows, uint32_t columns, const uint8_t* host_payload,
                                        size_t entry_bytes);
 
+/* The artifact container itself (G4A4MIX1 / G4A4BF16): ArtifactFile of the reference
+ * (include/gewell/models/gemma4/26b_a4b/artifact.h, src/models/gemma4/26b_a4b/artifact.cc:105-221).
+ * gw_artifact_open memory-maps the file and checks, like ArtifactFile::Open / ValidateMetadata:
+ * identity, the ten geometry fields, the tied-head alias, reserved bytes, the SHA-256 of the header
+ * and of the entry table, every 72-byte entry against the inventory (id, layer, role, rank, shape,
+ * running offset, byte count for its storage type), the five size fields against the file's length,
+ * and the global scales of every quantised entry.  gw_artifact_verify_full is VerifyFull: table
+ * padding, every payload (gw_validate_projection_entry), per-tensor and whole-payload SHA-256, zero
+ * padding between tensors.  The reference compiles the model's tensor inventory into the reader; here
+ * the caller passes it (one spec per physical tensor, in file order; `projection` != 0 marks the
+ * tensors that may be stored quantised; `columns` is ignored for rank 1).  Host code only; entry.data
+ * points into the mapping and is valid until gw_artifact_close. */
+typedef struct gw_artifact_tensor_spec {
+  int32_t layer;
+  uint32_t role, rank, rows, columns, projection;
+} gw_artifact_tensor_spec;
+typedef struct gw_artifact_entry {
+  uint64_t offset, bytes;
+  uint32_t storage;
+  uint8_t sha256[32];
+  const uint8_t* data;
+} gw_artifact_entry;
+typedef struct gw_artifact gw_artifact;
+gw_status gw_artifact_open(const char* path, const gw_artifact_tensor_spec* inventory, uint32_t count,
+                           gw_artifact** artifact);
+uint32_t gw_artifact_count(const gw_artifact* artifact);
+int gw_artifact_is_mixed(const gw_artifact* artifact);
+uint64_t gw_artifact_file_bytes(const gw_artifact* artifact);
+gw_status gw_artifact_entry_at(const gw_artifact* artifact, uint32_t id, gw_artifact_entry* entry);
+gw_status gw_artifact_verify_full(const gw_artifact* artifact);
+void gw_artifact_close(gw_artifact* artifact);
+
 /* ProjectionWorkspace (projection.cuh:19-41, projection.cu:52-145): shared scratch and plans for
  * sequential projections on ONE stream, bound at construction.  create() sizes the scratch for
  * max_rows and the given bindings and allocates it; prepare(rows, phase) builds the plans for a row
