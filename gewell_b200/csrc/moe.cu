@@ -2,6 +2,7 @@
 // the routing / permutation / quantise kernels and the two grouped tcgen05
 // GEMMs together on one stream.  Mirrors sm120::MoeWorkspace
 // (models/gemma4/26b_a4b/sm120/moe.cuh:20-48, moe.cu:462-545).
+#include <nvtx3/nvToolsExt.h>
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
@@ -108,7 +109,16 @@ struct gw_moe_workspace {
   bool capture = false;   // materialise the BF16 gate/up and activated intermediates on the fused path too
   cudaEvent_t events[7] = {};
   ~gw_moe_workspace() { for (auto& e : events) if (e) cudaEventDestroy(e); }
-  void mark(int i, cudaStream_t s) const { if (timing) cudaEventRecord(events[i], s); }
+  // Stage boundary i of a pass (0 = start ... 6 = end): closes the NVTX range of the stage that ends here and
+  // opens the next one (visible to a profiler that collects NVTX; near-free otherwise), and records the
+  // timing event when stage timing is on.
+  void mark(int i, cudaStream_t s) const {
+    static const char* const kStageNames[6] = {"gw.moe.route_permute", "gw.moe.gather_quantise", "gw.moe.gate_up_gemm",
+                                               "gw.moe.geglu_quantise", "gw.moe.down_gemm", "gw.moe.combine"};
+    if (i > 0) nvtxRangePop();
+    if (i < 6) nvtxRangePushA(kStageNames[i]);
+    if (timing) cudaEventRecord(events[i], s);
+  }
 };
 
 extern "C" {
