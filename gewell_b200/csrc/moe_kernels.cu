@@ -152,14 +152,28 @@ moe_route_kernel(const bf16* __restrict__ scores, const bf16* __restrict__ exper
   if (offsets == nullptr) return;
   // single block: offsets, positions, inverse (the scan and scatter steps of kernels 2 and 3)
   __shared__ int32_t base[kExperts];
-  if (threadIdx.x == 0) {
-    int32_t acc = 0;
-    for (int i = 0; i < kExperts; ++i) {
-      base[i] = acc;
-      offsets[i] = acc;
-      acc += __popc(bitmap[i][0]) + __popc(bitmap[i][1]);
+  if (warp == 0) {
+    // exclusive scan of the 128 expert counts in one warp: four consecutive experts per lane
+    int32_t count[4], mine = 0;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      count[q] = __popc(bitmap[4 * lane + q][0]) + __popc(bitmap[4 * lane + q][1]);
+      mine += count[q];
     }
-    offsets[kExperts] = acc;
+    int32_t running = mine;
+#pragma unroll
+    for (int step = 1; step < 32; step <<= 1) {
+      const int32_t below = __shfl_up_sync(0xffffffffu, running, step);
+      if (lane >= unsigned(step)) running += below;
+    }
+    int32_t acc = running - mine;        // rows of all experts before this lane's four
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      base[4 * lane + q] = acc;
+      offsets[4 * lane + q] = acc;
+      acc += count[q];
+    }
+    if (lane == 31) offsets[kExperts] = acc;
   }
   __syncthreads();                       // also orders this block's writes of `keys` before the reads below
   for (uint32_t i = threadIdx.x; i < kChunkTokens * kTopK; i += blockDim.x) {
