@@ -242,7 +242,9 @@ def run_expert_parallel(args, world: int, rank: int, local_rank: int):
     config["exchange"] = args.exchange
     if args.exchange in ("peer", "peer_pull"):
         layer = ep.PeerMemoryExpertParallelMoe(by_position, [6.0 / 2688] * E, rank, world, local_tokens, capacity,
-                                               placement=placement, send_home=args.exchange == "peer")
+                                               placement=placement, send_home=args.exchange == "peer",
+                                               exchange=args.sync)
+        config["sync"] = layer.exchange
         expert_ws = layer.expert_ws
     else:
         backend = ep.DeviceBackend(by_position, local_tokens, capacity)
@@ -390,6 +392,9 @@ def main():
                         help="expert-parallel run: rows cross NVLink inside the dispatch/combine kernels over peer "
                              "memory (peer_pull: the combine kernel pulls result rows; peer: the down GEMM's epilogue "
                              "stores them into the source rank) or through NCCL all-to-all")
+    parser.add_argument("--sync", default="peer", choices=["peer", "nccl"],
+                        help="expert-parallel run over peer memory: the histogram exchange and the two barriers of a "
+                             "step through mailboxes in peer memory, or through NCCL (all-gather + two all-reduces)")
     parser.add_argument("--placement", default="balanced", choices=["contiguous", "interleaved", "balanced"],
                         help="expert placement of the expert-parallel run")
     args = parser.parse_args()

@@ -169,6 +169,8 @@ _SIGNATURES = {
     "gw_ipc_free": (c_int, [c_void_p]),
     "gw_moe_ep_dispatch": (c_int, [c_void_p, c_void_p, c_uint32, c_void_p, c_void_p, c_void_p, c_void_p, c_uint32,
                                    c_void_p]),
+    "gw_moe_ep_mailbox_bytes": (c_size_t, []),
+    "gw_moe_ep_exchange": (c_int, [c_void_p, c_uint32, c_void_p, c_uint32, c_uint32, c_void_p, c_void_p, c_void_p]),
     "gw_moe_ep_tables": (c_int, [c_void_p, c_void_p, c_uint32, c_uint32, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_void_p]),
     "gw_moe_ep_run_experts": (c_int, [c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_uint32, c_void_p, c_void_p,

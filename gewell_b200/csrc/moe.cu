@@ -748,6 +748,20 @@ gw_status gw_ipc_free(void* pointer) {
   return GW_OK;
 }
 
+size_t gw_moe_ep_mailbox_bytes(void) { return kEpMailboxBytes; }
+
+gw_status gw_moe_ep_exchange(const int32_t* payload, uint32_t count, void* const* peer_mailboxes, uint32_t rank,
+                             uint32_t world, uint32_t* epoch_counter, int32_t* gathered, void* stream) {
+  clear_error();
+  if (!peer_mailboxes || !epoch_counter || world == 0 || world > 8 || rank >= world || count > kEpMailboxMaxInts ||
+      (count != 0 && (!payload || !gathered)))
+    return fail(GW_INVALID_ARGUMENT, "exchange requires the ranks' mailboxes, an epoch counter, at most 8 ranks and 252 values");
+  GW_CUDA_CHECK(launch_ep_exchange(payload, count, peer_mailboxes, rank, world, epoch_counter, gathered, device_error_word(),
+                                   as_stream(stream)),
+                "exchange over peer memory");
+  return GW_OK;
+}
+
 gw_status gw_moe_ep_tables(const int32_t* counts, const int32_t* physical, uint32_t rank, uint32_t world,
                            int32_t* dest_row0, int32_t* local_offsets, int32_t* segment_start, int32_t* home_base,
                            void* stream) {

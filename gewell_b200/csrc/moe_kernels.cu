@@ -888,6 +888,63 @@ gather_rows_kernel(const uint4* __restrict__ input, const int32_t* __restrict__ 
 }
 
 // ---------------------------------------------------------------------------
+// Expert parallelism: small all-to-all exchange + barrier over peer memory (replaces an NCCL
+// all-gather / all-reduce whose latency, not its bytes, is what a step pays for).  Every rank
+// owns a mailbox of 2 x 8 slots of 1024 bytes: slot (parity, source rank) = {flag, payload}.
+// A call takes the next epoch from a device counter (so a replay of a captured step keeps
+// counting), writes its payload into its slot of every rank's mailbox, orders those stores with
+// a system-scope fence, raises the slot's flag to the epoch in every mailbox, then waits -- with
+// a bound, after which it reports through the error word and returns -- until all `world` flags of
+// its own mailbox show the epoch, and copies the payloads out.  Flags and payloads of consecutive
+// epochs alternate between the two parities: a rank can be at most one exchange ahead of the
+// slowest, which has then finished reading the parity that is written next.
+// Ranks are different GPUs; one block per rank.
+// ---------------------------------------------------------------------------
+constexpr uint32_t kMailboxSlotBytes = 1024, kMailboxRanks = 8, kMailboxPayloadOffset = 16;
+
+__global__ void __launch_bounds__(256)
+ep_exchange_kernel(const int32_t* __restrict__ payload, uint32_t count, uint8_t* const* __restrict__ mailboxes,
+                   uint32_t rank, uint32_t world, uint32_t* __restrict__ epoch_counter, int32_t* __restrict__ gathered,
+                   uint32_t* __restrict__ error) {
+  __shared__ uint32_t shared_epoch;
+  if (threadIdx.x == 0) shared_epoch = ++(*epoch_counter);
+  __syncthreads();
+  const uint32_t epoch = shared_epoch, parity = epoch & 1u;
+  const size_t my_slot = (size_t(parity) * kMailboxRanks + rank) * kMailboxSlotBytes;
+  for (uint32_t i = threadIdx.x; i < world * count; i += blockDim.x) {
+    const uint32_t peer = i / count, word = i % count;
+    reinterpret_cast<int32_t*>(mailboxes[peer] + my_slot + kMailboxPayloadOffset)[word] = payload[word];
+  }
+  __threadfence_system();            // this thread's payload stores (and everything this GPU wrote before) first ...
+  __syncthreads();
+  if (threadIdx.x < world) {
+    __threadfence_system();
+    uint32_t* flag = reinterpret_cast<uint32_t*>(mailboxes[threadIdx.x] + my_slot);
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(epoch) : "memory");   // ... then the flag
+    const uint32_t* theirs = reinterpret_cast<const uint32_t*>(
+        mailboxes[rank] + (size_t(parity) * kMailboxRanks + threadIdx.x) * kMailboxSlotBytes);
+    const uint64_t start = ptx_global_timer();
+    for (uint32_t spin = 1;; ++spin) {
+      uint32_t seen;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(theirs) : "memory");
+      if (seen == epoch) break;
+      if ((spin & 63u) == 0 && ptx_global_timer() - start > 2000000000ull) {
+        if (error != nullptr) atomicCAS(error, 0u, 0x90000000u | (threadIdx.x << 8) | rank);
+        break;
+      }
+      __nanosleep(64);
+    }
+  }
+  __syncthreads();
+  for (uint32_t i = threadIdx.x; i < world * count; i += blockDim.x) {
+    const uint32_t source = i / count, word = i % count;
+    const int32_t* slot = reinterpret_cast<const int32_t*>(
+        mailboxes[rank] + (size_t(parity) * kMailboxRanks + source) * kMailboxSlotBytes + kMailboxPayloadOffset);
+    gathered[i] = __ldcv(slot + word);
+  }
+}
+
+// ---------------------------------------------------------------------------
 // 7. Expert parallelism over peer memory (no counterpart in the reference, which
 //    is single GPU).  A travelling row is a 1584-byte record: 1408 bytes of
 //    packed E2M1 (K = 2816) followed by its 176 E4M3 block scales in K order.
@@ -1220,6 +1277,16 @@ cudaError_t launch_ep_dispatch(const void* input, const int32_t* keys, const int
   launch_pdl(ep_dispatch_kernel, blocks_for(size_t(tokens) * 32), 256, stream, 
       static_cast<const uint4*>(input), keys, inverse, offsets, inverse_input_scale, dest_rank, dest_row0,
       reinterpret_cast<uint8_t* const*>(peer_records), tokens, capacity_rows, error);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ep_exchange(const int32_t* payload, uint32_t count, void* const* mailboxes, uint32_t rank,
+                               uint32_t world, uint32_t* epoch_counter, int32_t* gathered, uint32_t* error,
+                               cudaStream_t stream) {
+  // an ordinary launch: it must not start before the kernels queued before it have finished
+  ep_exchange_kernel<<<1, 256, 0, stream>>>(payload, count, reinterpret_cast<uint8_t* const*>(mailboxes), rank, world,
+                                            epoch_counter, gathered, error);
+  note_launch();
   return cudaGetLastError();
 }
 

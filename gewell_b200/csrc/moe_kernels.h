@@ -106,6 +106,12 @@ cudaError_t launch_ep_dispatch(const void* input, const int32_t* keys, const int
                                const float* inverse_input_scale, const int32_t* dest_rank, const int32_t* dest_row0,
                                void* const* peer_records, uint32_t tokens, uint32_t capacity_rows, uint32_t* error,
                                cudaStream_t stream);
+// Small all-to-all exchange + barrier over peer memory (see ep_exchange_kernel).
+constexpr size_t kEpMailboxBytes = 2 * 8 * 1024;
+constexpr uint32_t kEpMailboxMaxInts = (1024 - 16) / 4;
+cudaError_t launch_ep_exchange(const int32_t* payload, uint32_t count, void* const* mailboxes, uint32_t rank,
+                               uint32_t world, uint32_t* epoch_counter, int32_t* gathered, uint32_t* error,
+                               cudaStream_t stream);
 cudaError_t launch_ep_tables(const int32_t* counts, const int32_t* physical, uint32_t rank, uint32_t world,
                              int32_t* dest_row0, int32_t* local_offsets, int32_t* segment_start, int32_t* home_base,
                              cudaStream_t stream);

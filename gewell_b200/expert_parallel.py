@@ -308,8 +308,10 @@ class PeerMemoryExpertParallelMoe:
     of BF16) directly into the owning GPU's memory over NVLink, already at its
     expert-major position; the owner's grouped GEMMs read the records in place;
     the combine kernel reads each token's eight result rows from their owners'
-    memory and folds them in expert order.  Collectives are only used for the
-    128-integer histogram (all-gather) and for the two barriers of a step.
+    memory and folds them in expert order.  The 128-integer histograms and the
+    two barriers of a step go through mailboxes in peer memory as well
+    (gw_moe_ep_exchange); `exchange="nccl"` uses an all-gather and two all-reduces
+    instead.
 
     Needs experts whose gate and up projections share their input scale (one
     quantised copy of a row serves both), as the fused checkpoint tensors do.
@@ -320,7 +322,7 @@ class PeerMemoryExpertParallelMoe:
 
     def __init__(self, experts_by_position, input_scales, rank: int, world: int, local_tokens: int,
                  receive_capacity_rows: int, placement: Placement | None = None, group=None,
-                 send_home: bool = False):
+                 send_home: bool = False, exchange: str = "peer"):
         """experts_by_position: 128 entries indexed by physical position, None for
         experts of other ranks.  input_scales: the gate/up input scale of all 128
         experts by expert id (every rank quantises rows for every expert).
@@ -358,6 +360,16 @@ class PeerMemoryExpertParallelMoe:
         self.local_offsets = torch.zeros(self.per_rank + 1, dtype=torch.int32, device=self.device)
         self.flag = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.timer = None
+        if exchange not in ("peer", "nccl"):
+            raise ValueError("exchange must be 'peer' or 'nccl'")
+        self.exchange = exchange if world <= 8 else "nccl"
+        self.mailbox = None
+        if self.exchange == "peer":
+            self.mailbox = SharedBuffer(int(gw.lib.gw_moe_ep_mailbox_bytes()), rank, world, group)
+            torch.as_tensor(gw.ops._RawDeviceBytes(self.mailbox.local, self.mailbox.nbytes), device=self.device).zero_()
+            self.epoch = torch.zeros(1, dtype=torch.int32, device=self.device)
+            torch.cuda.synchronize()
+            dist.barrier(group=group)          # every mailbox is zero before the first flag arrives
 
     def _mark(self, name: str):
         if self.timer is not None:
@@ -365,7 +377,16 @@ class PeerMemoryExpertParallelMoe:
 
     def _barrier(self):
         # stream-ordered: completes on this rank only after every rank's earlier kernels have
-        dist.all_reduce(self.flag, group=self.group)
+        if self.exchange == "peer":
+            self._exchange(None, 0, None)
+        else:
+            dist.all_reduce(self.flag, group=self.group)
+
+    def _exchange(self, payload, count: int, gathered):
+        self.gw.ops._check(self.gw.lib.gw_moe_ep_exchange(
+            payload.data_ptr() if payload is not None else None, count, self.mailbox.pointer_table.data_ptr(), self.rank,
+            self.world, self.epoch.data_ptr(), gathered.data_ptr() if gathered is not None else None,
+            torch.cuda.current_stream().cuda_stream))
 
     def rows_received(self) -> int:
         """Rows this rank's experts processed in the last step (reads back one integer)."""
@@ -389,7 +410,10 @@ class PeerMemoryExpertParallelMoe:
         else:                                  # a rank without tokens still serves its experts
             counts = torch.zeros(EXPERTS, dtype=torch.int32, device=self.device)
         self._mark("route")
-        dist.all_gather_into_tensor(self.counts_all, counts, group=self.group)
+        if self.exchange == "peer":
+            self._exchange(counts, EXPERTS, self.counts_all)
+        else:
+            dist.all_gather_into_tensor(self.counts_all, counts, group=self.group)
         home = self.send_home
         check(lib.gw_moe_ep_tables(self.counts_all.data_ptr(), self.physical.data_ptr(), self.rank, self.world,
                                    self.dest_row0.data_ptr(), self.local_offsets.data_ptr(),
@@ -445,6 +469,6 @@ class PeerMemoryExpertParallelMoe:
 
     def close(self):
         self.records.close(self.group)
-        for buffer in (self.down, self.returned):
+        for buffer in (self.down, self.returned, self.mailbox):
             if buffer is not None:
                 buffer.close(self.group)

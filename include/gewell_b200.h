@@ -557,6 +557,22 @@ gw_status gw_moe_ep_dispatch(gw_moe_workspace* workspace, const void* input_bf16
                              const int32_t* dest_row0, void* const* peer_records,
                              uint32_t capacity_rows, void* stream);
 
+/* A small all-to-all exchange that is also a barrier, over peer memory (no collective library call):
+ * every rank publishes `count` int32 values (count <= 252; 0 = barrier only) to all ranks and returns,
+ * in stream order, once every rank has published its values of the same call -- by which time
+ * everything those ranks' GPUs wrote before their call (e.g. records stored into this rank's
+ * buffers) is visible here.  gathered[source rank][count] receives the values.
+ *   peer_mailboxes  device array of `world` pointers: rank r's mailbox (gw_moe_ep_mailbox_bytes()
+ *                   bytes from gw_ipc_alloc, zeroed once before the first call) as mapped here
+ *   epoch_counter   one uint32 in this rank's device memory, zeroed once; counts the calls (kept on
+ *                   the device so that a replayed step keeps counting); all ranks must make the
+ *                   same sequence of calls
+ * The wait is bounded (2 s): on a timeout the kernel reports 0x90000000 | source << 8 | rank through
+ * gw_debug_kernel_error and returns.  At most 8 ranks, each on its own GPU. */
+size_t gw_moe_ep_mailbox_bytes(void);
+gw_status gw_moe_ep_exchange(const int32_t* payload, uint32_t count, void* const* peer_mailboxes, uint32_t rank,
+                             uint32_t world, uint32_t* epoch_counter, int32_t* gathered, void* stream);
+
 /* The destination tables on the device, without a host round trip: from
  * counts[source rank][expert id] (world x 128 int32, the all-gathered routing
  * histograms) and physical[expert id] (position of the expert in (owner, id)

@@ -274,14 +274,16 @@ def _worker(rank: int, world: int, port: int, placement_name: str, exchange: str
         for e in mine:
             by_position[placement.physical[e]] = by_id[e]
         local = tokens // world
-        if exchange in ("peer", "peer_pull"):
+        if exchange in ("peer", "peer_pull", "peer_pull_nccl_sync"):
+            # histograms and barriers through mailboxes in peer memory, or ("..._nccl_sync") through NCCL
             moe = ep.PeerMemoryExpertParallelMoe(by_position, [6.0 / 2688] * E, rank, world, local, 8 * tokens,
-                                                 placement=placement, send_home=exchange == "peer")
+                                                 placement=placement, send_home=exchange == "peer",
+                                                 exchange="nccl" if exchange.endswith("nccl_sync") else "peer")
         else:
             backend = ep.DeviceBackend(by_position, local, 8 * tokens)
             moe = ep.ExpertParallelMoe(backend, rank, world, local, 8 * tokens, placement=placement)
         begin = rank * local
-        for _ in range(2):
+        for _ in range(3):                    # three steps: the mailboxes' two parities are both reused
             y = moe.run(x[begin:begin + local], scores[begin:begin + local], scales, local)
         torch.cuda.synchronize()
         assert gw.kernel_error() == 0
@@ -294,7 +296,7 @@ def _worker(rank: int, world: int, port: int, placement_name: str, exchange: str
 
 @pytest.mark.parametrize("world,placement_name,exchange", [
     (2, "contiguous", "nccl"), (2, "balanced", "nccl"), (2, "contiguous", "peer"), (2, "balanced", "peer"),
-    (2, "balanced", "peer_pull"),
+    (2, "balanced", "peer_pull"), (2, "balanced", "peer_pull_nccl_sync"),
     (4, "balanced", "peer_pull"), (4, "contiguous", "nccl"), (4, "interleaved", "peer"),
     (8, "balanced", "peer_pull"), (8, "interleaved", "nccl"), (8, "contiguous", "peer")])
 def test_ranks_equal_single_gpu(layer, tmp_path, world, placement_name, exchange):
@@ -318,3 +320,41 @@ def test_ranks_equal_single_gpu(layer, tmp_path, world, placement_name, exchange
     # the same kernels see the same rows; only the grouped-GEMM plan may differ with
     # the per-rank row count, and both plans accumulate the same products in FP32
     assert mismatch == 0.0, f"{mismatch:.2e} of the outputs differ between {world} ranks and 1 GPU"
+
+
+def test_exchange_single_rank_and_missing_rank():
+    """gw_moe_ep_exchange on one GPU: with one rank it hands back its own payload and counts its calls on the
+    device; with a second rank that never publishes, the bounded wait runs out and the error word names it
+    (the context stays usable)."""
+    import gewell_b200 as gw
+    lib = gw.lib
+    size = int(lib.gw_moe_ep_mailbox_bytes())
+    mailbox = torch.zeros(size, dtype=torch.uint8, device="cuda")
+    other = torch.zeros(size, dtype=torch.uint8, device="cuda")
+    epoch = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for call in range(1, 4):
+        payload = torch.arange(128, dtype=torch.int32, device="cuda") * call
+        gathered = torch.full((1, 128), -1, dtype=torch.int32, device="cuda")
+        table = torch.tensor([mailbox.data_ptr()], dtype=torch.int64, device="cuda")
+        gw.ops._check(lib.gw_moe_ep_exchange(payload.data_ptr(), 128, table.data_ptr(), 0, 1, epoch.data_ptr(),
+                                             gathered.data_ptr(), None))
+        torch.cuda.synchronize()
+        assert torch.equal(gathered[0], payload) and int(epoch.item()) == call
+    assert gw.kernel_error() == 0
+    # barrier only
+    gw.ops._check(lib.gw_moe_ep_exchange(None, 0, table.data_ptr(), 0, 1, epoch.data_ptr(), None, None))
+    torch.cuda.synchronize()
+    assert gw.kernel_error() == 0 and int(epoch.item()) == 4
+    # rank 1 of 2 never arrives
+    table = torch.tensor([mailbox.data_ptr(), other.data_ptr()], dtype=torch.int64, device="cuda")
+    payload = torch.ones(4, dtype=torch.int32, device="cuda")
+    gathered = torch.zeros((2, 4), dtype=torch.int32, device="cuda")
+    gw.ops._check(lib.gw_moe_ep_exchange(payload.data_ptr(), 4, table.data_ptr(), 0, 2, epoch.data_ptr(),
+                                         gathered.data_ptr(), None))
+    torch.cuda.synchronize()
+    assert gw.kernel_error() == 0x90000000 | (1 << 8) | 0
+    assert torch.equal(gathered[0], payload)                # its own values did arrive
+    assert gw.kernel_error() == 0                           # the word is cleared on read; the context is intact
+    with pytest.raises(gw.GewellInvalidArgument):
+        gw.ops._check(lib.gw_moe_ep_exchange(payload.data_ptr(), 4, table.data_ptr(), 0, 9, epoch.data_ptr(),
+                                             gathered.data_ptr(), None))
