@@ -234,16 +234,20 @@ def run_expert_parallel(args, world: int, rank: int, local_rank: int):
         placement = getattr(ep.Placement, args.placement)(world)
     config["placement"] = args.placement
     mine = placement.local_experts(rank)
-    by_id = build_experts(gw, torch, device, expert_ids=mine)
+    # "home": every rank also holds the down matrices of all experts (it finishes its own tokens' rows itself)
+    by_id = build_experts(gw, torch, device, expert_ids=None if args.exchange == "home" else mine)
     by_position = [None] * E
     for e in mine:
         by_position[placement.physical[e]] = by_id[e]
     capacity = TOPK * tokens          # worst case: every assignment lands on one rank
     config["exchange"] = args.exchange
-    if args.exchange in ("peer", "peer_pull"):
+    if args.exchange == "home":
+        config["parallelism"] = f"ep{world} for gate/up (experts sharded), down projection at the tokens' home rank (down matrices of all experts on every rank)"
+    if args.exchange in ("peer", "peer_pull", "home"):
         layer = ep.PeerMemoryExpertParallelMoe(by_position, [6.0 / 2688] * E, rank, world, local_tokens, capacity,
                                                placement=placement, send_home=args.exchange == "peer",
-                                               exchange=args.sync)
+                                               exchange=args.sync,
+                                               home_down=[w[2] for w in by_id] if args.exchange == "home" else None)
         config["sync"] = layer.exchange
         expert_ws = layer.expert_ws
     else:
@@ -322,7 +326,10 @@ def run_expert_parallel(args, world: int, rank: int, local_rank: int):
     # per-stage device times of this rank and the grouped GEMMs' roofline
     marks = []
     layer.timer = lambda name: marks.append((name, _record(torch, stream)))
-    expert_ws.stage_timing(True)
+    # the grouped GEMMs run in the owner-side workspace; with --exchange home the down GEMM runs in the routing one
+    timed_workspaces = [expert_ws] + ([layer.route_ws] if args.exchange == "home" else [])
+    for workspace in timed_workspaces:
+        workspace.stage_timing(True)
     stage_sum, gemm_sum = {}, 0.0
     for _ in range(max(3, args.steps // 4)):
         marks.clear()
@@ -334,10 +341,13 @@ def run_expert_parallel(args, world: int, rank: int, local_rank: int):
             stage_sum[name] = stage_sum.get(name, 0.0) + previous.elapsed_time(event)
             previous = event
         inner = expert_ws.stage_elapsed_ms()
-        gemm_sum += inner["gate_up_gemm"] + inner["down_gemm"]
+        gemm_sum += inner["gate_up_gemm"] + (0.0 if args.exchange == "home" else inner["down_gemm"])
+        if args.exchange == "home":
+            gemm_sum += layer.route_ws.stage_elapsed_ms()["down_gemm"]
     repeats = max(3, args.steps // 4)
     layer.timer = None
-    expert_ws.stage_timing(False)
+    for workspace in timed_workspaces:
+        workspace.stage_timing(False)
     stages = {k: v / repeats for k, v in stage_sum.items()}
     rows_received = layer.rows_received() if args.exchange != "nccl" else layer.last_layout.total
     received = torch.tensor([float(rows_received), gemm_sum / repeats], device=device)
@@ -388,10 +398,12 @@ def main():
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--tokens", type=int, default=0, help="override the token count (testing)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
-    parser.add_argument("--exchange", default="peer_pull", choices=["peer", "peer_pull", "nccl"],
+    parser.add_argument("--exchange", default="home", choices=["home", "peer", "peer_pull", "nccl"],
                         help="expert-parallel run: rows cross NVLink inside the dispatch/combine kernels over peer "
-                             "memory (peer_pull: the combine kernel pulls result rows; peer: the down GEMM's epilogue "
-                             "stores them into the source rank) or through NCCL all-to-all")
+                             "memory (home: the owners run gate/up only and every rank fetches its rows' quantised "
+                             "activations and runs the down projection itself, with the down matrices of all experts "
+                             "on every rank; peer_pull: the combine kernel pulls BF16 result rows; peer: the down "
+                             "GEMM's epilogue stores them into the source rank) or through NCCL all-to-all")
     parser.add_argument("--sync", default="peer", choices=["peer", "nccl"],
                         help="expert-parallel run over peer memory: the histogram exchange and the two barriers of a "
                              "step through mailboxes in peer memory, or through NCCL (all-gather + two all-reduces)")

@@ -169,6 +169,9 @@ _SIGNATURES = {
     "gw_ipc_free": (c_int, [c_void_p]),
     "gw_moe_ep_dispatch": (c_int, [c_void_p, c_void_p, c_uint32, c_void_p, c_void_p, c_void_p, c_void_p, c_uint32,
                                    c_void_p]),
+    "gw_moe_ep_activation_record_bytes": (c_size_t, []),
+    "gw_moe_ep_run_gate_up": (c_int, [c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_uint32, c_void_p, c_void_p, c_void_p]),
+    "gw_moe_ep_finish_at_home": (c_int, [c_void_p, c_uint32, c_void_p, c_void_p, c_void_p, c_uint32, c_void_p, c_void_p, c_void_p]),
     "gw_moe_ep_mailbox_bytes": (c_size_t, []),
     "gw_moe_ep_exchange": (c_int, [c_void_p, c_uint32, c_void_p, c_uint32, c_uint32, c_void_p, c_void_p, c_void_p]),
     "gw_moe_ep_tables": (c_int, [c_void_p, c_void_p, c_uint32, c_uint32, c_void_p, c_void_p, c_void_p, c_void_p,

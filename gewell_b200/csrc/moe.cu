@@ -142,6 +142,9 @@ gw_status gw_moe_expert_table_create(const gw_expert_weights* experts, uint32_t 
     const std::string who = " (expert " + std::to_string(e) + ")";
     for (int i = 0; i < 3; ++i) {
       const gw_projection& p = *proj[i];
+      // a projection kept elsewhere (expert parallelism with the down projection at the tokens' home:
+      // the owner's table may lack nothing, the home table holds only the down matrices)
+      if (p.storage == GW_STORAGE_ABSENT) continue;
       const uint32_t want_in = i < 2 ? kHidden : kInter, want_out = i < 2 ? kInter : kHidden;
       CUtensorMap* slot = &maps[e * kMoeMapsPerExpert];
       if (p.input != want_in || p.output != want_out)
@@ -186,8 +189,9 @@ gw_status gw_moe_expert_table_create(const gw_expert_weights* experts, uint32_t 
         return fail(GW_INVALID_ARGUMENT, "invalid 26B expert projection storage" + who);
       }
     }
-    if (experts[e].gate.storage != GW_STORAGE_NVFP4_W4A4 || experts[e].up.storage != GW_STORAGE_NVFP4_W4A4 ||
-        experts[e].gate.nvfp4_input_scale != experts[e].up.nvfp4_input_scale)
+    const bool no_first = experts[e].gate.storage == GW_STORAGE_ABSENT && experts[e].up.storage == GW_STORAGE_ABSENT;
+    if (!no_first && (experts[e].gate.storage != GW_STORAGE_NVFP4_W4A4 || experts[e].up.storage != GW_STORAGE_NVFP4_W4A4 ||
+                      experts[e].gate.nvfp4_input_scale != experts[e].up.nvfp4_input_scale))
       shared = false;
   }
   auto* t = new (std::nothrow) gw_expert_table();
@@ -347,9 +351,14 @@ namespace {
 // `records` != nullptr (expert parallelism): the rows arrive already quantised as 1584-byte
 // records (packed E2M1 + K-ordered scale bytes) written by the ranks that routed them; the
 // GEMM reads the packed part in place and only the scale bytes are re-tiled here.
+//
+// `stages`: kStageFirst runs up to the quantised down input (in the workspace's packed_act / scales_act),
+// kStageDown only the down GEMM over what those buffers hold; both by default.
+constexpr int kStageFirst = 1, kStageDown = 2;
 gw_status run_experts(gw_moe_workspace* w, const void* input, const int32_t* gather_index, uint32_t gather_divisor,
                       const int32_t* offsets, uint32_t n, const gw_expert_table* table, void* down_out, cudaStream_t s,
-                      const void* records = nullptr, const uint64_t* row_home = nullptr) {
+                      const void* records = nullptr, const uint64_t* row_home = nullptr,
+                      int stages = kStageFirst | kStageDown) {
   if (!table->all_nvfp4)
     return fail(GW_UNSUPPORTED, "this entry point runs NVFP4 (W4A4) expert tables only; mixed tables run through gw_moe_run");
   const auto* info = table->info.as<MoeExpertInfo>();
@@ -380,7 +389,9 @@ gw_status run_experts(gw_moe_workspace* w, const void* input, const int32_t* gat
                       block_n_first, block_n_down, table->shared_gate_up ? 1 : 0, device_error_word(), kMoeKindNvfp4, 1};
     GW_CUDA_CHECK(launch_moe_prepare_groups(plan, first_groups, down_groups, s), "MoE group descriptors");
   }
-  if (records != nullptr) {
+  if (!(stages & kStageFirst)) {
+    // the down input is in place already
+  } else if (records != nullptr) {
     GW_CUDA_CHECK(launch_ep_retile_scales(records, w->sorted_keys, offsets, n, w->scales_in.as<uint8_t>(), s),
                   "MoE scale re-tiling of received rows");
   } else if (gather_index == w->sorted_assignments && gather_divisor == 8 && n % 8 == 0 && n >= 8 * 512) {
@@ -396,13 +407,16 @@ gw_status run_experts(gw_moe_workspace* w, const void* input, const int32_t* gat
   }
   std::string error;
   const bool swap = form == kMoeFormSwap;
-  if (!w->first_map.get(records ? records : w->packed_in.data, kHidden / 2, size_t(parts) * n,
+  if ((stages & kStageFirst) &&
+      !w->first_map.get(records ? records : w->packed_in.data, kHidden / 2, size_t(parts) * n,
                         swap ? block_n_first : 128, records ? kEpRecordBytes : kHidden / 2, &error))
     return fail(GW_CUDA_ERROR, "MoE activation descriptor: " + error);
   if (!w->down_map.get(w->packed_act.data, kInter / 2, n, swap ? block_n_down : 128, kInter / 2, &error))
     return fail(GW_CUDA_ERROR, "MoE activation descriptor: " + error);
   w->mark(2, s);
-  if (pair_first) {
+  if (!(stages & kStageFirst)) {
+    w->mark(3, s);
+  } else if (pair_first) {
     PairMoeParams first{};
     first.map_tokens = w->first_map.map;
     first.map_table = table->maps.as<CUtensorMap>();
@@ -452,7 +466,9 @@ gw_status run_experts(gw_moe_workspace* w, const void* input, const int32_t* gat
     }
   }
   w->mark(4, s);
-  if (pair_down) {
+  if (!(stages & kStageDown)) {
+    // the caller takes the quantised activations from the workspace
+  } else if (pair_down) {
     PairMoeParams down{};
     down.map_tokens = w->down_map.map;
     down.map_table = table->maps.as<CUtensorMap>();
@@ -825,6 +841,61 @@ gw_status gw_moe_ep_run_experts(gw_moe_workspace* w, const void* records, const 
                                        push ? w->row_home.as<uint64_t>() : nullptr);
   w->mark(6, s);
   return status;
+}
+
+size_t gw_moe_ep_activation_record_bytes(void) { return kEpActivationRecordBytes; }
+
+gw_status gw_moe_ep_run_gate_up(gw_moe_workspace* w, const void* records, const int32_t* offsets, uint32_t first_expert,
+                                uint32_t expert_count, uint32_t total_rows, const gw_expert_table* table,
+                                void* activation_records, void* stream) {
+  clear_error();
+  if (!w || !table) return fail(GW_INVALID_ARGUMENT, "expert run requires a workspace and an expert table");
+  if (!table->shared_gate_up)
+    return fail(GW_UNSUPPORTED, "records carry one quantised copy of a row: gate and up must share their input scale");
+  if (total_rows > w->n) return fail(GW_INVALID_ARGUMENT, "received rows exceed workspace (8 x max_rows)");
+  if (!total_rows) return GW_OK;
+  if (!records || !offsets || !activation_records || expert_count == 0 || first_expert + expert_count > kExperts ||
+      reinterpret_cast<uintptr_t>(records) % 16 || reinterpret_cast<uintptr_t>(activation_records) % 16)
+    return fail(GW_INVALID_ARGUMENT, "expert run requires aligned buffers and an expert range inside 0..128");
+  cudaStream_t s = as_stream(stream);
+  w->mark(0, s);
+  GW_CUDA_CHECK(launch_moe_keys_from_offsets(offsets, first_expert, expert_count, total_rows, w->sorted_keys,
+                                             w->local_offsets, s),
+                "MoE keys from offsets");
+  const gw_status status =
+      run_experts(w, nullptr, nullptr, 1, w->local_offsets, total_rows, table, nullptr, s, records, nullptr, kStageFirst);
+  if (status != GW_OK) return status;
+  GW_CUDA_CHECK(launch_ep_export_activations(w->packed_act.data, w->scales_act.as<uint8_t>(), w->sorted_keys, w->local_offsets,
+                                             total_rows, activation_records, s),
+                "export of the quantised activations");
+  w->mark(6, s);
+  return GW_OK;
+}
+
+gw_status gw_moe_ep_finish_at_home(gw_moe_workspace* w, uint32_t rows, const int32_t* dest_rank, const int32_t* dest_row0,
+                                   void* const* peer_activation_records, uint32_t capacity_rows,
+                                   const gw_expert_table* down_table, void* output_bf16, void* stream) {
+  clear_error();
+  if (!w || !down_table) return fail(GW_INVALID_ARGUMENT, "finishing at home requires the workspace that routed the rows and a table of down projections");
+  if (rows > w->max_rows) return fail(GW_INVALID_ARGUMENT, "MoE rows exceed workspace");
+  if (!rows) return GW_OK;
+  if (!dest_rank || !dest_row0 || !peer_activation_records || !output_bf16 || reinterpret_cast<uintptr_t>(output_bf16) % 16)
+    return fail(GW_INVALID_ARGUMENT, "finishing at home requires the destination tables and a 16-byte aligned output");
+  for (const MoeExpertInfo& e : down_table->host_info)
+    if (e.storage[2] != GW_STORAGE_NVFP4_W4A4)
+      return fail(GW_INVALID_ARGUMENT, "the home table must hold the NVFP4 down projection of all 128 experts");
+  cudaStream_t s = as_stream(stream);
+  w->mark(0, s);
+  GW_CUDA_CHECK(launch_ep_import_activations(w->keys, w->inverse, w->offsets, dest_rank, dest_row0, peer_activation_records,
+                                             8 * rows, capacity_rows, device_error_word(), w->packed_act.data,
+                                             w->scales_act.as<uint8_t>(), s),
+                "import of the quantised activations");
+  const gw_status status = run_experts(w, nullptr, nullptr, 1, w->offsets, 8 * rows, down_table, w->down.data, s, nullptr,
+                                       nullptr, kStageDown);
+  if (status != GW_OK) return status;
+  GW_CUDA_CHECK(launch_moe_combine(w->down.data, w->inverse, w->weights, rows, kHidden, output_bf16, s), "MoE combine");
+  w->mark(6, s);
+  return GW_OK;
 }
 
 gw_status gw_moe_ep_combine(gw_moe_workspace* w, uint32_t rows, const int32_t* dest_rank, const int32_t* dest_row0,

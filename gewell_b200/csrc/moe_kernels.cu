@@ -1104,6 +1104,64 @@ ep_retile_scales_kernel(const uint8_t* __restrict__ records, const int32_t* __re
   *reinterpret_cast<uint32_t*>(scales + region + scale_offset(row - first, word * 4, kHidden)) = value;
 }
 
+// Expert parallelism with the down projection at the tokens' home: the owner of an expert runs gate/up
+// + GeGLU + FP4 quantisation only and exports every row of its expert-major order as a 416-byte
+// activation record (352 B of E2M1, 44 scale bytes in K order, padding to 16 bytes) that the row's home
+// rank fetches -- 14 times fewer bytes over NVLink than the BF16 result row of the down projection.
+//   export: one warp per row, from the workspace's packed rows and tiled scales
+__global__ void __launch_bounds__(256)
+ep_export_activations_kernel(const uint4* __restrict__ packed, const uint8_t* __restrict__ scales,
+                             const int32_t* __restrict__ sorted_keys, const int32_t* __restrict__ offsets, uint32_t rows,
+                             uint4* __restrict__ records) {
+  griddep_launch();
+  griddep_wait();     // results of earlier kernels in the stream are read from here on
+  const uint32_t row = (blockIdx.x * 256 + threadIdx.x) / 32, lane = threadIdx.x % 32;
+  if (row >= rows || row >= uint32_t(offsets[kExperts])) return;      // `rows` may be an upper bound
+  constexpr uint32_t kPackedVectors = kInter / 2 / 16;                // 22
+  constexpr uint32_t kScaleWords = kInter / 16 / 4;                   // 11
+  constexpr uint32_t kRecordVectors = kEpActivationRecordBytes / 16;  // 26
+  const int32_t e = sorted_keys[row];
+  const int32_t first = offsets[e];
+  uint4* record = records + size_t(row) * kRecordVectors;
+  if (lane < kPackedVectors) record[lane] = packed[size_t(row) * kPackedVectors + lane];
+  if (lane < kScaleWords) {
+    const size_t region = size_t(first / 128 + e) * 128 * (kInter / 16);
+    const uint32_t word = *reinterpret_cast<const uint32_t*>(scales + region + scale_offset(row - first, lane * 4, kInter));
+    reinterpret_cast<uint32_t*>(record + kPackedVectors)[lane] = word;
+  }
+}
+
+//   import: one warp per routed assignment of this rank; the record comes from the expert's owner
+//   (row dest_row0[e] + position of the assignment among this rank's rows of e) and lands at the
+//   assignment's position in this rank's own expert-sorted order, scales in the local tiled layout.
+__global__ void __launch_bounds__(128, 8)
+ep_import_activations_kernel(const int32_t* __restrict__ keys, const int32_t* __restrict__ inverse,
+                             const int32_t* __restrict__ offsets, const int32_t* __restrict__ dest_rank,
+                             const int32_t* __restrict__ dest_row0, const uint4* const* __restrict__ peer_records,
+                             uint32_t assignments, uint32_t capacity_rows, uint32_t* __restrict__ error,
+                             uint4* __restrict__ packed, uint8_t* __restrict__ scales) {
+  griddep_launch();
+  griddep_wait();     // results of earlier kernels in the stream are read from here on
+  const uint32_t assignment = (blockIdx.x * 128 + threadIdx.x) / 32, lane = threadIdx.x % 32;
+  if (assignment >= assignments) return;
+  constexpr uint32_t kPackedVectors = kInter / 2 / 16, kScaleWords = kInter / 16 / 4;
+  constexpr uint32_t kRecordVectors = kEpActivationRecordBytes / 16;
+  const int32_t e = keys[assignment];
+  const int32_t position = inverse[assignment], first = offsets[e];
+  const size_t remote_row = size_t(dest_row0[e] + position - first);
+  if (remote_row >= capacity_rows) {          // outside the owner's buffer: never read there, report
+    if (error != nullptr && lane == 0) atomicCAS(error, 0u, 0x70000400u | uint32_t(e));
+    return;
+  }
+  const uint4* record = peer_records[dest_rank[e]] + remote_row * kRecordVectors;
+  if (lane < kPackedVectors) packed[size_t(position) * kPackedVectors + lane] = record[lane];
+  if (lane < kScaleWords) {
+    const uint32_t word = reinterpret_cast<const uint32_t*>(record + kPackedVectors)[lane];
+    const size_t region = size_t(first / 128 + e) * 128 * (kInter / 16);
+    *reinterpret_cast<uint32_t*>(scales + region + scale_offset(position - first, lane * 4, kInter)) = word;
+  }
+}
+
 // Small blocks (128 threads, at most 64 registers): many independent blocks keep enough
 // remote loads in flight to cover the NVLink latency.
 __global__ void __launch_bounds__(128, 8)
@@ -1277,6 +1335,23 @@ cudaError_t launch_ep_dispatch(const void* input, const int32_t* keys, const int
   launch_pdl(ep_dispatch_kernel, blocks_for(size_t(tokens) * 32), 256, stream, 
       static_cast<const uint4*>(input), keys, inverse, offsets, inverse_input_scale, dest_rank, dest_row0,
       reinterpret_cast<uint8_t* const*>(peer_records), tokens, capacity_rows, error);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ep_export_activations(const void* packed, const uint8_t* scales, const int32_t* sorted_keys,
+                                         const int32_t* offsets, uint32_t rows, void* records, cudaStream_t stream) {
+  launch_pdl(ep_export_activations_kernel, blocks_for(size_t(rows) * 32), 256, stream, static_cast<const uint4*>(packed), scales,
+             sorted_keys, offsets, rows, static_cast<uint4*>(records));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ep_import_activations(const int32_t* keys, const int32_t* inverse, const int32_t* offsets,
+                                         const int32_t* dest_rank, const int32_t* dest_row0, void* const* peer_records,
+                                         uint32_t assignments, uint32_t capacity_rows, uint32_t* error, void* packed,
+                                         uint8_t* scales, cudaStream_t stream) {
+  launch_pdl(ep_import_activations_kernel, unsigned((size_t(assignments) * 32 + 127) / 128), 128, stream, keys, inverse, offsets,
+             dest_rank, dest_row0, reinterpret_cast<const uint4* const*>(peer_records), assignments, capacity_rows, error,
+             static_cast<uint4*>(packed), scales);
   return cudaGetLastError();
 }
 

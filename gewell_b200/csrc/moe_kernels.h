@@ -102,10 +102,18 @@ cudaError_t launch_gather_rows(const void* input, const int32_t* index, uint32_t
 
 // Expert parallelism over peer memory: 1584-byte records (1408 B packed E2M1 + 176 scale bytes).
 constexpr uint32_t kEpRecordBytes = 1584;
+// activation record of the down-at-home exchange: 352 B of E2M1, 44 scale bytes in K order, padded to 16 bytes
+constexpr uint32_t kEpActivationRecordBytes = 416;
 cudaError_t launch_ep_dispatch(const void* input, const int32_t* keys, const int32_t* inverse, const int32_t* offsets,
                                const float* inverse_input_scale, const int32_t* dest_rank, const int32_t* dest_row0,
                                void* const* peer_records, uint32_t tokens, uint32_t capacity_rows, uint32_t* error,
                                cudaStream_t stream);
+cudaError_t launch_ep_export_activations(const void* packed, const uint8_t* scales, const int32_t* sorted_keys,
+                                         const int32_t* offsets, uint32_t rows, void* records, cudaStream_t stream);
+cudaError_t launch_ep_import_activations(const int32_t* keys, const int32_t* inverse, const int32_t* offsets,
+                                         const int32_t* dest_rank, const int32_t* dest_row0, void* const* peer_records,
+                                         uint32_t assignments, uint32_t capacity_rows, uint32_t* error, void* packed,
+                                         uint8_t* scales, cudaStream_t stream);
 // Small all-to-all exchange + barrier over peer memory (see ep_exchange_kernel).
 constexpr size_t kEpMailboxBytes = 2 * 8 * 1024;
 constexpr uint32_t kEpMailboxMaxInts = (1024 - 16) / 4;

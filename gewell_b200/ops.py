@@ -449,7 +449,8 @@ class ExpertTable:
     def __init__(self, experts: list[tuple | None]):
         """experts[i] = (gate, up, down), each an Nvfp4Weight, an Fp8Weight or a BF16 tensor [N, K];
         `experts[i] is None` marks an expert whose weights live on another rank (expert parallelism):
-        no row may be routed to it on this rank."""
+        no row may be routed to it on this rank.  A single projection may be None as well (a table that
+        holds only the down matrices, for ranks that finish their own tokens' rows at home)."""
         self._lib = _library()
         self._keep = experts
         array = (_lib.ExpertWeights * len(experts))()
@@ -458,9 +459,11 @@ class ExpertTable:
                 array[i].gate.storage = array[i].up.storage = array[i].down.storage = _lib.STORAGE_ABSENT
                 continue
             gate, up, down = entry
-            array[i].gate = make_projection(gate, 2816, 704)
-            array[i].up = make_projection(up, 2816, 704)
-            array[i].down = make_projection(down, 704, 2816)
+            for slot, weight, k, n in (("gate", gate, 2816, 704), ("up", up, 2816, 704), ("down", down, 704, 2816)):
+                if weight is None:             # this projection is kept elsewhere
+                    getattr(array[i], slot).storage = _lib.STORAGE_ABSENT
+                else:
+                    setattr(array[i], slot, make_projection(weight, k, n))
         self._table = ctypes.c_void_p()
         _check(self._lib.gw_moe_expert_table_create(array, len(experts), ctypes.byref(self._table)))
 

@@ -589,6 +589,31 @@ gw_status gw_moe_ep_tables(const int32_t* counts, const int32_t* physical, uint3
  * of this rank's j-th expert came from rank s, where they are rows home_base[s][j]..
  * of its expert-sorted order. */
 
+/* The same exchange with the down projection at the tokens' home: 14 times fewer bytes come back over
+ * NVLink (a 416-byte record of the quantised down input -- 352 B of E2M1, 44 scale bytes in K order,
+ * padding -- instead of a 5632-byte BF16 result row), for the price of every rank holding the down
+ * matrices of all 128 experts (a third of the expert weights).  The arithmetic per row is unchanged, so
+ * the layer's output is the same bits.
+ *   gw_moe_ep_run_gate_up      owner side: gate/up GEMM + GeGLU + FP4 quantisation over the records this
+ *                              rank received (arguments as gw_moe_ep_run_experts), then one activation
+ *                              record per row, in the same expert-major order, into
+ *                              `activation_records` (capacity x gw_moe_ep_activation_record_bytes(),
+ *                              a gw_ipc_alloc buffer that the peers read)
+ *   gw_moe_ep_finish_at_home   home side, after a barrier: fetches the record of each of this rank's
+ *                              8 x rows assignments from its owner (same addressing as
+ *                              gw_moe_ep_combine) into the routing workspace's own expert-sorted order,
+ *                              runs the grouped down GEMM over them with `down_table` (an expert table
+ *                              whose 128 entries carry the down projection; gate and up may be
+ *                              GW_STORAGE_ABSENT) and folds each token's eight rows in expert order. */
+size_t gw_moe_ep_activation_record_bytes(void);
+gw_status gw_moe_ep_run_gate_up(gw_moe_workspace* workspace, const void* records, const int32_t* offsets,
+                                uint32_t first_expert, uint32_t expert_count, uint32_t total_rows,
+                                const gw_expert_table* table, void* activation_records, void* stream);
+gw_status gw_moe_ep_finish_at_home(gw_moe_workspace* workspace, uint32_t rows, const int32_t* dest_rank,
+                                   const int32_t* dest_row0, void* const* peer_activation_records,
+                                   uint32_t capacity_rows, const gw_expert_table* down_table, void* output_bf16,
+                                   void* stream);
+
 /* Owner side: grouped gate/up GEMM + GeGLU + grouped down GEMM over the
  * records this rank received, grouped by expert as `offsets` (expert_count + 1
  * entries, on the device) says; `total_rows` is an upper bound known to the host

@@ -269,16 +269,17 @@ def _worker(rank: int, world: int, port: int, placement_name: str, exchange: str
         else:
             placement = getattr(ep.Placement, placement_name)(world)
         mine = placement.local_experts(rank)
-        by_id = bench.build_experts(gw, torch, device, expert_ids=mine)
+        by_id = bench.build_experts(gw, torch, device, expert_ids=None if exchange == "home" else mine)
         by_position = [None] * E
         for e in mine:
             by_position[placement.physical[e]] = by_id[e]
         local = tokens // world
-        if exchange in ("peer", "peer_pull", "peer_pull_nccl_sync"):
+        if exchange in ("peer", "peer_pull", "peer_pull_nccl_sync", "home"):
             # histograms and barriers through mailboxes in peer memory, or ("..._nccl_sync") through NCCL
             moe = ep.PeerMemoryExpertParallelMoe(by_position, [6.0 / 2688] * E, rank, world, local, 8 * tokens,
                                                  placement=placement, send_home=exchange == "peer",
-                                                 exchange="nccl" if exchange.endswith("nccl_sync") else "peer")
+                                                 exchange="nccl" if exchange.endswith("nccl_sync") else "peer",
+                                                 home_down=[w[2] for w in by_id] if exchange == "home" else None)
         else:
             backend = ep.DeviceBackend(by_position, local, 8 * tokens)
             moe = ep.ExpertParallelMoe(backend, rank, world, local, 8 * tokens, placement=placement)
@@ -295,8 +296,11 @@ def _worker(rank: int, world: int, port: int, placement_name: str, exchange: str
 
 
 @pytest.mark.parametrize("world,placement_name,exchange", [
+    # one rank: the whole exchange machinery (records, mailboxes, activation records) on a single GPU
+    (1, "contiguous", "peer_pull"), (1, "contiguous", "home"),
     (2, "contiguous", "nccl"), (2, "balanced", "nccl"), (2, "contiguous", "peer"), (2, "balanced", "peer"),
-    (2, "balanced", "peer_pull"), (2, "balanced", "peer_pull_nccl_sync"),
+    (2, "balanced", "peer_pull"), (2, "balanced", "peer_pull_nccl_sync"), (2, "balanced", "home"), (2, "contiguous", "home"),
+    (4, "interleaved", "home"), (8, "balanced", "home"),
     (4, "balanced", "peer_pull"), (4, "contiguous", "nccl"), (4, "interleaved", "peer"),
     (8, "balanced", "peer_pull"), (8, "interleaved", "nccl"), (8, "contiguous", "peer")])
 def test_ranks_equal_single_gpu(layer, tmp_path, world, placement_name, exchange):
