@@ -261,8 +261,10 @@ def run_expert_parallel(args, world: int, rank: int, local_rank: int):
     y = torch.empty((local_tokens, H), dtype=torch.bfloat16, device=device)
     stream = torch.cuda.current_stream()
 
-    def step():
+    def eager_step():
         layer.run(x, scores, expert_scales, local_tokens, out=y)
+
+    step = eager_step
 
     def timed(fn, steps):
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -283,12 +285,40 @@ def run_expert_parallel(args, world: int, rank: int, local_rank: int):
     torch.cuda.synchronize()
     if gw.kernel_error() != 0:
         raise SystemExit("tensor-core kernel reported an error during warm-up")
+    # The step reads nothing back and keeps its mailbox epochs on the device, so it can be captured once
+    # and replayed: the gaps between its dependent launches weigh more the less work a rank has.  Every rank
+    # decides together (a rank that replays and a rank that launches eagerly would still meet at the barriers).
+    config["launch"] = "eager"
+    if args.graph and args.exchange in ("home", "peer", "peer_pull") and args.sync == "peer":
+        captured = None
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                eager_step()
+            captured = graph
+        except Exception as error:          # noqa: BLE001  (capture is an optimisation; eager launches remain)
+            print(f"rank {rank}: step not captured ({error}); launching eagerly", file=sys.stderr)
+        ok = torch.tensor([1 if captured is not None else 0], device=device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if int(ok.item()) == 1:
+            step = captured.replay
+            config["launch"] = "CUDA graph replay of one step"
+            for _ in range(2):
+                step()
+            torch.cuda.synchronize()
+            if gw.kernel_error() != 0:
+                raise SystemExit("tensor-core kernel reported an error during graph replay")
     sampler = ClockSampler(local_rank) if rank == 0 else None
     time.sleep(0.25)
     t0 = time.time()
     launches_before = gw.launch_count()
     ms = timed(step, args.steps)
     launches = gw.launch_count() - launches_before          # this rank's kernels inside the timed region
+    if launches == 0 and config["launch"] != "eager":       # replayed: the library's launch sites ran at capture time
+        before = gw.launch_count()
+        eager_step()
+        torch.cuda.synchronize()
+        launches = (gw.launch_count() - before) * args.steps
     flops = tokens * TOPK * FLOPS_PER_ASSIGNMENT
     value = flops / (ms * 1e-3) / 1e12
 
@@ -334,7 +364,7 @@ def run_expert_parallel(args, world: int, rank: int, local_rank: int):
     for _ in range(max(3, args.steps // 4)):
         marks.clear()
         first = _record(torch, stream)
-        step()
+        eager_step()           # (stage events are recorded by eager launches, not by a replayed graph)
         torch.cuda.synchronize()
         previous = first
         for name, event in marks:
@@ -404,6 +434,9 @@ def main():
                              "activations and runs the down projection itself, with the down matrices of all experts "
                              "on every rank; peer_pull: the combine kernel pulls BF16 result rows; peer: the down "
                              "GEMM's epilogue stores them into the source rank) or through NCCL all-to-all")
+    parser.add_argument("--graph", type=int, default=1,
+                        help="expert-parallel run over peer memory: capture one step in a CUDA graph and replay it (1), "
+                             "or launch every step eagerly (0)")
     parser.add_argument("--sync", default="peer", choices=["peer", "nccl"],
                         help="expert-parallel run over peer memory: the histogram exchange and the two barriers of a "
                              "step through mailboxes in peer memory, or through NCCL (all-gather + two all-reduces)")

@@ -1000,18 +1000,27 @@ ep_dispatch_kernel(const uint4* __restrict__ input, const int32_t* __restrict__ 
 #pragma unroll
     for (int i = 0; i < kPerLane; ++i) {
       const uint32_t kb = lane + 32 * i;
-      if (kb >= kBlocks) continue;
-      const uint8_t scale_code = float_to_e4m3(inverse_scale * (amax[i] * rcp_approx_ftz(6.0F)));
-      const float block_scale = e4m3_to_float(scale_code);
-      const float factor =
-          block_scale == 0.0F ? 0.0F : rcp_approx_ftz(block_scale * rcp_approx_ftz(inverse_scale));
-      uint32_t out[2] = {0, 0};
+      const bool valid = kb < kBlocks;            // whole groups of four lanes are valid or not (176 = 4 * 44)
+      uint32_t scale_code = 0;
+      if (valid) {
+        scale_code = float_to_e4m3(inverse_scale * (amax[i] * rcp_approx_ftz(6.0F)));
+        const float block_scale = e4m3_to_float(uint8_t(scale_code));
+        const float factor =
+            block_scale == 0.0F ? 0.0F : rcp_approx_ftz(block_scale * rcp_approx_ftz(inverse_scale));
+        uint32_t out[2] = {0, 0};
 #pragma unroll
-      for (int k = 0; k < 8; ++k)
-        out[k / 4] |= uint32_t(float2_to_e2m1x2(__uint_as_float(raw[i][k] << 16) * factor,
-                                                __uint_as_float(raw[i][k] & 0xFFFF0000u) * factor)) << (8 * (k % 4));
-      *reinterpret_cast<uint2*>(record + kb * 8) = make_uint2(out[0], out[1]);
-      record[kHidden / 2 + kb] = scale_code;
+        for (int k = 0; k < 8; ++k)
+          out[k / 4] |= uint32_t(float2_to_e2m1x2(__uint_as_float(raw[i][k] << 16) * factor,
+                                                  __uint_as_float(raw[i][k] & 0xFFFF0000u) * factor)) << (8 * (k % 4));
+        *reinterpret_cast<uint2*>(record + kb * 8) = make_uint2(out[0], out[1]);
+      }
+      // the scale bytes of four neighbouring K16 blocks leave as one 32-bit store (byte stores over NVLink
+      // cost a transaction each)
+      const uint32_t base = lane & ~3u;
+      const uint32_t word = __shfl_sync(0xffffffffu, scale_code, base) | (__shfl_sync(0xffffffffu, scale_code, base + 1) << 8) |
+                            (__shfl_sync(0xffffffffu, scale_code, base + 2) << 16) |
+                            (__shfl_sync(0xffffffffu, scale_code, base + 3) << 24);
+      if (valid && (lane & 3u) == 0) *reinterpret_cast<uint32_t*>(record + kHidden / 2 + kb) = word;
     }
   }
 }
