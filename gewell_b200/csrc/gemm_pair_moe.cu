@@ -467,7 +467,12 @@ pair_moe_gate_up_kernel(const __grid_constant__ PairMoeParams p) {
             adst[0] = make_uint4(aw[0], aw[1], aw[2], aw[3]); adst[1] = make_uint4(aw[4], aw[5], aw[6], aw[7]);
           }
         }
-        if (l_ok) {
+        if (l_ok && p.records_out != nullptr) {
+          uint8_t* record = p.records_out + row * size_t(kEpActivationRecordBytes);
+          *reinterpret_cast<uint4*>(record + channel0 / 2) =
+              make_uint4(packed_words[0], packed_words[1], packed_words[2], packed_words[3]);
+          *reinterpret_cast<uint16_t*>(record + kInter / 2 + channel0 / 16) = uint16_t(scale_pair);
+        } else if (l_ok) {
           *reinterpret_cast<uint4*>(p.packed_out + row * size_t(kInter / 2) + channel0 / 2) =
               make_uint4(packed_words[0], packed_words[1], packed_words[2], packed_words[3]);
           const size_t region = size_t(u.first / 128 + u.e) * 128 * (kInter / 16);

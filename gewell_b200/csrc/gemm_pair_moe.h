@@ -29,6 +29,8 @@ struct PairMoeParams {
   // gate/up: packed E2M1 [capacity, 352] + tiled scales (same regions, K = 704), optional BF16 captures
   uint8_t* packed_out;
   uint8_t* scales_out;
+  uint8_t* records_out;            // optional: instead of packed_out / scales_out, one 416-byte record per row (352 B of
+                                   // E2M1, then the 44 scale bytes in K order) -- what a row's home rank fetches
   void* capture_gate_up;           // optional BF16 [capacity, 1408]
   void* capture_activated;         // optional BF16 [capacity, 704]
   // down: BF16 [capacity, 2816] or per-row destinations

@@ -358,7 +358,8 @@ constexpr int kStageFirst = 1, kStageDown = 2;
 gw_status run_experts(gw_moe_workspace* w, const void* input, const int32_t* gather_index, uint32_t gather_divisor,
                       const int32_t* offsets, uint32_t n, const gw_expert_table* table, void* down_out, cudaStream_t s,
                       const void* records = nullptr, const uint64_t* row_home = nullptr,
-                      int stages = kStageFirst | kStageDown) {
+                      int stages = kStageFirst | kStageDown, void* activation_records = nullptr,
+                      bool* exported = nullptr) {
   if (!table->all_nvfp4)
     return fail(GW_UNSUPPORTED, "this entry point runs NVFP4 (W4A4) expert tables only; mixed tables run through gw_moe_run");
   const auto* info = table->info.as<MoeExpertInfo>();
@@ -426,6 +427,11 @@ gw_status run_experts(gw_moe_workspace* w, const void* input, const int32_t* gat
     first.capacity = n;
     first.packed_out = w->packed_act.as<uint8_t>();
     first.scales_out = w->scales_act.as<uint8_t>();
+    // expert parallelism with the down projection elsewhere: the epilogue writes the travelling records itself
+    if (activation_records != nullptr && !(stages & kStageDown) && !w->capture) {
+      first.records_out = static_cast<uint8_t*>(activation_records);
+      if (exported) *exported = true;
+    }
     first.capture_gate_up = w->capture ? w->gate_up.data : nullptr;
     first.capture_activated = w->capture ? w->activated.data : nullptr;
     first.error = device_error_word();
@@ -862,12 +868,14 @@ gw_status gw_moe_ep_run_gate_up(gw_moe_workspace* w, const void* records, const 
   GW_CUDA_CHECK(launch_moe_keys_from_offsets(offsets, first_expert, expert_count, total_rows, w->sorted_keys,
                                              w->local_offsets, s),
                 "MoE keys from offsets");
-  const gw_status status =
-      run_experts(w, nullptr, nullptr, 1, w->local_offsets, total_rows, table, nullptr, s, records, nullptr, kStageFirst);
+  bool exported = false;
+  const gw_status status = run_experts(w, nullptr, nullptr, 1, w->local_offsets, total_rows, table, nullptr, s, records, nullptr,
+                                       kStageFirst, activation_records, &exported);
   if (status != GW_OK) return status;
-  GW_CUDA_CHECK(launch_ep_export_activations(w->packed_act.data, w->scales_act.as<uint8_t>(), w->sorted_keys, w->local_offsets,
-                                             total_rows, activation_records, s),
-                "export of the quantised activations");
+  if (!exported)      // plans whose gate/up epilogue does not write the records itself
+    GW_CUDA_CHECK(launch_ep_export_activations(w->packed_act.data, w->scales_act.as<uint8_t>(), w->sorted_keys,
+                                               w->local_offsets, total_rows, activation_records, s),
+                  "export of the quantised activations");
   w->mark(6, s);
   return GW_OK;
 }

@@ -965,18 +965,22 @@ ep_dispatch_kernel(const uint4* __restrict__ input, const int32_t* __restrict__ 
                    uint32_t capacity_rows, uint32_t* __restrict__ error) {
   griddep_launch();
   griddep_wait();     // results of earlier kernels in the stream are read from here on
-  // token-major like kernel 5b: one warp reads a token once and writes its eight records
-  constexpr uint32_t kBlocks = kHidden / 16;
-  constexpr int kPerLane = (kBlocks + 31) / 32;
-  const uint32_t token = (blockIdx.x * 256 + threadIdx.x) / 32, lane = threadIdx.x % 32;
+  // token-major like kernel 5b: two warps per token, each with one half of the row (88 K16 blocks, three
+  // per lane), read once for the token's eight records; twice the warps in flight cover the remote stores
+  constexpr uint32_t kBlocks = kHidden / 16;            // 176
+  constexpr uint32_t kHalfBlocks = kBlocks / 2;         // 88
+  constexpr int kPerLane = (kHalfBlocks + 31) / 32;     // 3
+  const uint32_t warp_index = (blockIdx.x * 256 + threadIdx.x) / 32, lane = threadIdx.x % 32;
+  const uint32_t token = warp_index / 2, half = warp_index % 2;
   if (token >= tokens) return;
   uint32_t raw[kPerLane][8];
   float amax[kPerLane];
 #pragma unroll
   for (int i = 0; i < kPerLane; ++i) {
-    const uint32_t kb = lane + 32 * i;
+    const uint32_t local = lane + 32 * i;
+    const uint32_t kb = half * kHalfBlocks + local;
     amax[i] = 0.0F;
-    if (kb < kBlocks) {
+    if (local < kHalfBlocks) {
       const uint4 a = input[2 * (size_t(token) * kBlocks + kb)], b = input[2 * (size_t(token) * kBlocks + kb) + 1];
       raw[i][0] = a.x; raw[i][1] = a.y; raw[i][2] = a.z; raw[i][3] = a.w;
       raw[i][4] = b.x; raw[i][5] = b.y; raw[i][6] = b.z; raw[i][7] = b.w;
@@ -993,14 +997,15 @@ ep_dispatch_kernel(const uint4* __restrict__ input, const int32_t* __restrict__ 
     const float inverse_scale = inverse_input_scale[e];
     const uint32_t dest_row = uint32_t(dest_row0[e] + inverse[assignment] - offsets[e]);
     if (dest_row >= capacity_rows) {          // the owner's buffer is too small: report, never write outside it
-      if (lane == 0 && error != nullptr) atomicCAS(error, 0u, 0x70000000u | uint32_t(e));
+      if (lane == 0 && half == 0 && error != nullptr) atomicCAS(error, 0u, 0x70000000u | uint32_t(e));
       continue;
     }
     uint8_t* record = peer_records[dest_rank[e]] + size_t(dest_row) * kRecordBytes;
 #pragma unroll
     for (int i = 0; i < kPerLane; ++i) {
-      const uint32_t kb = lane + 32 * i;
-      const bool valid = kb < kBlocks;            // whole groups of four lanes are valid or not (176 = 4 * 44)
+      const uint32_t local = lane + 32 * i;
+      const uint32_t kb = half * kHalfBlocks + local;
+      const bool valid = local < kHalfBlocks;     // whole groups of four lanes are valid or not (88 = 4 * 22)
       uint32_t scale_code = 0;
       if (valid) {
         scale_code = float_to_e4m3(inverse_scale * (amax[i] * rcp_approx_ftz(6.0F)));
@@ -1341,7 +1346,7 @@ cudaError_t launch_ep_dispatch(const void* input, const int32_t* keys, const int
                                const float* inverse_input_scale, const int32_t* dest_rank, const int32_t* dest_row0,
                                void* const* peer_records, uint32_t tokens, uint32_t capacity_rows, uint32_t* error,
                                cudaStream_t stream) {
-  launch_pdl(ep_dispatch_kernel, blocks_for(size_t(tokens) * 32), 256, stream, 
+  launch_pdl(ep_dispatch_kernel, blocks_for(size_t(tokens) * 64), 256, stream, 
       static_cast<const uint4*>(input), keys, inverse, offsets, inverse_input_scale, dest_rank, dest_row0,
       reinterpret_cast<uint8_t* const*>(peer_records), tokens, capacity_rows, error);
   return cudaGetLastError();
