@@ -590,7 +590,10 @@ def main():
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "nvfp4 (e2m1 x e2m1, fp32 accumulate)", "data": "synthetic",
             "config": config, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
-            "roofline": roofline, "cpu_baseline": cpu, "config5_on_one_gpu": same_as_ep}
+            "roofline": roofline, "cpu_baseline": cpu, "config5_on_one_gpu": same_as_ep,
+            "scaling_note": "this line is config 4 (T = 8192, uniform routing); the lines at 2, 4 and 8 GPUs are config 5 "
+                            "(T = 32768, Zipf(1.2) routing, total work fixed): their like-for-like one-GPU figure is "
+                            "config5_on_one_gpu"}
     print(json.dumps(line))
 
 

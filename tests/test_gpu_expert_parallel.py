@@ -245,6 +245,73 @@ def test_undersized_receive_capacity_is_reported_not_overrun(layer):
     assert torch.isfinite(out.float()).all()
 
 
+@pytest.mark.parametrize("tokens", [40, 900])
+def test_activation_records_and_home_finish_on_one_rank(layer, tokens):
+    """The exchange with the down projection at the tokens' home, this GPU being the only rank, through
+    the C ABI: the travelling 416-byte activation records hold exactly the layer's quantised down input
+    (352 bytes of E2M1, 44 scale bytes in K order), whichever kernel writes them (the gate/up epilogue
+    for large batches, the export kernel for small ones); fetched back and finished with a table that
+    holds only down matrices they give the layer's output bit for bit; undersized buffers are reported,
+    not overrun."""
+    from oracle import nvfp4 as onv
+    gw, experts, table = layer
+    lib, check = gw.lib, gw.ops._check
+    stream = torch.cuda.current_stream().cuda_stream
+    x, scores, scales = (t.cuda() for t in _inputs(tokens, 62, True))
+    ws = gw.MoeWorkspace(tokens)
+    ws.capture(True)
+    y = torch.empty((tokens, H), dtype=torch.bfloat16, device="cuda")
+    ws.run(x, scores, scales, table, y, tokens)
+    torch.cuda.synchronize()
+    activated = ws.activated_capture().float().cpu().numpy()             # [8 * tokens, 704] in sorted order
+    record_bytes = int(lib.gw_moe_ep_activation_record_bytes())
+    assert record_bytes == 416
+    route_ws, expert_ws = gw.MoeWorkspace(tokens), gw.MoeWorkspace(tokens + 16)
+    capacity = 8 * (tokens + 16)
+    records = torch.full((capacity * 1584,), 0xFF, dtype=torch.uint8, device="cuda")
+    act_records = torch.full((capacity * record_bytes + 64,), 0xEE, dtype=torch.uint8, device="cuda")
+    route_ws.dispatch(scores, scales, tokens)
+    offsets, _, _, _ = route_ws.routing_state(tokens)
+    counts = (offsets[1:] - offsets[:-1]).contiguous()
+    physical = torch.arange(E, dtype=torch.int32, device="cuda")
+    dest_rank = torch.zeros(E, dtype=torch.int32, device="cuda")
+    row0 = torch.zeros(E, dtype=torch.int32, device="cuda")
+    local_offsets = torch.zeros(E + 1, dtype=torch.int32, device="cuda")
+    check(lib.gw_moe_ep_tables(counts.data_ptr(), physical.data_ptr(), 0, 1, row0.data_ptr(), local_offsets.data_ptr(),
+                               None, None, stream))
+    inverse_scales = (torch.ones(E) / torch.full((E,), 6.0 / 2688)).cuda()
+    record_table = torch.tensor([records.data_ptr()], dtype=torch.int64, device="cuda")
+    act_table = torch.tensor([act_records.data_ptr()], dtype=torch.int64, device="cuda")
+    check(lib.gw_moe_ep_dispatch(route_ws._ws, x.data_ptr(), tokens, inverse_scales.data_ptr(), dest_rank.data_ptr(),
+                                 row0.data_ptr(), record_table.data_ptr(), capacity, stream))
+    check(lib.gw_moe_ep_run_gate_up(expert_ws._ws, records.data_ptr(), local_offsets.data_ptr(), 0, E, capacity,
+                                    table.handle, act_records.data_ptr(), stream))
+    torch.cuda.synchronize()
+    assert gw.kernel_error() == 0
+    n = 8 * tokens
+    host = act_records[:n * record_bytes].reshape(n, record_bytes).cpu().numpy()
+    assert torch.all(act_records[capacity * record_bytes:] == 0xEE), "wrote beyond the record buffer"
+    expected = onv.quantize_activations(activated, 16.0 / 2688, rcp_fn=gw.rcp_approx)     # the experts' down input scale
+    assert np.array_equal(host[:, :352], expected.packed[:n])
+    assert np.array_equal(host[:, 352:396], expected.scales_linear)
+    # the home side: a table with the down matrices only
+    home_table = gw.ExpertTable([(None, None, e[2]) for e in experts])
+    out = torch.empty((tokens, H), dtype=torch.bfloat16, device="cuda")
+    check(lib.gw_moe_ep_finish_at_home(route_ws._ws, tokens, dest_rank.data_ptr(), row0.data_ptr(), act_table.data_ptr(),
+                                       capacity, home_table.handle, out.data_ptr(), stream))
+    torch.cuda.synchronize()
+    assert gw.kernel_error() == 0
+    assert np.array_equal(bits(out), bits(y))
+    # a table without down matrices is refused; an undersized record buffer is reported, never read beyond
+    with pytest.raises(gw.GewellInvalidArgument):
+        check(lib.gw_moe_ep_finish_at_home(route_ws._ws, tokens, dest_rank.data_ptr(), row0.data_ptr(), act_table.data_ptr(),
+                                           capacity, gw.ExpertTable([(e[0], e[1], None) for e in experts]).handle,
+                                           out.data_ptr(), stream))
+    check(lib.gw_moe_ep_finish_at_home(route_ws._ws, tokens, dest_rank.data_ptr(), row0.data_ptr(), act_table.data_ptr(),
+                                       8, home_table.handle, out.data_ptr(), stream))
+    assert gw.kernel_error() >> 28 == 7
+
+
 def _free_port() -> int:
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
