@@ -236,7 +236,7 @@ gw_status gw_nvfp4_plan_create(uint32_t rows, uint32_t input_width, uint32_t out
       return fail(GW_CUDA_ERROR, std::string("plan: tile counters of the K split: ") + cudaGetErrorString(counters));
     }
   }
-  if (p->descriptors.split_counters) p->total_bytes += align_up(dense_split_bytes(rows, output_width), 256);
+  if (p->descriptors.split_counters) p->total_bytes += align_up(dense_split_bytes(p->descriptors.tuning, rows, output_width), 256);
   *plan = p;
   return GW_OK;
 }
@@ -301,6 +301,7 @@ gw_status gw_fp8_pack_weights(const void* weights_bf16, uint32_t output_width, u
 struct gw_fp8_plan {
   uint32_t rows, input_width, output_width;
   bool channel_scales;
+  int gemv_rows = 0;      // GW_FP8_GEMV_ROWS, read when the plan is created
   size_t split_offset, total_bytes;
   DenseDescriptors descriptors;
 };
@@ -319,6 +320,7 @@ gw_status gw_fp8_plan_create(uint32_t rows, uint32_t input_width, uint32_t outpu
   p->input_width = input_width;
   p->output_width = output_width;
   p->channel_scales = channel_scales != 0;
+  if (const char* gemv_env = std::getenv("GW_FP8_GEMV_ROWS")) p->gemv_rows = std::atoi(gemv_env);
   p->split_offset = align_up(size_t(rows) * input_width, 256);
   // Decode shapes split the K loop evenly over the SMs; that needs per-tile counters owned
   // by the plan and room for FP32 partial tiles in the scratch.  Without a usable device
@@ -334,7 +336,7 @@ gw_status gw_fp8_plan_create(uint32_t rows, uint32_t input_width, uint32_t outpu
       return fail(GW_CUDA_ERROR, std::string("plan: tile counters of the K split: ") + cudaGetErrorString(counters));
     }
   }
-  if (p->descriptors.split_counters) p->total_bytes += align_up(dense_split_bytes(rows, output_width), 256);
+  if (p->descriptors.split_counters) p->total_bytes += align_up(dense_split_bytes(p->descriptors.tuning, rows, output_width), 256);
   *plan = p;
   return GW_OK;
 }
@@ -363,9 +365,7 @@ gw_status gw_fp8_plan_run(gw_fp8_plan* plan, const void* input_bf16, const uint8
   // quantised inside the kernel).  Measured on B200 it is slower than the tensor-core path
   // (55 us against 50 us for one row of the 43008 x 5376 projection, 82 us for two), so it is
   // off unless GW_FP8_GEMV_ROWS names a row limit.
-  const char* gemv_env = std::getenv("GW_FP8_GEMV_ROWS");
-  const int gemv_rows = gemv_env ? std::atoi(gemv_env) : 0;
-  if (transform == GW_TRANSFORM_IDENTITY && int(plan->rows) <= gemv_rows && gemv_fp8_supports(plan->rows, plan->input_width) &&
+  if (transform == GW_TRANSFORM_IDENTITY && int(plan->rows) <= plan->gemv_rows && gemv_fp8_supports(plan->rows, plan->input_width) &&
       aligned(input_bf16, 2)) {
     GW_CUDA_CHECK(launch_gemv_fp8(input_bf16, plan->rows, weight_data, 1.0F / input_scale, alpha,
                                   plan->channel_scales ? channel_scales : nullptr, plan->input_width, plan->output_width,
@@ -406,7 +406,7 @@ gw_status gw_bf16_plan_create(uint32_t rows, uint32_t input_width, uint32_t outp
   p->total_bytes = 0;
   const cudaError_t status = p->descriptors.allocate_split_counters(rows, output_width);
   if (status == cudaSuccess && p->descriptors.split_counters) {
-    p->total_bytes = align_up(dense_split_bytes(rows, output_width), 256);
+    p->total_bytes = align_up(dense_split_bytes(p->descriptors.tuning, rows, output_width), 256);
   } else if (status != cudaSuccess) {
     (void)cudaGetLastError();
     if (status != cudaErrorNoDevice && status != cudaErrorInsufficientDriver) {

@@ -6,40 +6,44 @@
 
 namespace gw {
 
-bool dense_uses_swap_form(uint32_t rows) {
-  if (const char* forced = std::getenv("GW_DENSE_FORM")) {   // tuning override: "swap" / "direct"
-    if (forced[0] == 's' && rows <= 128) return true;
-    if (forced[0] == 'd') return false;
-  }
+DenseTuning DenseTuning::from_environment() {
+  DenseTuning tuning;
+  if (const char* forced = std::getenv("GW_DENSE_FORM")) tuning.form = forced[0];
+  if (const char* forced = std::getenv("GW_DENSE_BLOCK_N")) tuning.block_n = std::atoi(forced);
+  tuning.no_pair = std::getenv("GW_DENSE_NO_PAIR") != nullptr;
+  tuning.no_split = std::getenv("GW_DENSE_NO_SPLIT") != nullptr;
+  return tuning;
+}
+
+bool dense_uses_swap_form(const DenseTuning& tuning, uint32_t rows) {
+  if (tuning.form == 's' && rows <= 128) return true;
+  if (tuning.form == 'd') return false;
   return rows <= 128;
 }
 
-int dense_block_n(uint32_t rows) {
-  if (dense_uses_swap_form(rows)) return rows <= 32 ? 32 : rows <= 64 ? 64 : 128;
-  if (const char* forced = std::getenv("GW_DENSE_BLOCK_N")) {   // tuning override
-    const int v = std::atoi(forced);
-    if (v == 128 || v == 256) return v;
-  }
+int dense_block_n(const DenseTuning& tuning, uint32_t rows) {
+  if (dense_uses_swap_form(tuning, rows)) return rows <= 32 ? 32 : rows <= 64 ? 64 : 128;
+  if (tuning.block_n == 128 || tuning.block_n == 256) return tuning.block_n;
   return 256;
 }
 
 namespace {
-size_t split_counter_bytes(uint32_t rows, uint32_t n) {
-  const int block_n = dense_block_n(rows);
+size_t split_counter_bytes(const DenseTuning& tuning, uint32_t rows, uint32_t n) {
+  const int block_n = dense_block_n(tuning, rows);
   const size_t tiles = size_t((n + 127) / 128) * ((rows + block_n - 1) / block_n);
   return align_up(tiles * sizeof(int32_t), 256);
 }
 }  // namespace
 
-size_t dense_split_bytes(uint32_t rows, uint32_t n) {
+size_t dense_split_bytes(const DenseTuning& tuning, uint32_t rows, uint32_t n) {
   (void)n;
-  if (!dense_uses_swap_form(rows) || std::getenv("GW_DENSE_NO_SPLIT")) return 0;
-  return size_t(2) * sm_count() * 128 * dense_block_n(rows) * sizeof(float);
+  if (!dense_uses_swap_form(tuning, rows) || tuning.no_split) return 0;
+  return size_t(2) * sm_count() * 128 * dense_block_n(tuning, rows) * sizeof(float);
 }
 
 cudaError_t DenseDescriptors::allocate_split_counters(uint32_t rows, uint32_t n) {
-  if (dense_split_bytes(rows, n) == 0) return cudaSuccess;
-  const size_t bytes = split_counter_bytes(rows, n);
+  if (dense_split_bytes(tuning, rows, n) == 0) return cudaSuccess;
+  const size_t bytes = split_counter_bytes(tuning, rows, n);
   cudaError_t status = cudaMalloc(&split_counters, bytes);
   if (status == cudaSuccess) status = cudaMemset(split_counters, 0, bytes);
   return status;
@@ -50,8 +54,9 @@ DenseDescriptors::~DenseDescriptors() {
 }
 
 gw_status launch_dense(const DenseProblem& q, DenseDescriptors* cache, cudaStream_t stream) {
-  const bool swap = dense_uses_swap_form(q.rows);
-  const int block_n = dense_block_n(q.rows);
+  const DenseTuning& tuning = cache->tuning;
+  const bool swap = dense_uses_swap_form(tuning, q.rows);
+  const int block_n = dense_block_n(tuning, q.rows);
   const bool fp4 = q.kind == GemmKind::nvfp4;
   const uint64_t row_bytes = fp4 ? q.k / 2 : (q.kind == GemmKind::bf16 ? uint64_t(2) * q.k : q.k);
   std::string error;
@@ -72,7 +77,7 @@ gw_status launch_dense(const DenseProblem& q, DenseDescriptors* cache, cudaStrea
     cache->activations = q.activations;
   }
   // NVFP4 prefill: the CTA-pair kernel (each CTA stages half of the weight tile) unless disabled
-  if (fp4 && single_box && q.rows >= 256 && !std::getenv("GW_DENSE_NO_PAIR")) {
+  if (fp4 && single_box && q.rows >= 256 && !tuning.no_pair) {
     if (cache->weight_half != q.weight) {
       if (!encode_tensor_map_2d(&cache->weight_half_map, q.weight, row_bytes, q.n, 128, &error))
         return fail(GW_CUDA_ERROR, "weight descriptor: " + error);

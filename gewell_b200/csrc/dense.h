@@ -8,7 +8,20 @@
 
 namespace gw {
 
+// Tuning overrides of the dense projections, read from the environment once per plan (when its
+// descriptors are first used), not at every call:
+//   GW_DENSE_FORM=swap|direct, GW_DENSE_BLOCK_N=128|256   operand roles / column tile
+//   GW_DENSE_NO_PAIR=1    NVFP4 projections with >= 256 rows stay on the single-CTA kernel
+//   GW_DENSE_NO_SPLIT=1   decode-shaped plans run whole tiles per CTA
+struct DenseTuning {
+  char form = 0;            // 's', 'd' or 0
+  int block_n = 0;
+  bool no_pair = false, no_split = false;
+  static DenseTuning from_environment();
+};
+
 struct DenseDescriptors {          // re-encoded only when a pointer changes
+  DenseTuning tuning = DenseTuning::from_environment();
   const void* weight = nullptr;
   const void* activations = nullptr;
   const void* weight_scales = nullptr;
@@ -40,11 +53,11 @@ struct DenseProblem {
 };
 
 // true: weights on the 128-lane operand and tokens on the column operand.
-bool dense_uses_swap_form(uint32_t rows);
-int dense_block_n(uint32_t rows);
+bool dense_uses_swap_form(const DenseTuning& tuning, uint32_t rows);
+int dense_block_n(const DenseTuning& tuning, uint32_t rows);
 
 // Bytes of split workspace a projection of this shape can use (0: none).
-size_t dense_split_bytes(uint32_t rows, uint32_t n);
+size_t dense_split_bytes(const DenseTuning& tuning, uint32_t rows, uint32_t n);
 
 gw_status launch_dense(const DenseProblem& problem, DenseDescriptors* cache, cudaStream_t stream);
 

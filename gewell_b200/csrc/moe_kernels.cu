@@ -10,6 +10,7 @@
 // builds the bitmaps, kernel 2 scans the per-chunk counts, kernel 3 scatters.
 #include "common.cuh"
 #include "moe_kernels.h"
+#include "ptx.cuh"
 
 namespace gw {
 namespace {
@@ -949,30 +950,37 @@ ep_exchange_kernel(const int32_t* __restrict__ payload, uint32_t count, uint8_t*
 //    is single GPU).  A travelling row is a 1584-byte record: 1408 bytes of
 //    packed E2M1 (K = 2816) followed by its 176 E4M3 block scales in K order.
 //    The dispatch kernel quantises a routed row with the destination expert's
-//    input scale (same arithmetic as kernel 5) and stores the record straight
-//    into the owning rank's buffer; the owner re-tiles the scale bytes locally
+//    input scale (same arithmetic as kernel 5), builds the record in shared memory
+//    and sends it into the owning rank's buffer with one bulk copy (shared ->
+//    global, no cluster fan-out); the owner re-tiles the scale bytes locally
 //    and runs the grouped GEMMs on the records in place; the combine kernel
 //    reads the eight result rows of a token from their owners' buffers and folds
-//    them as kernel 6 does.  All remote accesses are plain loads and stores.
+//    them as kernel 6 does.  All other remote accesses are plain loads and stores.
 // ---------------------------------------------------------------------------
 constexpr uint32_t kRecordBytes = kHidden / 2 + kHidden / 16;   // 1584
+static_assert(kRecordBytes % 16 == 0, "a record leaves as one bulk copy: 16-byte granules");
 
-__global__ void __launch_bounds__(256)
+constexpr uint32_t kDispatchTokensPerBlock = 2;
+
+__global__ void __launch_bounds__(64 * kDispatchTokensPerBlock)
 ep_dispatch_kernel(const uint4* __restrict__ input, const int32_t* __restrict__ keys,
                    const int32_t* __restrict__ inverse, const int32_t* __restrict__ offsets,
                    const float* __restrict__ inverse_input_scale, const int32_t* __restrict__ dest_rank,
                    const int32_t* __restrict__ dest_row0, uint8_t* const* __restrict__ peer_records, uint32_t tokens,
                    uint32_t capacity_rows, uint32_t* __restrict__ error) {
+  // The eight records of a token are built in shared memory and leave as eight bulk copies of 1584 bytes
+  // each: the copy engine keeps the NVLink writes in flight, the warps do not wait on remote stores.
+  __shared__ __align__(16) uint8_t staged[kDispatchTokensPerBlock][kTopK][kRecordBytes];
   griddep_launch();
   griddep_wait();     // results of earlier kernels in the stream are read from here on
   // token-major like kernel 5b: two warps per token, each with one half of the row (88 K16 blocks, three
-  // per lane), read once for the token's eight records; twice the warps in flight cover the remote stores
+  // per lane), read once for the token's eight records
   constexpr uint32_t kBlocks = kHidden / 16;            // 176
   constexpr uint32_t kHalfBlocks = kBlocks / 2;         // 88
   constexpr int kPerLane = (kHalfBlocks + 31) / 32;     // 3
-  const uint32_t warp_index = (blockIdx.x * 256 + threadIdx.x) / 32, lane = threadIdx.x % 32;
-  const uint32_t token = warp_index / 2, half = warp_index % 2;
-  if (token >= tokens) return;
+  const uint32_t slot = threadIdx.x / 64, half = (threadIdx.x / 32) % 2, lane = threadIdx.x % 32;
+  const uint32_t token = blockIdx.x * kDispatchTokensPerBlock + slot;
+  if (token >= tokens) return;                          // both warps of a token leave together
   uint32_t raw[kPerLane][8];
   float amax[kPerLane];
 #pragma unroll
@@ -992,40 +1000,38 @@ ep_dispatch_kernel(const uint4* __restrict__ input, const int32_t* __restrict__ 
     }
   }
   for (int j = 0; j < kTopK; ++j) {
-    const uint32_t assignment = token * kTopK + j;
-    const int32_t e = keys[assignment];
-    const float inverse_scale = inverse_input_scale[e];
-    const uint32_t dest_row = uint32_t(dest_row0[e] + inverse[assignment] - offsets[e]);
-    if (dest_row >= capacity_rows) {          // the owner's buffer is too small: report, never write outside it
-      if (lane == 0 && half == 0 && error != nullptr) atomicCAS(error, 0u, 0x70000000u | uint32_t(e));
-      continue;
-    }
-    uint8_t* record = peer_records[dest_rank[e]] + size_t(dest_row) * kRecordBytes;
+    const float inverse_scale = inverse_input_scale[keys[token * kTopK + j]];
+    uint8_t* record = staged[slot][j];
 #pragma unroll
     for (int i = 0; i < kPerLane; ++i) {
       const uint32_t local = lane + 32 * i;
       const uint32_t kb = half * kHalfBlocks + local;
-      const bool valid = local < kHalfBlocks;     // whole groups of four lanes are valid or not (88 = 4 * 22)
-      uint32_t scale_code = 0;
-      if (valid) {
-        scale_code = float_to_e4m3(inverse_scale * (amax[i] * rcp_approx_ftz(6.0F)));
-        const float block_scale = e4m3_to_float(uint8_t(scale_code));
-        const float factor =
-            block_scale == 0.0F ? 0.0F : rcp_approx_ftz(block_scale * rcp_approx_ftz(inverse_scale));
-        uint32_t out[2] = {0, 0};
+      if (local >= kHalfBlocks) continue;
+      const uint8_t scale_code = float_to_e4m3(inverse_scale * (amax[i] * rcp_approx_ftz(6.0F)));
+      const float block_scale = e4m3_to_float(scale_code);
+      const float factor =
+          block_scale == 0.0F ? 0.0F : rcp_approx_ftz(block_scale * rcp_approx_ftz(inverse_scale));
+      uint32_t out[2] = {0, 0};
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
-          out[k / 4] |= uint32_t(float2_to_e2m1x2(__uint_as_float(raw[i][k] << 16) * factor,
-                                                  __uint_as_float(raw[i][k] & 0xFFFF0000u) * factor)) << (8 * (k % 4));
-        *reinterpret_cast<uint2*>(record + kb * 8) = make_uint2(out[0], out[1]);
-      }
-      // the scale bytes of four neighbouring K16 blocks leave as one 32-bit store (byte stores over NVLink
-      // cost a transaction each)
-      const uint32_t base = lane & ~3u;
-      const uint32_t word = __shfl_sync(0xffffffffu, scale_code, base) | (__shfl_sync(0xffffffffu, scale_code, base + 1) << 8) |
-                            (__shfl_sync(0xffffffffu, scale_code, base + 2) << 16) |
-                            (__shfl_sync(0xffffffffu, scale_code, base + 3) << 24);
-      if (valid && (lane & 3u) == 0) *reinterpret_cast<uint32_t*>(record + kHidden / 2 + kb) = word;
+      for (int k = 0; k < 8; ++k)
+        out[k / 4] |= uint32_t(float2_to_e2m1x2(__uint_as_float(raw[i][k] << 16) * factor,
+                                                __uint_as_float(raw[i][k] & 0xFFFF0000u) * factor)) << (8 * (k % 4));
+      *reinterpret_cast<uint2*>(record + kb * 8) = make_uint2(out[0], out[1]);
+      record[kHidden / 2 + kb] = scale_code;
+    }
+  }
+  ptx::fence_proxy_async_smem();                        // the copy engine reads what these threads wrote
+  asm volatile("bar.sync %0, 64;" ::"r"(int(slot) + 1) : "memory");     // the token's two warps
+  if (half == 0 && lane < kTopK) {
+    const uint32_t assignment = token * kTopK + lane;
+    const int32_t e = keys[assignment];
+    const uint32_t dest_row = uint32_t(dest_row0[e] + inverse[assignment] - offsets[e]);
+    if (dest_row >= capacity_rows) {          // the owner's buffer is too small: report, never write outside it
+      if (error != nullptr) atomicCAS(error, 0u, 0x70000000u | uint32_t(e));
+    } else {
+      ptx::bulk_store(peer_records[dest_rank[e]] + size_t(dest_row) * kRecordBytes, staged[slot][lane], kRecordBytes);
+      ptx::bulk_store_commit();
+      ptx::bulk_store_wait_all();
     }
   }
 }
@@ -1346,7 +1352,8 @@ cudaError_t launch_ep_dispatch(const void* input, const int32_t* keys, const int
                                const float* inverse_input_scale, const int32_t* dest_rank, const int32_t* dest_row0,
                                void* const* peer_records, uint32_t tokens, uint32_t capacity_rows, uint32_t* error,
                                cudaStream_t stream) {
-  launch_pdl(ep_dispatch_kernel, blocks_for(size_t(tokens) * 64), 256, stream, 
+  launch_pdl(ep_dispatch_kernel, (tokens + kDispatchTokensPerBlock - 1) / kDispatchTokensPerBlock,
+             64 * kDispatchTokensPerBlock, stream,
       static_cast<const uint4*>(input), keys, inverse, offsets, inverse_input_scale, dest_rank, dest_row0,
       reinterpret_cast<uint8_t* const*>(peer_records), tokens, capacity_rows, error);
   return cudaGetLastError();

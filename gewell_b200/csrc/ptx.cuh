@@ -103,6 +103,18 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, 
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gmem_src)), "r"(bytes), "r"(smem_u32(bar))
       : "memory");
 }
+// Untiled bulk copy shared -> global (this GPU's memory or a peer's); both addresses 16-byte
+// aligned, size a multiple of 16 bytes.  The writing threads run fence_proxy_async_smem()
+// before the issuing thread starts the copy; the issuing thread commits the group and waits
+// for it (bulk_store_wait_all) before the shared memory is reused or the kernel ends.
+__device__ __forceinline__ void bulk_store(void* gmem_dst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+               ::"l"(reinterpret_cast<uint64_t>(gmem_dst)), "r"(smem_u32(smem_src)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// every committed bulk store of this thread has been written (not only read out of shared memory)
+__device__ __forceinline__ void bulk_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // A tensor map that lives in global memory and was written by the host needs
 // this acquire before the first TMA of the thread that uses it.
 __device__ __forceinline__ void tensormap_acquire(const CUtensorMap* map) {
