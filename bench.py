@@ -330,7 +330,8 @@ def run_expert_parallel(args, world: int, rank: int, local_rank: int):
     def layer_pass(dx, ds, dy, rows, _stream):
         layer.run(dx, ds, expert_scales, rows, out=dy)
 
-    runner = gw.HostStagedMoe(None, None, expert_scales, local_tokens, H, experts=E, depth=3, run=layer_pass)
+    runner = gw.HostStagedMoe(None, None, expert_scales, local_tokens, H, experts=E, depth=3, run=layer_pass,
+                              capture=config["launch"] != "eager")
     for i in range(3):
         runner.submit(hx, hs, hy[i % 3], local_tokens)
     runner.synchronize()
@@ -397,7 +398,8 @@ def run_expert_parallel(args, world: int, rank: int, local_rank: int):
                 "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                         "h2d_bytes_per_step": world * (hx.numel() + hs.numel()) * 2,
                         "d2h_bytes_per_step": world * hy[0].numel() * 2, "ms_per_step": e2e_ms,
-                        "note": "uploads, kernels and downloads of consecutive steps overlap (gewell_b200.HostStagedMoe)"},
+                        "note": "uploads, kernels and downloads of consecutive steps overlap (gewell_b200.HostStagedMoe); "
+                                "the layer pass of each ring slot is " + ("a CUDA graph replay" if config["launch"] != "eager" else "launched eagerly")},
                 # counted by the library at its launch sites on rank 0 (every rank launches the same
                 # sequence; the collectives are NCCL's and not counted)
                 "gpu_launches": launches * world, "clocks": clocks,

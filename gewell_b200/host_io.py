@@ -37,10 +37,14 @@ from .ops import ExpertTable, MoeWorkspace, _check, _library
 
 class HostStagedMoe:
     def __init__(self, workspace: MoeWorkspace, table: ExpertTable, expert_scales: torch.Tensor, max_rows: int,
-                 hidden: int, experts: int = 128, depth: int = 2, device=None, run=None):
+                 hidden: int, experts: int = 128, depth: int = 2, device=None, run=None, capture: bool = False):
         """`run(x, scores, y, rows, stream)`, when given, replaces `workspace.run` as the layer pass (the
         expert-parallel layers have their own entry point); it is called with the compute stream current
-        and must issue all of its work on that stream."""
+        and must issue all of its work on that stream.  With `capture`, the launches of `run` are recorded
+        once per ring slot and row count in a CUDA graph and replayed afterwards (a pass of the
+        expert-parallel layer is some thirty dependent launches: issued one by one from Python they, not
+        the GPU, bound short passes); `run` must then read nothing back to the host and must have been
+        called at least once before (its lazy initialisation cannot be recorded)."""
         if depth < 1:
             raise ValueError("depth must be at least 1")
         if not torch.cuda.is_available():
@@ -48,6 +52,8 @@ class HostStagedMoe:
         self.workspace, self.table, self.expert_scales = workspace, table, expert_scales
         self.max_rows, self.hidden, self.experts, self.depth = max_rows, hidden, experts, depth
         self._run = run
+        self._capture = bool(capture) and run is not None
+        self._graphs = {}
         device = device if device is not None else expert_scales.device
         self.device = device
         self._native = None
@@ -104,7 +110,7 @@ class HostStagedMoe:
         ticket = self._submitted
         slot = ticket % self.depth
         x, scores, y = self._x[slot], self._scores[slot], self._y[slot]
-        if rows > 0:
+        if rows > 0 or self._run is not None:     # a rank without rows still serves its experts in a custom pass
             with torch.cuda.stream(self.upload):
                 if self._computed[slot] is not None:        # the slot's previous pass no longer reads its inputs
                     self.upload.wait_event(self._computed[slot])
@@ -116,7 +122,15 @@ class HostStagedMoe:
                 self.compute.wait_event(uploaded)
                 if self._downloaded[slot] is not None:      # the slot's previous output has left the device
                     self.compute.wait_event(self._downloaded[slot])
-                if self._run is not None:
+                if self._capture:
+                    graph = self._graphs.get((slot, rows))
+                    if graph is None:
+                        graph = torch.cuda.CUDAGraph()
+                        with torch.cuda.graph(graph, stream=self.compute, capture_error_mode="thread_local"):
+                            self._run(x, scores, y, rows, self.compute)
+                        self._graphs[(slot, rows)] = graph
+                    graph.replay()
+                elif self._run is not None:
                     self._run(x, scores, y, rows, self.compute)
                 else:
                     self.workspace.run(x, scores, self.expert_scales, self.table, y, rows, stream=self.compute)

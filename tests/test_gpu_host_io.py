@@ -86,3 +86,46 @@ def test_host_staged_argument_checks(layer):
         runner.wait_for(0)                                                      # nothing submitted
     with pytest.raises(ValueError):
         gw.HostStagedMoe(ws, table, scales, 8, H, depth=0)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("capture", [False, True])
+def test_host_staged_custom_pass(layer, capture):
+    """A caller's own layer pass (the expert-parallel layers use this hook) staged through the ring,
+    launched eagerly or recorded once per ring slot and row count and replayed."""
+    gw, table, scales, _ = layer
+    device = torch.device("cuda")
+    max_rows = 64
+    ws = gw.MoeWorkspace(max_rows)
+    calls = []
+
+    def layer_pass(x, s, y, rows, stream):
+        calls.append(rows)
+        if rows:
+            ws.run(x, s, scales, table, y, rows, stream=stream)
+
+    warm = torch.zeros((max_rows, H), dtype=torch.bfloat16, device=device)
+    ws.run(warm, torch.zeros((max_rows, E), dtype=torch.bfloat16, device=device), scales, table, torch.empty_like(warm), max_rows)
+    torch.cuda.synchronize()
+    runner = gw.HostStagedMoe(None, None, scales, max_rows, H, depth=2, run=layer_pass, capture=capture)
+    g = torch.Generator().manual_seed(77)
+    batches = []
+    for rows in (64, 64, 64, 64, 9, 0, 9, 64):
+        x = torch.randn((max_rows, H), generator=g).bfloat16().pin_memory()
+        s = torch.randn((max_rows, E), generator=g).bfloat16().pin_memory()
+        y = torch.full((max_rows, H), 7.0, dtype=torch.bfloat16).pin_memory()
+        batches.append((rows, x, s, y))
+        runner.submit(x, s, y, rows)
+    runner.synchronize()
+    assert gw.kernel_error() == 0
+    # recorded passes call the hook once per (slot, rows); eager ones once per pass, zero rows included
+    assert len(calls) == (len({(i % 2, r) for i, (r, *_) in enumerate(batches)}) if capture else len(batches))
+    check = gw.MoeWorkspace(max_rows)
+    for rows, x, s, y in batches:
+        assert torch.all(y[rows:] == 7.0)
+        if rows == 0:
+            continue
+        expected = torch.empty((rows, H), dtype=torch.bfloat16, device=device)
+        check.run(x[:rows].to(device), s[:rows].to(device), scales, table, expected, rows)
+        torch.cuda.synchronize()
+        assert torch.equal(y[:rows], expected.cpu())
