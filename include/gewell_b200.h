@@ -550,8 +550,10 @@ gw_status gw_ipc_free(void* pointer);
  * 128 floats on the device) and store its record at row
  *   dest_row0[e] + (position of the row among this rank's rows of expert e)
  * of peer_records[dest_rank[e]].  dest_rank / dest_row0: 128 int32 each on the
- * device; peer_records: one device pointer per rank, in device memory.  The
- * caller orders this against the owners' reads (a barrier over the ranks). */
+ * device; peer_records: one device pointer per rank, in device memory, each
+ * 16-byte aligned (a record travels as one 1584-byte bulk copy; gw_ipc_alloc
+ * buffers are).  The caller orders this against the owners' reads (a barrier
+ * over the ranks). */
 gw_status gw_moe_ep_dispatch(gw_moe_workspace* workspace, const void* input_bf16, uint32_t rows,
                              const float* inverse_input_scales, const int32_t* dest_rank,
                              const int32_t* dest_row0, void* const* peer_records,
