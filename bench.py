@@ -91,10 +91,17 @@ def zipf_bias(alpha: float = 1.2):
     return (p / p.sum()).log()
 
 
-def build_experts(gw, torch, device, seed=4, expert_ids=None):
+def gate_up_input_scale(e: int, per_expert: bool) -> float:
+    """Input scale of expert e's gate and up projections: one value for the layer (as a checkpoint
+    calibrated with a layer-wide activation scale has it), or sixteen values over the experts."""
+    return 6.0 / 2688 * (1.0 + (e % 16) / 64.0) if per_expert else 6.0 / 2688
+
+
+def build_experts(gw, torch, device, seed=4, expert_ids=None, per_expert_scales=False):
     """The layer's experts ~ N(0, 0.02), packed to NVFP4 by the device packer;
     gate and up share one input scale per expert (they are one fused tensor in
-    the checkpoint), so the layer quantises its input once.  Every expert has
+    the checkpoint), so the layer quantises its input once per distinct scale
+    among a token's experts.  Every expert has
     its own sub-seed, so a rank that owns only some experts (`expert_ids`)
     builds exactly the tensors the single-GPU run builds; the other entries
     of the returned 128-list are None."""
@@ -104,7 +111,7 @@ def build_experts(gw, torch, device, seed=4, expert_ids=None):
         mats = [(torch.randn((I, H), generator=g, device=device) * 0.02).bfloat16(),
                 (torch.randn((I, H), generator=g, device=device) * 0.02).bfloat16(),
                 (torch.randn((H, I), generator=g, device=device) * 0.02).bfloat16()]
-        scales = [6.0 / 2688, 6.0 / 2688, 16.0 / 2688]
+        scales = [gate_up_input_scale(e, per_expert_scales)] * 2 + [16.0 / 2688]
         packs = []
         for m, s in zip(mats, scales):
             w = gw.nvfp4_pack_weights(m, s)
@@ -172,6 +179,12 @@ def run_reference_arm(args):
     print(json.dumps(line))
 
 
+INPUT_SCALE_NOTE = {
+    "layer": "one gate/up input scale for the layer: a token's eight routed copies are quantised once and written eight times",
+    "expert": "sixteen gate/up input scales over the experts: a token's copies are quantised per distinct scale among its experts",
+}
+
+
 def workload_config(n_gpus: int) -> dict:
     tokens = 8192 if n_gpus == 1 else 32768
     return {"workload": ("config 4: Gemma-4-26B-A4B MoE layer on one GPU" if n_gpus == 1 else
@@ -235,7 +248,10 @@ def run_expert_parallel(args, world: int, rank: int, local_rank: int):
     config["placement"] = args.placement
     mine = placement.local_experts(rank)
     # "home": every rank also holds the down matrices of all experts (it finishes its own tokens' rows itself)
-    by_id = build_experts(gw, torch, device, expert_ids=None if args.exchange == "home" else mine)
+    per_expert = args.input_scales == "expert"
+    config["input_scales"] = INPUT_SCALE_NOTE[args.input_scales]
+    by_id = build_experts(gw, torch, device, expert_ids=None if args.exchange == "home" else mine,
+                          per_expert_scales=per_expert)
     by_position = [None] * E
     for e in mine:
         by_position[placement.physical[e]] = by_id[e]
@@ -244,7 +260,8 @@ def run_expert_parallel(args, world: int, rank: int, local_rank: int):
     if args.exchange == "home":
         config["parallelism"] = f"ep{world} for gate/up (experts sharded), down projection at the tokens' home rank (down matrices of all experts on every rank)"
     if args.exchange in ("peer", "peer_pull", "home"):
-        layer = ep.PeerMemoryExpertParallelMoe(by_position, [6.0 / 2688] * E, rank, world, local_tokens, capacity,
+        layer = ep.PeerMemoryExpertParallelMoe(by_position, [gate_up_input_scale(e, per_expert) for e in range(E)],
+                                               rank, world, local_tokens, capacity,
                                                placement=placement, send_home=args.exchange == "peer",
                                                exchange=args.sync,
                                                home_down=[w[2] for w in by_id] if args.exchange == "home" else None)
@@ -442,6 +459,9 @@ def main():
     parser.add_argument("--sync", default="peer", choices=["peer", "nccl"],
                         help="expert-parallel run over peer memory: the histogram exchange and the two barriers of a "
                              "step through mailboxes in peer memory, or through NCCL (all-gather + two all-reduces)")
+    parser.add_argument("--input-scales", default="layer", choices=["layer", "expert"],
+                        help="gate/up input scales of the synthetic experts: one for the layer, or sixteen values over "
+                             "the experts (the quantiser then repeats its work for a token's experts that differ)")
     parser.add_argument("--placement", default="balanced", choices=["contiguous", "interleaved", "balanced"],
                         help="expert placement of the expert-parallel run")
     args = parser.parse_args()
@@ -463,7 +483,8 @@ def main():
     config = workload_config(1)
     tokens = args.tokens or config["tokens"]
     config["tokens"] = tokens
-    experts = build_experts(gw, torch, device)
+    config["input_scales"] = INPUT_SCALE_NOTE[args.input_scales]
+    experts = build_experts(gw, torch, device, per_expert_scales=args.input_scales == "expert")
     table = gw.ExpertTable(experts)
     ws = gw.MoeWorkspace(tokens)
     g = torch.Generator(device=device).manual_seed(1)

@@ -706,6 +706,11 @@ moe_quantize_tokens_kernel(const uint4* __restrict__ input, const int32_t* __res
       }
     }
   }
+  // The quantised row depends on the input scale only: consecutive copies with the same scale (experts
+  // calibrated together, or one scale for the whole layer) reuse the codes of the copy before them.
+  uint32_t out[kPerLane][2];
+  uint8_t scale_code[kPerLane];
+  float quantised_with = -1.0F;        // input scales are positive
   for (int j = 0; j < kTopK; ++j) {
     const uint32_t assignment = token * kTopK + j;
     const int32_t e = keys[assignment];
@@ -714,22 +719,28 @@ moe_quantize_tokens_kernel(const uint4* __restrict__ input, const int32_t* __res
     for (int part = 0; part < parts; ++part) {
       const float inverse_scale = experts[e].inverse_input_scale[part];
       const size_t region = (size_t(part) * scale_rows + size_t(first / 128 + e) * 128) * kBlocks;
+      if (inverse_scale != quantised_with) {     // the same for every lane of the warp
+        quantised_with = inverse_scale;
+#pragma unroll
+        for (int i = 0; i < kPerLane; ++i) {
+          scale_code[i] = float_to_e4m3(inverse_scale * (amax[i] * rcp_approx_ftz(6.0F)));
+          const float block_scale = e4m3_to_float(scale_code[i]);
+          const float factor =
+              block_scale == 0.0F ? 0.0F : rcp_approx_ftz(block_scale * rcp_approx_ftz(inverse_scale));
+          out[i][0] = out[i][1] = 0;
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            out[i][k / 4] |= uint32_t(float2_to_e2m1x2(__uint_as_float(raw[i][k] << 16) * factor,
+                                                       __uint_as_float(raw[i][k] & 0xFFFF0000u) * factor)) << (8 * (k % 4));
+        }
+      }
 #pragma unroll
       for (int i = 0; i < kPerLane; ++i) {
         const uint32_t local = lane + 32 * i;
         const uint32_t kb = half * kHalfBlocks + local;
         if (local >= kHalfBlocks) continue;
-        const uint8_t scale_code = float_to_e4m3(inverse_scale * (amax[i] * rcp_approx_ftz(6.0F)));
-        const float block_scale = e4m3_to_float(scale_code);
-        const float factor =
-            block_scale == 0.0F ? 0.0F : rcp_approx_ftz(block_scale * rcp_approx_ftz(inverse_scale));
-        uint32_t out[2] = {0, 0};
-#pragma unroll
-        for (int k = 0; k < 8; ++k)
-          out[k / 4] |= uint32_t(float2_to_e2m1x2(__uint_as_float(raw[i][k] << 16) * factor,
-                                                  __uint_as_float(raw[i][k] & 0xFFFF0000u) * factor)) << (8 * (k % 4));
-        packed[(size_t(part) * n + row) * kBlocks + kb] = make_uint2(out[0], out[1]);
-        scales[region + scale_offset(row - first, kb, kHidden)] = scale_code;
+        packed[(size_t(part) * n + row) * kBlocks + kb] = make_uint2(out[i][0], out[i][1]);
+        scales[region + scale_offset(row - first, kb, kHidden)] = scale_code[i];
       }
     }
   }
@@ -999,8 +1010,20 @@ ep_dispatch_kernel(const uint4* __restrict__ input, const int32_t* __restrict__ 
       }
     }
   }
+  // A record depends on the input scale only: a copy whose expert has the scale of the copy before it
+  // is sent from that copy's staged record (four bits per copy say which record it leaves from).
+  uint32_t staged_in = 0;
+  int last_built = 0;
+  float built_with = -1.0F;            // input scales are positive
   for (int j = 0; j < kTopK; ++j) {
     const float inverse_scale = inverse_input_scale[keys[token * kTopK + j]];
+    if (inverse_scale == built_with) {           // the same for every thread of the token
+      staged_in |= uint32_t(last_built) << (4 * j);
+      continue;
+    }
+    built_with = inverse_scale;
+    last_built = j;
+    staged_in |= uint32_t(j) << (4 * j);
     uint8_t* record = staged[slot][j];
 #pragma unroll
     for (int i = 0; i < kPerLane; ++i) {
@@ -1029,7 +1052,8 @@ ep_dispatch_kernel(const uint4* __restrict__ input, const int32_t* __restrict__ 
     if (dest_row >= capacity_rows) {          // the owner's buffer is too small: report, never write outside it
       if (error != nullptr) atomicCAS(error, 0u, 0x70000000u | uint32_t(e));
     } else {
-      ptx::bulk_store(peer_records[dest_rank[e]] + size_t(dest_row) * kRecordBytes, staged[slot][lane], kRecordBytes);
+      ptx::bulk_store(peer_records[dest_rank[e]] + size_t(dest_row) * kRecordBytes,
+                      staged[slot][(staged_in >> (4 * lane)) & 15u], kRecordBytes);
       ptx::bulk_store_commit();
       ptx::bulk_store_wait_all();
     }

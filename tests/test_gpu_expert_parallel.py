@@ -203,6 +203,53 @@ def test_record_path_on_one_rank_equals_layer(layer, tokens, send_home):
     assert gw.kernel_error() >> 28 == 7
 
 
+@pytest.mark.parametrize("distinct", [3, 128])
+def test_dispatch_records_with_expert_input_scales(layer, distinct):
+    """Every travelling record is quantised with the input scale of ITS expert.  With three scale values
+    over the experts some of a token's eight copies repeat the scale of the copy before them (those leave
+    from that copy's staged record), with 128 values none does; byte for byte against the oracle."""
+    from oracle import nvfp4 as onv
+    gw, _, _ = layer
+    lib, check = gw.lib, gw.ops._check
+    stream = torch.cuda.current_stream().cuda_stream
+    tokens = 48
+    x, scores, scales = (t.cuda() for t in _inputs(tokens, 63, True))
+    route_ws = gw.MoeWorkspace(tokens)
+    route_ws.dispatch(scores, scales, tokens)
+    offsets, _, _, _ = route_ws.routing_state(tokens)
+    counts = (offsets[1:] - offsets[:-1]).contiguous()
+    physical = torch.arange(E, dtype=torch.int32, device="cuda")
+    dest_rank = torch.zeros(E, dtype=torch.int32, device="cuda")
+    row0 = torch.zeros(E, dtype=torch.int32, device="cuda")
+    local_offsets = torch.zeros(E + 1, dtype=torch.int32, device="cuda")
+    check(lib.gw_moe_ep_tables(counts.data_ptr(), physical.data_ptr(), 0, 1, row0.data_ptr(), local_offsets.data_ptr(),
+                               None, None, stream))
+    input_scales = np.float32(6.0 / 2688) * (np.float32(1) + np.float32(0.03125) * (np.arange(E) % distinct).astype(np.float32))
+    inverse_scales = torch.from_numpy((np.float32(1) / input_scales).astype(np.float32)).cuda()
+    capacity = 8 * tokens
+    records = torch.full((capacity * 1584,), 0xFF, dtype=torch.uint8, device="cuda")
+    record_table = torch.tensor([records.data_ptr()], dtype=torch.int64, device="cuda")
+    check(lib.gw_moe_ep_dispatch(route_ws._ws, x.data_ptr(), tokens, inverse_scales.data_ptr(), dest_rank.data_ptr(),
+                                 row0.data_ptr(), record_table.data_ptr(), capacity, stream))
+    torch.cuda.synchronize()
+    assert gw.kernel_error() == 0
+    host_records = records.reshape(capacity, 1584).cpu().numpy()
+    route_ws.rows = tokens
+    order = route_ws.sorted_assignments().cpu().numpy()
+    bounds = offsets.cpu().numpy()
+    xf = x.float().cpu().numpy()
+    checked = 0
+    for e in range(E):
+        first, last = int(bounds[e]), int(bounds[e + 1])
+        if first == last:
+            continue
+        q = onv.quantize_activations(xf[order[first:last] // 8], float(input_scales[e]), rcp_fn=gw.rcp_approx)
+        assert np.array_equal(host_records[first:last, :1408], q.packed[:last - first]), f"expert {e}"
+        assert np.array_equal(host_records[first:last, 1408:], q.scales_linear[:last - first]), f"expert {e}"
+        checked += last - first
+    assert checked == capacity
+
+
 def test_undersized_receive_capacity_is_reported_not_overrun(layer):
     """The group boundaries of a rank come from the other ranks' histograms.  If they describe more
     rows than the receive buffers were sized for, the grouped GEMMs must stop at the declared
