@@ -688,6 +688,18 @@ moe_quantize_tokens_kernel(const uint4* __restrict__ input, const int32_t* __res
   const uint32_t token = warp_index / 2, half = warp_index % 2;
   if (token >= tokens) return;
   const uint32_t n = tokens * kTopK;
+  // Lane j < 8 fetches what copy j needs (expert, destination row, the expert's first row and input
+  // scales): one round of dependent loads for the token instead of one per copy.
+  int32_t copy_expert = 0, copy_first = 0;
+  uint32_t copy_row = 0;
+  float copy_scale[2] = {0.0F, 0.0F};
+  if (lane < kTopK) {
+    copy_expert = keys[token * kTopK + lane];
+    copy_row = uint32_t(inverse[token * kTopK + lane]);
+    copy_first = offsets[copy_expert];
+    copy_scale[0] = experts[copy_expert].inverse_input_scale[0];
+    if (parts > 1) copy_scale[1] = experts[copy_expert].inverse_input_scale[1];
+  }
   uint32_t raw[kPerLane][8];
   float amax[kPerLane];
 #pragma unroll
@@ -712,12 +724,12 @@ moe_quantize_tokens_kernel(const uint4* __restrict__ input, const int32_t* __res
   uint8_t scale_code[kPerLane];
   float quantised_with = -1.0F;        // input scales are positive
   for (int j = 0; j < kTopK; ++j) {
-    const uint32_t assignment = token * kTopK + j;
-    const int32_t e = keys[assignment];
-    const uint32_t row = uint32_t(inverse[assignment]);
-    const int32_t first = offsets[e];
+    const int32_t e = __shfl_sync(0xffffffffu, copy_expert, j);
+    const uint32_t row = __shfl_sync(0xffffffffu, copy_row, j);
+    const int32_t first = __shfl_sync(0xffffffffu, copy_first, j);
+    const float scale_of_part[2] = {__shfl_sync(0xffffffffu, copy_scale[0], j), __shfl_sync(0xffffffffu, copy_scale[1], j)};
     for (int part = 0; part < parts; ++part) {
-      const float inverse_scale = experts[e].inverse_input_scale[part];
+      const float inverse_scale = scale_of_part[part];
       const size_t region = (size_t(part) * scale_rows + size_t(first / 128 + e) * 128) * kBlocks;
       if (inverse_scale != quantised_with) {     // the same for every lane of the warp
         quantised_with = inverse_scale;
@@ -992,6 +1004,8 @@ ep_dispatch_kernel(const uint4* __restrict__ input, const int32_t* __restrict__ 
   const uint32_t slot = threadIdx.x / 64, half = (threadIdx.x / 32) % 2, lane = threadIdx.x % 32;
   const uint32_t token = blockIdx.x * kDispatchTokensPerBlock + slot;
   if (token >= tokens) return;                          // both warps of a token leave together
+  // lane j < 8 fetches the input scale of copy j's expert: one round of dependent loads for the token
+  const float copy_scale = lane < kTopK ? inverse_input_scale[keys[token * kTopK + lane]] : 0.0F;
   uint32_t raw[kPerLane][8];
   float amax[kPerLane];
 #pragma unroll
@@ -1016,7 +1030,7 @@ ep_dispatch_kernel(const uint4* __restrict__ input, const int32_t* __restrict__ 
   int last_built = 0;
   float built_with = -1.0F;            // input scales are positive
   for (int j = 0; j < kTopK; ++j) {
-    const float inverse_scale = inverse_input_scale[keys[token * kTopK + j]];
+    const float inverse_scale = __shfl_sync(0xffffffffu, copy_scale, j);
     if (inverse_scale == built_with) {           // the same for every thread of the token
       staged_in |= uint32_t(last_built) << (4 * j);
       continue;
