@@ -146,7 +146,7 @@ gw_status launch_dense(const DenseProblem& q, DenseDescriptors* cache, cudaStrea
   if (swap && q.split_workspace != nullptr && cache->split_counters != nullptr) {
     params.split_counters = cache->split_counters;
     params.split_partials = static_cast<float*>(q.split_workspace);
-    const long long stages = (long long)((row_bytes + 127) / 128) * params.total_work;
+    const long long stages = (long long)gemm_tc_k_stages(q.kind, GemmEpilogue::swap_store, row_bytes) * params.total_work;
     grid = stages < sm_count() ? int(stages) : sm_count();
   }
   GW_CUDA_CHECK(launch_gemm_tc(q.kind, swap ? GemmEpilogue::swap_store : GemmEpilogue::direct_store, block_n, params,

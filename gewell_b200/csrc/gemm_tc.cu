@@ -35,15 +35,26 @@ constexpr int kThreads = 32 * (2 + kScaleWarps + kEpilogueWarps);
 constexpr int kTileL = 128;
 constexpr int kStageRowBytes = 128;   // bytes of K per stage row (= swizzle span)
 constexpr int kAtomBytes = 512;       // one scale atom: 128 rows x 4 K16 blocks
-constexpr int kKBlocksPerStage = 4;   // MMAs per stage (K=64 FP4 / K=32 FP8 each: 32 bytes)
+constexpr int kKBlocksPerStage = 4;   // MMAs per 128-byte slab of K (K=64 FP4 / K=32 FP8 each: 32 bytes)
 
-template <bool kNvfp4, int BLOCK_N>
+// Slabs (128 bytes of K each) per ring stage.  The FP8 swap form -- the decode shapes, which stream
+// the weights once -- takes two: a stage's barrier round (wait, commit, release, refill) costs about
+// as much as two of its MMAs, and with 256 bytes of K per round it is paid half as often.
+__host__ __device__ constexpr int slabs_per_stage(GemmKind kind, GemmEpilogue epilogue) {
+  return kind == GemmKind::fp8 && epilogue == GemmEpilogue::swap_store ? 2 : 1;
+}
+
+template <bool kNvfp4, int BLOCK_N, int SLABS = 1>
 struct Config {
+  static_assert(SLABS == 1 || !kNvfp4, "the scale slots are laid out for one slab per stage");
+  static constexpr int kSlabs = SLABS;
+  static constexpr int kLSlabBytes = kTileL * kStageRowBytes;
+  static constexpr int kCSlabBytes = BLOCK_N * kStageRowBytes;
   static constexpr int kAccStages = BLOCK_N >= 256 ? 1 : 2;
   static constexpr int kHalves = BLOCK_N > 128 ? BLOCK_N / 128 : 1;
   static constexpr int kHalfRows = BLOCK_N / kHalves;
-  static constexpr int kLBytes = kTileL * kStageRowBytes;
-  static constexpr int kCBytes = BLOCK_N * kStageRowBytes;
+  static constexpr int kLBytes = SLABS * kLSlabBytes;
+  static constexpr int kCBytes = SLABS * kCSlabBytes;
   static constexpr int kSflBytes = kNvfp4 ? kKBlocksPerStage * kAtomBytes : 0;
   static constexpr int kSfcBytes = kNvfp4 ? kHalves * kKBlocksPerStage * kAtomBytes : 0;
   static constexpr int kStageBytes = kLBytes + kCBytes + kSflBytes + kSfcBytes;
@@ -146,7 +157,9 @@ template <GemmKind KIND, int BLOCK_N, GemmEpilogue EPI, bool kProfile>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ GemmParams p) {
   constexpr bool kNvfp4 = KIND == GemmKind::nvfp4;
-  using C = Config<kNvfp4, BLOCK_N>;
+  using C = Config<kNvfp4, BLOCK_N, slabs_per_stage(KIND, EPI)>;
+  constexpr int kSlabs = C::kSlabs;
+  constexpr int kKbPerStage = kKBlocksPerStage * kSlabs;    // MMAs per stage
   constexpr bool prof = kProfile;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -199,7 +212,7 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
   // bytes of K per row: two E2M1 values, one E4M3 value or half a BF16 value per byte
   const int k_bytes = kNvfp4 ? p.k / 2 : (KIND == GemmKind::bf16 ? 2 * p.k : p.k);
   const int total_kb = (k_bytes + 31) / 32;                 // MMA K-blocks (32 bytes of K each)
-  const int k_stages = (total_kb + kKBlocksPerStage - 1) / kKBlocksPerStage;
+  const int k_stages = (total_kb + kKbPerStage - 1) / kKbPerStage;
   const int k_atoms = p.k / 64;                             // scale atoms per 128-row block (NVFP4)
   const bool split = p.split_partials != nullptr;
 
@@ -268,10 +281,10 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
       // 256-row box and one two-row box of scale atoms replace four copies (the copy
       // engine's cost per operation, not per byte, is what limits the fill rate)
       const bool single_box = C::kHalves == 2 && p.c_single_box != 0;
-      const uint32_t c_bytes = single_box ? uint32_t(C::kCBytes) : uint32_t(halves * C::kHalfRows * kStageRowBytes);
+      const uint32_t c_bytes = single_box ? uint32_t(C::kCBytes) : uint32_t(kSlabs * halves * C::kHalfRows * kStageRowBytes);
       // one stage's copies; `weights` / `tokens` select the L-side and the C-side copies
       auto issue = [&](int ks, int st, bool l_side, bool c_side) {
-        const int nkb = min(kKBlocksPerStage, total_kb - ks * kKBlocksPerStage);
+        const int nkb = min(kKbPerStage, total_kb - ks * kKbPerStage);
         uint8_t* base = smem + st * C::kStageBytes;
         uint64_t* bar = full_bar + st;
         if (l_side) {                      // the stage's byte count is announced with its first copies
@@ -279,7 +292,10 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
           if constexpr (kNvfp4)
             bytes += nkb * kAtomBytes + (single_box ? uint32_t(C::kSfcBytes) : uint32_t(nkb * kAtomBytes * halves));
           ptx::mbar_expect_tx(bar, bytes);
-          ptx::tma_load_2d(base, map_l, ks * kStageRowBytes, l_row, bar);
+          // a slab past the end of K is filled with zeros by the copy engine (and skipped by the MMAs)
+#pragma unroll
+          for (int slab = 0; slab < kSlabs; ++slab)
+            ptx::tma_load_2d(base + slab * C::kLSlabBytes, map_l, (ks * kSlabs + slab) * kStageRowBytes, l_row, bar);
           if constexpr (kNvfp4)
             ptx::bulk_load(base + C::kLBytes + C::kCBytes, sfl_src + size_t(ks) * kKBlocksPerStage * kAtomBytes,
                            nkb * kAtomBytes, bar);
@@ -290,9 +306,12 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
           } else {
 #pragma unroll
             for (int h = 0; h < C::kHalves; ++h)     // compile-time bound: map_c / c_row stay in registers
-              if (h < halves)
-                ptx::tma_load_2d(base + C::kLBytes + h * C::kHalfRows * kStageRowBytes, map_c[h], ks * kStageRowBytes,
-                                 c_row[h], bar);
+              if (h < halves) {
+#pragma unroll
+                for (int slab = 0; slab < kSlabs; ++slab)
+                  ptx::tma_load_2d(base + C::kLBytes + slab * C::kCSlabBytes + h * C::kHalfRows * kStageRowBytes, map_c[h],
+                                   (ks * kSlabs + slab) * kStageRowBytes, c_row[h], bar);
+              }
           }
           if constexpr (kNvfp4) {
             const size_t atom_offset = size_t(ks) * kKBlocksPerStage * kAtomBytes;
@@ -389,24 +408,26 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p) {
         if (lane == 0) {
           // Single in-order instruction stream: descriptors are a constant plus
           // stage * (kStageBytes >> 4) in their low word, the loop is unrolled.
-          const int nkb = min(kKBlocksPerStage, total_kb - ks * kKBlocksPerStage);
+          const int nkb = min(kKbPerStage, total_kb - ks * kKbPerStage);
           const uint32_t base16 = smem_base16 + uint32_t(stage) * uint32_t(C::kStageBytes >> 4);
           const uint32_t sfl_t = sfl_tmem + uint32_t(stage) * C::kSfSlotCols;
           const uint32_t sfc_t = sfc_tmem + uint32_t(stage) * C::kSfSlotCols;
           const uint32_t first = ks == ks0 ? 0u : 1u;
 #pragma unroll
-          for (int kb = 0; kb < kKBlocksPerStage; ++kb) {
+          for (int kb = 0; kb < kKbPerStage; ++kb) {
             if (kb < nkb) {
+              // operand addresses of K-block kb: its slab, then 32 bytes per K-block inside the slab's swizzle span
+              const uint32_t l16 = base16 + uint32_t(kb / kKBlocksPerStage) * uint32_t(C::kLSlabBytes >> 4) +
+                                   2 * uint32_t(kb % kKBlocksPerStage);
+              const uint32_t c16 = base16 + kCOff16 + uint32_t(kb / kKBlocksPerStage) * uint32_t(C::kCSlabBytes >> 4) +
+                                   2 * uint32_t(kb % kKBlocksPerStage);
               if constexpr (kNvfp4)
-                ptx::tc_mma_nvfp4(d_tmem, make_desc(kDescHiSw128, base16 + 2 * kb),
-                                  make_desc(kDescHiSw128, base16 + kCOff16 + 2 * kb), idesc, sfl_t + 4 * kb,
+                ptx::tc_mma_nvfp4(d_tmem, make_desc(kDescHiSw128, l16), make_desc(kDescHiSw128, c16), idesc, sfl_t + 4 * kb,
                                   sfc_t + kb * C::kSfcColsPerKb, kb == 0 ? first : 1u);
               else if constexpr (KIND == GemmKind::bf16)
-                ptx::tc_mma_bf16(d_tmem, make_desc(kDescHiSw128, base16 + 2 * kb),
-                                 make_desc(kDescHiSw128, base16 + kCOff16 + 2 * kb), idesc, kb == 0 ? first : 1u);
+                ptx::tc_mma_bf16(d_tmem, make_desc(kDescHiSw128, l16), make_desc(kDescHiSw128, c16), idesc, kb == 0 ? first : 1u);
               else
-                ptx::tc_mma_fp8(d_tmem, make_desc(kDescHiSw128, base16 + 2 * kb),
-                                make_desc(kDescHiSw128, base16 + kCOff16 + 2 * kb), idesc, kb == 0 ? first : 1u);
+                ptx::tc_mma_fp8(d_tmem, make_desc(kDescHiSw128, l16), make_desc(kDescHiSw128, c16), idesc, kb == 0 ? first : 1u);
             }
           }
           ptx::tc_commit(empty_bar + stage);
@@ -825,7 +846,7 @@ unsigned g_profile_launches = 0;
 
 template <GemmKind KIND, int BLOCK_N, GemmEpilogue EPI, bool kProfile>
 cudaError_t launch_instance(const GemmParams& params, int grid, cudaStream_t stream) {
-  using C = Config<KIND == GemmKind::nvfp4, BLOCK_N>;
+  using C = Config<KIND == GemmKind::nvfp4, BLOCK_N, slabs_per_stage(KIND, EPI)>;
   static bool configured_on[kMaxDeviceSlots] = {};   // the attribute is per GPU
   bool& configured = configured_on[current_device_slot()];
   if (!configured) {
@@ -888,6 +909,11 @@ cudaError_t launch_kind(GemmEpilogue epilogue, int block_n, const GemmParams& pa
   return cudaErrorInvalidValue;
 }
 }  // namespace
+
+int gemm_tc_k_stages(GemmKind kind, GemmEpilogue epilogue, uint64_t row_bytes) {
+  const uint64_t stage_row_bytes = uint64_t(kStageRowBytes) * uint64_t(slabs_per_stage(kind, epilogue));
+  return int((row_bytes + stage_row_bytes - 1) / stage_row_bytes);
+}
 
 cudaError_t launch_gemm_tc(GemmKind kind, GemmEpilogue epilogue, int block_n, const GemmParams& params, int grid,
                            cudaStream_t stream) {

@@ -88,6 +88,10 @@ enum class GemmEpilogue { swap_store, direct_store, geglu_quant };
 cudaError_t launch_gemm_tc(GemmKind kind, GemmEpilogue epilogue, int block_n, const GemmParams& params, int grid,
                            cudaStream_t stream);
 
+// Ring stages of one work item's K loop (row_bytes = bytes of K per operand row): the unit in which the
+// split mode divides a launch over the CTAs.
+int gemm_tc_k_stages(GemmKind kind, GemmEpilogue epilogue, uint64_t row_bytes);
+
 // Debug aid: subsequent launches write per-CTA cycle counters ([2][148][8] int64:
 // producer wait, MMA wait for data, MMA issue, MMA wait for accumulator, epilogue
 // wait, epilogue work, total, epilogue TMEM-load time) into this device buffer; nullptr turns it off.
